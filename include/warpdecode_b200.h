@@ -1,0 +1,173 @@
+/* warpdecode_b200 — C ABI of the B200 (sm_100a) batch-1 MoE decode path.
+ *
+ * This is the boundary a host engine binds: plain pointers and sizes, int status codes,
+ * no C++ or torch types. It stands in for the C++ entry points the reference engine calls
+ * for its MoE block (the reference has no C ABI of its own; each function below names the
+ * reference interface it replaces, paths relative to the reference project).
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative WD_E_* code; wd_last_error() gives
+ *     the message of the calling thread's most recent failure
+ *   - "ggml layout" means the on-disk GGUF block layout, row-major, experts contiguous
+ *   - device pointers are CUDA device pointers of the engine's device; `stream` is a
+ *     cudaStream_t passed as void* (NULL = the engine's own stream)
+ *   - an engine is driven by one host thread at a time (as the reference's is)
+ */
+#ifndef WARPDECODE_B200_H
+#define WARPDECODE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WD_OK 0
+#define WD_E_INVALID (-1)     /* bad argument or unsupported geometry */
+#define WD_E_CUDA (-2)        /* a CUDA runtime call failed */
+#define WD_E_STATE (-3)       /* call order: weights missing, layer out of range, ... */
+#define WD_E_DEVICE (-4)      /* the kernel reported an error word (timeout, miss, bad slot) */
+#define WD_E_NOMEM (-5)
+
+/* ggml tensor type ids (src/gguf.hpp:26-44). */
+#define WD_TYPE_F32 0
+#define WD_TYPE_Q4_0 2
+#define WD_TYPE_Q8_0 8
+#define WD_TYPE_IQ3_S 21
+#define WD_TYPE_IQ2_S 22
+
+typedef struct wd_engine wd_engine;
+
+/* Geometry of the MoE stack. Replaces the fields load_qwen38_runtime() derives from the
+ * GGUF (src/qwen38_runtime.cuh:117-147, src/qwen38_layout.hpp:102-211) and the limits of
+ * Qwen38MoeScratch::initialize (src/qwen38_moe.cuh:1709-1714: experts <= 4096, k <= 16). */
+typedef struct {
+    int32_t hidden;          /* multiple of 256, power-of-two number of superblocks <= 32 */
+    int32_t expert_ffn;      /* same constraint */
+    int32_t shared_ffn;      /* 0 = no shared expert; else multiple of 128 */
+    int32_t n_experts;       /* multiple of 8, <= 1024 */
+    int32_t top_k;           /* 1..16 */
+    int32_t n_layers;
+    int32_t gate_type, up_type, down_type;   /* WD_TYPE_IQ3_S or WD_TYPE_IQ2_S */
+    float w_scale;           /* expert_weights_scale; 0 or 1 = none */
+    int32_t ep_rank, ep_size;/* this engine owns experts [rank*E/size, (rank+1)*E/size) */
+    int32_t max_tokens;      /* tokens per forward call, 1..4 (batch verify) */
+    int32_t device;          /* CUDA device ordinal */
+    int64_t cache_mib;       /* expert slot pool size; <= 0: size it to hold every owned expert.
+                                Same meaning as WARODECODE_EXPERT_CACHE_MIB
+                                (src/qwen38_tuning.hpp:113-116). */
+    float rms_eps;           /* epsilon of the optional fused RMSNorm prologue */
+} wd_config;
+
+/* ---- lifetime ------------------------------------------------------------------------ */
+/* Replaces load_qwen38_runtime() + Qwen38DecodeState::initialize() for the MoE part
+ * (src/qwen38_runtime.cuh:117, src/qwen38_state.cuh:59-120): allocates the slot pool, the
+ * per-layer tables and all scratch once; forward calls allocate nothing. */
+int wd_engine_create(const wd_config *cfg, wd_engine **out);
+void wd_engine_destroy(wd_engine *e);
+const char *wd_last_error(void);
+/* Library/ABI version, (major << 16) | minor. */
+int wd_version(void);
+
+/* Default slot pool size for a GPU with `memory_mib` of memory:
+ * clamp(0.75 * memory_mib - 8192, 512, 65536), overridden by the environment variable
+ * WARODECODE_EXPERT_CACHE_MIB when it holds a positive integer
+ * (qwen38_tuning_for_gpu, src/qwen38_tuning.hpp:88-116). */
+int64_t wd_default_cache_mib(int64_t memory_mib);
+
+/* ---- weights ------------------------------------------------------------------------- */
+/* Router of one layer: Q8_0 [n_experts][hidden] in ggml layout, host memory; optional F32
+ * per-expert logit bias. Replaces upload_matrix(router) (src/qwen38_runtime.cuh:198). */
+int wd_set_router(wd_engine *e, int layer, const void *router_q8_0, const float *bias);
+/* Shared expert of one layer: F32 gate vector [hidden] and Q8_0 gate/up [shared_ffn][hidden],
+ * down [hidden][shared_ffn]. Replaces load_qwen38_shared_expert (src/qwen38_moe.cuh:564-599). */
+int wd_set_shared(wd_engine *e, int layer, const float *gate_vec, const void *gate_q8_0,
+                  const void *up_q8_0, const void *down_q8_0);
+/* RMSNorm weight applied to the block input when the fused prologue is used (may be NULL). */
+int wd_set_norm(wd_engine *e, int layer, const float *weight);
+/* Routed experts of one layer: three 3-D tensors in ggml layout in HOST memory (typically
+ * the GGUF mapping). The pointers are retained: they must stay valid for the engine's
+ * lifetime, exactly as the reference requires of its GgufFile (src/qwen38_runtime.cuh:201).
+ * Experts this rank owns are uploaded now when the pool holds them all, otherwise on demand. */
+int wd_set_experts(wd_engine *e, int layer, const void *gate, const void *up, const void *down);
+/* Same, from ggml-layout tensors already in DEVICE memory (used by the synthetic model
+ * generator); needs a pool that holds every owned expert. Nothing is retained. */
+int wd_set_experts_device(wd_engine *e, int layer, const void *gate, const void *up, const void *down);
+
+/* ---- expert slot cache (GpuExpertCache, src/expert_cache.cuh:2156-2536) ---------------- */
+/* Number of slots in the pool / bytes of one slot (gate + up + down of one expert). */
+int64_t wd_cache_slot_count(const wd_engine *e);
+int64_t wd_cache_slot_bytes(const wd_engine *e);
+/* Makes (layer, expert) resident and returns its slot index; a miss fills the least
+ * recently used slot from the host tensors. Replaces GpuExpertCache::acquire (:2252). */
+int wd_cache_acquire(wd_engine *e, int layer, int expert, int *slot);
+/* hits / misses / evictions since creation (ExpertCacheMonitor counters, :1671). */
+int wd_cache_stats(const wd_engine *e, int64_t stats[3]);
+
+/* ---- forward --------------------------------------------------------------------------- */
+/* One MoE block on device buffers: x [n_tokens][hidden] F32 -> out [n_tokens][hidden] F32
+ * (router select, selected experts, ordered weighted combine, shared expert, finish).
+ * Replaces run_qwen38_routed_moe_separate_f32_x + run_qwen38_shared_expert_f32_x +
+ * q38_finish_moe_f32 (src/qwen38_moe.cuh:3761, :3963, :2442). Enqueues on `stream` and
+ * returns without synchronising when every selected expert can be resident. */
+int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, int n_tokens,
+                   void *stream);
+/* Same through HOST buffers: copies x in, runs the block, copies out back, synchronises. */
+int wd_moe_forward_host(wd_engine *e, int layer, const float *x_host, float *out_host, int n_tokens);
+/* One decode token through layers [0, n_layers) of the stack: per layer
+ * x = RMSNorm(residual) * norm_weight, residual += moe(x). residual_dev is [hidden] F32,
+ * updated in place. The whole token is one CUDA graph after the first call. */
+int wd_stack_step(wd_engine *e, float *residual_dev, void *stream);
+int wd_stack_step_host(wd_engine *e, const float *residual_in_host, float *residual_out_host);
+
+/* ---- inspection (parity tests; not on the hot path) ------------------------------------- */
+#define WD_TAP_LOGITS 0       /* F32 [n_experts] */
+#define WD_TAP_IDS 1          /* I32 [top_k] */
+#define WD_TAP_WEIGHTS 2      /* F32 [top_k] */
+#define WD_TAP_ACT 3          /* F32 [top_k][expert_ffn]  silu(gate)*up */
+#define WD_TAP_EXPERT_OUT 4   /* F32 [top_k][hidden] */
+#define WD_TAP_ROUTED 5       /* F32 [hidden] */
+#define WD_TAP_SHARED 6       /* F32 [hidden] shared expert before its gate */
+#define WD_TAP_SHARED_GATE 7  /* F32 [1] */
+#define WD_TAP_SHARED_ACT 8   /* F32 [shared_ffn] */
+/* Copies a tap of the most recent forward of token `token` to host memory (synchronises).
+ * The post-conditions the reference's callers read from Qwen38MoeScratch
+ * (d_logits/h_ids/h_weights/d_accum/down_f32/d_shared_gate, src/qwen38_moe.cuh:1804-1830). */
+int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes);
+/* Device error word of the last forward (0 = none) and a reset of the barrier state. */
+int wd_device_status(wd_engine *e, int *status);
+
+/* ---- stand-alone pieces (unit parity tests) ---------------------------------------------- */
+/* Router chain on given logits: softmax over all experts, top-k, renormalised weights
+ * (q38_launch_topk_softmax, src/qwen38_moe.cuh:1065-1083). Host in, host out. */
+int wd_router_topk_host(const float *logits, int n_experts, int k, float w_scale, int *ids,
+                        float *weights, float *probs);
+/* Activation quantisers on host buffers, output in ggml block layout (Q8_0: 34-byte blocks;
+ * Q8_K: 292-byte blocks d/qs/bsums) (src/qwen38_hc.cuh:368, src/lowbit.cuh:815). */
+int wd_quantize_q8_0_host(const float *x, int n, void *blocks);
+int wd_quantize_q8_K_host(const float *x, int n, void *blocks);
+/* y = W x for one low-bit matrix in ggml layout (host), through the same repack + decode the
+ * engine uses. `partials`, if not NULL, receives the int32 sums [rows][cols/256][8] (IQ types). */
+int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, float *y,
+                   int32_t *partials);
+
+/* ---- synthetic model generator (device side) ----------------------------------------------- */
+/* Fills `dst` (device) with `rows` x `cols` N(0, sigma) weights drawn from (seed, stream_id)
+ * and quantised to `type` in ggml layout. Used to build full-size synthetic models in HBM. */
+int wd_synth_tensor_device(int type, int rows, int cols, float sigma, uint64_t seed,
+                           uint64_t stream_id, void *dst_dev, void *stream);
+/* Builds every layer of the engine's model from `seed` directly on the device. */
+int wd_synth_model(wd_engine *e, uint64_t seed, float sigma, float bias_sigma);
+/* Copies one owned expert's ggml-layout tensors (as the generator produced them) to host
+ * buffers so a CPU oracle can consume the same bytes. Regenerates them from the seed. */
+int wd_synth_expert_host(wd_engine *e, uint64_t seed, float sigma, int layer, int expert,
+                         void *gate, void *up, void *down);
+int wd_synth_dense_host(wd_engine *e, uint64_t seed, float sigma, float bias_sigma, int layer,
+                        void *router, float *bias, float *gate_vec, void *sh_gate, void *sh_up,
+                        void *sh_down);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WARPDECODE_B200_H */

@@ -549,9 +549,21 @@ int wdo_moe_block(const wdo_moe_weights *w, const float *x, wdo_moe_result *r, i
     return 0;
 }
 
+/* Sum of squares as a perfect binary tree over consecutive elements (zero-padded to a power of
+ * two), every node one rounded double addition. The tree, not a running sum, is the definition:
+ * it is the order a parallel reduction produces, so the CUDA path can match it bit for bit. */
+static double sumsq_tree(const float *x, int lo, int width, int n) {
+    if (lo >= n) return 0.0;
+    if (width == 1) return (double)x[lo] * (double)x[lo];
+    const double a = sumsq_tree(x, lo, width / 2, n);
+    const double b = sumsq_tree(x, lo + width / 2, width / 2, n);
+    return a + b;
+}
+
 void wdo_rmsnorm(const float *x, const float *weight, float eps, int n, float *y) {
-    double ss = 0.0;
-    for (int i = 0; i < n; ++i) ss += (double)x[i] * (double)x[i];
+    int width = 1;
+    while (width < n) width *= 2;
+    const double ss = sumsq_tree(x, 0, width, n);
     const float scale = (float)(1.0 / sqrt(ss / (double)n + (double)eps));
     for (int i = 0; i < n; ++i) {
         const float v = mul_rn(x[i], scale);

@@ -1,0 +1,97 @@
+"""CPU-side checks: the C-ABI library loads and exports every symbol the header declares, the
+synthetic encoders produce blocks their own decoders (and gguf-py's, when importable) read back,
+and the GGUF writer round-trips."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_builds_and_exports_every_declared_symbol():
+    import warpdecode_b200 as wd
+    path = wd.build()
+    L = ctypes.CDLL(path)
+    header = open(os.path.join(ROOT, "include", "warpdecode_b200.h")).read()
+    names = set(re.findall(r"\b(wd_[a-z0-9_]+)\s*\(", header))
+    assert len(names) >= 25
+    for n in sorted(names):
+        assert hasattr(L, n), n
+    assert L.wd_version() >= 1
+
+
+def test_default_cache_rule_and_env_override(monkeypatch):
+    import warpdecode_b200 as wd
+    L = wd.lib()
+    monkeypatch.delenv("WARODECODE_EXPERT_CACHE_MIB", raising=False)
+    assert L.wd_default_cache_mib(40 * 1024) == 40 * 1024 * 3 // 4 - 8192          # 22 GiB on a 40 GB card
+    assert L.wd_default_cache_mib(183359) == 65536                                  # clamp high
+    assert L.wd_default_cache_mib(8 * 1024) == 512                                  # clamp low
+    monkeypatch.setenv("WARODECODE_EXPERT_CACHE_MIB", "8192")
+    assert L.wd_default_cache_mib(183359) == 8192
+    monkeypatch.setenv("WARODECODE_EXPERT_CACHE_MIB", "-3")
+    assert L.wd_default_cache_mib(183359) == 65536
+
+
+@pytest.mark.parametrize("t", [ol.TYPE_Q8_0, ol.TYPE_Q4_0, ol.TYPE_IQ3_S, ol.TYPE_IQ2_S])
+def test_synth_encoders_decode_close_to_the_weights(t):
+    from warpdecode_b200 import synth
+    rng = np.random.Generator(np.random.PCG64(3))
+    w = (rng.standard_normal((8, 512)) * 0.02).astype(np.float32)
+    blob = synth.QUANTIZERS[t](w)
+    assert blob.shape == (8, synth.row_bytes(t, 512))
+    back = synth.dequantize(t, blob, 8, 512)
+    rel = np.linalg.norm(back - w) / np.linalg.norm(w)
+    assert rel < {ol.TYPE_Q8_0: 0.01, ol.TYPE_Q4_0: 0.12, ol.TYPE_IQ3_S: 0.35, ol.TYPE_IQ2_S: 0.6}[t]
+    try:
+        import gguf
+        from gguf import quants
+    except Exception:
+        return
+    qt = {ol.TYPE_Q8_0: gguf.GGMLQuantizationType.Q8_0, ol.TYPE_Q4_0: gguf.GGMLQuantizationType.Q4_0,
+          ol.TYPE_IQ3_S: gguf.GGMLQuantizationType.IQ3_S, ol.TYPE_IQ2_S: gguf.GGMLQuantizationType.IQ2_S}[t]
+    theirs = quants.dequantize(blob, qt)
+    assert np.array_equal(theirs.astype(np.float32), back.astype(np.float32))
+
+
+def test_oracle_rows_agree_with_dequantised_weights(oracle):
+    # the row dot of the oracle equals sum(dequant(w) * dequant(q8k(x))) up to float rounding
+    from warpdecode_b200 import synth
+    rng = np.random.Generator(np.random.PCG64(4))
+    w = (rng.standard_normal((4, 512)) * 0.02).astype(np.float32)
+    x = rng.standard_normal(512).astype(np.float32)
+    for t in (ol.TYPE_IQ3_S, ol.TYPE_IQ2_S):
+        blob = synth.QUANTIZERS[t](w)
+        wf = synth.dequantize(t, blob, 4, 512).astype(np.float64)
+        xq = oracle.quantize_q8_K(x)
+        xf = np.concatenate([xq[i * 292 + 4:i * 292 + 260].view(np.int8).astype(np.float64) *
+                             float(xq[i * 292:i * 292 + 4].view(np.float32)[0]) for i in range(2)])
+        for r in range(4):
+            got = float(oracle.row(t, blob[r], xq, 512))
+            assert abs(got - float(wf[r] @ xf)) <= 1e-4 * max(1.0, abs(got))
+
+
+def test_gguf_writer_round_trip(tmp_path):
+    from warpdecode_b200 import synth
+    m = synth.make_moe_block(5, 256, 256, 8, 2, 128)
+    path = str(tmp_path / "tiny.gguf")
+    meta = {"general.architecture": "qwen4exp", "qwen4exp.block_count": 1, "qwen4exp.expert_count": 8,
+            "qwen4exp.expert_used_count": 2, "qwen4exp.embedding_length": 256,
+            "qwen4exp.expert_feed_forward_length": 256, "qwen4exp.expert_weights_scale": 1.0}
+    synth.write_gguf(path, meta, synth.moe_block_tensors(m, 0))
+    try:
+        import gguf
+    except Exception:
+        pytest.skip("gguf-py not importable")
+    r = gguf.GGUFReader(path)
+    names = {t.name: t for t in r.tensors}
+    t = names["blk.0.ffn_gate_exps.weight"]
+    assert list(map(int, t.shape)) == [256, 256, 8]
+    assert int(t.tensor_type) == ol.TYPE_IQ3_S
+    assert np.array_equal(np.asarray(t.data).reshape(-1).view(np.uint8), m["gate"])
+    assert np.array_equal(np.asarray(names["blk.0.ffn_gate_inp_shexp.weight"].data).reshape(-1), m["shared_gate_vec"])

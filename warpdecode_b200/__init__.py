@@ -1,0 +1,246 @@
+"""warpdecode_b200: B200 (sm_100a) implementation of the batch-1 MoE decode hot path.
+
+The product is the C-ABI shared library built from csrc/ (include/warpdecode_b200.h); this
+module is the thin Python binding used by the tests, the bench and the smoke check. There is
+no CPU fallback: loading fails loudly when the library is missing, and every call reports the
+library's own error text.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+LIB_PATH = os.path.join(HERE, "libwarpdecode_b200.so")
+SOURCES = [os.path.join(HERE, "csrc", f) for f in
+           ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_formats.cuh", "wd_device.cuh",
+            "wd_grids.h")] + [os.path.join(ROOT, "include", "warpdecode_b200.h")]
+
+TYPE_F32, TYPE_Q4_0, TYPE_Q8_0, TYPE_IQ3_S, TYPE_IQ2_S = 0, 2, 8, 21, 22
+TAPS = dict(logits=0, ids=1, weights=2, act=3, expert_out=4, routed=5, shared=6, shared_gate=7, shared_act=8)
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-diag-suppress", "1886", "-shared", "-Xcompiler", "-fPIC"]
+
+
+def build(force=False, verbose=False):
+    """Compile csrc/ into libwarpdecode_b200.so with nvcc (cross-compiles without a GPU)."""
+    if not force and os.path.exists(LIB_PATH):
+        newest = max(os.path.getmtime(s) for s in SOURCES)
+        if os.path.getmtime(LIB_PATH) >= newest:
+            return LIB_PATH
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH, SOURCES[0]]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)
+    if verbose:
+        print(r.stderr)
+    return LIB_PATH
+
+
+class Config(C.Structure):
+    _fields_ = [("hidden", C.c_int32), ("expert_ffn", C.c_int32), ("shared_ffn", C.c_int32),
+                ("n_experts", C.c_int32), ("top_k", C.c_int32), ("n_layers", C.c_int32),
+                ("gate_type", C.c_int32), ("up_type", C.c_int32), ("down_type", C.c_int32),
+                ("w_scale", C.c_float), ("ep_rank", C.c_int32), ("ep_size", C.c_int32),
+                ("max_tokens", C.c_int32), ("device", C.c_int32), ("cache_mib", C.c_int64),
+                ("rms_eps", C.c_float)]
+
+
+_lib = None
+
+
+def lib():
+    """The loaded C-ABI library. Raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: run warpdecode_b200.build() (needs nvcc); "
+                               "there is no CPU fallback")
+        L = C.CDLL(LIB_PATH)
+        L.wd_last_error.restype = C.c_char_p
+        L.wd_default_cache_mib.restype = C.c_int64
+        L.wd_default_cache_mib.argtypes = [C.c_int64]
+        L.wd_cache_slot_count.restype = C.c_int64
+        L.wd_cache_slot_bytes.restype = C.c_int64
+        L.wd_cache_slot_count.argtypes = [C.c_void_p]
+        L.wd_cache_slot_bytes.argtypes = [C.c_void_p]
+        L.wd_engine_create.argtypes = [C.POINTER(Config), C.POINTER(C.c_void_p)]
+        L.wd_engine_destroy.argtypes = [C.c_void_p]
+        L.wd_engine_destroy.restype = None
+        vp, i = C.c_void_p, C.c_int
+        L.wd_set_router.argtypes = [vp, i, vp, vp]
+        L.wd_set_shared.argtypes = [vp, i, vp, vp, vp, vp]
+        L.wd_set_norm.argtypes = [vp, i, vp]
+        L.wd_set_experts.argtypes = [vp, i, vp, vp, vp]
+        L.wd_set_experts_device.argtypes = [vp, i, vp, vp, vp]
+        L.wd_cache_acquire.argtypes = [vp, i, i, C.POINTER(C.c_int)]
+        L.wd_cache_stats.argtypes = [vp, C.POINTER(C.c_int64)]
+        L.wd_moe_forward.argtypes = [vp, i, vp, vp, i, vp]
+        L.wd_moe_forward_host.argtypes = [vp, i, vp, vp, i]
+        L.wd_stack_step.argtypes = [vp, vp, vp]
+        L.wd_stack_step_host.argtypes = [vp, vp, vp]
+        L.wd_read_tap.argtypes = [vp, i, i, vp, C.c_size_t]
+        L.wd_device_status.argtypes = [vp, C.POINTER(C.c_int)]
+        L.wd_router_topk_host.argtypes = [vp, i, i, C.c_float, vp, vp, vp]
+        L.wd_quantize_q8_0_host.argtypes = [vp, i, vp]
+        L.wd_quantize_q8_K_host.argtypes = [vp, i, vp]
+        L.wd_matvec_host.argtypes = [i, vp, i, i, vp, vp, vp]
+        L.wd_synth_model.argtypes = [vp, C.c_uint64, C.c_float, C.c_float]
+        L.wd_synth_expert_host.argtypes = [vp, C.c_uint64, C.c_float, i, i, vp, vp, vp]
+        L.wd_synth_dense_host.argtypes = [vp, C.c_uint64, C.c_float, C.c_float, i, vp, vp, vp, vp, vp, vp]
+        _lib = L
+    return _lib
+
+
+class WdError(RuntimeError):
+    pass
+
+
+def _check(rc):
+    if rc != 0:
+        raise WdError(f"warpdecode_b200 error {rc}: {lib().wd_last_error().decode(errors='replace')}")
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data
+
+
+class Engine:
+    """One MoE stack on one GPU (wd_engine)."""
+
+    def __init__(self, hidden, expert_ffn, n_experts, top_k, shared_ffn=0, n_layers=1, expert_type=TYPE_IQ3_S,
+                 w_scale=1.0, ep_rank=0, ep_size=1, device=0, cache_mib=0, rms_eps=1e-6):
+        self.cfg = Config(hidden, expert_ffn, shared_ffn, n_experts, top_k, n_layers, expert_type, expert_type,
+                          expert_type, w_scale, ep_rank, ep_size, 1, device, cache_mib, rms_eps)
+        self.h = C.c_void_p()
+        _check(lib().wd_engine_create(C.byref(self.cfg), C.byref(self.h)))
+        self._keep = []
+
+    def close(self):
+        if self.h:
+            lib().wd_engine_destroy(self.h)
+            self.h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- weights -----------------------------------------------------------------------------
+    def load_block(self, layer, m):
+        """m: dict in the layout of synth.make_moe_block (ggml block bytes, host numpy arrays)."""
+        u8 = lambda a: np.ascontiguousarray(a, np.uint8)
+        f32 = lambda a: np.ascontiguousarray(a, np.float32)
+        router = u8(m["router"])
+        bias = f32(m["router_bias"]) if m.get("router_bias") is not None else None
+        _check(lib().wd_set_router(self.h, layer, _ptr(router), _ptr(bias)))
+        if self.cfg.shared_ffn:
+            gv, sg, su, sd = f32(m["shared_gate_vec"]), u8(m["shared_gate"]), u8(m["shared_up"]), u8(m["shared_down"])
+            _check(lib().wd_set_shared(self.h, layer, _ptr(gv), _ptr(sg), _ptr(su), _ptr(sd)))
+        g, u, d = u8(m["gate"]), u8(m["up"]), u8(m["down"])
+        self._keep += [g, u, d]           # the library retains these host pointers
+        _check(lib().wd_set_experts(self.h, layer, _ptr(g), _ptr(u), _ptr(d)))
+
+    def set_norm(self, layer, w):
+        w = None if w is None else np.ascontiguousarray(w, np.float32)
+        _check(lib().wd_set_norm(self.h, layer, _ptr(w)))
+
+    def synth_model(self, seed, sigma=0.02, bias_sigma=0.0):
+        _check(lib().wd_synth_model(self.h, seed, sigma, bias_sigma))
+
+    def synth_expert_host(self, seed, sigma, layer, expert):
+        c = self.cfg
+        gb = c.expert_ffn * (c.hidden // 256) * 110
+        db = c.hidden * (c.expert_ffn // 256) * 110
+        g, u, d = np.zeros(gb, np.uint8), np.zeros(gb, np.uint8), np.zeros(db, np.uint8)
+        _check(lib().wd_synth_expert_host(self.h, seed, sigma, layer, expert, _ptr(g), _ptr(u), _ptr(d)))
+        return g, u, d
+
+    def synth_dense_host(self, seed, sigma, bias_sigma, layer):
+        c = self.cfg
+        q8 = lambda r, cols: np.zeros(r * (cols // 32) * 34, np.uint8)
+        out = dict(router=q8(c.n_experts, c.hidden))
+        out["router_bias"] = np.zeros(c.n_experts, np.float32) if bias_sigma > 0 else None
+        if c.shared_ffn:
+            out.update(shared_gate_vec=np.zeros(c.hidden, np.float32), shared_gate=q8(c.shared_ffn, c.hidden),
+                       shared_up=q8(c.shared_ffn, c.hidden), shared_down=q8(c.hidden, c.shared_ffn))
+        _check(lib().wd_synth_dense_host(self.h, seed, sigma, bias_sigma, layer, _ptr(out["router"]),
+                                         _ptr(out["router_bias"]), _ptr(out.get("shared_gate_vec")),
+                                         _ptr(out.get("shared_gate")), _ptr(out.get("shared_up")),
+                                         _ptr(out.get("shared_down"))))
+        return out
+
+    # -- forward -----------------------------------------------------------------------------
+    def forward_host(self, layer, x):
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.zeros(self.cfg.hidden, np.float32)
+        _check(lib().wd_moe_forward_host(self.h, layer, _ptr(x), _ptr(out), 1))
+        return out
+
+    def forward_device(self, layer, x_ptr, out_ptr, stream=None):
+        _check(lib().wd_moe_forward(self.h, layer, x_ptr, out_ptr, 1, stream))
+
+    def stack_step_host(self, residual):
+        r = np.ascontiguousarray(residual, np.float32)
+        out = np.zeros_like(r)
+        _check(lib().wd_stack_step_host(self.h, _ptr(r), _ptr(out)))
+        return out
+
+    def stack_step_device(self, residual_ptr, stream=None):
+        _check(lib().wd_stack_step(self.h, residual_ptr, stream))
+
+    def device_status(self):
+        st = C.c_int()
+        _check(lib().wd_device_status(self.h, C.byref(st)))
+        return st.value
+
+    def tap(self, name):
+        c = self.cfg
+        shapes = dict(logits=(c.n_experts,), ids=(c.top_k,), weights=(c.top_k,), act=(c.top_k, c.expert_ffn),
+                      expert_out=(c.top_k, c.hidden), routed=(c.hidden,), shared=(c.hidden,), shared_gate=(1,),
+                      shared_act=(max(c.shared_ffn, 1),))
+        a = np.zeros(shapes[name], np.int32 if name == "ids" else np.float32)
+        _check(lib().wd_read_tap(self.h, TAPS[name], 0, _ptr(a), a.nbytes))
+        return a
+
+    def slot_count(self):
+        return lib().wd_cache_slot_count(self.h)
+
+    def slot_bytes(self):
+        return lib().wd_cache_slot_bytes(self.h)
+
+
+# -- stand-alone pieces ------------------------------------------------------------------------
+def router_topk(logits, k, w_scale=1.0):
+    logits = np.ascontiguousarray(logits, np.float32)
+    ids, w, p = np.zeros(k, np.int32), np.zeros(k, np.float32), np.zeros(logits.size, np.float32)
+    _check(lib().wd_router_topk_host(_ptr(logits), logits.size, k, w_scale, _ptr(ids), _ptr(w), _ptr(p)))
+    return p, ids, w
+
+
+def quantize_q8_0(x):
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.zeros(x.size // 32 * 34, np.uint8)
+    _check(lib().wd_quantize_q8_0_host(_ptr(x), x.size, _ptr(out)))
+    return out
+
+
+def quantize_q8_K(x):
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.zeros(x.size // 256 * 292, np.uint8)
+    _check(lib().wd_quantize_q8_K_host(_ptr(x), x.size, _ptr(out)))
+    return out
+
+
+def matvec(t, w, rows, cols, x, partials=False):
+    w = np.ascontiguousarray(w, np.uint8)
+    x = np.ascontiguousarray(x, np.float32)
+    y = np.zeros(rows, np.float32)
+    p = np.zeros((rows, cols // 256, 8), np.int32) if partials else None
+    _check(lib().wd_matvec_host(t, _ptr(w), rows, cols, _ptr(x), _ptr(y), _ptr(p)))
+    return (y, p) if partials else y

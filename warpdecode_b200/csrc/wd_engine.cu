@@ -1,0 +1,914 @@
+// Host side of the C ABI declared in include/warpdecode_b200.h: engine state, weight upload
+// and repack, the expert slot cache, launches, CUDA-graph capture of the per-token stack.
+#include "../../include/warpdecode_b200.h"
+
+#include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <list>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "wd_aux_kernels.cuh"
+#include "wd_grids.h"
+
+namespace {
+
+thread_local std::string g_error;
+
+int fail(int code, const std::string &msg) {
+    g_error = msg;
+    return code;
+}
+
+#define WD_CUDA(call)                                                                          \
+    do {                                                                                       \
+        cudaError_t e__ = (call);                                                              \
+        if (e__ != cudaSuccess)                                                                \
+            return fail(WD_E_CUDA, std::string(#call) + ": " + cudaGetErrorString(e__));       \
+    } while (0)
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+struct Layer {
+    uint8_t *router = nullptr;
+    float *bias = nullptr;
+    float *gate_vec = nullptr;
+    uint8_t *sh_gate = nullptr, *sh_up = nullptr, *sh_down = nullptr;
+    float *norm = nullptr;
+    int *slot_of_expert = nullptr;              // device [E]
+    std::vector<int> h_slot;                    // host mirror
+    const uint8_t *h_gate = nullptr, *h_up = nullptr, *h_down = nullptr;   // retained host tensors
+    bool have_router = false, have_shared = false, have_experts = false;
+};
+
+}  // namespace
+
+struct wd_engine {
+    wd_config cfg{};
+    int n_sm = 0;
+    cudaStream_t stream = nullptr;
+    int nsb_h = 0, nsb_f = 0, e_first = 0, e_count = 0;
+    size_t gate_bytes = 0, down_bytes = 0, slot_bytes = 0;
+    int64_t n_slots = 0;
+    bool resident = false;
+    uint8_t *pool = nullptr;
+    std::vector<Layer> layers;
+    // cache bookkeeping (used when not every owned expert fits)
+    std::vector<int64_t> slot_key;                              // (layer << 32 | expert) or -1
+    std::list<int> lru;                                         // front = most recent
+    std::vector<std::list<int>::iterator> lru_pos;
+    std::unordered_map<int64_t, int> key_slot;
+    int64_t hits = 0, misses = 0, evictions = 0;
+    // device scratch
+    uint16_t *grid_packed = nullptr;
+    uint16_t *synth_lut = nullptr;
+    unsigned *sync = nullptr;
+    float *logits = nullptr, *weights = nullptr, *act = nullptr, *expert_out = nullptr, *routed = nullptr,
+          *shared_act = nullptr, *shared_down = nullptr, *shared_gate = nullptr, *x_buf = nullptr, *out_buf = nullptr,
+          *residual_buf = nullptr;
+    int *ids = nullptr;
+    uint8_t *staging = nullptr;       // device, ggml-layout upload buffer
+    size_t staging_bytes = 0;
+    void *pinned = nullptr;           // host, for the *_host entry points and miss fills
+    size_t pinned_bytes = 0;
+    wd::MoeParams base{};
+    size_t smem_bytes = 0;
+    cudaGraphExec_t stack_graph = nullptr;
+    float *stack_graph_residual = nullptr;
+    cudaStream_t stack_graph_stream = nullptr;
+};
+
+namespace {
+
+int plan_shared_memory(wd_engine *e) {
+    wd::MoeParams &p = e->base;
+    const wd_config &c = e->cfg;
+    const int ncta = e->n_sm;
+    const int nbh = c.hidden / 32, nbs = c.shared_ffn / 32;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off = align_up(off + bytes, 128);
+        return static_cast<unsigned>(o);
+    };
+    p.off_tab = take(wd::kGridTableBytes);
+    p.off_xq0 = take(c.hidden);
+    p.off_xd0 = take(nbh * 4);
+    p.off_xk = take(e->nsb_h * wd::kActSbStride);
+    p.off_xdk = take(e->nsb_h * 4);
+    p.off_actk = take(static_cast<size_t>(c.top_k) * e->nsb_f * wd::kActSbStride);
+    p.off_actd = take(static_cast<size_t>(c.top_k) * e->nsb_f * 4);
+    p.off_shq = take(std::max(c.shared_ffn, 16));
+    p.off_shd = take(std::max(nbs, 4) * 4);
+    p.off_misc = take(4 * static_cast<size_t>(std::max(c.hidden, 512 + wd::kMaxExperts + c.shared_ffn)));
+    const int r_h = 32 / e->nsb_h, r_f = 32 / e->nsb_f;
+    const int scr_floats = std::max(r_h * (e->nsb_h * 8 + 8) + 32, r_f * (e->nsb_f * 8 + 8) + 32);
+    p.scr_bytes = static_cast<unsigned>(align_up(scr_floats * 4, 128));
+    p.off_scr = take(static_cast<size_t>(p.scr_bytes) * wd::kWarps);
+    const int n_rt = c.n_experts / 4, n_st = c.shared_ffn / 4;
+    const int t2 = c.expert_ffn / r_h, t3 = c.hidden / r_f;
+    p.n1r = (n_rt + ncta - 1) / ncta;
+    p.n1s = (n_st + ncta - 1) / ncta;
+    p.n2 = (c.top_k * t2 + ncta - 1) / ncta;
+    const int n_sd = c.shared_ffn > 0 ? c.hidden / 4 : 0;
+    const int total3 = c.top_k * t3 + n_sd;
+    p.n3 = (c.top_k * t3 + ncta - 1) / ncta;
+    p.nsd = n_sd > 0 ? (total3 + ncta - 1) / ncta : 0;   // upper bound on shared-down tasks of one CTA
+    if (p.n1r + p.n1s + p.n2 + p.n3 + p.nsd > wd::kMaxBars)
+        return fail(WD_E_INVALID, "geometry needs more staging slots per CTA than the kernel supports");
+    p.off_bar = take(wd::kMaxBars * 8);
+    const size_t rt_bytes = static_cast<size_t>(nbh) * 136;
+    const size_t stage_a = std::max(static_cast<size_t>(p.n1r + p.n1s) * 2 * rt_bytes,
+                                    static_cast<size_t>(p.n2) * 2 * wd::kIq3TileBytes);
+    p.off_stage_a = take(stage_a);
+    p.off_stage_b = take(static_cast<size_t>(p.n3) * wd::kIq3TileBytes + static_cast<size_t>(p.nsd) * nbs * 136);
+    e->smem_bytes = off;
+    if (e->smem_bytes > 227 * 1024)
+        return fail(WD_E_INVALID, "geometry needs " + std::to_string(e->smem_bytes) +
+                                      " bytes of shared memory per CTA; the limit is 232448");
+    return WD_OK;
+}
+
+int upload_repacked_q8(wd_engine *e, const void *host_ggml, int rows, int cols, uint8_t **dev_out) {
+    const size_t bytes = static_cast<size_t>(rows) * (cols / 32) * 34;
+    if (bytes > e->staging_bytes) return fail(WD_E_STATE, "staging buffer too small for a Q8_0 tensor");
+    if (!*dev_out) WD_CUDA(cudaMalloc(dev_out, bytes));
+    WD_CUDA(cudaMemcpyAsync(e->staging, host_ggml, bytes, cudaMemcpyHostToDevice, e->stream));
+    const long long n = static_cast<long long>(rows) * (cols / 32);
+    wd::repack_q8_0_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, e->stream>>>(e->staging, *dev_out, rows,
+                                                                                         cols / 32);
+    WD_CUDA(cudaGetLastError());
+    WD_CUDA(cudaStreamSynchronize(e->stream));
+    return WD_OK;
+}
+
+int upload_f32(wd_engine *e, const float *host, size_t n, float **dev_out) {
+    if (!*dev_out) WD_CUDA(cudaMalloc(dev_out, n * 4));
+    WD_CUDA(cudaMemcpy(*dev_out, host, n * 4, cudaMemcpyHostToDevice));
+    (void)e;
+    return WD_OK;
+}
+
+// Repack one expert's three ggml tensors (device pointers) into slot `slot`.
+int repack_expert_into_slot(wd_engine *e, const uint8_t *g, const uint8_t *u, const uint8_t *d, int slot,
+                            cudaStream_t s) {
+    uint8_t *dst = e->pool + static_cast<size_t>(slot) * e->slot_bytes;
+    const long long nb_gu = static_cast<long long>(e->cfg.expert_ffn) * e->nsb_h;
+    const long long nb_d = static_cast<long long>(e->cfg.hidden) * e->nsb_f;
+    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_gu + 127) / 128), 128, 0, s>>>(g, dst, nb_gu);
+    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_gu + 127) / 128), 128, 0, s>>>(u, dst + e->gate_bytes, nb_gu);
+    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_d + 127) / 128), 128, 0, s>>>(d, dst + 2 * e->gate_bytes, nb_d);
+    WD_CUDA(cudaGetLastError());
+    return WD_OK;
+}
+
+int check_layer(const wd_engine *e, int layer) {
+    if (!e) return fail(WD_E_INVALID, "null engine");
+    if (layer < 0 || layer >= e->cfg.n_layers) return fail(WD_E_STATE, "layer index out of range");
+    return WD_OK;
+}
+
+void touch_slot(wd_engine *e, int slot) {
+    e->lru.erase(e->lru_pos[slot]);
+    e->lru.push_front(slot);
+    e->lru_pos[slot] = e->lru.begin();
+}
+
+int launch_layer(wd_engine *e, int layer, const float *x, float *residual, float *out, cudaStream_t s) {
+    Layer &L = e->layers[layer];
+    if (!L.have_router || !L.have_experts || (e->cfg.shared_ffn > 0 && !L.have_shared))
+        return fail(WD_E_STATE, "layer " + std::to_string(layer) + " has no weights yet");
+    wd::MoeParams p = e->base;
+    p.router_w = L.router;
+    p.router_bias = L.bias;
+    p.sh_gate_vec = L.gate_vec;
+    p.sh_gate = L.sh_gate;
+    p.sh_up = L.sh_up;
+    p.sh_down = L.sh_down;
+    p.norm_w = L.norm;
+    p.slot_of_expert = L.slot_of_expert;
+    p.x = x;
+    p.residual = residual;
+    p.out = out;
+    void *args[] = {&p};
+    WD_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(wd::moe_layer_kernel), dim3(e->n_sm),
+                                        dim3(wd::kThreads), args, e->smem_bytes, s));
+    return WD_OK;
+}
+
+int check_device_status(wd_engine *e) {
+    unsigned st = 0;
+    WD_CUDA(cudaMemcpy(&st, e->sync + 2, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st != 0) {
+        // leave the barrier words in a usable state for the next launch
+        cudaMemset(e->sync, 0, 4096);
+        return fail(WD_E_DEVICE, "kernel raised status " + std::to_string(st) +
+                                     " (1 barrier timeout, 2 copy timeout, 4 expert without slot, 8 geometry)");
+    }
+    return WD_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *wd_last_error(void) { return g_error.c_str(); }
+int wd_version(void) { return (0 << 16) | 1; }
+
+int64_t wd_default_cache_mib(int64_t memory_mib) {
+    int64_t cache = memory_mib * 3 / 4 - 8 * 1024;
+    cache = std::max<int64_t>(512, std::min<int64_t>(64 * 1024, cache));
+    if (const char *v = std::getenv("WARODECODE_EXPERT_CACHE_MIB")) {
+        const long mib = std::atol(v);
+        if (mib > 0) cache = mib;
+    }
+    return cache;
+}
+
+int wd_engine_create(const wd_config *cfg, wd_engine **out) {
+    if (!cfg || !out) return fail(WD_E_INVALID, "null argument");
+    const wd_config &c = *cfg;
+    if (c.hidden % 256 || !pow2(c.hidden / 256) || c.hidden / 256 > 32)
+        return fail(WD_E_INVALID, "hidden must be 256 * 2^n, n <= 5");
+    if (c.expert_ffn % 256 || !pow2(c.expert_ffn / 256) || c.expert_ffn / 256 > 8)
+        return fail(WD_E_INVALID, "expert_ffn must be 256 * 2^n, n <= 3");
+    if (c.shared_ffn < 0 || c.shared_ffn % 128) return fail(WD_E_INVALID, "shared_ffn must be a multiple of 128");
+    if (c.n_experts <= 0 || c.n_experts % 8 || c.n_experts > wd::kMaxExperts)
+        return fail(WD_E_INVALID, "n_experts must be a multiple of 8, at most 1024");
+    if (c.top_k < 1 || c.top_k > wd::kMaxK || c.top_k > c.n_experts) return fail(WD_E_INVALID, "top_k must be 1..16");
+    if (c.n_layers < 1) return fail(WD_E_INVALID, "n_layers must be positive");
+    if (c.gate_type != WD_TYPE_IQ3_S || c.up_type != WD_TYPE_IQ3_S || c.down_type != WD_TYPE_IQ3_S)
+        return fail(WD_E_INVALID, "only IQ3_S expert tensors are supported by this build");
+    if (c.ep_size < 1 || c.ep_rank < 0 || c.ep_rank >= c.ep_size || c.n_experts % c.ep_size)
+        return fail(WD_E_INVALID, "ep_rank/ep_size must partition n_experts evenly");
+    if (c.max_tokens != 1) return fail(WD_E_INVALID, "max_tokens must be 1 in this build");
+    int ndev = 0;
+    WD_CUDA(cudaGetDeviceCount(&ndev));
+    if (c.device < 0 || c.device >= ndev) return fail(WD_E_INVALID, "no such CUDA device");
+    WD_CUDA(cudaSetDevice(c.device));
+    cudaDeviceProp prop{};
+    WD_CUDA(cudaGetDeviceProperties(&prop, c.device));
+    if (prop.major < 10) return fail(WD_E_INVALID, "this library is built for sm_100a only");
+
+    wd_engine *e = new wd_engine();
+    e->cfg = c;
+    e->n_sm = prop.multiProcessorCount;
+    e->nsb_h = c.hidden / 256;
+    e->nsb_f = c.expert_ffn / 256;
+    e->e_count = c.n_experts / c.ep_size;
+    e->e_first = c.ep_rank * e->e_count;
+    e->gate_bytes = static_cast<size_t>(c.expert_ffn) * e->nsb_h * 110;
+    e->down_bytes = static_cast<size_t>(c.hidden) * e->nsb_f * 110;
+    e->slot_bytes = align_up(2 * e->gate_bytes + e->down_bytes, 256);
+    const int64_t owned = static_cast<int64_t>(e->e_count) * c.n_layers;
+    if (c.cache_mib <= 0) {
+        e->n_slots = owned;
+    } else {
+        e->n_slots = std::min<int64_t>(owned, (c.cache_mib << 20) / static_cast<int64_t>(e->slot_bytes));
+        if (e->n_slots < c.top_k) {
+            delete e;
+            return fail(WD_E_INVALID, "expert cache smaller than one layer's selection");
+        }
+    }
+    e->resident = e->n_slots == owned;
+    int rc = WD_OK;
+    auto bail = [&](int code) {
+        wd_engine_destroy(e);
+        return code;
+    };
+    cudaError_t ce;
+#define WD_TRY(call)                                                                  \
+    if ((ce = (call)) != cudaSuccess) {                                               \
+        fail(WD_E_CUDA, std::string(#call) + ": " + cudaGetErrorString(ce));          \
+        return bail(WD_E_CUDA);                                                       \
+    }
+    WD_TRY(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+    WD_TRY(cudaMalloc(&e->pool, static_cast<size_t>(e->n_slots) * e->slot_bytes));
+    e->layers.resize(c.n_layers);
+    for (Layer &L : e->layers) {
+        L.h_slot.assign(c.n_experts, -1);
+        WD_TRY(cudaMalloc(&L.slot_of_expert, c.n_experts * sizeof(int)));
+        WD_TRY(cudaMemset(L.slot_of_expert, 0xff, c.n_experts * sizeof(int)));
+    }
+    e->slot_key.assign(e->n_slots, -1);
+    e->lru_pos.resize(e->n_slots);
+    for (int64_t s = 0; s < e->n_slots; ++s) {
+        e->lru.push_back(static_cast<int>(s));
+        e->lru_pos[s] = std::prev(e->lru.end());
+    }
+    WD_TRY(cudaMalloc(&e->grid_packed, sizeof(wd_iq3s_grid_packed)));
+    WD_TRY(cudaMemcpy(e->grid_packed, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
+    WD_TRY(cudaMalloc(&e->sync, 4096 + sizeof(unsigned) * (c.hidden / 4)));
+    WD_TRY(cudaMemset(e->sync, 0, 4096 + sizeof(unsigned) * (c.hidden / 4)));
+    const int H = c.hidden, F = c.expert_ffn, K = c.top_k, E = c.n_experts, SF = std::max(c.shared_ffn, 1);
+    WD_TRY(cudaMalloc(&e->logits, E * 4));
+    WD_TRY(cudaMalloc(&e->ids, K * 4));
+    WD_TRY(cudaMalloc(&e->weights, K * 4));
+    WD_TRY(cudaMalloc(&e->act, static_cast<size_t>(K) * F * 4));
+    WD_TRY(cudaMalloc(&e->expert_out, static_cast<size_t>(K) * H * 4));
+    WD_TRY(cudaMalloc(&e->routed, H * 4));
+    WD_TRY(cudaMalloc(&e->shared_act, SF * 4));
+    WD_TRY(cudaMalloc(&e->shared_down, H * 4));
+    WD_TRY(cudaMalloc(&e->shared_gate, 4));
+    WD_TRY(cudaMalloc(&e->x_buf, H * 4));
+    WD_TRY(cudaMalloc(&e->out_buf, H * 4));
+    WD_TRY(cudaMalloc(&e->residual_buf, H * 4));
+    WD_TRY(cudaMemset(e->expert_out, 0, static_cast<size_t>(K) * H * 4));
+    WD_TRY(cudaMemset(e->act, 0, static_cast<size_t>(K) * F * 4));
+    WD_TRY(cudaMemset(e->shared_down, 0, H * 4));
+    WD_TRY(cudaMemset(e->shared_gate, 0, 4));
+    // staging: one layer's routed experts in ggml layout (or a dense tensor, whichever is larger)
+    const size_t dense = static_cast<size_t>(std::max(E, std::max(c.shared_ffn, H))) * (std::max(H, c.shared_ffn) / 32) * 34;
+    const size_t one_expert = 2 * e->gate_bytes + e->down_bytes;
+    e->staging_bytes = align_up(std::max(dense, one_expert * 8), 256);
+    WD_TRY(cudaMalloc(&e->staging, e->staging_bytes));
+    e->pinned_bytes = align_up(std::max<size_t>(one_expert, static_cast<size_t>(H) * 8), 256);
+    WD_TRY(cudaMallocHost(&e->pinned, e->pinned_bytes));
+#undef WD_TRY
+
+    wd::MoeParams &p = e->base;
+    p.H = H; p.F = F; p.SF = c.shared_ffn; p.E = E; p.K = K;
+    p.nsb_h = e->nsb_h; p.nsb_f = e->nsb_f;
+    p.e_first = e->e_first; p.e_count = e->e_count;
+    p.w_scale = c.w_scale; p.eps = c.rms_eps > 0 ? c.rms_eps : 1e-6f;
+    p.pool = e->pool; p.slot_bytes = e->slot_bytes;
+    p.gate_off = 0; p.up_off = static_cast<unsigned>(e->gate_bytes); p.down_off = static_cast<unsigned>(2 * e->gate_bytes);
+    p.grid_packed = e->grid_packed;
+    p.logits = e->logits; p.ids = e->ids; p.weights = e->weights; p.act = e->act; p.expert_out = e->expert_out;
+    p.routed = e->routed; p.shared_act = e->shared_act; p.shared_down = e->shared_down; p.shared_gate = e->shared_gate;
+    p.sync = e->sync;
+    if ((rc = plan_shared_memory(e)) != WD_OK) return bail(rc);
+    cudaError_t ae = cudaFuncSetAttribute(wd::moe_layer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(e->smem_bytes));
+    if (ae != cudaSuccess) {
+        fail(WD_E_CUDA, std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(ae));
+        return bail(WD_E_CUDA);
+    }
+    int occ = 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, wd::moe_layer_kernel, wd::kThreads, e->smem_bytes);
+    if (occ < 1) {
+        fail(WD_E_INVALID, "the layer kernel does not fit one CTA per SM with this geometry");
+        return bail(WD_E_INVALID);
+    }
+    *out = e;
+    return WD_OK;
+}
+
+void wd_engine_destroy(wd_engine *e) {
+    if (!e) return;
+    cudaSetDevice(e->cfg.device);
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    if (e->stack_graph) cudaGraphExecDestroy(e->stack_graph);
+    for (Layer &L : e->layers) {
+        cudaFree(L.router); cudaFree(L.bias); cudaFree(L.gate_vec); cudaFree(L.sh_gate); cudaFree(L.sh_up);
+        cudaFree(L.sh_down); cudaFree(L.norm); cudaFree(L.slot_of_expert);
+    }
+    void *bufs[] = {e->pool, e->grid_packed, e->synth_lut, e->sync, e->logits, e->ids, e->weights, e->act,
+                    e->expert_out, e->routed, e->shared_act, e->shared_down, e->shared_gate, e->x_buf, e->out_buf,
+                    e->residual_buf, e->staging};
+    for (void *b : bufs) cudaFree(b);
+    if (e->pinned) cudaFreeHost(e->pinned);
+    if (e->stream) cudaStreamDestroy(e->stream);
+    delete e;
+}
+
+int wd_set_router(wd_engine *e, int layer, const void *router_q8_0, const float *bias) {
+    int rc = check_layer(e, layer);
+    if (rc) return rc;
+    if (!router_q8_0) return fail(WD_E_INVALID, "null router");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    Layer &L = e->layers[layer];
+    if ((rc = upload_repacked_q8(e, router_q8_0, e->cfg.n_experts, e->cfg.hidden, &L.router))) return rc;
+    if (bias) {
+        if ((rc = upload_f32(e, bias, e->cfg.n_experts, &L.bias))) return rc;
+    }
+    L.have_router = true;
+    return WD_OK;
+}
+
+int wd_set_shared(wd_engine *e, int layer, const float *gate_vec, const void *g, const void *u, const void *d) {
+    int rc = check_layer(e, layer);
+    if (rc) return rc;
+    if (e->cfg.shared_ffn == 0) return fail(WD_E_STATE, "engine was created without a shared expert");
+    if (!gate_vec || !g || !u || !d) return fail(WD_E_INVALID, "null shared expert tensor");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    Layer &L = e->layers[layer];
+    if ((rc = upload_f32(e, gate_vec, e->cfg.hidden, &L.gate_vec))) return rc;
+    if ((rc = upload_repacked_q8(e, g, e->cfg.shared_ffn, e->cfg.hidden, &L.sh_gate))) return rc;
+    if ((rc = upload_repacked_q8(e, u, e->cfg.shared_ffn, e->cfg.hidden, &L.sh_up))) return rc;
+    if ((rc = upload_repacked_q8(e, d, e->cfg.hidden, e->cfg.shared_ffn, &L.sh_down))) return rc;
+    L.have_shared = true;
+    return WD_OK;
+}
+
+int wd_set_norm(wd_engine *e, int layer, const float *weight) {
+    int rc = check_layer(e, layer);
+    if (rc) return rc;
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    Layer &L = e->layers[layer];
+    if (!weight) {
+        cudaFree(L.norm);
+        L.norm = nullptr;
+        return WD_OK;
+    }
+    return upload_f32(e, weight, e->cfg.hidden, &L.norm);
+}
+
+static int fill_slot_from_host(wd_engine *e, int layer, int expert, int slot) {
+    Layer &L = e->layers[layer];
+    const size_t gb = e->gate_bytes, db = e->down_bytes;
+    uint8_t *st = e->staging;
+    // pageable or mapped host memory -> pinned bounce buffer -> device staging -> repack into the slot
+    uint8_t *pin = static_cast<uint8_t *>(e->pinned);
+    memcpy(pin, L.h_gate + static_cast<size_t>(expert) * gb, gb);
+    memcpy(pin + gb, L.h_up + static_cast<size_t>(expert) * gb, gb);
+    memcpy(pin + 2 * gb, L.h_down + static_cast<size_t>(expert) * db, db);
+    WD_CUDA(cudaMemcpyAsync(st, pin, 2 * gb + db, cudaMemcpyHostToDevice, e->stream));
+    int rc = repack_expert_into_slot(e, st, st + gb, st + 2 * gb, slot, e->stream);
+    if (rc) return rc;
+    WD_CUDA(cudaStreamSynchronize(e->stream));   // the bounce buffers are reused by the next fill
+    return WD_OK;
+}
+
+static int bind_slot(wd_engine *e, int layer, int expert, int slot) {
+    Layer &L = e->layers[layer];
+    const int64_t old = e->slot_key[slot];
+    if (old >= 0) {
+        Layer &OL = e->layers[static_cast<int>(old >> 32)];
+        const int oe = static_cast<int>(old & 0xffffffff);
+        OL.h_slot[oe] = -1;
+        const int minus1 = -1;
+        WD_CUDA(cudaMemcpyAsync(OL.slot_of_expert + oe, &minus1, sizeof(int), cudaMemcpyHostToDevice, e->stream));
+        e->key_slot.erase(old);
+        ++e->evictions;
+    }
+    const int64_t key = (static_cast<int64_t>(layer) << 32) | static_cast<uint32_t>(expert);
+    e->slot_key[slot] = key;
+    e->key_slot[key] = slot;
+    L.h_slot[expert] = slot;
+    WD_CUDA(cudaMemcpyAsync(L.slot_of_expert + expert, &slot, sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    WD_CUDA(cudaStreamSynchronize(e->stream));
+    return WD_OK;
+}
+
+int wd_set_experts(wd_engine *e, int layer, const void *gate, const void *up, const void *down) {
+    int rc = check_layer(e, layer);
+    if (rc) return rc;
+    if (!gate || !up || !down) return fail(WD_E_INVALID, "null expert tensor");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    Layer &L = e->layers[layer];
+    L.h_gate = static_cast<const uint8_t *>(gate);
+    L.h_up = static_cast<const uint8_t *>(up);
+    L.h_down = static_cast<const uint8_t *>(down);
+    L.have_experts = true;
+    if (e->resident) {
+        for (int x = 0; x < e->e_count; ++x) {
+            const int expert = e->e_first + x;
+            const int slot = layer * e->e_count + x;
+            if ((rc = fill_slot_from_host(e, layer, expert, slot))) return rc;
+            if ((rc = bind_slot(e, layer, expert, slot))) return rc;
+            touch_slot(e, slot);
+        }
+    }
+    return WD_OK;
+}
+
+int wd_set_experts_device(wd_engine *e, int layer, const void *gate, const void *up, const void *down) {
+    int rc = check_layer(e, layer);
+    if (rc) return rc;
+    if (!e->resident) return fail(WD_E_STATE, "device-side expert upload needs a pool that holds every owned expert");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    Layer &L = e->layers[layer];
+    const uint8_t *g = static_cast<const uint8_t *>(gate), *u = static_cast<const uint8_t *>(up),
+                  *d = static_cast<const uint8_t *>(down);
+    std::vector<int> slots(e->cfg.n_experts, -1);
+    for (int x = 0; x < e->e_count; ++x) {
+        const int expert = e->e_first + x, slot = layer * e->e_count + x;
+        if ((rc = repack_expert_into_slot(e, g + static_cast<size_t>(expert) * e->gate_bytes,
+                                          u + static_cast<size_t>(expert) * e->gate_bytes,
+                                          d + static_cast<size_t>(expert) * e->down_bytes, slot, e->stream)))
+            return rc;
+        slots[expert] = slot;
+        const int64_t key = (static_cast<int64_t>(layer) << 32) | static_cast<uint32_t>(expert);
+        e->slot_key[slot] = key;
+        e->key_slot[key] = slot;
+    }
+    L.h_slot = slots;
+    WD_CUDA(cudaMemcpyAsync(L.slot_of_expert, slots.data(), slots.size() * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    WD_CUDA(cudaStreamSynchronize(e->stream));
+    L.have_experts = true;
+    return WD_OK;
+}
+
+int64_t wd_cache_slot_count(const wd_engine *e) { return e ? e->n_slots : 0; }
+int64_t wd_cache_slot_bytes(const wd_engine *e) { return e ? static_cast<int64_t>(e->slot_bytes) : 0; }
+
+int wd_cache_acquire(wd_engine *e, int layer, int expert, int *slot_out) {
+    int rc = check_layer(e, layer);
+    if (rc) return rc;
+    if (expert < e->e_first || expert >= e->e_first + e->e_count)
+        return fail(WD_E_INVALID, "expert is not owned by this rank");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    Layer &L = e->layers[layer];
+    int slot = L.h_slot[expert];
+    if (slot >= 0) {
+        ++e->hits;
+        touch_slot(e, slot);
+    } else {
+        if (!L.h_gate) return fail(WD_E_STATE, "no host tensors to fill the slot from");
+        ++e->misses;
+        slot = e->lru.back();
+        if ((rc = fill_slot_from_host(e, layer, expert, slot))) return rc;
+        if ((rc = bind_slot(e, layer, expert, slot))) return rc;
+        touch_slot(e, slot);
+    }
+    if (slot_out) *slot_out = slot;
+    return WD_OK;
+}
+
+int wd_cache_stats(const wd_engine *e, int64_t stats[3]) {
+    if (!e || !stats) return fail(WD_E_INVALID, "null argument");
+    stats[0] = e->hits; stats[1] = e->misses; stats[2] = e->evictions;
+    return WD_OK;
+}
+
+int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, int n_tokens, void *stream) {
+    int rc = check_layer(e, layer);
+    if (rc) return rc;
+    if (n_tokens != 1) return fail(WD_E_INVALID, "n_tokens must be 1 in this build");
+    if (!x_dev || !out_dev) return fail(WD_E_INVALID, "null buffer");
+    if (!e->resident) return fail(WD_E_STATE, "a capped expert cache is not supported by this build");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
+    return launch_layer(e, layer, x_dev, nullptr, out_dev, s);
+}
+
+int wd_moe_forward_host(wd_engine *e, int layer, const float *x_host, float *out_host, int n_tokens) {
+    int rc = check_layer(e, layer);
+    if (rc) return rc;
+    if (n_tokens != 1) return fail(WD_E_INVALID, "n_tokens must be 1 in this build");
+    const size_t bytes = static_cast<size_t>(e->cfg.hidden) * 4;
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    float *pin = static_cast<float *>(e->pinned);
+    memcpy(pin, x_host, bytes);
+    WD_CUDA(cudaMemcpyAsync(e->x_buf, pin, bytes, cudaMemcpyHostToDevice, e->stream));
+    if ((rc = wd_moe_forward(e, layer, e->x_buf, e->out_buf, 1, e->stream))) return rc;
+    WD_CUDA(cudaMemcpyAsync(pin + e->cfg.hidden, e->out_buf, bytes, cudaMemcpyDeviceToHost, e->stream));
+    WD_CUDA(cudaStreamSynchronize(e->stream));
+    memcpy(out_host, pin + e->cfg.hidden, bytes);
+    return check_device_status(e);
+}
+
+int wd_stack_step(wd_engine *e, float *residual_dev, void *stream) {
+    if (!e || !residual_dev) return fail(WD_E_INVALID, "null argument");
+    if (!e->resident) return fail(WD_E_STATE, "a capped expert cache is not supported by this build");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
+    if (e->stack_graph && (e->stack_graph_residual != residual_dev)) {
+        cudaGraphExecDestroy(e->stack_graph);
+        e->stack_graph = nullptr;
+    }
+    if (!e->stack_graph) {
+        // capture the whole token; if capture of cooperative launches is refused, run the layers directly
+        cudaGraph_t graph = nullptr;
+        int rc = WD_OK;
+        if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+            for (int l = 0; l < e->cfg.n_layers && rc == WD_OK; ++l)
+                rc = launch_layer(e, l, nullptr, residual_dev, e->out_buf, s);
+            cudaError_t ce = cudaStreamEndCapture(s, &graph);
+            if (rc == WD_OK && ce == cudaSuccess && graph &&
+                cudaGraphInstantiate(&e->stack_graph, graph, 0) == cudaSuccess) {
+                e->stack_graph_residual = residual_dev;
+            } else {
+                e->stack_graph = nullptr;
+                cudaGetLastError();
+            }
+            if (graph) cudaGraphDestroy(graph);
+        } else {
+            cudaGetLastError();
+        }
+    }
+    if (e->stack_graph) {
+        WD_CUDA(cudaGraphLaunch(e->stack_graph, s));
+        return WD_OK;
+    }
+    for (int l = 0; l < e->cfg.n_layers; ++l) {
+        int rc = launch_layer(e, l, nullptr, residual_dev, e->out_buf, s);
+        if (rc) return rc;
+    }
+    return WD_OK;
+}
+
+int wd_stack_step_host(wd_engine *e, const float *in_host, float *out_host) {
+    if (!e || !in_host || !out_host) return fail(WD_E_INVALID, "null argument");
+    const size_t bytes = static_cast<size_t>(e->cfg.hidden) * 4;
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    float *pin = static_cast<float *>(e->pinned);
+    memcpy(pin, in_host, bytes);
+    WD_CUDA(cudaMemcpyAsync(e->residual_buf, pin, bytes, cudaMemcpyHostToDevice, e->stream));
+    int rc = wd_stack_step(e, e->residual_buf, e->stream);
+    if (rc) return rc;
+    WD_CUDA(cudaMemcpyAsync(pin + e->cfg.hidden, e->residual_buf, bytes, cudaMemcpyDeviceToHost, e->stream));
+    WD_CUDA(cudaStreamSynchronize(e->stream));
+    memcpy(out_host, pin + e->cfg.hidden, bytes);
+    return check_device_status(e);
+}
+
+int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
+    if (!e || !dst) return fail(WD_E_INVALID, "null argument");
+    if (token != 0) return fail(WD_E_INVALID, "token out of range");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    const wd_config &c = e->cfg;
+    const void *src = nullptr;
+    size_t n = 0;
+    switch (tap) {
+        case WD_TAP_LOGITS: src = e->logits; n = c.n_experts * 4; break;
+        case WD_TAP_IDS: src = e->ids; n = c.top_k * 4; break;
+        case WD_TAP_WEIGHTS: src = e->weights; n = c.top_k * 4; break;
+        case WD_TAP_ACT: src = e->act; n = static_cast<size_t>(c.top_k) * c.expert_ffn * 4; break;
+        case WD_TAP_EXPERT_OUT: src = e->expert_out; n = static_cast<size_t>(c.top_k) * c.hidden * 4; break;
+        case WD_TAP_ROUTED: src = e->routed; n = c.hidden * 4; break;
+        case WD_TAP_SHARED: src = e->shared_down; n = c.hidden * 4; break;
+        case WD_TAP_SHARED_GATE: src = e->shared_gate; n = 4; break;
+        case WD_TAP_SHARED_ACT: src = e->shared_act; n = static_cast<size_t>(c.shared_ffn) * 4; break;
+        default: return fail(WD_E_INVALID, "unknown tap");
+    }
+    if (bytes < n) return fail(WD_E_INVALID, "tap buffer too small");
+    WD_CUDA(cudaStreamSynchronize(e->stream));
+    WD_CUDA(cudaDeviceSynchronize());
+    WD_CUDA(cudaMemcpy(dst, src, n, cudaMemcpyDeviceToHost));
+    return WD_OK;
+}
+
+int wd_device_status(wd_engine *e, int *status) {
+    if (!e || !status) return fail(WD_E_INVALID, "null argument");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    WD_CUDA(cudaDeviceSynchronize());
+    unsigned st = 0;
+    WD_CUDA(cudaMemcpy(&st, e->sync + 2, sizeof(st), cudaMemcpyDeviceToHost));
+    *status = static_cast<int>(st);
+    if (st) WD_CUDA(cudaMemset(e->sync, 0, 4096));
+    return WD_OK;
+}
+
+// ---- stand-alone pieces -------------------------------------------------------------------------
+int wd_router_topk_host(const float *logits, int n_experts, int k, float w_scale, int *ids, float *weights,
+                        float *probs) {
+    if (!logits || !ids || !weights) return fail(WD_E_INVALID, "null argument");
+    if (n_experts <= 0 || n_experts % 8 || n_experts > wd::kMaxExperts || k < 1 || k > wd::kMaxK)
+        return fail(WD_E_INVALID, "n_experts must be a multiple of 8 up to 1024, k 1..16");
+    float *d_l = nullptr, *d_w = nullptr, *d_p = nullptr;
+    int *d_i = nullptr;
+    WD_CUDA(cudaMalloc(&d_l, n_experts * 4));
+    WD_CUDA(cudaMalloc(&d_p, n_experts * 4));
+    WD_CUDA(cudaMalloc(&d_w, wd::kMaxK * 4));
+    WD_CUDA(cudaMalloc(&d_i, wd::kMaxK * 4));
+    WD_CUDA(cudaMemcpy(d_l, logits, n_experts * 4, cudaMemcpyHostToDevice));
+    wd::test_router_kernel<<<1, 32>>>(d_l, n_experts, k, w_scale, d_i, d_w, d_p);
+    WD_CUDA(cudaGetLastError());
+    WD_CUDA(cudaDeviceSynchronize());
+    WD_CUDA(cudaMemcpy(ids, d_i, k * 4, cudaMemcpyDeviceToHost));
+    WD_CUDA(cudaMemcpy(weights, d_w, k * 4, cudaMemcpyDeviceToHost));
+    if (probs) WD_CUDA(cudaMemcpy(probs, d_p, n_experts * 4, cudaMemcpyDeviceToHost));
+    cudaFree(d_l); cudaFree(d_p); cudaFree(d_w); cudaFree(d_i);
+    return WD_OK;
+}
+
+static int quantize_host(const float *x, int n, void *q80, void *q8k) {
+    if (!x || n <= 0 || n % 256 || n > 8192) return fail(WD_E_INVALID, "n must be a multiple of 256 up to 8192");
+    float *d_x = nullptr;
+    uint8_t *d_0 = nullptr, *d_k = nullptr;
+    WD_CUDA(cudaMalloc(&d_x, n * 4));
+    WD_CUDA(cudaMemcpy(d_x, x, n * 4, cudaMemcpyHostToDevice));
+    if (q80) WD_CUDA(cudaMalloc(&d_0, n / 32 * 34));
+    if (q8k) WD_CUDA(cudaMalloc(&d_k, n / 256 * 292));
+    const size_t smem = n * 4 + n + n / 32 * 4 + (n / 256 + 1) * wd::kActSbStride + (n / 256 + 4) * 4 + 64;
+    WD_CUDA(cudaFuncSetAttribute(wd::test_quantize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    wd::test_quantize_kernel<<<1, 512, smem>>>(d_x, n, d_0, d_k);
+    WD_CUDA(cudaGetLastError());
+    WD_CUDA(cudaDeviceSynchronize());
+    if (q80) WD_CUDA(cudaMemcpy(q80, d_0, n / 32 * 34, cudaMemcpyDeviceToHost));
+    if (q8k) WD_CUDA(cudaMemcpy(q8k, d_k, n / 256 * 292, cudaMemcpyDeviceToHost));
+    cudaFree(d_x); cudaFree(d_0); cudaFree(d_k);
+    return WD_OK;
+}
+int wd_quantize_q8_0_host(const float *x, int n, void *blocks) { return quantize_host(x, n, blocks, nullptr); }
+int wd_quantize_q8_K_host(const float *x, int n, void *blocks) { return quantize_host(x, n, nullptr, blocks); }
+
+int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, float *y, int32_t *partials) {
+    if (!w || !x || !y) return fail(WD_E_INVALID, "null argument");
+    float *d_x = nullptr, *d_y = nullptr;
+    uint8_t *d_src = nullptr, *d_dst = nullptr;
+    int *d_p = nullptr;
+    uint16_t *d_grid = nullptr;
+    if (type == WD_TYPE_IQ3_S) {
+        const int nsb = cols / 256;
+        if (cols % 256 || !pow2(nsb) || nsb > 32 || rows % (32 / nsb))
+            return fail(WD_E_INVALID, "IQ3_S matvec: cols must be 256*2^n (n<=5), rows a multiple of 32/(cols/256)");
+        const size_t bytes = static_cast<size_t>(rows) * nsb * 110;
+        WD_CUDA(cudaMalloc(&d_src, bytes));
+        WD_CUDA(cudaMalloc(&d_dst, bytes));
+        WD_CUDA(cudaMalloc(&d_x, cols * 4));
+        WD_CUDA(cudaMalloc(&d_y, rows * 4));
+        WD_CUDA(cudaMalloc(&d_grid, sizeof(wd_iq3s_grid_packed)));
+        WD_CUDA(cudaMemcpy(d_grid, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
+        if (partials) WD_CUDA(cudaMalloc(&d_p, static_cast<size_t>(rows) * nsb * 8 * 4));
+        WD_CUDA(cudaMemcpy(d_src, w, bytes, cudaMemcpyHostToDevice));
+        WD_CUDA(cudaMemcpy(d_x, x, cols * 4, cudaMemcpyHostToDevice));
+        const long long nblocks = static_cast<long long>(rows) * nsb;
+        wd::repack_iq3s_kernel<<<static_cast<unsigned>((nblocks + 127) / 128), 128>>>(d_src, d_dst, nblocks);
+        const int nw = 8;
+        const size_t smem = wd::kGridTableBytes + nsb * wd::kActSbStride + 32 * 4 + nw * wd::kIq3TileBytes + nw * 640 * 4 + 256;
+        WD_CUDA(cudaFuncSetAttribute(wd::test_matvec_iq3s_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        wd::test_matvec_iq3s_kernel<<<64, nw * 32, smem>>>(d_dst, rows, nsb, d_x, d_y, d_p, d_grid);
+        WD_CUDA(cudaGetLastError());
+        WD_CUDA(cudaDeviceSynchronize());
+        WD_CUDA(cudaMemcpy(y, d_y, rows * 4, cudaMemcpyDeviceToHost));
+        if (partials) WD_CUDA(cudaMemcpy(partials, d_p, static_cast<size_t>(rows) * nsb * 8 * 4, cudaMemcpyDeviceToHost));
+    } else if (type == WD_TYPE_Q8_0) {
+        const int nb = cols / 32;
+        if (cols % 128 || rows % 4 || cols > 8192) return fail(WD_E_INVALID, "Q8_0 matvec: cols % 128, rows % 4");
+        const size_t bytes = static_cast<size_t>(rows) * nb * 34;
+        WD_CUDA(cudaMalloc(&d_src, bytes));
+        WD_CUDA(cudaMalloc(&d_dst, bytes));
+        WD_CUDA(cudaMalloc(&d_x, cols * 4));
+        WD_CUDA(cudaMalloc(&d_y, rows * 4));
+        WD_CUDA(cudaMemcpy(d_src, w, bytes, cudaMemcpyHostToDevice));
+        WD_CUDA(cudaMemcpy(d_x, x, cols * 4, cudaMemcpyHostToDevice));
+        const long long n = static_cast<long long>(rows) * nb;
+        wd::repack_q8_0_kernel<<<static_cast<unsigned>((n + 255) / 256), 256>>>(d_src, d_dst, rows, nb);
+        const int nw = 8;
+        const size_t smem = cols * 4 + cols + nb * 4 + nw * nb * 136 + 256;
+        WD_CUDA(cudaFuncSetAttribute(wd::test_matvec_q8_0_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        wd::test_matvec_q8_0_kernel<<<64, nw * 32, smem>>>(d_dst, rows, nb, d_x, d_y);
+        WD_CUDA(cudaGetLastError());
+        WD_CUDA(cudaDeviceSynchronize());
+        WD_CUDA(cudaMemcpy(y, d_y, rows * 4, cudaMemcpyDeviceToHost));
+    } else {
+        return fail(WD_E_INVALID, "matvec supports IQ3_S and Q8_0");
+    }
+    cudaFree(d_x); cudaFree(d_y); cudaFree(d_src); cudaFree(d_dst); cudaFree(d_p); cudaFree(d_grid);
+    return WD_OK;
+}
+
+// ---- synthetic model ----------------------------------------------------------------------------------
+static int ensure_lut(wd_engine *e, cudaStream_t s) {
+    if (e->synth_lut) return WD_OK;
+    WD_CUDA(cudaMalloc(&e->synth_lut, 65536 * 2));
+    wd::synth_iq3s_lut_kernel<<<256, 256, 0, s>>>(e->grid_packed, e->synth_lut);
+    WD_CUDA(cudaGetLastError());
+    return WD_OK;
+}
+
+static int synth_into(wd_engine *e, int type, long long rows, int cols, float sigma, uint64_t seed, uint64_t sid,
+                      void *dst, cudaStream_t s, long long first_row = 0) {
+    if (type == WD_TYPE_Q8_0) {
+        const long long nb = rows * (cols / 32);
+        wd::synth_q8_0_kernel<<<static_cast<unsigned>((nb + 127) / 128), 128, 0, s>>>(static_cast<uint8_t *>(dst), nb,
+                                                                                     sigma, seed, sid);
+    } else if (type == WD_TYPE_IQ3_S) {
+        int rc = ensure_lut(e, s);
+        if (rc) return rc;
+        const long long nb = rows * (cols / 256);
+        wd::synth_iq3s_kernel<<<static_cast<unsigned>((nb + 63) / 64), 64, 0, s>>>(
+            static_cast<uint8_t *>(dst), first_row * (cols / 256), nb, sigma, seed, sid, e->synth_lut);
+    } else if (type == WD_TYPE_F32) {
+        const long long n = rows * cols;
+        wd::synth_f32_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(static_cast<float *>(dst), n, sigma,
+                                                                                   seed, sid);
+    } else {
+        return fail(WD_E_INVALID, "synthetic generator supports F32, Q8_0 and IQ3_S");
+    }
+    WD_CUDA(cudaGetLastError());
+    return WD_OK;
+}
+
+int wd_synth_tensor_device(int type, int rows, int cols, float sigma, uint64_t seed, uint64_t stream_id,
+                           void *dst_dev, void *stream) {
+    (void)type; (void)rows; (void)cols; (void)sigma; (void)seed; (void)stream_id; (void)dst_dev; (void)stream;
+    return fail(WD_E_STATE, "use wd_synth_model / wd_synth_expert_host (they own the codebook lookup table)");
+}
+
+// stream ids of the tensors of layer l: l*16 + {0 router, 1 bias, 2 gate vec, 3..5 shared gate/up/down,
+// 6 norm (unused), 8 gate exps, 9 up exps, 10 down exps}
+static uint64_t sid(int layer, int which) { return static_cast<uint64_t>(layer) * 16 + which; }
+
+int wd_synth_model(wd_engine *e, uint64_t seed, float sigma, float bias_sigma) {
+    if (!e) return fail(WD_E_INVALID, "null engine");
+    if (!e->resident) return fail(WD_E_STATE, "the device-side generator needs a pool that holds every owned expert");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    const wd_config &c = e->cfg;
+    cudaStream_t s = e->stream;
+    const size_t gb = e->gate_bytes, db = e->down_bytes;
+    const size_t need = static_cast<size_t>(c.n_experts) * (2 * gb + db);
+    uint8_t *big = nullptr;
+    WD_CUDA(cudaMalloc(&big, need));
+    int rc = WD_OK;
+    for (int l = 0; l < c.n_layers && rc == WD_OK; ++l) {
+        Layer &L = e->layers[l];
+        const size_t q8_eh = static_cast<size_t>(c.n_experts) * (c.hidden / 32) * 34;
+        auto dense = [&](int which, int rows, int cols, uint8_t **dst) -> int {
+            const size_t bytes = static_cast<size_t>(rows) * (cols / 32) * 34;
+            if (!*dst) WD_CUDA(cudaMalloc(dst, bytes));
+            int r = synth_into(e, WD_TYPE_Q8_0, rows, cols, sigma, seed, sid(l, which), e->staging, s);
+            if (r) return r;
+            const long long n = static_cast<long long>(rows) * (cols / 32);
+            wd::repack_q8_0_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(e->staging, *dst, rows, cols / 32);
+            WD_CUDA(cudaGetLastError());
+            return WD_OK;
+        };
+        (void)q8_eh;
+        if ((rc = dense(0, c.n_experts, c.hidden, &L.router))) break;
+        if (bias_sigma > 0) {
+            if (!L.bias) WD_CUDA(cudaMalloc(&L.bias, c.n_experts * 4));
+            if ((rc = synth_into(e, WD_TYPE_F32, 1, c.n_experts, bias_sigma, seed, sid(l, 1), L.bias, s))) break;
+        }
+        L.have_router = true;
+        if (c.shared_ffn > 0) {
+            if (!L.gate_vec) WD_CUDA(cudaMalloc(&L.gate_vec, c.hidden * 4));
+            if ((rc = synth_into(e, WD_TYPE_F32, 1, c.hidden, sigma, seed, sid(l, 2), L.gate_vec, s))) break;
+            if ((rc = dense(3, c.shared_ffn, c.hidden, &L.sh_gate))) break;
+            if ((rc = dense(4, c.shared_ffn, c.hidden, &L.sh_up))) break;
+            if ((rc = dense(5, c.hidden, c.shared_ffn, &L.sh_down))) break;
+            L.have_shared = true;
+        }
+        uint8_t *g = big, *u = big + static_cast<size_t>(c.n_experts) * gb, *d = u + static_cast<size_t>(c.n_experts) * gb;
+        if ((rc = synth_into(e, WD_TYPE_IQ3_S, static_cast<long long>(c.n_experts) * c.expert_ffn, c.hidden, sigma, seed,
+                             sid(l, 8), g, s)))
+            break;
+        if ((rc = synth_into(e, WD_TYPE_IQ3_S, static_cast<long long>(c.n_experts) * c.expert_ffn, c.hidden, sigma, seed,
+                             sid(l, 9), u, s)))
+            break;
+        if ((rc = synth_into(e, WD_TYPE_IQ3_S, static_cast<long long>(c.n_experts) * c.hidden, c.expert_ffn, sigma, seed,
+                             sid(l, 10), d, s)))
+            break;
+        if ((rc = wd_set_experts_device(e, l, g, u, d))) break;
+    }
+    cudaStreamSynchronize(s);
+    cudaFree(big);
+    return rc;
+}
+
+int wd_synth_expert_host(wd_engine *e, uint64_t seed, float sigma, int layer, int expert, void *gate, void *up,
+                         void *down) {
+    int rc = check_layer(e, layer);
+    if (rc) return rc;
+    if (expert < 0 || expert >= e->cfg.n_experts || !gate || !up || !down) return fail(WD_E_INVALID, "bad argument");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    const wd_config &c = e->cfg;
+    const size_t gb = e->gate_bytes, db = e->down_bytes;
+    // regenerate this expert's rows only: the generator indexes values by absolute block number
+    cudaStream_t s = e->stream;
+    uint8_t *st = e->staging;
+    if (2 * gb + db > e->staging_bytes) return fail(WD_E_STATE, "staging buffer too small");
+    const long long F = c.expert_ffn, H = c.hidden;
+    if ((rc = synth_into(e, WD_TYPE_IQ3_S, F, c.hidden, sigma, seed, sid(layer, 8), st, s, expert * F))) return rc;
+    if ((rc = synth_into(e, WD_TYPE_IQ3_S, F, c.hidden, sigma, seed, sid(layer, 9), st + gb, s, expert * F))) return rc;
+    if ((rc = synth_into(e, WD_TYPE_IQ3_S, H, c.expert_ffn, sigma, seed, sid(layer, 10), st + 2 * gb, s, expert * H))) return rc;
+    WD_CUDA(cudaMemcpyAsync(gate, st, gb, cudaMemcpyDeviceToHost, s));
+    WD_CUDA(cudaMemcpyAsync(up, st + gb, gb, cudaMemcpyDeviceToHost, s));
+    WD_CUDA(cudaMemcpyAsync(down, st + 2 * gb, db, cudaMemcpyDeviceToHost, s));
+    WD_CUDA(cudaStreamSynchronize(s));
+    return WD_OK;
+}
+
+int wd_synth_dense_host(wd_engine *e, uint64_t seed, float sigma, float bias_sigma, int layer, void *router,
+                        float *bias, float *gate_vec, void *sh_gate, void *sh_up, void *sh_down) {
+    int rc = check_layer(e, layer);
+    if (rc) return rc;
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    const wd_config &c = e->cfg;
+    cudaStream_t s = e->stream;
+    auto q8 = [&](int which, int rows, int cols, void *dst) -> int {
+        if (!dst) return WD_OK;
+        int r = synth_into(e, WD_TYPE_Q8_0, rows, cols, sigma, seed, sid(layer, which), e->staging, s);
+        if (r) return r;
+        WD_CUDA(cudaMemcpyAsync(dst, e->staging, static_cast<size_t>(rows) * (cols / 32) * 34, cudaMemcpyDeviceToHost, s));
+        WD_CUDA(cudaStreamSynchronize(s));
+        return WD_OK;
+    };
+    auto f32 = [&](int which, int n, float sg, float *dst) -> int {
+        if (!dst) return WD_OK;
+        int r = synth_into(e, WD_TYPE_F32, 1, n, sg, seed, sid(layer, which), e->staging, s);
+        if (r) return r;
+        WD_CUDA(cudaMemcpyAsync(dst, e->staging, static_cast<size_t>(n) * 4, cudaMemcpyDeviceToHost, s));
+        WD_CUDA(cudaStreamSynchronize(s));
+        return WD_OK;
+    };
+    if ((rc = q8(0, c.n_experts, c.hidden, router))) return rc;
+    if (bias_sigma > 0 && (rc = f32(1, c.n_experts, bias_sigma, bias))) return rc;
+    if (c.shared_ffn > 0) {
+        if ((rc = f32(2, c.hidden, sigma, gate_vec))) return rc;
+        if ((rc = q8(3, c.shared_ffn, c.hidden, sh_gate))) return rc;
+        if ((rc = q8(4, c.shared_ffn, c.hidden, sh_up))) return rc;
+        if ((rc = q8(5, c.hidden, c.shared_ffn, sh_down))) return rc;
+    }
+    return WD_OK;
+}
+
+}  // extern "C"
