@@ -116,9 +116,9 @@ int plan_shared_memory(wd_engine *e) {
     p.n1s = (n_st + ncta - 1) / ncta;
     p.n2 = (c.top_k * t2 + ncta - 1) / ncta;
     const int n_sd = c.shared_ffn > 0 ? c.hidden / 4 : 0;
-    const int total3 = c.top_k * t3 + n_sd;
+    // a CTA takes every ncta-th entry of [tiles | shared-down tasks]: at most ceil(len / ncta) of each part
     p.n3 = (c.top_k * t3 + ncta - 1) / ncta;
-    p.nsd = n_sd > 0 ? (total3 + ncta - 1) / ncta : 0;   // upper bound on shared-down tasks of one CTA
+    p.nsd = (n_sd + ncta - 1) / ncta;
     if (p.n1r + p.n1s + p.n2 + p.n3 + p.nsd > wd::kMaxBars)
         return fail(WD_E_INVALID, "geometry needs more staging slots per CTA than the kernel supports");
     p.off_bar = take(wd::kMaxBars * 8);

@@ -75,11 +75,19 @@ __device__ __forceinline__ uint32_t word_of(const uint4 &v, int i) {
     return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
 }
 
+// prmt.b32 with the full 4-bit selector nibbles: bit 3 of a nibble replicates the sign bit of the
+// selected byte over the whole result byte (the __byte_perm intrinsic only documents 3 bits).
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
 // One chunk: table lookup, sign application, dp4a.
 __device__ __forceinline__ int iq3_chunk_dot(uint32_t addr, uint32_t sword_shifted, int a_word,
                                              const uint8_t *tab) {
     const uint32_t g = *reinterpret_cast<const uint32_t *>(tab + addr);
-    const uint32_t m = __byte_perm(sword_shifted, 0u, 0xba98);      // 0xff where the value is negative
+    const uint32_t m = prmt(sword_shifted, 0u, 0xba98u);      // 0xff where the value is negative
     const uint32_t neg = 0x01010100u - g;                           // per-byte two's complement (g bytes >= 1)
     const uint32_t sgn = (g & ~m) | (neg & m);
     return dp4a_s8(a_word, static_cast<int>(sgn), 0);
@@ -99,8 +107,8 @@ __device__ __forceinline__ void iq3_subblock(const Iq3Regs &r, const uint4 a_lo,
         const int p = iq3_hb_bit(I, k);               // bit of chunk k; chunk k+4 is 8 above
         const uint32_t sh = p >= 7 ? (hw >> (p - 7)) : (hw << (7 - p));
         const uint32_t q = (sh & 0x8080u) | lane4x2;  // byte0: chunk k, byte1: chunk k+4; bytes 2,3 zero
-        const uint32_t addr_lo = __byte_perm(qs_lo, q, 0x7604u | (k << 4));
-        const uint32_t addr_hi = __byte_perm(qs_hi, q, 0x7605u | (k << 4));
+        const uint32_t addr_lo = prmt(qs_lo, q, 0x7604u | (k << 4));
+        const uint32_t addr_hi = prmt(qs_hi, q, 0x7605u | (k << 4));
         const int a0 = static_cast<int>(word_of(a_lo, k));
         const int a1 = static_cast<int>(word_of(a_hi, k));
         const int d0 = iq3_chunk_dot(addr_lo, sw << k, a0, tab);
