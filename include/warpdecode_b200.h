@@ -131,10 +131,18 @@ int wd_stack_step_host(wd_engine *e, const float *residual_in_host, float *resid
 #define WD_TAP_SHARED 6       /* F32 [hidden] shared expert before its gate */
 #define WD_TAP_SHARED_GATE 7  /* F32 [1] */
 #define WD_TAP_SHARED_ACT 8   /* F32 [shared_ffn] */
+#define WD_TAP_STAMPS 9       /* U64 [sm_count][16] phase timestamps (ns), see wd_set_profiling */
 /* Copies a tap of the most recent forward of token `token` to host memory (synchronises).
  * The post-conditions the reference's callers read from Qwen38MoeScratch
  * (d_logits/h_ids/h_weights/d_accum/down_f32/d_shared_gate, src/qwen38_moe.cuh:1804-1830). */
 int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes);
+/* Per-phase device timestamps (the role of the reference's Q38MoeKernelProfiler sites,
+ * src/qwen38_moe.cuh:296-535): when on, every CTA of the layer kernel records the global timer at
+ * its phase boundaries (0 start, 1 table, 2 x quantised, 3 rows done, 4 barrier, 5 selection,
+ * 6 copies issued, 7 gate/up done, 8 barrier, 9 activations quantised, 10 end). Off by default. */
+int wd_set_profiling(wd_engine *e, int on);
+/* Number of SMs = CTAs of the layer kernel. */
+int wd_sm_count(const wd_engine *e);
 /* Device error word of the last forward (0 = none) and a reset of the barrier state. */
 int wd_device_status(wd_engine *e, int *status);
 

@@ -85,6 +85,8 @@ def lib():
         L.wd_stack_step_host.argtypes = [vp, vp, vp]
         L.wd_read_tap.argtypes = [vp, i, i, vp, C.c_size_t]
         L.wd_device_status.argtypes = [vp, C.POINTER(C.c_int)]
+        L.wd_set_profiling.argtypes = [vp, i]
+        L.wd_sm_count.argtypes = [vp]
         L.wd_router_topk_host.argtypes = [vp, i, i, C.c_float, vp, vp, vp]
         L.wd_quantize_q8_0_host.argtypes = [vp, i, vp]
         L.wd_quantize_q8_K_host.argtypes = [vp, i, vp]
@@ -206,6 +208,16 @@ class Engine:
                       shared_act=(max(c.shared_ffn, 1),))
         a = np.zeros(shapes[name], np.int32 if name == "ids" else np.float32)
         _check(lib().wd_read_tap(self.h, TAPS[name], 0, _ptr(a), a.nbytes))
+        return a
+
+    def set_profiling(self, on):
+        _check(lib().wd_set_profiling(self.h, int(on)))
+
+    def stamps(self):
+        """[sm_count, 16] uint64 global-timer values of the last launch (profiling on)."""
+        n = lib().wd_sm_count(self.h)
+        a = np.zeros((n, 16), np.uint64)
+        _check(lib().wd_read_tap(self.h, 9, 0, _ptr(a), a.nbytes))
         return a
 
     def slot_count(self):

@@ -203,9 +203,8 @@ __global__ void test_quantize_kernel(const float *x, int n, uint8_t *q80_blocks,
             q80_blocks[b * 34 + 2 + (i & 31)] = q0[((b >> 2) * 8 + l) * 16 + (b & 3) * 4 + k];
         }
         for (int b = threadIdx.x; b < n / 32; b += blockDim.x) {
-            const uint16_t h = __half_as_ushort(__float2half_rn(d0[b]));
-            q80_blocks[b * 34] = h & 0xff;
-            q80_blocks[b * 34 + 1] = h >> 8;
+            // d0 holds the f16-rounded scale as a float; the conversion back is exact
+            *reinterpret_cast<__half *>(q80_blocks + b * 34) = __float2half_rn(d0[b]);
         }
     }
     if (q8k_blocks) {

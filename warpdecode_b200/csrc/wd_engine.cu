@@ -68,6 +68,8 @@ struct wd_engine {
     uint16_t *grid_packed = nullptr;
     uint16_t *synth_lut = nullptr;
     unsigned *sync = nullptr;
+    unsigned long long *stamps = nullptr;   // [n_sm][16] phase timestamps when profiling is on
+    bool profiling = false;
     float *logits = nullptr, *weights = nullptr, *act = nullptr, *expert_out = nullptr, *routed = nullptr,
           *shared_act = nullptr, *shared_down = nullptr, *shared_gate = nullptr, *x_buf = nullptr, *out_buf = nullptr,
           *residual_buf = nullptr;
@@ -195,6 +197,7 @@ int launch_layer(wd_engine *e, int layer, const float *x, float *residual, float
     p.x = x;
     p.residual = residual;
     p.out = out;
+    p.stamps = e->profiling ? e->stamps : nullptr;
     void *args[] = {&p};
     WD_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(wd::moe_layer_kernel), dim3(e->n_sm),
                                         dim3(wd::kThreads), args, e->smem_bytes, s));
@@ -306,6 +309,8 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     WD_TRY(cudaMalloc(&e->sync, 4096 + sizeof(unsigned) * (c.hidden / 4)));
     WD_TRY(cudaMemset(e->sync, 0, 4096 + sizeof(unsigned) * (c.hidden / 4)));
     const int H = c.hidden, F = c.expert_ffn, K = c.top_k, E = c.n_experts, SF = std::max(c.shared_ffn, 1);
+    WD_TRY(cudaMalloc(&e->stamps, static_cast<size_t>(e->n_sm) * 16 * 8));
+    WD_TRY(cudaMemset(e->stamps, 0, static_cast<size_t>(e->n_sm) * 16 * 8));
     WD_TRY(cudaMalloc(&e->logits, E * 4));
     WD_TRY(cudaMalloc(&e->ids, K * 4));
     WD_TRY(cudaMalloc(&e->weights, K * 4));
@@ -370,7 +375,7 @@ void wd_engine_destroy(wd_engine *e) {
     }
     void *bufs[] = {e->pool, e->grid_packed, e->synth_lut, e->sync, e->logits, e->ids, e->weights, e->act,
                     e->expert_out, e->routed, e->shared_act, e->shared_down, e->shared_gate, e->x_buf, e->out_buf,
-                    e->residual_buf, e->staging};
+                    e->residual_buf, e->staging, e->stamps};
     for (void *b : bufs) cudaFree(b);
     if (e->pinned) cudaFreeHost(e->pinned);
     if (e->stream) cudaStreamDestroy(e->stream);
@@ -636,6 +641,7 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
         case WD_TAP_SHARED: src = e->shared_down; n = c.hidden * 4; break;
         case WD_TAP_SHARED_GATE: src = e->shared_gate; n = 4; break;
         case WD_TAP_SHARED_ACT: src = e->shared_act; n = static_cast<size_t>(c.shared_ffn) * 4; break;
+        case WD_TAP_STAMPS: src = e->stamps; n = static_cast<size_t>(e->n_sm) * 16 * 8; break;
         default: return fail(WD_E_INVALID, "unknown tap");
     }
     if (bytes < n) return fail(WD_E_INVALID, "tap buffer too small");
@@ -644,6 +650,18 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
     WD_CUDA(cudaMemcpy(dst, src, n, cudaMemcpyDeviceToHost));
     return WD_OK;
 }
+
+int wd_set_profiling(wd_engine *e, int on) {
+    if (!e) return fail(WD_E_INVALID, "null engine");
+    e->profiling = on != 0;
+    if (e->stack_graph) {          // the captured launches carry the old setting
+        cudaGraphExecDestroy(e->stack_graph);
+        e->stack_graph = nullptr;
+    }
+    return WD_OK;
+}
+
+int wd_sm_count(const wd_engine *e) { return e ? e->n_sm : 0; }
 
 int wd_device_status(wd_engine *e, int *status) {
     if (!e || !status) return fail(WD_E_INVALID, "null argument");

@@ -55,6 +55,7 @@ struct MoeParams {
     float *shared_act;           // [SF]
     float *shared_down;          // [H]
     float *shared_gate;          // [1]
+    unsigned long long *stamps;  // nullable: [cta][16] globaltimer values at phase boundaries (profiling)
     unsigned *sync;              // [0] barrier count, [1] generation, [2] error word, [16..] tile counters
     // shared memory plan (byte offsets from the dynamic shared base; all 16-byte aligned)
     unsigned off_tab, off_xq0, off_xd0, off_xk, off_xdk, off_actk, off_actd, off_shq, off_shd,
@@ -351,6 +352,13 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     int *loc_n = reinterpret_cast<int *>(misc + 288);   // [1]
     float *red = misc + 320;                            // [64] reduction scratch (as double pairs)
 
+#define WD_STAMP(i)                                                                            \
+    if (P.stamps != nullptr && tid == 0) {                                                     \
+        unsigned long long t__;                                                                \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                \
+        P.stamps[cta * 16 + (i)] = t__;                                                        \
+    }
+    WD_STAMP(0);
     const int n_bars = P.n1r + P.n1s + P.n2 + P.n3 + P.nsd;
     if (tid == 0) {
         for (int i = 0; i < n_bars; ++i) mbar_init(&bars[i], 1);
@@ -358,6 +366,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     }
     build_grid_table(tab, P.grid_packed);
     __syncthreads();
+    WD_STAMP(1);   // table built
 
     // ---- issue phase-1 copies: router tasks and shared gate/up tasks of this CTA --------------
     const int n_rt = P.E >> 2;                     // router tasks (4 rows each)
@@ -425,6 +434,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         quantize_q8_K_warp(v, lane, xk + sb * kActSbStride, &xdk[sb]);
     }
     __syncthreads();
+    WD_STAMP(2);   // x quantised
 
     // ---- phase 1: Q8_0 row tasks ------------------------------------------------------------
     {
@@ -457,7 +467,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
             if (lane == 0) *P.shared_gate = sigmoid_ggml(d);
         }
     }
+    WD_STAMP(3);   // phase 1 done (before barrier 1)
     grid_barrier(P.sync, P.sync + 1, ncta, err);
+    WD_STAMP(4);   // after barrier 1
 
     // ---- phase 1b: selection (warp 0) and shared activation -> Q8_0 (all threads) ------------
     if (warp == 0) {
@@ -494,6 +506,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     }
     fence_proxy_async();
     __syncthreads();
+    WD_STAMP(5);   // selection done
 
     // ---- issue every remaining copy of this CTA: gate/up units, down tiles, shared-down tasks -
     const int n_loc = *loc_n;
@@ -532,6 +545,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         }
     }
 
+    WD_STAMP(6);   // copies issued
     // ---- phase 2: gate + up tiles -> act ---------------------------------------------------------
     {
         const int R = 32 / P.nsb_h;
@@ -562,7 +576,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
             }
         }
     }
+    WD_STAMP(7);   // phase 2 done (before barrier 2)
     grid_barrier(P.sync, P.sync + 1, ncta, err);
+    WD_STAMP(8);   // after barrier 2
 
     // ---- phase 3: act -> Q8_K, down tiles, shared-down rows, ordered combine ----------------------
     for (int w = warp; w < n_loc * P.nsb_f; w += kWarps) {
@@ -574,6 +590,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         quantize_q8_K_warp(v, lane, actk + (jl * P.nsb_f + sb) * kActSbStride, &actd[jl * P.nsb_f + sb]);
     }
     __syncthreads();
+    WD_STAMP(9);   // activations quantised
     {
         const int R = 32 / P.nsb_f;                 // rows per down tile
         const int expected = n_loc + (P.SF > 0 ? R / 4 : 0);
@@ -641,6 +658,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
             }
         }
     }
+    WD_STAMP(10);   // done
+#undef WD_STAMP
 }
 
 }  // namespace wd

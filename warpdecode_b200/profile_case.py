@@ -1,0 +1,43 @@
+"""A small, self-ending workload for profilers (ncu): a few forward calls of the MoE layer kernel
+at the headline block shape, with direct launches (no CUDA graph) so every launch is one kernel.
+
+    python -m warpdecode_b200.profile_case [--layers 2] [--iters 4] [--stamps]
+
+Holds about 0.7 GB per layer on the device. With --stamps it prints the kernel's own per-phase
+timestamps (mean over CTAs) instead, which needs no profiler.
+"""
+import argparse
+
+import numpy as np
+
+import warpdecode_b200 as wd
+
+PHASES = ["table", "x_quant", "q8_rows", "barrier1", "select", "issue", "gate_up", "barrier2", "act_quant", "down"]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--iters", type=int, default=4)
+    ap.add_argument("--stamps", action="store_true")
+    a = ap.parse_args()
+    eng = wd.Engine(2048, 512, 512, 10, 512, a.layers)
+    eng.synth_model(3, 0.02, 0.0)
+    eng.set_profiling(a.stamps)
+    rng = np.random.Generator(np.random.PCG64(1))
+    rows = []
+    for it in range(a.iters):
+        for layer in range(a.layers):
+            eng.forward_host(layer, rng.standard_normal(2048).astype(np.float32))
+            if a.stamps:
+                st = eng.stamps().astype(np.int64)
+                rows.append(np.concatenate([np.diff(st[:, :11], axis=1).mean(0), [st[:, 10].max() - st[:, 0].min()]]))
+    assert eng.device_status() == 0
+    if a.stamps:
+        m = np.array(rows[a.layers:]).mean(0)          # skip the first pass (cold)
+        print("mean ns per phase:", {n: int(v) for n, v in zip(PHASES + ["kernel"], m)})
+    print("done")
+
+
+if __name__ == "__main__":
+    main()
