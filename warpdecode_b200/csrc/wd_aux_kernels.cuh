@@ -17,8 +17,8 @@ __global__ void repack_iq3s_kernel(const uint8_t *__restrict__ src, uint8_t *__r
     const int lane = static_cast<int>(b & 31);
     tile[kIq3OffD + lane * 2] = s[0];
     tile[kIq3OffD + lane * 2 + 1] = s[1];
-    for (int p = 0; p < 4; ++p)
-        for (int k = 0; k < 16; ++k) tile[p * 512 + lane * 16 + k] = s[2 + p * 16 + k];
+    for (int i = 0; i < 8; ++i)
+        for (int k = 0; k < 8; ++k) tile[i * 256 + lane * 8 + k] = s[2 + i * 8 + k];
     const uint8_t *qh = s + 66, *sg = s + 74;
     for (int i = 0; i < 8; ++i) {
         uint32_t word = 0;
@@ -27,15 +27,9 @@ __global__ void repack_iq3s_kernel(const uint8_t *__restrict__ src, uint8_t *__r
             for (int j = 0; j < 4; ++j)
                 if ((nib >> j) & 1u) word |= 1u << (8 * j + 7 - c);
         }
-        *reinterpret_cast<uint32_t *>(tile + kIq3OffSG + (i >> 2) * 512 + lane * 16 + (i & 3) * 4) = word;
+        *reinterpret_cast<uint32_t *>(tile + kIq3OffSG + i * 128 + lane * 4) = word;
     }
-    for (int w = 0; w < 2; ++w) {
-        uint32_t word = 0;
-        for (int ii = 0; ii < 4; ++ii)
-            for (int c = 0; c < 8; ++c)
-                if ((qh[4 * w + ii] >> c) & 1u) word |= 1u << iq3_hb_bit(4 * w + ii, c);
-        *reinterpret_cast<uint32_t *>(tile + kIq3OffHB + lane * 8 + w * 4) = word;
-    }
+    for (int k = 0; k < 8; ++k) tile[kIq3OffHB + lane * 8 + k] = qh[k];
     for (int k = 0; k < 4; ++k) tile[kIq3OffSC + lane * 4 + k] = s[106 + k];
 }
 
@@ -169,19 +163,27 @@ __global__ void synth_iq3s_kernel(uint8_t *dst, long long first_block, long long
 // ---------------------------------------------------------------------------------------------
 __global__ void test_router_kernel(const float *logits, int E, int K, float w_scale, int *ids, float *weights,
                                    float *probs) {
+    // launched with kThreads threads
     __shared__ float lg[kMaxExperts];
+    __shared__ float pr[kMaxExperts];
     __shared__ float gsum[kMaxExperts / 8];
+    __shared__ float red[kWarps];
     __shared__ float topv[kMaxK];
+    __shared__ uint32_t champ[2 * kWarps * 2];
+    __shared__ double dsum[2];
     __shared__ int sid[kMaxK];
     __shared__ float sw[kMaxK];
-    const int lane = threadIdx.x;
-    for (int i = lane; i < E; i += 32) lg[i] = logits[i];
-    __syncwarp();
-    router_topk_warp(lg, E, K, w_scale, lane, gsum, topv, sid, sw, probs);
-    for (int j = lane; j < K; j += 32) {
+    for (int i = threadIdx.x; i < E; i += blockDim.x) lg[i] = logits[i];
+    __syncthreads();
+    RouterScratch rs;
+    rs.probs = pr; rs.gsum = gsum; rs.red = red; rs.top = topv; rs.champ = champ; rs.dsum = dsum;
+    router_select_cta(lg, E, K, w_scale, rs, sid, sw);
+    for (int j = threadIdx.x; j < K; j += blockDim.x) {
         ids[j] = sid[j];
         weights[j] = sw[j];
     }
+    if (probs)
+        for (int i = threadIdx.x; i < E; i += blockDim.x) probs[i] = pr[i];
 }
 
 // Quantises n floats both ways with the fused kernel's routines and writes ggml block layouts.
@@ -254,11 +256,9 @@ __global__ void test_matvec_iq3s_kernel(const uint8_t *tiles, int rows, int nsb,
         const uint4 *src = reinterpret_cast<const uint4 *>(tiles + static_cast<size_t>(t) * kIq3TileBytes);
         for (int i = lane; i < kIq3TileBytes / 16; i += 32) reinterpret_cast<uint4 *>(ts)[i] = src[i];
         __syncwarp();
-        Iq3Regs r;
-        iq3_load(ts, lane, r);
         const int sb = lane % nsb, rl = lane / nsb;
         int p[8];
-        iq3_block_partials(r, xk + sb * kActSbStride, lane4x2, tab, p);
+        iq3_block_partials(ts, lane, xk + sb * kActSbStride, lane4x2, tab, p);
         if (partials)
             for (int c = 0; c < 8; ++c) partials[(static_cast<size_t>(t * R + rl) * nsb + sb) * 8 + c] = p[c];
         const float dw = half_bits_to_float(*reinterpret_cast<const uint16_t *>(ts + kIq3OffD + lane * 2));

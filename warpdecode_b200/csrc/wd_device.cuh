@@ -72,33 +72,35 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsign
 // ---------------------------------------------------------------------------------------------
 // grid barrier (all CTAs co-resident: cooperative launch). Sense = generation counter.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ unsigned ld_acquire(const unsigned *p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void grid_barrier(unsigned *count, unsigned *gen, unsigned nblocks, unsigned *err) {
+// One 64-bit counter that only ever grows: a CTA arrives with a release add and waits until the
+// counter reaches the next multiple of the grid size. No reset, no second word, no full fence: one
+// atomic and a few polling loads per barrier. (The host zeroes the counter after a reported error.)
+__device__ __forceinline__ void grid_barrier(unsigned long long *ctr, unsigned nblocks, unsigned *err) {
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned g = ld_acquire(gen);
-        __threadfence();
-        if (atomicAdd(count, 1u) == nblocks - 1u) {
-            atomicExch(count, 0u);
-            __threadfence();
-            atomicAdd(gen, 1u);
-        } else {
-            unsigned i = 0;
-            while (ld_acquire(gen) == g) {
-                if (++i > kSpinLimit) {
-                    atomicOr(err, kErrBarrierTimeout);
-                    break;
-                }
+        unsigned long long old, now;
+        asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(old) : "l"(ctr) : "memory");
+        const unsigned long long target = (old / nblocks + 1ull) * nblocks;
+        unsigned i = 0;
+        for (;;) {
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(now) : "l"(ctr) : "memory");
+            if (now >= target) break;
+            if (++i > kSpinLimit) {
+                atomicOr(err, kErrBarrierTimeout);
+                break;
             }
         }
-        __threadfence();
     }
     __syncthreads();
 }
+
+// Order-preserving map float -> u32 for selection: larger float = larger key, NaN = 0 (never wins).
+__device__ __forceinline__ uint32_t order_key(float v) {
+    const uint32_t b = __float_as_uint(v);
+    if (v != v) return 0u;
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+constexpr uint32_t kKeyNegInf = 0x007fffffu;   // order_key(-inf): nothing at or below it is selectable
 
 // ---------------------------------------------------------------------------------------------
 // scalar math in the reference's order

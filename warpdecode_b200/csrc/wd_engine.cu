@@ -107,7 +107,7 @@ int plan_shared_memory(wd_engine *e) {
     p.off_actd = take(static_cast<size_t>(c.top_k) * e->nsb_f * 4);
     p.off_shq = take(std::max(c.shared_ffn, 16));
     p.off_shd = take(std::max(nbs, 4) * 4);
-    p.off_misc = take(4 * static_cast<size_t>(std::max(c.hidden, 512 + wd::kMaxExperts + c.shared_ffn)));
+    p.off_misc = take(4 * static_cast<size_t>(std::max(c.hidden, wd::kMiscSharedAct + c.shared_ffn)));
     const int r_h = 32 / e->nsb_h, r_f = 32 / e->nsb_f;
     const int scr_floats = std::max(r_h * (e->nsb_h * 8 + 8) + 32, r_f * (e->nsb_f * 8 + 8) + 32);
     p.scr_bytes = static_cast<unsigned>(align_up(scr_floats * 4, 128));
@@ -209,7 +209,7 @@ int check_device_status(wd_engine *e) {
     WD_CUDA(cudaMemcpy(&st, e->sync + 2, sizeof(st), cudaMemcpyDeviceToHost));
     if (st != 0) {
         // leave the barrier words in a usable state for the next launch
-        cudaMemset(e->sync, 0, 4096);
+        cudaMemset(e->sync, 0, 8192);
         return fail(WD_E_DEVICE, "kernel raised status " + std::to_string(st) +
                                      " (1 barrier timeout, 2 copy timeout, 4 expert without slot, 8 geometry)");
     }
@@ -306,8 +306,8 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     }
     WD_TRY(cudaMalloc(&e->grid_packed, sizeof(wd_iq3s_grid_packed)));
     WD_TRY(cudaMemcpy(e->grid_packed, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
-    WD_TRY(cudaMalloc(&e->sync, 4096 + sizeof(unsigned) * (c.hidden / 4)));
-    WD_TRY(cudaMemset(e->sync, 0, 4096 + sizeof(unsigned) * (c.hidden / 4)));
+    WD_TRY(cudaMalloc(&e->sync, 8192 + sizeof(unsigned) * (c.hidden / 4)));
+    WD_TRY(cudaMemset(e->sync, 0, 8192 + sizeof(unsigned) * (c.hidden / 4)));
     const int H = c.hidden, F = c.expert_ffn, K = c.top_k, E = c.n_experts, SF = std::max(c.shared_ffn, 1);
     WD_TRY(cudaMalloc(&e->stamps, static_cast<size_t>(e->n_sm) * 16 * 8));
     WD_TRY(cudaMemset(e->stamps, 0, static_cast<size_t>(e->n_sm) * 16 * 8));
@@ -347,6 +347,9 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     p.logits = e->logits; p.ids = e->ids; p.weights = e->weights; p.act = e->act; p.expert_out = e->expert_out;
     p.routed = e->routed; p.shared_act = e->shared_act; p.shared_down = e->shared_down; p.shared_gate = e->shared_gate;
     p.sync = e->sync;
+    p.barrier = reinterpret_cast<unsigned long long *>(e->sync + 4);
+    p.act_amax = e->sync + 1024 + c.hidden / 4 + 16;   // behind the output-tile counters
+    { int t2 = F * e->nsb_h / 32, t3 = H * e->nsb_f / 32; p.t2_log2 = 0; while ((1 << p.t2_log2) < t2) ++p.t2_log2; p.t3_log2 = 0; while ((1 << p.t3_log2) < t3) ++p.t3_log2; }
     if ((rc = plan_shared_memory(e)) != WD_OK) return bail(rc);
     cudaError_t ae = cudaFuncSetAttribute(wd::moe_layer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           static_cast<int>(e->smem_bytes));
@@ -670,7 +673,7 @@ int wd_device_status(wd_engine *e, int *status) {
     unsigned st = 0;
     WD_CUDA(cudaMemcpy(&st, e->sync + 2, sizeof(st), cudaMemcpyDeviceToHost));
     *status = static_cast<int>(st);
-    if (st) WD_CUDA(cudaMemset(e->sync, 0, 4096));
+    if (st) WD_CUDA(cudaMemset(e->sync, 0, 8192));
     return WD_OK;
 }
 
@@ -687,7 +690,7 @@ int wd_router_topk_host(const float *logits, int n_experts, int k, float w_scale
     WD_CUDA(cudaMalloc(&d_w, wd::kMaxK * 4));
     WD_CUDA(cudaMalloc(&d_i, wd::kMaxK * 4));
     WD_CUDA(cudaMemcpy(d_l, logits, n_experts * 4, cudaMemcpyHostToDevice));
-    wd::test_router_kernel<<<1, 32>>>(d_l, n_experts, k, w_scale, d_i, d_w, d_p);
+    wd::test_router_kernel<<<1, wd::kThreads>>>(d_l, n_experts, k, w_scale, d_i, d_w, d_p);
     WD_CUDA(cudaGetLastError());
     WD_CUDA(cudaDeviceSynchronize());
     WD_CUDA(cudaMemcpy(ids, d_i, k * 4, cudaMemcpyDeviceToHost));
