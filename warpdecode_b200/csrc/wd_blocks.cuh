@@ -189,17 +189,47 @@ __device__ __forceinline__ void router_select_cta(const float *logits, int E, in
         if (h1) S.gsum[e1 >> 3] = g1;
     }
     __syncthreads();
-    if (tid == 0) {
-        double sum = 0.0;
-        for (int g = 0; g < (E >> 3); ++g) sum = __dadd_rn(sum, static_cast<double>(S.gsum[g]));
-        S.dsum[0] = sum;
+    if (warp == 0) {
+        // The reference adds the group sums one by one, ascending, into a double. When every partial
+        // sum is exactly representable the order cannot matter, and a shuffle tree gives the same bits:
+        // all terms are non-negative multiples of the smallest term's last bit q, so any partial sum is
+        // a multiple of q below the total; it is exact if total < 2^53 * q, i.e. if the exponent span
+        // between the total and the smallest non-zero term (minus its 23 mantissa bits) stays under 53.
+        // Otherwise (and for inf/nan/denormal terms) one lane replays the reference's order.
+        const int ng = E >> 3;
+        double part = 0.0;
+        int min_exp = 0x7fffffff, bad = 0;
+        for (int g = lane; g < ng; g += 32) {
+            const float v = S.gsum[g];
+            const int ex = static_cast<int>((__float_as_uint(v) >> 23) & 0xffu);
+            if (v != 0.0f) {
+                if (ex == 0 || ex == 255 || v < 0.0f) bad = 1;
+                min_exp = min(min_exp, ex);
+            }
+            part = __dadd_rn(part, static_cast<double>(v));
+        }
+#pragma unroll
+        for (int s = 1; s < 32; s <<= 1) part = __dadd_rn(part, __shfl_xor_sync(0xffffffffu, part, s));
+        min_exp = __reduce_min_sync(0xffffffffu, min_exp);
+        bad = __any_sync(0xffffffffu, bad);
+        const int tot_exp = static_cast<int>((__double_as_longlong(part) >> 52) & 0x7ff) - 1023 + 127;   // float-biased
+        double sum = part;
+        if (bad || (min_exp != 0x7fffffff && tot_exp + 1 - (min_exp - 23) > 52)) {
+            sum = 0.0;
+            if (lane == 0)
+                for (int g = 0; g < ng; ++g) sum = __dadd_rn(sum, static_cast<double>(S.gsum[g]));
+        }
+        if (lane == 0) {
+            S.dsum[0] = sum;
+            S.dsum[1] = sum == 0.0 ? 0.0 : static_cast<double>(__double2float_rn(__ddiv_rn(1.0, sum)));
+        }
     }
     __syncthreads();
     const double sum = S.dsum[0];
     if (sum == 0.0) {
         p0 = p1 = -INFINITY;
     } else {
-        const float inv = __double2float_rn(__ddiv_rn(1.0, sum));
+        const float inv = static_cast<float>(S.dsum[1]);
         p0 = __fmul_rn(p0, inv);
         p1 = __fmul_rn(p1, inv);
     }

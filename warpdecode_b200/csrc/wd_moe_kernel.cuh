@@ -68,7 +68,7 @@ struct MoeParams {
 // float offsets inside the `misc` region once phase 1 is over (before that it holds x as floats)
 constexpr int kMiscLogits = 0, kMiscProbs = 1024, kMiscGsum = 2048, kMiscRed = 2176, kMiscTop = 2192,
               kMiscChamp = 2208, kMiscDsum = 2272, kMiscIds = 2288, kMiscW = 2304, kMiscLocJ = 2320,
-              kMiscLocSlot = 2336, kMiscLocN = 2352, kMiscSharedAct = 2368;
+              kMiscLocSlot = 2336, kMiscLocN = 2352, kMiscSlots = 2368, kMiscSharedAct = 3392;
 
 extern __shared__ __align__(128) uint8_t wd_smem[];
 

@@ -31,11 +31,15 @@ def main():
             eng.forward_host(layer, rng.standard_normal(2048).astype(np.float32))
             if a.stamps:
                 st = eng.stamps().astype(np.int64)
-                rows.append(np.concatenate([np.diff(st[:, :11], axis=1).mean(0), [st[:, 10].max() - st[:, 0].min()]]))
+                extra = [(st[:, 12] - st[:, 4]).mean(), (st[:, 13] - st[:, 12]).mean(), (st[:, 5] - st[:, 13]).mean(),
+                         (st[:, 11] - st[:, 6]).mean()]
+                rows.append(np.concatenate([np.diff(st[:, :11], axis=1).mean(0), [st[:, 10].max() - st[:, 0].min()],
+                                            extra]))
     assert eng.device_status() == 0
     if a.stamps:
         m = np.array(rows[a.layers:]).mean(0)          # skip the first pass (cold)
-        print("mean ns per phase:", {n: int(v) for n, v in zip(PHASES + ["kernel"], m)})
+        names = PHASES + ["kernel", "select.load", "select.router", "select.rest", "gate_up.first_copy_wait"]
+        print("mean ns per phase:", {n: int(v) for n, v in zip(names, m)})
     print("done")
 
 
