@@ -210,11 +210,8 @@ __global__ void test_quantize_kernel(const float *x, int n, uint8_t *q80_blocks,
         }
     }
     if (q8k_blocks) {
-        for (int sb = warp; sb < n / 256; sb += blockDim.x / 32) {
-            float v[8];
-            for (int j = 0; j < 8; ++j) v[j] = xf[sb * 256 + lane * 8 + j];
-            quantize_q8_K_warp(v, lane, qk + sb * kActSbStride, &dk[sb]);
-        }
+        for (int sb = warp; sb < n / 256; sb += blockDim.x / 32)
+            quantize_q8_K_warp(xf + sb * 256, lane, qk + sb * kActSbStride, &dk[sb]);
         __syncthreads();
         for (int sb = warp; sb < n / 256; sb += blockDim.x / 32) {
             uint8_t *o = q8k_blocks + sb * 292;
@@ -242,33 +239,21 @@ __global__ void test_matvec_iq3s_kernel(const uint8_t *tiles, int rows, int nsb,
     float *scr_all = reinterpret_cast<float *>(tile_s + (blockDim.x / 32) * kIq3TileBytes);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x / 32;
     build_grid_table(tab, grid_packed);
-    for (int sb = warp; sb < nsb; sb += nw) {
-        float v[8];
-        for (int j = 0; j < 8; ++j) v[j] = x[sb * 256 + lane * 8 + j];
-        quantize_q8_K_warp(v, lane, xk + sb * kActSbStride, &xdk[sb]);
-    }
+    for (int sb = warp; sb < nsb; sb += nw) quantize_q8_K_warp(x + sb * 256, lane, xk + sb * kActSbStride, &xdk[sb]);
     __syncthreads();
     const int R = 32 / nsb, ntiles = rows / R;
     const uint32_t lane4x2 = static_cast<uint32_t>(lane * 4) * 0x0101u;
     uint8_t *ts = tile_s + warp * kIq3TileBytes;
-    float *scr = scr_all + warp * 640;
+    float *scr = scr_all + warp * 640;          // 544 floats of chain scratch, then 32 row results
+    float *rows_out = scr + 576;
     for (int t = blockIdx.x * nw + warp; t < ntiles; t += gridDim.x * nw) {
         const uint4 *src = reinterpret_cast<const uint4 *>(tiles + static_cast<size_t>(t) * kIq3TileBytes);
         for (int i = lane; i < kIq3TileBytes / 16; i += 32) reinterpret_cast<uint4 *>(ts)[i] = src[i];
         __syncwarp();
         const int sb = lane % nsb, rl = lane / nsb;
-        int p[8];
-        iq3_block_partials(ts, lane, xk + sb * kActSbStride, lane4x2, tab, p);
-        if (partials)
-            for (int c = 0; c < 8; ++c) partials[(static_cast<size_t>(t * R + rl) * nsb + sb) * 8 + c] = p[c];
-        const float dw = half_bits_to_float(*reinterpret_cast<const uint16_t *>(ts + kIq3OffD + lane * 2));
-        float out[8];
-        iq_tile_rows<8>(p, __fmul_rn(dw, xdk[sb]), nsb, lane, scr, out);
-        const int nit = (R * 8 + 31) / 32;
-        for (int it = 0; it < 8; ++it) {
-            const int rr = it * 4 + (lane >> 3);
-            if (it < nit && rr < R && (lane & 7) == 0) y[t * R + rr] = out[it];
-        }
+        int *dump = partials ? partials + (static_cast<size_t>(t * R + rl) * nsb + sb) * 8 : nullptr;
+        iq3_tile_to_rows(ts, xk + sb * kActSbStride, xdk[sb], nsb, lane, lane4x2, tab, scr, rows_out, dump);
+        for (int rr = lane; rr < R; rr += 32) y[t * R + rr] = rows_out[rr];
         __syncwarp();
     }
 }

@@ -42,6 +42,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 // global -> this CTA's shared memory; dst, src 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
     asm volatile(
@@ -75,21 +78,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsign
 // One 64-bit counter that only ever grows: a CTA arrives with a release add and waits until the
 // counter reaches the next multiple of the grid size. No reset, no second word, no full fence: one
 // atomic and a few polling loads per barrier. (The host zeroes the counter after a reported error.)
-__device__ __forceinline__ void grid_barrier(unsigned long long *ctr, unsigned nblocks, unsigned *err) {
+// `target` is the counter value at which this barrier opens; the host hands every launch the value
+// the counter had before it, so the kernel needs no returned value: the arrival is a fire-and-forget
+// release reduction, the wait polls with relaxed loads and takes one acquire fence at the end.
+__device__ __forceinline__ void grid_barrier(unsigned long long *ctr, unsigned long long target, unsigned *err) {
     __syncthreads();
     if (threadIdx.x == 0) {
-        unsigned long long old, now;
-        asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(old) : "l"(ctr) : "memory");
-        const unsigned long long target = (old / nblocks + 1ull) * nblocks;
+        unsigned long long now;
+        asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory");
         unsigned i = 0;
         for (;;) {
-            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(now) : "l"(ctr) : "memory");
+            asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(now) : "l"(ctr) : "memory");
             if (now >= target) break;
             if (++i > kSpinLimit) {
                 atomicOr(err, kErrBarrierTimeout);
                 break;
             }
         }
+        asm volatile("fence.acquire.gpu;" ::: "memory");
     }
     __syncthreads();
 }
@@ -106,7 +112,7 @@ constexpr uint32_t kKeyNegInf = 0x007fffffu;   // order_key(-inf): nothing at or
 // scalar math in the reference's order
 // ---------------------------------------------------------------------------------------------
 // One lane of ggml's AVX2 ggml_v_expf (src/qwen38_exact_math.cuh:94-115, src/qwen38_cpu_moe.cuh:816-834).
-__device__ __forceinline__ float exp_ggml(float x) {
+__device__ __noinline__ float exp_ggml(float x) {
     const float r = 0x1.8p23f;
     const float z = __fmaf_rn(x, 0x1.715476p+0f, r);
     const float n = __fsub_rn(z, r);

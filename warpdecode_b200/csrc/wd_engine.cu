@@ -70,6 +70,10 @@ struct wd_engine {
     unsigned *sync = nullptr;
     unsigned long long *stamps = nullptr;   // [n_sm][16] phase timestamps when profiling is on
     bool profiling = false;
+    int stamp_layer = 0;                    // offset of the profiled layer inside a launch
+    wd::LayerDev *layer_table = nullptr;    // device copy of the per-layer pointers
+    bool layer_table_dirty = true;
+    unsigned long long barrier_count = 0;   // value of the device barrier counter after the launches so far
     float *logits = nullptr, *weights = nullptr, *act = nullptr, *expert_out = nullptr, *routed = nullptr,
           *shared_act = nullptr, *shared_down = nullptr, *shared_gate = nullptr, *x_buf = nullptr, *out_buf = nullptr,
           *residual_buf = nullptr;
@@ -110,7 +114,8 @@ int plan_shared_memory(wd_engine *e) {
     p.off_misc = take(4 * static_cast<size_t>(std::max(c.hidden, wd::kMiscSharedAct + c.shared_ffn)));
     const int r_h = 32 / e->nsb_h, r_f = 32 / e->nsb_f;
     const int scr_floats = std::max(r_h * (e->nsb_h * 8 + 8) + 32, r_f * (e->nsb_f * 8 + 8) + 32);
-    p.scr_bytes = static_cast<unsigned>(align_up(scr_floats * 4, 128));
+    p.scr_rows = static_cast<unsigned>(scr_floats);
+    p.scr_bytes = static_cast<unsigned>(align_up((scr_floats + 64) * 4, 128));
     p.off_scr = take(static_cast<size_t>(p.scr_bytes) * wd::kWarps);
     const int n_rt = c.n_experts / 4, n_st = c.shared_ffn / 4;
     const int t2 = c.expert_ffn / r_h, t3 = c.hidden / r_f;
@@ -128,7 +133,9 @@ int plan_shared_memory(wd_engine *e) {
     const size_t stage_a = std::max(static_cast<size_t>(p.n1r + p.n1s) * 2 * rt_bytes,
                                     static_cast<size_t>(p.n2) * 2 * wd::kIq3TileBytes);
     p.off_stage_a = take(stage_a);
-    p.off_stage_b = take(static_cast<size_t>(p.n3) * wd::kIq3TileBytes + static_cast<size_t>(p.nsd) * nbs * 136);
+    // stage B also holds the F32 shared gate vector during phase 1
+    p.off_stage_b = take(std::max(static_cast<size_t>(p.n3) * wd::kIq3TileBytes + static_cast<size_t>(p.nsd) * nbs * 136,
+                                  static_cast<size_t>(c.hidden) * 4));
     e->smem_bytes = off;
     if (e->smem_bytes > 227 * 1024)
         return fail(WD_E_INVALID, "geometry needs " + std::to_string(e->smem_bytes) +
@@ -181,27 +188,49 @@ void touch_slot(wd_engine *e, int slot) {
     e->lru_pos[slot] = e->lru.begin();
 }
 
-int launch_layer(wd_engine *e, int layer, const float *x, float *residual, float *out, cudaStream_t s) {
-    Layer &L = e->layers[layer];
-    if (!L.have_router || !L.have_experts || (e->cfg.shared_ffn > 0 && !L.have_shared))
-        return fail(WD_E_STATE, "layer " + std::to_string(layer) + " has no weights yet");
+// Uploads the per-layer pointer table when any layer's pointers changed since the last launch.
+int sync_layer_table(wd_engine *e, cudaStream_t s) {
+    if (!e->layer_table_dirty) return WD_OK;
+    std::vector<wd::LayerDev> host(e->layers.size());
+    for (size_t i = 0; i < e->layers.size(); ++i) {
+        const Layer &L = e->layers[i];
+        host[i] = wd::LayerDev{L.router, L.bias, L.gate_vec, L.sh_gate, L.sh_up, L.sh_down, L.norm, L.slot_of_expert};
+    }
+    WD_CUDA(cudaMemcpyAsync(e->layer_table, host.data(), host.size() * sizeof(wd::LayerDev), cudaMemcpyHostToDevice, s));
+    WD_CUDA(cudaStreamSynchronize(s));      // `host` goes out of scope
+    e->layer_table_dirty = false;
+    return WD_OK;
+}
+
+// Layers [begin, end) in one cooperative launch.
+int launch_layers(wd_engine *e, int begin, int end, const float *x, float *residual, float *out, cudaStream_t s) {
+    for (int l = begin; l < end; ++l) {
+        const Layer &L = e->layers[l];
+        if (!L.have_router || !L.have_experts || (e->cfg.shared_ffn > 0 && !L.have_shared))
+            return fail(WD_E_STATE, "layer " + std::to_string(l) + " has no weights yet");
+    }
+    int rc = sync_layer_table(e, s);
+    if (rc) return rc;
     wd::MoeParams p = e->base;
-    p.router_w = L.router;
-    p.router_bias = L.bias;
-    p.sh_gate_vec = L.gate_vec;
-    p.sh_gate = L.sh_gate;
-    p.sh_up = L.sh_up;
-    p.sh_down = L.sh_down;
-    p.norm_w = L.norm;
-    p.slot_of_expert = L.slot_of_expert;
+    p.layers = e->layer_table;
+    p.layer_begin = begin;
+    p.layer_end = end;
+    p.stamp_layer = std::min(end - 1, begin + e->stamp_layer);
     p.x = x;
     p.residual = residual;
     p.out = out;
     p.stamps = e->profiling ? e->stamps : nullptr;
+    p.barrier_base = e->barrier_count;
     void *args[] = {&p};
     WD_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(wd::moe_layer_kernel), dim3(e->n_sm),
                                         dim3(wd::kThreads), args, e->smem_bytes, s));
+    // two barriers inside every layer and one between consecutive layers
+    e->barrier_count += static_cast<unsigned long long>(e->n_sm) * (3ull * (end - begin) - 1ull);
     return WD_OK;
+}
+
+int launch_layer(wd_engine *e, int layer, const float *x, float *residual, float *out, cudaStream_t s) {
+    return launch_layers(e, layer, layer + 1, x, residual, out, s);
 }
 
 int check_device_status(wd_engine *e) {
@@ -210,6 +239,7 @@ int check_device_status(wd_engine *e) {
     if (st != 0) {
         // leave the barrier words in a usable state for the next launch
         cudaMemset(e->sync, 0, 8192);
+        e->barrier_count = 0;
         return fail(WD_E_DEVICE, "kernel raised status " + std::to_string(st) +
                                      " (1 barrier timeout, 2 copy timeout, 4 expert without slot, 8 geometry)");
     }
@@ -311,6 +341,7 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     const int H = c.hidden, F = c.expert_ffn, K = c.top_k, E = c.n_experts, SF = std::max(c.shared_ffn, 1);
     WD_TRY(cudaMalloc(&e->stamps, static_cast<size_t>(e->n_sm) * 16 * 8));
     WD_TRY(cudaMemset(e->stamps, 0, static_cast<size_t>(e->n_sm) * 16 * 8));
+    WD_TRY(cudaMalloc(&e->layer_table, sizeof(wd::LayerDev) * c.n_layers));
     WD_TRY(cudaMalloc(&e->logits, E * 4));
     WD_TRY(cudaMalloc(&e->ids, K * 4));
     WD_TRY(cudaMalloc(&e->weights, K * 4));
@@ -378,7 +409,7 @@ void wd_engine_destroy(wd_engine *e) {
     }
     void *bufs[] = {e->pool, e->grid_packed, e->synth_lut, e->sync, e->logits, e->ids, e->weights, e->act,
                     e->expert_out, e->routed, e->shared_act, e->shared_down, e->shared_gate, e->x_buf, e->out_buf,
-                    e->residual_buf, e->staging, e->stamps};
+                    e->residual_buf, e->staging, e->stamps, e->layer_table};
     for (void *b : bufs) cudaFree(b);
     if (e->pinned) cudaFreeHost(e->pinned);
     if (e->stream) cudaStreamDestroy(e->stream);
@@ -396,6 +427,7 @@ int wd_set_router(wd_engine *e, int layer, const void *router_q8_0, const float 
         if ((rc = upload_f32(e, bias, e->cfg.n_experts, &L.bias))) return rc;
     }
     L.have_router = true;
+    e->layer_table_dirty = true;
     return WD_OK;
 }
 
@@ -411,12 +443,14 @@ int wd_set_shared(wd_engine *e, int layer, const float *gate_vec, const void *g,
     if ((rc = upload_repacked_q8(e, u, e->cfg.shared_ffn, e->cfg.hidden, &L.sh_up))) return rc;
     if ((rc = upload_repacked_q8(e, d, e->cfg.hidden, e->cfg.shared_ffn, &L.sh_down))) return rc;
     L.have_shared = true;
+    e->layer_table_dirty = true;
     return WD_OK;
 }
 
 int wd_set_norm(wd_engine *e, int layer, const float *weight) {
     int rc = check_layer(e, layer);
     if (rc) return rc;
+    e->layer_table_dirty = true;
     WD_CUDA(cudaSetDevice(e->cfg.device));
     Layer &L = e->layers[layer];
     if (!weight) {
@@ -577,39 +611,7 @@ int wd_stack_step(wd_engine *e, float *residual_dev, void *stream) {
     if (!e->resident) return fail(WD_E_STATE, "a capped expert cache is not supported by this build");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
-    if (e->stack_graph && (e->stack_graph_residual != residual_dev)) {
-        cudaGraphExecDestroy(e->stack_graph);
-        e->stack_graph = nullptr;
-    }
-    if (!e->stack_graph) {
-        // capture the whole token; if capture of cooperative launches is refused, run the layers directly
-        cudaGraph_t graph = nullptr;
-        int rc = WD_OK;
-        if (cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
-            for (int l = 0; l < e->cfg.n_layers && rc == WD_OK; ++l)
-                rc = launch_layer(e, l, nullptr, residual_dev, e->out_buf, s);
-            cudaError_t ce = cudaStreamEndCapture(s, &graph);
-            if (rc == WD_OK && ce == cudaSuccess && graph &&
-                cudaGraphInstantiate(&e->stack_graph, graph, 0) == cudaSuccess) {
-                e->stack_graph_residual = residual_dev;
-            } else {
-                e->stack_graph = nullptr;
-                cudaGetLastError();
-            }
-            if (graph) cudaGraphDestroy(graph);
-        } else {
-            cudaGetLastError();
-        }
-    }
-    if (e->stack_graph) {
-        WD_CUDA(cudaGraphLaunch(e->stack_graph, s));
-        return WD_OK;
-    }
-    for (int l = 0; l < e->cfg.n_layers; ++l) {
-        int rc = launch_layer(e, l, nullptr, residual_dev, e->out_buf, s);
-        if (rc) return rc;
-    }
-    return WD_OK;
+    return launch_layers(e, 0, e->cfg.n_layers, nullptr, residual_dev, e->out_buf, s);
 }
 
 int wd_stack_step_host(wd_engine *e, const float *in_host, float *out_host) {
@@ -657,10 +659,7 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
 int wd_set_profiling(wd_engine *e, int on) {
     if (!e) return fail(WD_E_INVALID, "null engine");
     e->profiling = on != 0;
-    if (e->stack_graph) {          // the captured launches carry the old setting
-        cudaGraphExecDestroy(e->stack_graph);
-        e->stack_graph = nullptr;
-    }
+    e->stamp_layer = on > 1 ? on - 1 : 0;   // on = 1 + offset of the profiled layer within a launch
     return WD_OK;
 }
 
@@ -673,7 +672,10 @@ int wd_device_status(wd_engine *e, int *status) {
     unsigned st = 0;
     WD_CUDA(cudaMemcpy(&st, e->sync + 2, sizeof(st), cudaMemcpyDeviceToHost));
     *status = static_cast<int>(st);
-    if (st) WD_CUDA(cudaMemset(e->sync, 0, 8192));
+    if (st) {
+        WD_CUDA(cudaMemset(e->sync, 0, 8192));
+        e->barrier_count = 0;
+    }
     return WD_OK;
 }
 
@@ -821,6 +823,7 @@ static uint64_t sid(int layer, int which) { return static_cast<uint64_t>(layer) 
 
 int wd_synth_model(wd_engine *e, uint64_t seed, float sigma, float bias_sigma) {
     if (!e) return fail(WD_E_INVALID, "null engine");
+    e->layer_table_dirty = true;
     if (!e->resident) return fail(WD_E_STATE, "the device-side generator needs a pool that holds every owned expert");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     const wd_config &c = e->cfg;

@@ -33,7 +33,7 @@ constexpr int kActSbStride = 272;             // 256 int8 + 16 pad: the 8 superb
 // Lane-private copy of the IQ3_S codebook: entry idx = byte | h << 8 for lane L lives at byte
 // offset byte*256 + h*128 + L*4, so the 32 lanes of a warp always hit 32 different banks.
 // Each lane expands one entry; the warp then writes whole 128-byte rows (no bank conflicts).
-__device__ __forceinline__ void build_grid_table(uint8_t *tab, const uint16_t *packed_global) {
+__device__ __noinline__ void build_grid_table(uint8_t *tab, const uint16_t *packed_global) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
     uint32_t *t = reinterpret_cast<uint32_t *>(tab);
     for (int base = warp * 32; base < 512; base += nw * 32) {
@@ -112,24 +112,6 @@ __device__ __forceinline__ void iq3_block_partials(const uint8_t *tile, int lane
     const uint4 *av = reinterpret_cast<const uint4 *>(a);
 #pragma unroll 1
     for (int i = 0; i < 8; ++i) iq3_subblock(tile, h, i, lane, av[2 * i], av[2 * i + 1], lane4x2, tab, partial);
-}
-
-// Two blocks (gate and up tiles) against the same activations: the activation words are loaded once.
-__device__ __forceinline__ void iq3_block_partials2(const uint8_t *tile0, const uint8_t *tile1, int lane,
-                                                    const uint8_t *a, uint32_t lane4x2, const uint8_t *tab,
-                                                    int p0[8], int p1[8]) {
-    Iq3Head h0, h1;
-    iq3_head(tile0, lane, h0);
-    iq3_head(tile1, lane, h1);
-#pragma unroll
-    for (int c = 0; c < 8; ++c) p0[c] = p1[c] = 0;
-    const uint4 *av = reinterpret_cast<const uint4 *>(a);
-#pragma unroll 1
-    for (int i = 0; i < 8; ++i) {
-        const uint4 lo = av[2 * i], hi = av[2 * i + 1];
-        iq3_subblock(tile0, h0, i, lane, lo, hi, lane4x2, tab, p0);
-        iq3_subblock(tile1, h1, i, lane, lo, hi, lane4x2, tab, p1);
-    }
 }
 
 }  // namespace wd
