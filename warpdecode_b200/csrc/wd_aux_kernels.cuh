@@ -9,9 +9,13 @@ namespace wd {
 // ---------------------------------------------------------------------------------------------
 // repack: ggml IQ3_S blocks (110 B: d, qs[64], qh[8], signs[32], scales[4]) -> tiles
 // ---------------------------------------------------------------------------------------------
-__global__ void repack_iq3s_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, long long nblocks) {
+// blockIdx.y walks a batch of matrices `src_stride` / `dst_stride` bytes apart (one launch per layer).
+__global__ void repack_iq3s_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, long long nblocks,
+                                   long long src_stride, long long dst_stride) {
     const long long b = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
     if (b >= nblocks) return;
+    src += blockIdx.y * src_stride;
+    dst += blockIdx.y * dst_stride;
     const uint8_t *s = src + b * 110;
     uint8_t *tile = dst + (b >> 5) * kIq3TileBytes;
     const int lane = static_cast<int>(b & 31);

@@ -169,9 +169,9 @@ int repack_expert_into_slot(wd_engine *e, const uint8_t *g, const uint8_t *u, co
     uint8_t *dst = e->pool + static_cast<size_t>(slot) * e->slot_bytes;
     const long long nb_gu = static_cast<long long>(e->cfg.expert_ffn) * e->nsb_h;
     const long long nb_d = static_cast<long long>(e->cfg.hidden) * e->nsb_f;
-    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_gu + 127) / 128), 128, 0, s>>>(g, dst, nb_gu);
-    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_gu + 127) / 128), 128, 0, s>>>(u, dst + e->gate_bytes, nb_gu);
-    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_d + 127) / 128), 128, 0, s>>>(d, dst + 2 * e->gate_bytes, nb_d);
+    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_gu + 127) / 128), 128, 0, s>>>(g, dst, nb_gu, 0, 0);
+    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_gu + 127) / 128), 128, 0, s>>>(u, dst + e->gate_bytes, nb_gu, 0, 0);
+    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_d + 127) / 128), 128, 0, s>>>(d, dst + 2 * e->gate_bytes, nb_d, 0, 0);
     WD_CUDA(cudaGetLastError());
     return WD_OK;
 }
@@ -529,12 +529,22 @@ int wd_set_experts_device(wd_engine *e, int layer, const void *gate, const void 
     const uint8_t *g = static_cast<const uint8_t *>(gate), *u = static_cast<const uint8_t *>(up),
                   *d = static_cast<const uint8_t *>(down);
     std::vector<int> slots(e->cfg.n_experts, -1);
+    {
+        // the owned experts of a layer occupy consecutive slots: three launches repack them all
+        const int slot0 = layer * e->e_count;
+        uint8_t *dst = e->pool + static_cast<size_t>(slot0) * e->slot_bytes;
+        const long long nb_gu = static_cast<long long>(e->cfg.expert_ffn) * e->nsb_h;
+        const long long nb_d = static_cast<long long>(e->cfg.hidden) * e->nsb_f;
+        const long long gb = static_cast<long long>(e->gate_bytes), db = static_cast<long long>(e->down_bytes);
+        const long long sb = static_cast<long long>(e->slot_bytes);
+        const dim3 grid_gu(static_cast<unsigned>((nb_gu + 127) / 128), e->e_count), grid_d(static_cast<unsigned>((nb_d + 127) / 128), e->e_count);
+        wd::repack_iq3s_kernel<<<grid_gu, 128, 0, e->stream>>>(g + e->e_first * gb, dst, nb_gu, gb, sb);
+        wd::repack_iq3s_kernel<<<grid_gu, 128, 0, e->stream>>>(u + e->e_first * gb, dst + gb, nb_gu, gb, sb);
+        wd::repack_iq3s_kernel<<<grid_d, 128, 0, e->stream>>>(d + e->e_first * db, dst + 2 * gb, nb_d, db, sb);
+        WD_CUDA(cudaGetLastError());
+    }
     for (int x = 0; x < e->e_count; ++x) {
         const int expert = e->e_first + x, slot = layer * e->e_count + x;
-        if ((rc = repack_expert_into_slot(e, g + static_cast<size_t>(expert) * e->gate_bytes,
-                                          u + static_cast<size_t>(expert) * e->gate_bytes,
-                                          d + static_cast<size_t>(expert) * e->down_bytes, slot, e->stream)))
-            return rc;
         slots[expert] = slot;
         const int64_t key = (static_cast<int64_t>(layer) << 32) | static_cast<uint32_t>(expert);
         e->slot_key[slot] = key;
@@ -744,7 +754,7 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
         WD_CUDA(cudaMemcpy(d_src, w, bytes, cudaMemcpyHostToDevice));
         WD_CUDA(cudaMemcpy(d_x, x, cols * 4, cudaMemcpyHostToDevice));
         const long long nblocks = static_cast<long long>(rows) * nsb;
-        wd::repack_iq3s_kernel<<<static_cast<unsigned>((nblocks + 127) / 128), 128>>>(d_src, d_dst, nblocks);
+        wd::repack_iq3s_kernel<<<static_cast<unsigned>((nblocks + 127) / 128), 128>>>(d_src, d_dst, nblocks, 0, 0);
         const int nw = 8;
         const size_t smem = wd::kGridTableBytes + nsb * wd::kActSbStride + 32 * 4 + nw * wd::kIq3TileBytes + nw * 640 * 4 + 256;
         WD_CUDA(cudaFuncSetAttribute(wd::test_matvec_iq3s_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
