@@ -159,6 +159,17 @@ int wd_quantize_q8_K_host(const float *x, int n, void *blocks);
  * engine uses. `partials`, if not NULL, receives the int32 sums [rows][cols/256][8] (IQ types). */
 int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, float *y,
                    int32_t *partials);
+/* Has no counterpart in the reference. y = W x for one IQ3_S matrix like wd_matvec_host, for callers
+ * that must not allocate device memory (HBM already handed to the expert pool, a latency-critical
+ * token loop where cudaMalloc's device-wide synchronisation is unacceptable, memory owned by another
+ * allocator): w_dev (ggml layout), x_dev, y_dev are DEVICE buffers of the caller; the only scratch is
+ * a fixed 8 MiB array inside the library that every GPU loading it holds until exit, so rows*cols/256*110
+ * must not exceed 8 MiB - 1 KiB (larger is refused with a message). Work is enqueued on `stream`.
+ * The first call on each device looks up the array's device address; make that call before any stream
+ * capture. All calls share the array, which keeps the last call's contents (nothing needs clearing:
+ * every byte read is first rewritten); calls that overlap on the GPU race on it. */
+int wd_matvec_iq3s_noalloc(const void *w_dev, int rows, int cols, const float *x_dev, float *y_dev,
+                           void *stream);
 
 /* ---- synthetic model generator (device side) ----------------------------------------------- */
 /* Fills `dst` (device) with `rows` x `cols` N(0, sigma) weights drawn from (seed, stream_id)

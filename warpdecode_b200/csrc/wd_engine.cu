@@ -946,3 +946,77 @@ int wd_synth_dense_host(wd_engine *e, uint64_t seed, float sigma, float bias_sig
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free matvec.
+//
+// Some callers must not trigger a device allocation: a decode loop that has already handed nearly all
+// of HBM to the expert slot pool (a cudaMalloc there can fail, and even when it succeeds it synchronises
+// the whole device), code running between the steps of a latency-critical token loop, or a host engine
+// whose memory is owned by another allocator. For them this entry point computes y = W x for one IQ3_S
+// matrix with the same repack + decode kernels as wd_matvec_host, but takes every buffer from the
+// caller (device pointers) and keeps its only scratch - the packed codebook and the repacked tiles - in
+// the fixed array below, which every GPU that loads this library holds until the process exits.
+//
+// The array's name is only a host-side handle; the device address the kernels need comes from
+// cudaGetSymbolAddress, looked up once per device by the first call made with that device current. That
+// first call should happen before any stream capture. All calls share the array: it keeps the previous
+// call's tiles (each call overwrites every byte it later reads, so nothing has to be cleared), and two
+// calls that overlap on the GPU - different streams, or one stream re-entered from two host threads -
+// race on it.
+// ---------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = 8u << 20;            // 8 MiB per GPU
+constexpr size_t kNoAllocGridBytes = 1024;                   // packed codebook at the front
+static __device__ __align__(256) unsigned char wd_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kNoAllocMaxDevices = 64;
+void *g_noalloc_ptr[kNoAllocMaxDevices] = {};
+
+int noalloc_scratch_for_current_device(void **out) {
+    int dev = -1;
+    WD_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return fail(WD_E_INVALID, "device ordinal out of range");
+    if (!g_noalloc_ptr[dev]) {
+        void *p = nullptr;
+        const cudaError_t ce = cudaGetSymbolAddress(&p, wd_noalloc_scratch);
+        if (ce != cudaSuccess || p == nullptr)
+            return fail(WD_E_CUDA, std::string("cudaGetSymbolAddress(wd_noalloc_scratch): ") + cudaGetErrorString(ce));
+        g_noalloc_ptr[dev] = p;
+    }
+    *out = g_noalloc_ptr[dev];
+    return WD_OK;
+}
+
+}  // namespace
+
+extern "C" int wd_matvec_iq3s_noalloc(const void *w_dev, int rows, int cols, const float *x_dev, float *y_dev,
+                                      void *stream) {
+    if (!w_dev || !x_dev || !y_dev) return fail(WD_E_INVALID, "null buffer");
+    const int nsb = cols / 256;
+    if (rows <= 0 || cols <= 0 || cols % 256 || !pow2(nsb) || nsb > 32 || rows % (32 / nsb))
+        return fail(WD_E_INVALID, "cols must be 256*2^n (n<=5) and rows a multiple of 32/(cols/256)");
+    const size_t tile_bytes = static_cast<size_t>(rows) * nsb * 110;
+    if (tile_bytes > kNoAllocScratchBytes - kNoAllocGridBytes)
+        return fail(WD_E_INVALID, "matrix of " + std::to_string(tile_bytes) + " bytes exceeds the fixed scratch of " +
+                                      std::to_string(kNoAllocScratchBytes - kNoAllocGridBytes) +
+                                      " bytes of the allocation-free matvec");
+    void *base = nullptr;
+    int rc = noalloc_scratch_for_current_device(&base);
+    if (rc) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint16_t *grid = static_cast<uint16_t *>(base);
+    uint8_t *tiles = static_cast<uint8_t *>(base) + kNoAllocGridBytes;
+    static_assert(sizeof(wd_iq3s_grid_packed) == kNoAllocGridBytes, "packed codebook size");
+    WD_CUDA(cudaMemcpyAsync(grid, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice, s));
+    const long long nblocks = static_cast<long long>(rows) * nsb;
+    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nblocks + 127) / 128), 128, 0, s>>>(
+        static_cast<const uint8_t *>(w_dev), tiles, nblocks, 0, 0);
+    const int nw = 8;
+    const size_t smem = wd::kGridTableBytes + nsb * wd::kActSbStride + 32 * 4 + nw * wd::kIq3TileBytes + nw * 640 * 4 + 256;
+    WD_CUDA(cudaFuncSetAttribute(wd::test_matvec_iq3s_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    wd::test_matvec_iq3s_kernel<<<64, nw * 32, smem, s>>>(tiles, rows, nsb, x_dev, y_dev, nullptr, grid);
+    WD_CUDA(cudaGetLastError());
+    return WD_OK;
+}
