@@ -14,13 +14,13 @@ namespace wd {
 
 // Error bits a kernel can raise in the engine's device status word.
 enum : unsigned {
-    kErrBarrierTimeout = 1u,   // a grid barrier wait ran out
+    kErrBarrierTimeout = 1u,   // a wait for another CTA's (or GPU's) value ran out
     kErrCopyTimeout = 2u,      // a bulk copy never completed
     kErrExpertMiss = 4u,       // a selected expert has no slot
     kErrGeometry = 8u,         // launch geometry does not match the parameters
 };
 
-constexpr unsigned kSpinLimit = 1u << 22;   // polls before a wait gives up (well under a second)
+constexpr unsigned kSpinLimit = 1u << 20;   // polls before a wait gives up (about a second)
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -73,31 +73,85 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsign
 }
 
 // ---------------------------------------------------------------------------------------------
-// grid barrier (all CTAs co-resident: cooperative launch). Sense = generation counter.
+// Tagged words: a float and the tag of the layer that produced it, published with ONE 8-byte store.
+// A consumer polls the word itself until the tag matches, so no fence and no separate flag is needed
+// (an aligned 8-byte access is single-copy atomic). Tags grow monotonically over layers and launches.
 // ---------------------------------------------------------------------------------------------
-// One 64-bit counter that only ever grows: a CTA arrives with a release add and waits until the
-// counter reaches the next multiple of the grid size. No reset, no second word, no full fence: one
-// atomic and a few polling loads per barrier. (The host zeroes the counter after a reported error.)
-// `target` is the counter value at which this barrier opens; the host hands every launch the value
-// the counter had before it, so the kernel needs no returned value: the arrival is a fire-and-forget
-// release reduction, the wait polls with relaxed loads and takes one acquire fence at the end.
-__device__ __forceinline__ void grid_barrier(unsigned long long *ctr, unsigned long long target, unsigned *err) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        unsigned long long now;
-        asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory");
-        unsigned i = 0;
-        for (;;) {
-            asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(now) : "l"(ctr) : "memory");
-            if (now >= target) break;
-            if (++i > kSpinLimit) {
-                atomicOr(err, kErrBarrierTimeout);
-                break;
-            }
-        }
-        asm volatile("fence.acquire.gpu;" ::: "memory");
+typedef unsigned long long tagged_t;
+
+// True when a polling loop should give up: its own limit ran out, or some other wait of this launch
+// already failed (then the remaining waits end after 1024 polls instead of the full limit, so that a
+// broken launch still terminates quickly). Raises kErrBarrierTimeout.
+__device__ __forceinline__ bool wait_expired(unsigned it, unsigned *err) {
+    if ((it & 0x3ffu) != 0x3ffu) return false;
+    if (it >= kSpinLimit || (*reinterpret_cast<volatile unsigned *>(err) & (kErrBarrierTimeout | kErrCopyTimeout)) != 0u) {
+        atomicOr(err, kErrBarrierTimeout);
+        return true;
     }
-    __syncthreads();
+    return false;
+}
+
+__device__ __forceinline__ tagged_t make_tagged(float v, uint32_t tag) {
+    return (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(v);
+}
+__device__ __forceinline__ void st_tagged(tagged_t *p, float v, uint32_t tag) {
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(make_tagged(v, tag)) : "memory");
+}
+// same, to memory that may belong to another GPU
+__device__ __forceinline__ void st_tagged_sys(tagged_t *p, float v, uint32_t tag) {
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(make_tagged(v, tag)) : "memory");
+}
+__device__ __forceinline__ tagged_t ld_tagged(const tagged_t *p) {
+    tagged_t w;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
+// Polls up to N words (word i at p[i * stride], i < n) until every tag matches; values to out[].
+// Bounded: on timeout raises kErrBarrierTimeout and returns what it has.
+template <int N>
+__device__ __forceinline__ void wait_tagged(const tagged_t *p, int stride, int n, uint32_t tag, float out[N],
+                                            unsigned *err) {
+    tagged_t w[N] = {};
+    for (unsigned it = 0;; ++it) {
+        // all loads first, then the checks, so that the loads are in flight together
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+            if (i < n) w[i] = ld_tagged(p + static_cast<size_t>(i) * stride);
+        unsigned bad = 0;
+#pragma unroll
+        for (int i = 0; i < N; ++i) bad |= (i < n) & (static_cast<uint32_t>(w[i] >> 32) != tag);
+        if (!bad) break;
+        if (wait_expired(it, err)) break;
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = i < n ? __uint_as_float(static_cast<uint32_t>(w[i])) : 0.0f;
+}
+
+// Same with one address per word.
+template <int N>
+__device__ __forceinline__ void wait_tagged_at(const tagged_t *const p[N], int n, uint32_t tag, float out[N],
+                                               unsigned *err) {
+    tagged_t w[N] = {};
+    for (unsigned it = 0;; ++it) {
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+            if (i < n) w[i] = ld_tagged(p[i]);
+        unsigned bad = 0;
+#pragma unroll
+        for (int i = 0; i < N; ++i) bad |= (i < n) & (static_cast<uint32_t>(w[i] >> 32) != tag);
+        if (!bad) break;
+        if (wait_expired(it, err)) break;
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = i < n ? __uint_as_float(static_cast<uint32_t>(w[i])) : 0.0f;
+}
+// Waits until the tag of *p has reached `tag` (tags compared as a wrapping sequence).
+__device__ __forceinline__ void wait_tag_reached(const tagged_t *p, uint32_t tag, unsigned *err) {
+    for (unsigned it = 0;; ++it) {
+        const uint32_t t = static_cast<uint32_t>(ld_tagged(p) >> 32);
+        if (static_cast<int32_t>(t - tag) >= 0) break;
+        if (wait_expired(it, err)) break;
+    }
 }
 
 // Order-preserving map float -> u32 for selection: larger float = larger key, NaN = 0 (never wins).

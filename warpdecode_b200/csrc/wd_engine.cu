@@ -73,10 +73,11 @@ struct wd_engine {
     int stamp_layer = 0;                    // offset of the profiled layer inside a launch
     wd::LayerDev *layer_table = nullptr;    // device copy of the per-layer pointers
     bool layer_table_dirty = true;
-    unsigned long long barrier_count = 0;   // value of the device barrier counter after the launches so far
-    float *logits = nullptr, *weights = nullptr, *act = nullptr, *expert_out = nullptr, *routed = nullptr,
-          *shared_act = nullptr, *shared_down = nullptr, *shared_gate = nullptr, *x_buf = nullptr, *out_buf = nullptr,
-          *residual_buf = nullptr;
+    // exchange buffers of the layer kernel: tagged words, two halves (by layer parity) per buffer
+    wd::tagged_t *tagged = nullptr;
+    size_t tagged_words = 0;
+    int last_parity = 0;                    // half that holds the last launch's last layer (for the taps)
+    float *weights = nullptr, *routed = nullptr, *x_buf = nullptr, *out_buf = nullptr, *residual_buf = nullptr;
     int *ids = nullptr;
     uint8_t *staging = nullptr;       // device, ggml-layout upload buffer
     size_t staging_bytes = 0;
@@ -130,8 +131,10 @@ int plan_shared_memory(wd_engine *e) {
         return fail(WD_E_INVALID, "geometry needs more staging slots per CTA than the kernel supports");
     p.off_bar = take(wd::kMaxBars * 8);
     const size_t rt_bytes = static_cast<size_t>(nbh) * 136;
-    const size_t stage_a = std::max(static_cast<size_t>(p.n1r + p.n1s) * 2 * rt_bytes,
-                                    static_cast<size_t>(p.n2) * 2 * wd::kIq3TileBytes);
+    // stage A: phase-1 tasks, then gate/up tile pairs, then the selected experts' activations as floats
+    const size_t stage_a = std::max(std::max(static_cast<size_t>(p.n1r + p.n1s) * 2 * rt_bytes,
+                                             static_cast<size_t>(p.n2) * 2 * wd::kIq3TileBytes),
+                                    static_cast<size_t>(c.top_k) * c.expert_ffn * 4);
     p.off_stage_a = take(stage_a);
     // stage B also holds the F32 shared gate vector during phase 1
     p.off_stage_b = take(std::max(static_cast<size_t>(p.n3) * wd::kIq3TileBytes + static_cast<size_t>(p.nsd) * nbs * 136,
@@ -220,12 +223,10 @@ int launch_layers(wd_engine *e, int begin, int end, const float *x, float *resid
     p.residual = residual;
     p.out = out;
     p.stamps = e->profiling ? e->stamps : nullptr;
-    p.barrier_base = e->barrier_count;
     void *args[] = {&p};
     WD_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(wd::moe_layer_kernel), dim3(e->n_sm),
                                         dim3(wd::kThreads), args, e->smem_bytes, s));
-    // two barriers inside every layer and one between consecutive layers
-    e->barrier_count += static_cast<unsigned long long>(e->n_sm) * (3ull * (end - begin) - 1ull);
+    e->last_parity = (end - begin - 1) & 1;
     return WD_OK;
 }
 
@@ -237,11 +238,11 @@ int check_device_status(wd_engine *e) {
     unsigned st = 0;
     WD_CUDA(cudaMemcpy(&st, e->sync + 2, sizeof(st), cudaMemcpyDeviceToHost));
     if (st != 0) {
-        // leave the barrier words in a usable state for the next launch
+        // an interrupted launch leaves the tag epoch and the exchange words undefined: start over
         cudaMemset(e->sync, 0, 8192);
-        e->barrier_count = 0;
+        cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t));
         return fail(WD_E_DEVICE, "kernel raised status " + std::to_string(st) +
-                                     " (1 barrier timeout, 2 copy timeout, 4 expert without slot, 8 geometry)");
+                                     " (1 wait timeout, 2 copy timeout, 4 expert without slot, 8 geometry)");
     }
     return WD_OK;
 }
@@ -336,28 +337,26 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     }
     WD_TRY(cudaMalloc(&e->grid_packed, sizeof(wd_iq3s_grid_packed)));
     WD_TRY(cudaMemcpy(e->grid_packed, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
-    WD_TRY(cudaMalloc(&e->sync, 8192 + sizeof(unsigned) * (c.hidden / 4)));
-    WD_TRY(cudaMemset(e->sync, 0, 8192 + sizeof(unsigned) * (c.hidden / 4)));
+    WD_TRY(cudaMalloc(&e->sync, 8192));
+    WD_TRY(cudaMemset(e->sync, 0, 8192));
     const int H = c.hidden, F = c.expert_ffn, K = c.top_k, E = c.n_experts, SF = std::max(c.shared_ffn, 1);
     WD_TRY(cudaMalloc(&e->stamps, static_cast<size_t>(e->n_sm) * 16 * 8));
     WD_TRY(cudaMemset(e->stamps, 0, static_cast<size_t>(e->n_sm) * 16 * 8));
     WD_TRY(cudaMalloc(&e->layer_table, sizeof(wd::LayerDev) * c.n_layers));
-    WD_TRY(cudaMalloc(&e->logits, E * 4));
     WD_TRY(cudaMalloc(&e->ids, K * 4));
     WD_TRY(cudaMalloc(&e->weights, K * 4));
-    WD_TRY(cudaMalloc(&e->act, static_cast<size_t>(K) * F * 4));
-    WD_TRY(cudaMalloc(&e->expert_out, static_cast<size_t>(K) * H * 4));
     WD_TRY(cudaMalloc(&e->routed, H * 4));
-    WD_TRY(cudaMalloc(&e->shared_act, SF * 4));
-    WD_TRY(cudaMalloc(&e->shared_down, H * 4));
-    WD_TRY(cudaMalloc(&e->shared_gate, 4));
     WD_TRY(cudaMalloc(&e->x_buf, H * 4));
     WD_TRY(cudaMalloc(&e->out_buf, H * 4));
     WD_TRY(cudaMalloc(&e->residual_buf, H * 4));
-    WD_TRY(cudaMemset(e->expert_out, 0, static_cast<size_t>(K) * H * 4));
-    WD_TRY(cudaMemset(e->act, 0, static_cast<size_t>(K) * F * 4));
-    WD_TRY(cudaMemset(e->shared_down, 0, H * 4));
-    WD_TRY(cudaMemset(e->shared_gate, 0, 4));
+    // tagged exchange words: logits, shared act, shared gate, act, expert out, shared down, residual (x2), progress
+    const size_t tw_logits = 0, tw_shact = tw_logits + 2 * static_cast<size_t>(E), tw_shgate = tw_shact + 2 * static_cast<size_t>(SF),
+                 tw_act = tw_shgate + 2, tw_eo = tw_act + 2 * static_cast<size_t>(K) * F,
+                 tw_shdown = tw_eo + 2 * static_cast<size_t>(K) * H, tw_res = tw_shdown + 2 * static_cast<size_t>(H),
+                 tw_prog = tw_res + 2 * static_cast<size_t>(H);
+    e->tagged_words = tw_prog + static_cast<size_t>(e->n_sm);
+    WD_TRY(cudaMalloc(&e->tagged, e->tagged_words * sizeof(wd::tagged_t)));
+    WD_TRY(cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t)));
     // staging: one layer's routed experts in ggml layout (or a dense tensor, whichever is larger)
     const size_t dense = static_cast<size_t>(std::max(E, std::max(c.shared_ffn, H))) * (std::max(H, c.shared_ffn) / 32) * 34;
     const size_t one_expert = 2 * e->gate_bytes + e->down_bytes;
@@ -375,11 +374,12 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     p.pool = e->pool; p.slot_bytes = e->slot_bytes;
     p.gate_off = 0; p.up_off = static_cast<unsigned>(e->gate_bytes); p.down_off = static_cast<unsigned>(2 * e->gate_bytes);
     p.grid_packed = e->grid_packed;
-    p.logits = e->logits; p.ids = e->ids; p.weights = e->weights; p.act = e->act; p.expert_out = e->expert_out;
-    p.routed = e->routed; p.shared_act = e->shared_act; p.shared_down = e->shared_down; p.shared_gate = e->shared_gate;
+    p.ids = e->ids; p.weights = e->weights; p.routed = e->routed;
+    p.t_logits = e->tagged + tw_logits; p.t_shared_act = e->tagged + tw_shact; p.t_shared_gate = e->tagged + tw_shgate;
+    p.t_act = e->tagged + tw_act; p.t_expert_out = e->tagged + tw_eo; p.t_shared_down = e->tagged + tw_shdown;
+    p.t_residual = e->tagged + tw_res; p.t_progress = e->tagged + tw_prog;
+    p.n_peers = 0;
     p.sync = e->sync;
-    p.barrier = reinterpret_cast<unsigned long long *>(e->sync + 4);
-    p.act_amax = e->sync + 1024 + c.hidden / 4 + 16;   // behind the output-tile counters
     { int t2 = F * e->nsb_h / 32, t3 = H * e->nsb_f / 32; p.t2_log2 = 0; while ((1 << p.t2_log2) < t2) ++p.t2_log2; p.t3_log2 = 0; while ((1 << p.t3_log2) < t3) ++p.t3_log2; }
     if ((rc = plan_shared_memory(e)) != WD_OK) return bail(rc);
     cudaError_t ae = cudaFuncSetAttribute(wd::moe_layer_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -407,9 +407,8 @@ void wd_engine_destroy(wd_engine *e) {
         cudaFree(L.router); cudaFree(L.bias); cudaFree(L.gate_vec); cudaFree(L.sh_gate); cudaFree(L.sh_up);
         cudaFree(L.sh_down); cudaFree(L.norm); cudaFree(L.slot_of_expert);
     }
-    void *bufs[] = {e->pool, e->grid_packed, e->synth_lut, e->sync, e->logits, e->ids, e->weights, e->act,
-                    e->expert_out, e->routed, e->shared_act, e->shared_down, e->shared_gate, e->x_buf, e->out_buf,
-                    e->residual_buf, e->staging, e->stamps, e->layer_table};
+    void *bufs[] = {e->pool, e->grid_packed, e->synth_lut, e->sync, e->tagged, e->ids, e->weights, e->routed,
+                    e->x_buf, e->out_buf, e->residual_buf, e->staging, e->stamps, e->layer_table};
     for (void *b : bufs) cudaFree(b);
     if (e->pinned) cudaFreeHost(e->pinned);
     if (e->stream) cudaStreamDestroy(e->stream);
@@ -644,25 +643,44 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
     if (token != 0) return fail(WD_E_INVALID, "token out of range");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     const wd_config &c = e->cfg;
-    const void *src = nullptr;
+    const wd::MoeParams &p = e->base;
+    const size_t par = static_cast<size_t>(e->last_parity);
+    const void *src = nullptr;              // plain buffer
+    const wd::tagged_t *tsrc = nullptr;     // or tagged words of the last layer's half
     size_t n = 0;
     switch (tap) {
-        case WD_TAP_LOGITS: src = e->logits; n = c.n_experts * 4; break;
+        case WD_TAP_LOGITS: tsrc = p.t_logits + par * c.n_experts; n = c.n_experts * 4; break;
         case WD_TAP_IDS: src = e->ids; n = c.top_k * 4; break;
         case WD_TAP_WEIGHTS: src = e->weights; n = c.top_k * 4; break;
-        case WD_TAP_ACT: src = e->act; n = static_cast<size_t>(c.top_k) * c.expert_ffn * 4; break;
-        case WD_TAP_EXPERT_OUT: src = e->expert_out; n = static_cast<size_t>(c.top_k) * c.hidden * 4; break;
+        case WD_TAP_ACT:
+            n = static_cast<size_t>(c.top_k) * c.expert_ffn * 4;
+            tsrc = p.t_act + par * (n / 4);
+            break;
+        case WD_TAP_EXPERT_OUT:
+            n = static_cast<size_t>(c.top_k) * c.hidden * 4;
+            tsrc = p.t_expert_out + par * (n / 4);
+            break;
         case WD_TAP_ROUTED: src = e->routed; n = c.hidden * 4; break;
-        case WD_TAP_SHARED: src = e->shared_down; n = c.hidden * 4; break;
-        case WD_TAP_SHARED_GATE: src = e->shared_gate; n = 4; break;
-        case WD_TAP_SHARED_ACT: src = e->shared_act; n = static_cast<size_t>(c.shared_ffn) * 4; break;
+        case WD_TAP_SHARED: tsrc = p.t_shared_down + par * c.hidden; n = c.hidden * 4; break;
+        case WD_TAP_SHARED_GATE: tsrc = p.t_shared_gate + par; n = 4; break;
+        case WD_TAP_SHARED_ACT:
+            tsrc = p.t_shared_act + par * std::max(c.shared_ffn, 1);
+            n = static_cast<size_t>(c.shared_ffn) * 4;
+            break;
         case WD_TAP_STAMPS: src = e->stamps; n = static_cast<size_t>(e->n_sm) * 16 * 8; break;
         default: return fail(WD_E_INVALID, "unknown tap");
     }
     if (bytes < n) return fail(WD_E_INVALID, "tap buffer too small");
     WD_CUDA(cudaStreamSynchronize(e->stream));
     WD_CUDA(cudaDeviceSynchronize());
-    WD_CUDA(cudaMemcpy(dst, src, n, cudaMemcpyDeviceToHost));
+    if (tsrc) {     // drop the tags
+        std::vector<wd::tagged_t> words(n / 4);
+        WD_CUDA(cudaMemcpy(words.data(), tsrc, words.size() * sizeof(wd::tagged_t), cudaMemcpyDeviceToHost));
+        uint32_t *o = static_cast<uint32_t *>(dst);
+        for (size_t i = 0; i < words.size(); ++i) o[i] = static_cast<uint32_t>(words[i]);
+    } else {
+        WD_CUDA(cudaMemcpy(dst, src, n, cudaMemcpyDeviceToHost));
+    }
     return WD_OK;
 }
 
@@ -684,7 +702,7 @@ int wd_device_status(wd_engine *e, int *status) {
     *status = static_cast<int>(st);
     if (st) {
         WD_CUDA(cudaMemset(e->sync, 0, 8192));
-        e->barrier_count = 0;
+        WD_CUDA(cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t)));
     }
     return WD_OK;
 }

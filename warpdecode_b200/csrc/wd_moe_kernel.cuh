@@ -1,14 +1,19 @@
-// The fused MoE layer kernel: one persistent cooperative launch per layer (batch 1).
+// The fused MoE layer kernel: one persistent cooperative launch runs a range of layers (batch 1).
+//
+// Values that cross CTAs travel as tagged words (value + layer tag in one 8-byte store) that the consumer
+// polls; there is no grid barrier and no fence anywhere in the layer loop.
 //
 //   phase 0  every CTA: x (optionally RMSNorm(residual) * w) -> Q8_0 and Q8_K blocks in shared memory
 //   phase 1  Q8_0 row tasks spread over the grid: router logits, shared-expert gate/up + SiLU,
-//            shared gate scalar                                        -> grid barrier
-//   phase 1b every CTA: softmax / top-k (whole CTA), shared activation -> Q8_0; then ALL bulk copies of
-//            this CTA's share of the selected experts' gate/up/down tiles are issued at once
-//   phase 2  gate+up tiles -> SiLU(g)*u per expert row (+ running max per superblock);
-//            shared-expert down rows on the warps that have no tile      -> grid barrier
-//   phase 3  expert activations -> Q8_K; down tiles; the warp that delivers the last contribution
-//            of an output tile performs the ordered combine and the finish
+//            shared gate scalar                                        -> published
+//   phase 1b every CTA gathers the logits and the shared activation: softmax / top-k (whole CTA), shared
+//            activation -> Q8_0; then ALL bulk copies of this CTA's share of the selected experts'
+//            gate/up/down tiles are issued at once
+//   phase 2  gate+up tiles -> SiLU(g)*u per expert row; shared-expert down rows on the warps that have
+//            no tile                                                    -> published
+//   phase 3  gather the owned experts' activations -> Q8_K; down tiles   -> published (also to peers)
+//   combine  each CTA owns a band of output rows: ordered weighted sum + shared expert + residual update,
+//            the new residual published for the next layer's phase 0
 //
 // Reference call sites this replaces: q38_moe_select_experts_f32_x (src/qwen38_moe.cuh:2323),
 // q38_moe_run_batched_experts (:3312, five launches), run_qwen38_shared_expert_f32_x (:3963, nine
@@ -38,8 +43,8 @@ struct MoeParams {
     int t2_log2, t3_log2;        // log2 of the tiles per expert: gate/up (F*nsb_h/32) and down (H*nsb_f/32)
     int e_first, e_count;        // owned expert range
     float w_scale, eps;
-    // layers [layer_begin, layer_end) run back to back inside one launch (a grid barrier between them),
-    // so that after the first layer every instruction comes from the instruction cache
+    // layers [layer_begin, layer_end) run back to back inside one launch, so that after the first layer
+    // every instruction comes from the instruction cache
     const LayerDev *layers;      // device array, one entry per layer of the stack
     int layer_begin, layer_end;
     int stamp_layer;             // the layer whose phase timestamps are recorded
@@ -51,21 +56,25 @@ struct MoeParams {
     const float *x;              // [H] (used when residual == nullptr)
     float *residual;             // nullable: x = RMSNorm(residual) * norm_w, residual += out
     float *out;                  // [H]
-    // scratch (global)
-    float *logits;               // [E]
-    int *ids;                    // [K]
+    // exchange buffers (global): every value travels as a tagged word (value + layer tag, one 8-byte
+    // store) that its consumers poll; there is no grid barrier and no fence. Each buffer exists twice,
+    // indexed by layer parity, so that a CTA one layer ahead never overwrites words still being read.
+    tagged_t *t_logits;          // [2][E]
+    tagged_t *t_shared_act;      // [2][SF]
+    tagged_t *t_shared_gate;     // [2][1]
+    tagged_t *t_act;             // [2][K][F]
+    tagged_t *t_expert_out;      // [2][K][H]
+    tagged_t *t_shared_down;     // [2][H]
+    tagged_t *t_residual;        // [2][H]   updated residual = next layer's input
+    tagged_t *t_progress;        // [grid]   tag of the last layer each CTA has completely left
+    tagged_t *peer_expert_out[8];// expert-parallel peers' t_expert_out buffers (n_peers entries)
+    int n_peers;                 // 0: single GPU (or partial sums only); else every rank combines all K experts
+    int *ids;                    // [K]   (plain copies for inspection, written by CTA 0)
     float *weights;              // [K]
-    float *act;                  // [K][F]
-    unsigned *act_amax;          // [K][nsb_f] bit pattern of max |act| per superblock
-    float *expert_out;           // [K][H]
     float *routed;               // [H]
-    float *shared_act;           // [SF]
-    float *shared_down;          // [H]
-    float *shared_gate;          // [1]
     unsigned long long *stamps;  // nullable: [cta][16] globaltimer values at phase boundaries (profiling)
-    unsigned long long *barrier; // grid barrier counter (only ever grows)
-    unsigned long long barrier_base;   // its value when this launch starts
-    unsigned *sync;              // [2] error word, [16..] output-tile counters
+    unsigned *sync;              // [2] error word, [8] tag epoch (tag of layer `layer_begin` is epoch + 1; the
+                                 // last CTA to leave advances it by the layers run), [9] count of CTAs that left
     // shared memory plan (byte offsets from the dynamic shared base; all 128-byte aligned)
     unsigned off_tab, off_xq0, off_xd0, off_xk, off_xdk, off_actk, off_actd, off_shq, off_shd,
         off_misc, off_scr, off_bar, off_stage_a, off_stage_b;
@@ -98,7 +107,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     uint8_t *stage_a = sm + P.off_stage_a;
     uint8_t *stage_b = sm + P.off_stage_b;
     unsigned *err = P.sync + 2;
-    unsigned *tile_cnt = P.sync + 16;
+    uint32_t epoch;
+    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(P.sync + 8) : "memory");
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int cta = blockIdx.x, ncta = gridDim.x;
@@ -127,15 +137,27 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     }
     build_grid_table(tab, P.grid_packed);          // first needed in phase 2
     __syncthreads();
-    unsigned long long bar_target = P.barrier_base;
 
 #pragma unroll 1
     for (int layer = P.layer_begin; layer < P.layer_end; ++layer) {
     const LayerDev L = P.layers[layer];
     const uint32_t par = static_cast<uint32_t>(layer - P.layer_begin) & 1u;   // every mbarrier completes once per layer
+    const uint32_t tag = epoch + static_cast<uint32_t>(layer - P.layer_begin) + 1u;
     const bool stamp_on = P.stamps != nullptr && tid == 0 && layer == P.stamp_layer;
+    // this layer's halves of the exchange buffers
+    tagged_t *t_logits = P.t_logits + par * P.E;
+    tagged_t *t_shact = P.t_shared_act + par * (P.SF > 0 ? P.SF : 1);
+    tagged_t *t_shgate = P.t_shared_gate + par;
+    tagged_t *t_act = P.t_act + static_cast<size_t>(par) * P.K * P.F;
+    tagged_t *t_eo = P.t_expert_out + static_cast<size_t>(par) * P.K * P.H;
+    tagged_t *t_shdown = P.t_shared_down + par * P.H;
+    tagged_t *t_res = P.t_residual + par * P.H;
     WD_STAMP(0);
-    if (cta == 0 && tid < P.K * P.nsb_f) P.act_amax[tid] = 0u;
+    if (P.stamps != nullptr && tid == 0 && layer == P.stamp_layer + 1) {   // start of the next layer: the layer period
+        unsigned long long t__;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));
+        P.stamps[cta * 16 + 14] = t__;
+    }
 
     // ---- issue phase-1 copies: router tasks and shared gate/up tasks of this CTA --------------
     const int n_rt = P.E >> 2;                     // router tasks (4 rows each)
@@ -166,11 +188,31 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         float rv[16];
         if (tid * epl < P.H) {
             double loc[16];
+            if (layer == P.layer_begin) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                rv[i] = i < epl ? P.residual[tid * epl + i] : 0.0f;
-                loc[i] = __dmul_rn(static_cast<double>(rv[i]), static_cast<double>(rv[i]));
+                for (int i = 0; i < 16; ++i) rv[i] = i < epl ? P.residual[tid * epl + i] : 0.0f;
+            } else {
+                // the previous layer's combine publishes the updated residual row by row; the same round trips
+                // check that no CTA is still inside the layer whose exchange buffers this layer overwrites
+                const bool chk = layer >= P.layer_begin + 2 && tid < ncta;
+                tagged_t w[16] = {};
+                const tagged_t *src = P.t_residual + (par ^ 1u) * P.H + tid * epl;
+                for (unsigned it = 0;; ++it) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        if (i < epl) w[i] = ld_tagged(src + i);
+                    const tagged_t wp = chk ? ld_tagged(P.t_progress + tid) : 0;
+                    unsigned bad = chk & (static_cast<int32_t>(static_cast<uint32_t>(wp >> 32) - (tag - 2u)) < 0);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) bad |= (i < epl) & (static_cast<uint32_t>(w[i] >> 32) != tag - 1u);
+                    if (!bad) break;
+                    if (wait_expired(it, err)) break;
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) rv[i] = i < epl ? __uint_as_float(static_cast<uint32_t>(w[i])) : 0.0f;
             }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) loc[i] = __dmul_rn(static_cast<double>(rv[i]), static_cast<double>(rv[i]));
 #pragma unroll
             for (int w = 1; w < 16; w <<= 1)
 #pragma unroll
@@ -202,6 +244,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
             }
         }
     } else {
+        if (layer >= P.layer_begin + 2 && tid < ncta) wait_tag_reached(P.t_progress + tid, tag - 2u, err);
         for (int i = tid; i < P.H; i += kThreads) xf[i] = P.x[i];
     }
     // the one CTA that computes the shared gate scalar brings the gate vector in with one round trip
@@ -218,10 +261,17 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
 #include "wd_moe_kernel_phases.inc"
 
     WD_STAMP(10);
-    // the next layer reads the residual and reuses every shared and global scratch buffer
-    if (layer + 1 < P.layer_end) grid_barrier(P.barrier, bar_target += ncta, err);
+    __syncthreads();    // the next layer reuses this CTA's shared memory
+    if (tid == 0) st_tagged(P.t_progress + cta, 0.0f, tag);
     }   // layers
 #undef WD_STAMP
+    if (tid == 0) {
+        // every CTA read the epoch before it got here, so the last one to leave may advance it
+        if (atomicAdd(P.sync + 9, 1u) == static_cast<unsigned>(ncta) - 1u) {
+            P.sync[9] = 0u;
+            P.sync[8] = epoch + static_cast<uint32_t>(P.layer_end - P.layer_begin);
+        }
+    }
 }
 
 }  // namespace wd

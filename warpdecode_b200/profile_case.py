@@ -1,18 +1,29 @@
 """A small, self-ending workload for profilers (ncu): a few forward calls of the MoE layer kernel
 at the headline block shape, with direct launches (no CUDA graph) so every launch is one kernel.
 
-    python -m warpdecode_b200.profile_case [--layers 2] [--iters 4] [--stamps]
+    python -m warpdecode_b200.profile_case [--layers 2] [--iters 4] [--stamps] [--stack]
 
 Holds about 0.7 GB per layer on the device. With --stamps it prints the kernel's own per-phase
 timestamps (mean over CTAs) instead, which needs no profiler.
 """
 import argparse
+import time
 
 import numpy as np
 
 import warpdecode_b200 as wd
 
-PHASES = ["table", "x_quant", "q8_rows", "barrier1", "select", "issue", "gate_up", "barrier2", "act_quant", "down"]
+# stamp indices in the order the kernel passes them, and the name of the span that ends at each
+ORDER = [0, 1, 2, 3, 4, 12, 13, 5, 6, 11, 7, 9, 8, 10]
+PHASES = ["issue_p1", "x_wait_quant", "q8_rows", "gather_logits", "select.setup", "select.router", "select.rest",
+          "issue_tiles", "first_tile_wait", "gate_up", "gather_act_quant", "down", "combine"]
+
+
+def phase_row(st, with_period):
+    d = [(st[:, ORDER[i + 1]] - st[:, ORDER[i]]).mean() for i in range(len(ORDER) - 1)]
+    d.append((st[:, 10] - st[:, 0]).mean())                         # a CTA's time inside the layer
+    d.append((st[:, 14] - st[:, 0]).mean() if with_period else 0)   # start of this layer to start of the next
+    return d
 
 
 def main():
@@ -31,29 +42,25 @@ def main():
         eng.set_profiling(1 + a.layers // 2 if a.stamps else 0)
         res = rng.standard_normal(2048).astype(np.float32)
         for it in range(a.iters + 1):
+            t0 = time.perf_counter()
             res = eng.stack_step_host(res)
+            wall = time.perf_counter() - t0
             if a.stamps:
-                st = eng.stamps().astype(np.int64)
-                extra = [(st[:, 12] - st[:, 4]).mean(), (st[:, 13] - st[:, 12]).mean(), (st[:, 5] - st[:, 13]).mean(),
-                         (st[:, 11] - st[:, 6]).mean()]
-                rows.append(np.concatenate([np.diff(st[:, :11], axis=1).mean(0), [st[:, 10].max() - st[:, 0].min()],
-                                            extra]))
-        a.layers = 1
+                rows.append(phase_row(eng.stamps().astype(np.int64), a.layers // 2 + 1 < a.layers))
+        print("last stack step, host wall clock: %.1f us per layer" % (wall * 1e6 / a.layers))
+        skip = 1
     else:
         eng.set_profiling(a.stamps)
-    for it in range(0 if a.stack else a.iters):
-        for layer in range(a.layers):
-            eng.forward_host(layer, rng.standard_normal(2048).astype(np.float32))
-            if a.stamps:
-                st = eng.stamps().astype(np.int64)
-                extra = [(st[:, 12] - st[:, 4]).mean(), (st[:, 13] - st[:, 12]).mean(), (st[:, 5] - st[:, 13]).mean(),
-                         (st[:, 11] - st[:, 6]).mean()]
-                rows.append(np.concatenate([np.diff(st[:, :11], axis=1).mean(0), [st[:, 10].max() - st[:, 0].min()],
-                                            extra]))
+        for it in range(a.iters):
+            for layer in range(a.layers):
+                eng.forward_host(layer, rng.standard_normal(2048).astype(np.float32))
+                if a.stamps:
+                    rows.append(phase_row(eng.stamps().astype(np.int64), False))
+        skip = a.layers
     assert eng.device_status() == 0
     if a.stamps:
-        m = np.array(rows[a.layers:]).mean(0)          # skip the first pass (cold)
-        names = PHASES + ["kernel", "select.load", "select.router", "select.rest", "gate_up.first_copy_wait"]
+        m = np.array(rows[skip:]).mean(0)          # skip the first pass (cold)
+        names = PHASES + ["cta_in_layer", "layer_period"]
         print("mean ns per phase:", {n: int(v) for n, v in zip(names, m)})
     print("done")
 
