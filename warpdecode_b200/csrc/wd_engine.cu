@@ -127,7 +127,7 @@ int plan_shared_memory(wd_engine *e) {
     // a CTA takes every ncta-th entry of [tiles | shared-down tasks]: at most ceil(len / ncta) of each part
     p.n3 = (c.top_k * t3 + ncta - 1) / ncta;
     p.nsd = (n_sd + ncta - 1) / ncta;
-    if (p.n1r + p.n1s + p.n2 + p.n3 + p.nsd > wd::kMaxBars)
+    if (p.n1r + p.n1s + p.n2 + p.n3 + p.nsd > wd::kMaxBars - 1)
         return fail(WD_E_INVALID, "geometry needs more staging slots per CTA than the kernel supports");
     p.off_bar = take(wd::kMaxBars * 8);
     const size_t rt_bytes = static_cast<size_t>(nbh) * 136;

@@ -130,8 +130,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                \
         P.stamps[cta * 16 + (i)] = t__;                                                        \
     }
-    const int n_bars = P.n1r + P.n1s + P.n2 + P.n3 + P.nsd;
-    if (tid < n_bars) {
+    if (tid < kMaxBars) {       // the last one belongs to the shared gate vector
         mbar_init(&bars[tid], 1);
         mbar_fence_init();
     }
@@ -176,6 +175,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
             mbar_expect_tx(&bars[s], 2u * rt_bytes);
             bulk_load(stage_a + s * a1_slot, L.sh_gate + static_cast<size_t>(t) * rt_bytes, rt_bytes, &bars[s]);
             bulk_load(stage_a + s * a1_slot + rt_bytes, L.sh_up + static_cast<size_t>(t) * rt_bytes, rt_bytes, &bars[s]);
+        }
+        // the one CTA that computes the shared gate scalar brings the F32 gate vector into stage B
+        if (P.SF > 0 && cta == ncta / 2) {
+            mbar_expect_tx(&bars[kMaxBars - 1], static_cast<unsigned>(P.H) * 4u);
+            bulk_load(stage_b, L.sh_gate_vec, static_cast<unsigned>(P.H) * 4u, &bars[kMaxBars - 1]);
         }
     }
     WD_STAMP(1);
@@ -247,10 +251,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         if (layer >= P.layer_begin + 2 && tid < ncta) wait_tag_reached(P.t_progress + tid, tag - 2u, err);
         for (int i = tid; i < P.H; i += kThreads) xf[i] = P.x[i];
     }
-    // the one CTA that computes the shared gate scalar brings the gate vector in with one round trip
-    float *gate_vec_s = reinterpret_cast<float *>(stage_b);
-    if (P.SF > 0 && cta == ncta / 2)
-        for (int i = tid; i < P.H; i += kThreads) gate_vec_s[i] = L.sh_gate_vec[i];
+    const float *gate_vec_s = reinterpret_cast<const float *>(stage_b);
     __syncthreads();
     quantize_q8_0_cta(xf, P.H, xq0, xd0);
     for (int sb = warp; sb < P.nsb_h; sb += kWarps)
