@@ -168,20 +168,17 @@ __global__ void synth_iq3s_kernel(uint8_t *dst, long long first_block, long long
 __global__ void test_router_kernel(const float *logits, int E, int K, float w_scale, int *ids, float *weights,
                                    float *probs) {
     // launched with kThreads threads
-    __shared__ float lg[kMaxExperts];
     __shared__ float pr[kMaxExperts];
     __shared__ float gsum[kMaxExperts / 8];
     __shared__ float red[kWarps];
-    __shared__ float topv[kMaxK];
-    __shared__ uint32_t champ[2 * kWarps * 2];
-    __shared__ double dsum[2];
+    __shared__ float first[1];
+    __shared__ uint32_t cand[2 * kWarps * kMaxK];
     __shared__ int sid[kMaxK];
     __shared__ float sw[kMaxK];
-    for (int i = threadIdx.x; i < E; i += blockDim.x) lg[i] = logits[i];
-    __syncthreads();
+    const int t = threadIdx.x;
     RouterScratch rs;
-    rs.probs = pr; rs.gsum = gsum; rs.red = red; rs.top = topv; rs.champ = champ; rs.dsum = dsum;
-    router_select_cta(lg, E, K, w_scale, rs, sid, sw);
+    rs.probs = pr; rs.gsum = gsum; rs.red = red; rs.first = first; rs.cand = cand;
+    router_select_cta(t < E ? logits[t] : 0.0f, t + kThreads < E ? logits[t + kThreads] : 0.0f, E, K, w_scale, rs, sid, sw);
     for (int j = threadIdx.x; j < K; j += blockDim.x) {
         ids[j] = sid[j];
         weights[j] = sw[j];

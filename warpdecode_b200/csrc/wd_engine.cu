@@ -127,9 +127,10 @@ int plan_shared_memory(wd_engine *e) {
     // a CTA takes every ncta-th entry of [tiles | shared-down tasks]: at most ceil(len / ncta) of each part
     p.n3 = (c.top_k * t3 + ncta - 1) / ncta;
     p.nsd = (n_sd + ncta - 1) / ncta;
-    if (p.n1r + p.n1s + p.n2 + p.n3 + p.nsd > wd::kMaxBars - 1)
+    if (p.n1r + p.n1s + p.n2 + p.n3 + p.nsd > wd::kMaxBars - 2)
         return fail(WD_E_INVALID, "geometry needs more staging slots per CTA than the kernel supports");
     p.off_bar = take(wd::kMaxBars * 8);
+    p.off_slots = take(static_cast<size_t>(c.n_experts) * 4);
     const size_t rt_bytes = static_cast<size_t>(nbh) * 136;
     // stage A: phase-1 tasks, then gate/up tile pairs, then the selected experts' activations as floats
     const size_t stage_a = std::max(std::max(static_cast<size_t>(p.n1r + p.n1s) * 2 * rt_bytes,
@@ -371,6 +372,7 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     p.nsb_h = e->nsb_h; p.nsb_f = e->nsb_f;
     p.e_first = e->e_first; p.e_count = e->e_count;
     p.w_scale = c.w_scale; p.eps = c.rms_eps > 0 ? c.rms_eps : 1e-6f;
+    p.inv_h = (H & (H - 1)) == 0 ? 1.0 / static_cast<double>(H) : 0.0;
     p.pool = e->pool; p.slot_bytes = e->slot_bytes;
     p.gate_off = 0; p.up_off = static_cast<unsigned>(e->gate_bytes); p.down_off = static_cast<unsigned>(2 * e->gate_bytes);
     p.grid_packed = e->grid_packed;

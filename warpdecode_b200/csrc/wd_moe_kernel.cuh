@@ -43,6 +43,7 @@ struct MoeParams {
     int t2_log2, t3_log2;        // log2 of the tiles per expert: gate/up (F*nsb_h/32) and down (H*nsb_f/32)
     int e_first, e_count;        // owned expert range
     float w_scale, eps;
+    double inv_h;                // 1 / H when H is a power of two (the division is then an exact multiply), else 0
     // layers [layer_begin, layer_end) run back to back inside one launch, so that after the first layer
     // every instruction comes from the instruction cache
     const LayerDev *layers;      // device array, one entry per layer of the stack
@@ -77,7 +78,7 @@ struct MoeParams {
                                  // last CTA to leave advances it by the layers run), [9] count of CTAs that left
     // shared memory plan (byte offsets from the dynamic shared base; all 128-byte aligned)
     unsigned off_tab, off_xq0, off_xd0, off_xk, off_xdk, off_actk, off_actd, off_shq, off_shd,
-        off_misc, off_scr, off_bar, off_stage_a, off_stage_b;
+        off_misc, off_scr, off_bar, off_slots, off_stage_a, off_stage_b;
     unsigned scr_bytes;          // per-warp transposition scratch
     unsigned scr_rows;           // float offset of the two 32-float row buffers inside it
     unsigned n1r, n1s, n2, n3, nsd;   // staging slots per CTA: router tasks, shared g/u tasks, phase-2 units,
@@ -104,6 +105,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     float *shd = reinterpret_cast<float *>(sm + P.off_shd);
     float *misc = reinterpret_cast<float *>(sm + P.off_misc);
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm + P.off_bar);
+    int *slot_tab = reinterpret_cast<int *>(sm + P.off_slots);      // this layer's slot of every expert
     uint8_t *stage_a = sm + P.off_stage_a;
     uint8_t *stage_b = sm + P.off_stage_b;
     unsigned *err = P.sync + 2;
@@ -130,7 +132,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                \
         P.stamps[cta * 16 + (i)] = t__;                                                        \
     }
-    if (tid < kMaxBars) {       // the last one belongs to the shared gate vector
+    if (tid < kMaxBars) {       // the last two belong to the shared gate vector and the slot table
         mbar_init(&bars[tid], 1);
         mbar_fence_init();
     }
@@ -176,6 +178,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
             bulk_load(stage_a + s * a1_slot, L.sh_gate + static_cast<size_t>(t) * rt_bytes, rt_bytes, &bars[s]);
             bulk_load(stage_a + s * a1_slot + rt_bytes, L.sh_up + static_cast<size_t>(t) * rt_bytes, rt_bytes, &bars[s]);
         }
+        mbar_expect_tx(&bars[kMaxBars - 2], static_cast<unsigned>(P.E) * 4u);
+        bulk_load(slot_tab, L.slot_of_expert, static_cast<unsigned>(P.E) * 4u, &bars[kMaxBars - 2]);
         // the one CTA that computes the shared gate scalar brings the F32 gate vector into stage B
         if (P.SF > 0 && cta == ncta / 2) {
             mbar_expect_tx(&bars[kMaxBars - 1], static_cast<unsigned>(P.H) * 4u);
@@ -236,7 +240,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
 #pragma unroll
             for (int i = 0; i + w < kWarps; i += 2 * w) tot[i] = __dadd_rn(tot[i], tot[i + w]);
         const float scale = __double2float_rn(
-            __ddiv_rn(1.0, __dsqrt_rn(__dadd_rn(__ddiv_rn(tot[0], static_cast<double>(P.H)), static_cast<double>(P.eps)))));
+            __ddiv_rn(1.0, __dsqrt_rn(__dadd_rn(P.inv_h != 0.0 ? __dmul_rn(tot[0], P.inv_h)
+                                                               : __ddiv_rn(tot[0], static_cast<double>(P.H)),
+                                                static_cast<double>(P.eps)))));
         if (tid * epl < P.H) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {

@@ -7,39 +7,47 @@ namespace wd {
 
 // ---------------------------------------------------------------------------------------------
 // router: softmax over all experts + top-k by the whole CTA (src/qwen38_moe.cuh:711-818).
-// Thread t owns experts t and t + kThreads (E <= 1024). Every float step is the reference's:
-// running max; exp_ggml(x - max); groups of eight summed in the AVX2 lane order; the group sums
-// accumulated ascending into a double by one thread; p * (float)(1 / sum); k rungs of "largest
-// remaining probability, ties to the lower index, NaN never, nothing above -inf gives id 0";
+// Thread t owns experts t and t + kThreads (E <= 1024) and receives their logits in registers. Every
+// float step is the reference's: running max; exp_ggml(x - max); groups of eight summed in the AVX2
+// lane order; the group sums accumulated ascending into a double; p * (float)(1 / sum); k rungs of
+// "largest remaining probability, ties to the lower index, NaN never, nothing above -inf gives id 0";
 // weights = picked / max((float)double_sum, 2^-14), times w_scale unless it is 0 or 1.
-// The rungs run as a tournament: each warp keeps its champion (key, index) in shared memory, all
-// warps read the 16 champions and agree on the winner with two redux steps, and only the winner's
-// warp recomputes its champion. One __syncthreads per rung.
-// Shared scratch: probs[E], gsum[E/8], champ[2][kWarps][2] u32, dsum[2] double, top[kMaxK].
+// The rungs run in two stages with one __syncthreads between them: every warp lists its own k best
+// (key, index) pairs in rung order with two redux steps per rung; warp 0 then merges the 16 sorted
+// lists, one head per lane. The order (larger key, then lower index) is total, so the merged rungs are
+// exactly the rungs over all experts.
+// Shared scratch: gsum[E/8], red[kWarps], cand[2][kWarps][kMaxK] u32, first[1];
+// probs[E] is optional (nullptr: not stored).
 // ---------------------------------------------------------------------------------------------
 struct RouterScratch {
-    float *probs;       // [E]
+    float *probs;       // [E] or nullptr
     float *gsum;        // [E/8]
-    uint32_t *champ;    // [2][kWarps][2]
-    double *dsum;       // [2]
+    uint32_t *cand;     // [2][kWarps][kMaxK]: keys, then indices
     float *red;         // [kWarps]
-    float *top;         // [kMaxK]
+    float *first;       // [1] probability of expert 0 (what a rung reports when nothing is selectable)
 };
 
-__device__ __noinline__ void router_select_cta(const float *logits, int E, int K, float w_scale,
-                                                  const RouterScratch &S, int *ids_out, float *w_out) {
+// inverse of order_key for keys above kKeyNegInf
+__device__ __forceinline__ float key_to_float(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
+}
+
+__device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K, float w_scale, const RouterScratch &S,
+                                                  int *ids_out, float *w_out) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int e0 = tid, e1 = tid + kThreads;
     const bool h0 = e0 < E, h1 = e1 < E;
-    const float l0 = h0 ? logits[e0] : -INFINITY, l1 = h1 ? logits[e1] : -INFINITY;
+    if (!h0) l0 = -INFINITY;
+    if (!h1) l1 = -INFINITY;
     float mx = fmaxf(l0, l1);
 #pragma unroll
     for (int s = 1; s < 32; s <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
     if (lane == 0) S.red[warp] = mx;
     __syncthreads();
-    mx = S.red[0];
+    mx = lane < kWarps ? S.red[lane] : -INFINITY;
 #pragma unroll
-    for (int w = 1; w < kWarps; ++w) mx = fmaxf(mx, S.red[w]);
+    for (int s = 1; s < kWarps; s <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+    mx = __shfl_sync(0xffffffffu, mx, 0);
     float p0 = h0 ? exp_ggml(__fsub_rn(l0, mx)) : 0.0f;
     float p1 = h1 ? exp_ggml(__fsub_rn(l1, mx)) : 0.0f;
     const float g0 = hsum8_lanes(p0), g1 = hsum8_lanes(p1);   // the reference's 8-lane tree
@@ -48,13 +56,14 @@ __device__ __noinline__ void router_select_cta(const float *logits, int E, int K
         if (h1) S.gsum[e1 >> 3] = g1;
     }
     __syncthreads();
-    if (warp == 0) {
+    {
         // The reference adds the group sums one by one, ascending, into a double. When every partial
         // sum is exactly representable the order cannot matter, and a shuffle tree gives the same bits:
         // all terms are non-negative multiples of the smallest term's last bit q, so any partial sum is
         // a multiple of q below the total; it is exact if total < 2^53 * q, i.e. if the exponent span
         // between the total and the smallest non-zero term (minus its 23 mantissa bits) stays under 53.
         // Otherwise (and for inf/nan/denormal terms) one lane replays the reference's order.
+        // Every warp computes the sum for itself: cheaper than one more block-wide hand-over.
         const int ng = E >> 3;
         double part = 0.0;
         int min_exp = 0x7fffffff, bad = 0;
@@ -75,69 +84,74 @@ __device__ __noinline__ void router_select_cta(const float *logits, int E, int K
         double sum = part;
         if (bad || (min_exp != 0x7fffffff && tot_exp + 1 - (min_exp - 23) > 52)) {
             sum = 0.0;
-            if (lane == 0)
-                for (int g = 0; g < ng; ++g) sum = __dadd_rn(sum, static_cast<double>(S.gsum[g]));
+            for (int g = 0; g < ng; ++g) sum = __dadd_rn(sum, static_cast<double>(S.gsum[g]));
         }
-        if (lane == 0) {
-            S.dsum[0] = sum;
-            S.dsum[1] = sum == 0.0 ? 0.0 : static_cast<double>(__double2float_rn(__ddiv_rn(1.0, sum)));
+        if (sum == 0.0) {
+            p0 = p1 = -INFINITY;
+        } else {
+            const float inv = __double2float_rn(__ddiv_rn(1.0, sum));
+            p0 = __fmul_rn(p0, inv);
+            p1 = __fmul_rn(p1, inv);
         }
     }
-    __syncthreads();
-    const double sum = S.dsum[0];
-    if (sum == 0.0) {
-        p0 = p1 = -INFINITY;
-    } else {
-        const float inv = static_cast<float>(S.dsum[1]);
-        p0 = __fmul_rn(p0, inv);
-        p1 = __fmul_rn(p1, inv);
+    if (S.probs) {
+        if (h0) S.probs[e0] = p0;
+        if (h1) S.probs[e1] = p1;
     }
-    if (h0) S.probs[e0] = p0;
-    if (h1) S.probs[e1] = p1;
+    if (tid == 0) *S.first = p0;
+    // stage 1: this warp's k best, in rung order
     uint32_t k0 = h0 ? order_key(p0) : 0u, k1 = h1 ? order_key(p1) : 0u;
-    bool dirty = true;
+    uint32_t *ck = S.cand, *ci = S.cand + kWarps * kMaxK;
     for (int j = 0; j < K; ++j) {
-        uint32_t *cw = S.champ + (j & 1) * kWarps * 2;
-        if (dirty) {
-            const uint32_t mine = max(k0, k1);
-            const uint32_t m = __reduce_max_sync(0xffffffffu, mine);
-            const uint32_t cand = (k0 == m) ? static_cast<uint32_t>(e0) : ((k1 == m) ? static_cast<uint32_t>(e1) : 0xffffffffu);
-            const uint32_t mi = __reduce_min_sync(0xffffffffu, cand);
-            if (lane == 0) {
-                cw[warp * 2] = m;
-                cw[warp * 2 + 1] = mi;
-            }
-            dirty = false;
-        } else if (lane == 0) {
-            const uint32_t *pw = S.champ + ((j & 1) ^ 1) * kWarps * 2;
-            cw[warp * 2] = pw[warp * 2];
-            cw[warp * 2 + 1] = pw[warp * 2 + 1];
+        const uint32_t m = __reduce_max_sync(0xffffffffu, max(k0, k1));
+        const uint32_t cand = (k0 == m) ? static_cast<uint32_t>(e0) : ((k1 == m) ? static_cast<uint32_t>(e1) : 0xffffffffu);
+        const uint32_t mi = __reduce_min_sync(0xffffffffu, cand);
+        if (lane == 0) {
+            ck[warp * kMaxK + j] = m;
+            ci[warp * kMaxK + j] = mi;
         }
-        __syncthreads();
-        const uint32_t cm = lane < kWarps ? cw[lane * 2] : 0u;
-        const uint32_t ci = lane < kWarps ? cw[lane * 2 + 1] : 0xffffffffu;
-        const uint32_t M = __reduce_max_sync(0xffffffffu, cm);
-        uint32_t win = __reduce_min_sync(0xffffffffu, cm == M ? ci : 0xffffffffu);
-        if (M <= kKeyNegInf) win = 0u;                 // nothing selectable: the rung keeps expert 0
-        else {
-            if (win == static_cast<uint32_t>(e0)) k0 = 0u;
-            if (win == static_cast<uint32_t>(e1)) k1 = 0u;
-            if (((win & (kThreads - 1)) >> 5) == static_cast<uint32_t>(warp)) dirty = true;
+        if (m <= kKeyNegInf) {          // nothing selectable is left in this warp: the rest of its list is empty
+            if (lane == 0)
+                for (int q = j + 1; q < K; ++q) ck[warp * kMaxK + q] = 0u;
+            break;
         }
-        if (tid == 0) {
-            ids_out[j] = static_cast<int>(win);
-            S.top[j] = S.probs[win];
-        }
+        if (mi == static_cast<uint32_t>(e0)) k0 = 0u;
+        if (mi == static_cast<uint32_t>(e1)) k1 = 0u;
     }
     __syncthreads();
-    if (tid == 0) {
-        double wsum = 0.0;
-        for (int j = 0; j < K; ++j) wsum = __dadd_rn(wsum, static_cast<double>(S.top[j]));
-        const float denom = fmaxf(__double2float_rn(wsum), 6.103515625e-5f);
+    // stage 2: warp 0 merges the lists; lane w holds the head of warp w's list
+    if (warp == 0) {
+        int ptr = 0;
+        uint32_t my_id = 0u;
+        float my_p = 0.0f;
+        const float p_first = *S.first;
         for (int j = 0; j < K; ++j) {
-            float w = __fdiv_rn(S.top[j], denom);
+            const bool live = lane < kWarps && ptr < K;
+            const uint32_t hk = live ? ck[lane * kMaxK + ptr] : 0u;
+            const uint32_t hi = live ? ci[lane * kMaxK + ptr] : 0xffffffffu;
+            const uint32_t M = __reduce_max_sync(0xffffffffu, hk);
+            uint32_t win = __reduce_min_sync(0xffffffffu, hk == M ? hi : 0xffffffffu);
+            float p;
+            if (M <= kKeyNegInf) {      // nothing selectable: the rung keeps expert 0
+                win = 0u;
+                p = p_first;
+            } else {
+                p = key_to_float(M);
+                if (static_cast<uint32_t>(lane) == ((win & (kThreads - 1)) >> 5)) ++ptr;
+            }
+            if (lane == j) {
+                my_id = win;
+                my_p = p;
+            }
+        }
+        double wsum = 0.0;
+        for (int j = 0; j < K; ++j) wsum = __dadd_rn(wsum, static_cast<double>(__shfl_sync(0xffffffffu, my_p, j)));
+        const float denom = fmaxf(__double2float_rn(wsum), 6.103515625e-5f);
+        if (lane < K) {
+            float w = __fdiv_rn(my_p, denom);
             if (w_scale != 0.0f && w_scale != 1.0f) w = __fmul_rn(w, w_scale);
-            w_out[j] = w;
+            ids_out[lane] = static_cast<int>(my_id);
+            w_out[lane] = w;
         }
     }
     __syncthreads();

@@ -14,8 +14,8 @@ import numpy as np
 import warpdecode_b200 as wd
 
 # stamp indices in the order the kernel passes them, and the name of the span that ends at each
-ORDER = [0, 1, 2, 3, 4, 12, 13, 5, 6, 11, 7, 9, 8, 10]
-PHASES = ["issue_p1", "x_wait_quant", "q8_rows", "gather_logits", "select.setup", "select.router", "select.rest",
+ORDER = [0, 1, 2, 3, 4, 13, 5, 6, 11, 7, 9, 8, 10]
+PHASES = ["issue_p1", "x_wait_quant", "q8_rows", "gather_logits", "select.router", "select.rest",
           "issue_tiles", "first_tile_wait", "gate_up", "gather_act_quant", "down", "combine"]
 
 
