@@ -117,7 +117,7 @@ int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, 
 int wd_moe_forward_host(wd_engine *e, int layer, const float *x_host, float *out_host, int n_tokens);
 /* One decode token through layers [0, n_layers) of the stack: per layer
  * x = RMSNorm(residual) * norm_weight, residual += moe(x). residual_dev is [hidden] F32,
- * updated in place. The whole token is one CUDA graph after the first call. */
+ * updated in place. The whole token is one kernel launch. */
 int wd_stack_step(wd_engine *e, float *residual_dev, void *stream);
 int wd_stack_step_host(wd_engine *e, const float *residual_in_host, float *residual_out_host);
 
@@ -159,6 +159,29 @@ int wd_quantize_q8_K_host(const float *x, int n, void *blocks);
  * engine uses. `partials`, if not NULL, receives the int32 sums [rows][cols/256][8] (IQ types). */
 int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, float *y,
                    int32_t *partials);
+/* ---- expert parallelism ------------------------------------------------------------------ */
+/* The reference runs on one GPU; its expert tables (src/expert_cache.cuh:2116-2146) shard by expert, and
+ * these calls add that. An engine created with ep_size > 1 holds and computes only the experts of its
+ * rank; the router and the shared expert are replicated, so every rank selects the same experts. Until
+ * it is connected, wd_moe_forward returns this rank's PARTIAL routed sum (+ shared expert). Once
+ * connected, the kernel of every rank stores the output rows of its selected experts straight into
+ * every peer's row buffer (value and layer tag in one 8-byte store over NVLink), and every rank performs
+ * the ordered combine over all top_k rows: results are bit-identical to one GPU for any ep_size.
+ * All ranks must then issue the same sequence of forward calls; a rank that waits about a second for
+ * a peer's rows gives up and raises device status bit 1.
+ * wd_ep_export writes wd_ep_handle_bytes() bytes that another PROCESS passes to wd_ep_connect
+ * (`handles` = the ep_size - 1 other ranks' handles back to back, any order); engines of one process
+ * on different devices use wd_ep_connect_local. Disconnect (or destroy) only while no rank is running. */
+int wd_ep_handle_bytes(void);
+int wd_ep_export(wd_engine *e, void *handle_out);
+int wd_ep_connect(wd_engine *e, int n_peers, const void *handles);
+int wd_ep_connect_local(wd_engine *e, int n_peers, wd_engine *const *peers);
+int wd_ep_disconnect(wd_engine *e);
+/* Clears the status word, the layer-tag epoch and every exchange word of this engine. After any rank of a
+ * connected group reported a non-zero device status, call this on EVERY rank (all idle) before the next
+ * forward: the ranks' tag epochs must agree. (wd_device_status does it for the reporting engine only.) */
+int wd_reset_exchange(wd_engine *e);
+
 /* Has no counterpart in the reference. y = W x for one IQ3_S matrix like wd_matvec_host, for callers
  * that must not allocate device memory (HBM already handed to the expert pool, a latency-critical
  * token loop where cudaMalloc's device-wide synchronisation is unacceptable, memory owned by another

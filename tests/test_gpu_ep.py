@@ -1,0 +1,122 @@
+"""Expert parallelism on two GPUs of one process: every rank must produce the single-GPU bits.
+
+Needs two CUDA devices with peer access; skipped otherwise. The ranks' kernels wait for one another's
+rows, so each step launches on both devices before anything synchronises.
+"""
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(a):
+    return ol.fbits(a)
+
+
+@pytest.fixture(scope="module")
+def wd():
+    import warpdecode_b200 as w
+    w.lib()
+    return w
+
+
+@pytest.fixture(scope="module")
+def torch2():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    return torch
+
+
+H, F, E, K, SF, L = 512, 256, 64, 6, 256, 3
+
+
+def _blocks_and_norms():
+    from warpdecode_b200 import synth
+    rng = np.random.Generator(np.random.PCG64(77))
+    ms = [synth.make_moe_block(300 + l, H, F, E, K, SF, bias_sigma=1.0) for l in range(L)]
+    norms = [(1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32) for _ in range(L)]
+    return ms, norms, rng
+
+
+def _engine(wd, ms, norms, rank, size, device):
+    eng = wd.Engine(H, F, E, K, SF, L, ep_rank=rank, ep_size=size, device=device)
+    for l in range(L):
+        eng.load_block(l, ms[l])
+        eng.set_norm(l, norms[l])
+    return eng
+
+
+def test_two_ranks_reproduce_one_gpu_bit_for_bit(wd, oracle, torch2):
+    torch = torch2
+    ms, norms, rng = _blocks_and_norms()
+    single = _engine(wd, ms, norms, 0, 1, 0)
+    ranks = [_engine(wd, ms, norms, r, 2, r) for r in range(2)]
+    ranks[0].ep_connect_local([ranks[1]])
+    ranks[1].ep_connect_local([ranks[0]])
+    res = rng.standard_normal(H).astype(np.float32)
+    dev = [torch.zeros(H, dtype=torch.float32, device=f"cuda:{r}") for r in range(2)]
+    for step in range(4):
+        want = single.stack_step_host(res)
+        ref = res.copy()
+        for l in range(L):
+            x = oracle.rmsnorm(ref, norms[l], 1e-6)
+            ref = (ref + oracle.moe_block(ms[l], x)["out"]).astype(np.float32)
+        assert np.array_equal(bits(want), bits(ref))
+        for r in range(2):
+            dev[r].copy_(torch.from_numpy(res))
+        torch.cuda.synchronize(0), torch.cuda.synchronize(1)
+        for r in range(2):
+            ranks[r].stack_step_device(dev[r].data_ptr())
+        torch.cuda.synchronize(0), torch.cuda.synchronize(1)
+        for r in range(2):
+            assert ranks[r].device_status() == 0
+            assert np.array_equal(bits(dev[r].cpu().numpy()), bits(want)), (step, r)
+            assert np.array_equal(ranks[r].tap("ids"), single.tap("ids"))
+            assert np.array_equal(bits(ranks[r].tap("expert_out")), bits(single.tap("expert_out")))
+        res = want
+    # the ranks really split the work: each holds half of the experts
+    assert ranks[0].slot_count() == L * E // 2
+    for e in ranks + [single]:
+        e.ep_disconnect()
+        e.close()
+
+
+def test_unconnected_ranks_return_partial_sums(wd, oracle, torch2):
+    ms, norms, rng = _blocks_and_norms()
+    single = _engine(wd, ms, norms, 0, 1, 0)
+    ranks = [_engine(wd, ms, norms, r, 2, r) for r in range(2)]
+    x = rng.standard_normal(H).astype(np.float32)
+    want = single.forward_host(0, x)
+    shared = single.tap("shared") * single.tap("shared_gate")[0]
+    parts = [ranks[r].forward_host(0, x) - shared for r in range(2)]      # routed partial of each rank
+    got = parts[0] + parts[1] + shared
+    assert np.allclose(got, want, rtol=1e-3, atol=1e-5)       # a different float order: the 1e-3 contract
+    for e in ranks + [single]:
+        e.close()
+
+
+def test_silent_peer_ends_in_a_status_not_a_hang(wd, torch2):
+    # rank 1 never launches: rank 0 waits about a second for its rows, then reports and returns
+    torch = torch2
+    ms, norms, rng = _blocks_and_norms()
+    ranks = [_engine(wd, ms, norms, r, 2, r) for r in range(2)]
+    ranks[0].ep_connect_local([ranks[1]])
+    ranks[1].ep_connect_local([ranks[0]])
+    x = torch.from_numpy(rng.standard_normal(H).astype(np.float32)).to("cuda:0")
+    ranks[0].stack_step_device(x.data_ptr())
+    torch.cuda.synchronize(0)
+    assert ranks[0].device_status() & 1
+    for e in ranks:
+        e.reset_exchange()
+    # and the group works again afterwards
+    dev = [torch.zeros(H, dtype=torch.float32, device=f"cuda:{r}") for r in range(2)]
+    for r in range(2):
+        ranks[r].stack_step_device(dev[r].data_ptr())
+    torch.cuda.synchronize(0), torch.cuda.synchronize(1)
+    assert ranks[0].device_status() == 0 and ranks[1].device_status() == 0
+    for e in ranks:
+        e.ep_disconnect()
+        e.close()

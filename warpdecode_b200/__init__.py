@@ -95,6 +95,11 @@ def lib():
         L.wd_synth_model.argtypes = [vp, C.c_uint64, C.c_float, C.c_float]
         L.wd_synth_expert_host.argtypes = [vp, C.c_uint64, C.c_float, i, i, vp, vp, vp]
         L.wd_synth_dense_host.argtypes = [vp, C.c_uint64, C.c_float, C.c_float, i, vp, vp, vp, vp, vp, vp]
+        L.wd_ep_export.argtypes = [vp, vp]
+        L.wd_ep_connect.argtypes = [vp, i, vp]
+        L.wd_ep_connect_local.argtypes = [vp, i, C.POINTER(vp)]
+        L.wd_ep_disconnect.argtypes = [vp]
+        L.wd_reset_exchange.argtypes = [vp]
         _lib = L
     return _lib
 
@@ -196,6 +201,29 @@ class Engine:
 
     def stack_step_device(self, residual_ptr, stream=None):
         _check(lib().wd_stack_step(self.h, residual_ptr, stream))
+
+    # expert parallelism (one engine per GPU, created with ep_rank / ep_size)
+    def ep_export(self):
+        """This engine's exchange-buffer handle, to be passed to the other ranks' ep_connect."""
+        buf = C.create_string_buffer(lib().wd_ep_handle_bytes())
+        _check(lib().wd_ep_export(self.h, buf))
+        return buf.raw
+
+    def ep_connect(self, handles):
+        """handles: the other ranks' ep_export() results (another process each)."""
+        blob = b"".join(handles)
+        _check(lib().wd_ep_connect(self.h, len(handles), C.c_char_p(blob) if handles else None))
+
+    def ep_connect_local(self, peers):
+        """peers: the other ranks' Engine objects of this process (different devices)."""
+        arr = (C.c_void_p * max(len(peers), 1))(*[p.h.value for p in peers])
+        _check(lib().wd_ep_connect_local(self.h, len(peers), arr))
+
+    def ep_disconnect(self):
+        _check(lib().wd_ep_disconnect(self.h))
+
+    def reset_exchange(self):
+        _check(lib().wd_reset_exchange(self.h))
 
     def device_status(self):
         st = C.c_int()

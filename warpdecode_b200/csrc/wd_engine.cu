@@ -77,6 +77,10 @@ struct wd_engine {
     wd::tagged_t *tagged = nullptr;
     size_t tagged_words = 0;
     int last_parity = 0;                    // half that holds the last launch's last layer (for the taps)
+    size_t tagged_eo_offset = 0;            // word offset of the expert-output buffer inside `tagged`
+    // expert-parallel peers
+    int n_peers = 0;
+    void *peer_mapped[8] = {};              // bases opened from IPC handles (closed on disconnect); null for local peers
     float *weights = nullptr, *routed = nullptr, *x_buf = nullptr, *out_buf = nullptr, *residual_buf = nullptr;
     int *ids = nullptr;
     uint8_t *staging = nullptr;       // device, ggml-layout upload buffer
@@ -85,9 +89,6 @@ struct wd_engine {
     size_t pinned_bytes = 0;
     wd::MoeParams base{};
     size_t smem_bytes = 0;
-    cudaGraphExec_t stack_graph = nullptr;
-    float *stack_graph_residual = nullptr;
-    cudaStream_t stack_graph_stream = nullptr;
 };
 
 namespace {
@@ -380,6 +381,7 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     p.t_logits = e->tagged + tw_logits; p.t_shared_act = e->tagged + tw_shact; p.t_shared_gate = e->tagged + tw_shgate;
     p.t_act = e->tagged + tw_act; p.t_expert_out = e->tagged + tw_eo; p.t_shared_down = e->tagged + tw_shdown;
     p.t_residual = e->tagged + tw_res; p.t_progress = e->tagged + tw_prog;
+    e->tagged_eo_offset = tw_eo;
     p.n_peers = 0;
     p.sync = e->sync;
     { int t2 = F * e->nsb_h / 32, t3 = H * e->nsb_f / 32; p.t2_log2 = 0; while ((1 << p.t2_log2) < t2) ++p.t2_log2; p.t3_log2 = 0; while ((1 << p.t3_log2) < t3) ++p.t3_log2; }
@@ -404,7 +406,7 @@ void wd_engine_destroy(wd_engine *e) {
     if (!e) return;
     cudaSetDevice(e->cfg.device);
     if (e->stream) cudaStreamSynchronize(e->stream);
-    if (e->stack_graph) cudaGraphExecDestroy(e->stack_graph);
+    wd_ep_disconnect(e);
     for (Layer &L : e->layers) {
         cudaFree(L.router); cudaFree(L.bias); cudaFree(L.gate_vec); cudaFree(L.sh_gate); cudaFree(L.sh_up);
         cudaFree(L.sh_down); cudaFree(L.norm); cudaFree(L.slot_of_expert);
@@ -694,6 +696,97 @@ int wd_set_profiling(wd_engine *e, int on) {
 }
 
 int wd_sm_count(const wd_engine *e) { return e ? e->n_sm : 0; }
+
+// ---- expert parallelism ----------------------------------------------------------------------------
+int wd_ep_handle_bytes(void) { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
+
+int wd_ep_export(wd_engine *e, void *handle_out) {
+    if (!e || !handle_out) return fail(WD_E_INVALID, "null argument");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    cudaIpcMemHandle_t h;
+    WD_CUDA(cudaIpcGetMemHandle(&h, e->tagged));
+    memcpy(handle_out, &h, sizeof(h));
+    return WD_OK;
+}
+
+namespace {
+int ep_check_connect(wd_engine *e, int n_peers) {
+    if (!e) return fail(WD_E_INVALID, "null engine");
+    if (n_peers != e->cfg.ep_size - 1) return fail(WD_E_INVALID, "expected ep_size - 1 peers");
+    if (n_peers > 7) return fail(WD_E_INVALID, "at most 8 expert-parallel ranks");
+    if (e->n_peers) return fail(WD_E_STATE, "already connected");
+    return WD_OK;
+}
+}  // namespace
+
+int wd_ep_connect(wd_engine *e, int n_peers, const void *handles) {
+    int rc = ep_check_connect(e, n_peers);
+    if (rc) return rc;
+    if (n_peers > 0 && !handles) return fail(WD_E_INVALID, "null handles");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    WD_CUDA(cudaDeviceSynchronize());
+    for (int p = 0; p < n_peers; ++p) {
+        cudaIpcMemHandle_t h;
+        memcpy(&h, static_cast<const uint8_t *>(handles) + static_cast<size_t>(p) * sizeof(h), sizeof(h));
+        void *base = nullptr;
+        cudaError_t ce = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+        if (ce != cudaSuccess) {
+            for (int q = 0; q < p; ++q) cudaIpcCloseMemHandle(e->peer_mapped[q]);
+            return fail(WD_E_CUDA, std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(ce));
+        }
+        e->peer_mapped[p] = base;
+        e->base.peer_expert_out[p] = static_cast<wd::tagged_t *>(base) + e->tagged_eo_offset;
+    }
+    e->n_peers = e->base.n_peers = n_peers;
+    return WD_OK;
+}
+
+int wd_ep_connect_local(wd_engine *e, int n_peers, wd_engine *const *peers) {
+    int rc = ep_check_connect(e, n_peers);
+    if (rc) return rc;
+    if (n_peers > 0 && !peers) return fail(WD_E_INVALID, "null peers");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    for (int p = 0; p < n_peers; ++p) {
+        const wd_engine *o = peers[p];
+        if (!o || o == e || o->tagged_words != e->tagged_words || o->cfg.ep_size != e->cfg.ep_size)
+            return fail(WD_E_INVALID, "peer engines must be distinct and share the geometry");
+        if (o->cfg.device != e->cfg.device) {
+            int can = 0;
+            WD_CUDA(cudaDeviceCanAccessPeer(&can, e->cfg.device, o->cfg.device));
+            if (!can) return fail(WD_E_STATE, "no peer access between the two devices");
+            cudaError_t ce = cudaDeviceEnablePeerAccess(o->cfg.device, 0);
+            if (ce == cudaErrorPeerAccessAlreadyEnabled) cudaGetLastError();
+            else if (ce != cudaSuccess) return fail(WD_E_CUDA, std::string("cudaDeviceEnablePeerAccess: ") + cudaGetErrorString(ce));
+        }
+        e->peer_mapped[p] = nullptr;
+        e->base.peer_expert_out[p] = o->tagged + o->tagged_eo_offset;
+    }
+    e->n_peers = e->base.n_peers = n_peers;
+    return WD_OK;
+}
+
+int wd_ep_disconnect(wd_engine *e) {
+    if (!e) return fail(WD_E_INVALID, "null engine");
+    if (!e->n_peers) return WD_OK;
+    cudaSetDevice(e->cfg.device);
+    cudaDeviceSynchronize();
+    for (int p = 0; p < e->n_peers; ++p) {
+        if (e->peer_mapped[p]) cudaIpcCloseMemHandle(e->peer_mapped[p]);
+        e->peer_mapped[p] = nullptr;
+        e->base.peer_expert_out[p] = nullptr;
+    }
+    e->n_peers = e->base.n_peers = 0;
+    return WD_OK;
+}
+
+int wd_reset_exchange(wd_engine *e) {
+    if (!e) return fail(WD_E_INVALID, "null engine");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    WD_CUDA(cudaDeviceSynchronize());
+    WD_CUDA(cudaMemset(e->sync, 0, 8192));
+    WD_CUDA(cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t)));
+    return WD_OK;
+}
 
 int wd_device_status(wd_engine *e, int *status) {
     if (!e || !status) return fail(WD_E_INVALID, "null argument");
