@@ -132,6 +132,7 @@ int plan_shared_memory(wd_engine *e) {
         return fail(WD_E_INVALID, "geometry needs more staging slots per CTA than the kernel supports");
     p.off_bar = take(wd::kMaxBars * 8);
     p.off_slots = take(static_cast<size_t>(c.n_experts) * 4);
+    p.off_rowbuf = take(static_cast<size_t>(2 * p.n2) * r_h * 4);
     const size_t rt_bytes = static_cast<size_t>(nbh) * 136;
     // stage A: phase-1 tasks, then gate/up tile pairs, then the selected experts' activations as floats
     const size_t stage_a = std::max(std::max(static_cast<size_t>(p.n1r + p.n1s) * 2 * rt_bytes,

@@ -102,16 +102,23 @@ __device__ __forceinline__ void iq3_subblock(const uint8_t *tile, const Iq3Head 
     }
 }
 
-// Full block against the 256 int8 activations at `a` (shared memory, 16-byte aligned).
-__device__ __forceinline__ void iq3_block_partials(const uint8_t *tile, int lane, const uint8_t *a, uint32_t lane4x2,
-                                                   const uint8_t *tab, int partial[8]) {
+// Sub-blocks [i0, i1) of one block against the 256 int8 activations at `a` (shared memory, 16-byte aligned).
+__device__ __forceinline__ void iq3_block_partials_range(const uint8_t *tile, int lane, const uint8_t *a,
+                                                         uint32_t lane4x2, const uint8_t *tab, int partial[8], int i0,
+                                                         int i1) {
     Iq3Head h;
     iq3_head(tile, lane, h);
 #pragma unroll
     for (int c = 0; c < 8; ++c) partial[c] = 0;
     const uint4 *av = reinterpret_cast<const uint4 *>(a);
 #pragma unroll 1
-    for (int i = 0; i < 8; ++i) iq3_subblock(tile, h, i, lane, av[2 * i], av[2 * i + 1], lane4x2, tab, partial);
+    for (int i = i0; i < i1; ++i) iq3_subblock(tile, h, i, lane, av[2 * i], av[2 * i + 1], lane4x2, tab, partial);
+}
+
+// Full block.
+__device__ __forceinline__ void iq3_block_partials(const uint8_t *tile, int lane, const uint8_t *a, uint32_t lane4x2,
+                                                   const uint8_t *tab, int partial[8]) {
+    iq3_block_partials_range(tile, lane, a, lane4x2, tab, partial, 0, 8);
 }
 
 }  // namespace wd

@@ -78,7 +78,7 @@ struct MoeParams {
                                  // last CTA to leave advances it by the layers run), [9] count of CTAs that left
     // shared memory plan (byte offsets from the dynamic shared base; all 128-byte aligned)
     unsigned off_tab, off_xq0, off_xd0, off_xk, off_xdk, off_actk, off_actd, off_shq, off_shd,
-        off_misc, off_scr, off_bar, off_slots, off_stage_a, off_stage_b;
+        off_misc, off_scr, off_bar, off_slots, off_rowbuf, off_stage_a, off_stage_b;
     unsigned scr_bytes;          // per-warp transposition scratch
     unsigned scr_rows;           // float offset of the two 32-float row buffers inside it
     unsigned n1r, n1s, n2, n3, nsd;   // staging slots per CTA: router tasks, shared g/u tasks, phase-2 units,
@@ -86,6 +86,7 @@ struct MoeParams {
 };
 
 // float offsets inside the `misc` region once phase 1 is over (before that it holds x as floats)
+constexpr int kLeftInts = 2048;     // = kMiscGsum: the x floats / router candidates region, reused in phase 2
 constexpr int kMiscLogits = 0, kMiscProbs = 1024, kMiscGsum = 2048, kMiscRed = 2176, kMiscTop = 2192,
               kMiscChamp = 2208, kMiscDsum = 2272, kMiscIds = 2288, kMiscW = 2304, kMiscLocJ = 2320,
               kMiscLocSlot = 2336, kMiscLocN = 2352, kMiscSlots = 2368, kMiscSharedAct = 2400;
@@ -106,6 +107,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     float *misc = reinterpret_cast<float *>(sm + P.off_misc);
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm + P.off_bar);
     int *slot_tab = reinterpret_cast<int *>(sm + P.off_slots);      // this layer's slot of every expert
+    float *rowbuf = reinterpret_cast<float *>(sm + P.off_rowbuf);    // row sums of this CTA's gate and up tiles
+    int *left_ints = reinterpret_cast<int *>(misc);                  // integer partials of sliced tile tasks: the
+                                                                     // first kLeftInts words of misc, free in phase 2
     uint8_t *stage_a = sm + P.off_stage_a;
     uint8_t *stage_b = sm + P.off_stage_b;
     unsigned *err = P.sync + 2;
