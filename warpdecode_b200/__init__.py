@@ -255,6 +255,17 @@ class Engine:
     def slot_bytes(self):
         return lib().wd_cache_slot_bytes(self.h)
 
+    def cache_acquire(self, layer, expert):
+        slot = C.c_int()
+        _check(lib().wd_cache_acquire(self.h, layer, expert, C.byref(slot)))
+        return slot.value
+
+    def cache_stats(self):
+        """(hits, misses, evictions) since creation."""
+        st = (C.c_int64 * 3)()
+        _check(lib().wd_cache_stats(self.h, st))
+        return tuple(st)
+
 
 # -- stand-alone pieces ------------------------------------------------------------------------
 def router_topk(logits, k, w_scale=1.0):

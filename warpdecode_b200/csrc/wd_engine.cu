@@ -3,11 +3,15 @@
 #include "../../include/warpdecode_b200.h"
 
 #include <algorithm>
+#include <condition_variable>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <functional>
 #include <list>
+#include <mutex>
 #include <string>
+#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -44,6 +48,62 @@ struct Layer {
     std::vector<int> h_slot;                    // host mirror
     const uint8_t *h_gate = nullptr, *h_up = nullptr, *h_down = nullptr;   // retained host tensors
     bool have_router = false, have_shared = false, have_experts = false;
+    bool host_pinned = false;                   // the retained host tensors are page-locked: no bounce copy
+};
+
+// A few host threads that copy missed experts from the caller's (pageable or mapped) tensors into the
+// pinned ring, several experts at a time. The counterpart of the reference's ExpertPreadPool
+// (src/expert_cache.cuh:357-508), minus the file offsets: the source here is memory.
+class CopyPool {
+public:
+    explicit CopyPool(int n) {
+        for (int i = 0; i < n; ++i) workers_.emplace_back([this] { run(); });
+    }
+    ~CopyPool() {
+        {
+            std::lock_guard<std::mutex> g(m_);
+            stop_ = true;
+        }
+        cv_.notify_all();
+        for (std::thread &t : workers_) t.join();
+    }
+    void submit(std::function<void()> f) {
+        {
+            std::lock_guard<std::mutex> g(m_);
+            tasks_.push_back(std::move(f));
+            ++pending_;
+        }
+        cv_.notify_one();
+    }
+    void wait_all() {
+        std::unique_lock<std::mutex> g(m_);
+        done_.wait(g, [this] { return pending_ == 0; });
+    }
+
+private:
+    void run() {
+        for (;;) {
+            std::function<void()> f;
+            {
+                std::unique_lock<std::mutex> g(m_);
+                cv_.wait(g, [this] { return stop_ || !tasks_.empty(); });
+                if (tasks_.empty()) return;
+                f = std::move(tasks_.front());
+                tasks_.pop_front();
+            }
+            f();
+            {
+                std::lock_guard<std::mutex> g(m_);
+                if (--pending_ == 0) done_.notify_all();
+            }
+        }
+    }
+    std::vector<std::thread> workers_;
+    std::list<std::function<void()>> tasks_;
+    std::mutex m_;
+    std::condition_variable cv_, done_;
+    int pending_ = 0;
+    bool stop_ = false;
 };
 
 }  // namespace
@@ -64,6 +124,12 @@ struct wd_engine {
     std::vector<std::list<int>::iterator> lru_pos;
     std::unordered_map<int64_t, int> key_slot;
     int64_t hits = 0, misses = 0, evictions = 0;
+    // miss path of a capped cache: pinned ring and device staging of top_k experts, a copy stream
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t fill_done = nullptr;
+    uint8_t *miss_pinned = nullptr, *miss_staging = nullptr;
+    int *pinned_ids = nullptr;
+    CopyPool *copy_pool = nullptr;
     // device scratch
     uint16_t *grid_packed = nullptr;
     uint16_t *synth_lut = nullptr;
@@ -209,7 +275,8 @@ int sync_layer_table(wd_engine *e, cudaStream_t s) {
 }
 
 // Layers [begin, end) in one cooperative launch.
-int launch_layers(wd_engine *e, int begin, int end, const float *x, float *residual, float *out, cudaStream_t s) {
+int launch_layers(wd_engine *e, int begin, int end, const float *x, float *residual, float *out, cudaStream_t s,
+                  bool select_only = false) {
     for (int l = begin; l < end; ++l) {
         const Layer &L = e->layers[l];
         if (!L.have_router || !L.have_experts || (e->cfg.shared_ffn > 0 && !L.have_shared))
@@ -226,6 +293,7 @@ int launch_layers(wd_engine *e, int begin, int end, const float *x, float *resid
     p.residual = residual;
     p.out = out;
     p.stamps = e->profiling ? e->stamps : nullptr;
+    p.select_only = select_only ? 1 : 0;
     void *args[] = {&p};
     WD_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(wd::moe_layer_kernel), dim3(e->n_sm),
                                         dim3(wd::kThreads), args, e->smem_bytes, s));
@@ -235,6 +303,96 @@ int launch_layers(wd_engine *e, int begin, int end, const float *x, float *resid
 
 int launch_layer(wd_engine *e, int layer, const float *x, float *residual, float *out, cudaStream_t s) {
     return launch_layers(e, layer, layer + 1, x, residual, out, s);
+}
+
+// Capped cache: one layer = a selection pass, the host's slot bookkeeping with the misses streamed in on
+// the copy stream, then the full layer (which repeats the selection bit for bit and finds every slot).
+// The flow of q38_moe_select_experts_f32_x + GpuExpertCache::acquire + ExpertStagePath
+// (src/qwen38_moe.cuh:2323-2380, src/expert_cache.cuh:2252, :1166-1273).
+int acquire_selected(wd_engine *e, int layer, cudaStream_t s) {
+    const wd_config &c = e->cfg;
+    Layer &L = e->layers[layer];
+    WD_CUDA(cudaMemcpyAsync(e->pinned_ids, e->ids, sizeof(int) * c.top_k, cudaMemcpyDeviceToHost, s));
+    WD_CUDA(cudaStreamSynchronize(s));
+    if (!L.h_gate) return fail(WD_E_STATE, "no host tensors to fill the slots from");
+    std::vector<int> owned;
+    for (int j = 0; j < c.top_k; ++j) {
+        const int x = e->pinned_ids[j];
+        if (x < 0 || x >= c.n_experts) return fail(WD_E_DEVICE, "the selection pass returned an expert id out of range");
+        if (x >= e->e_first && x < e->e_first + e->e_count && std::find(owned.begin(), owned.end(), x) == owned.end())
+            owned.push_back(x);
+    }
+    // hits first: they move to the front of the LRU list, so no victim below can be one of this layer's experts
+    std::vector<int> missing;
+    for (int x : owned) {
+        if (L.h_slot[x] >= 0) {
+            ++e->hits;
+            touch_slot(e, L.h_slot[x]);
+        } else {
+            missing.push_back(x);
+        }
+    }
+    if (missing.empty()) return WD_OK;
+    const size_t gb = e->gate_bytes, db = e->down_bytes, one = 2 * gb + db;
+    std::vector<int> changed_layers{layer};
+    std::vector<int> slots(missing.size());
+    for (size_t m = 0; m < missing.size(); ++m) {
+        const int x = missing[m], slot = e->lru.back();
+        ++e->misses;
+        const int64_t old = e->slot_key[slot];
+        if (old >= 0) {
+            const int ol = static_cast<int>(old >> 32);
+            e->layers[ol].h_slot[static_cast<int>(old & 0xffffffff)] = -1;
+            e->key_slot.erase(old);
+            ++e->evictions;
+            if (std::find(changed_layers.begin(), changed_layers.end(), ol) == changed_layers.end()) changed_layers.push_back(ol);
+        }
+        const int64_t key = (static_cast<int64_t>(layer) << 32) | static_cast<uint32_t>(x);
+        e->slot_key[slot] = key;
+        e->key_slot[key] = slot;
+        L.h_slot[x] = slot;
+        touch_slot(e, slot);
+        slots[m] = slot;
+        if (!L.host_pinned) {
+            uint8_t *pin = e->miss_pinned + m * one;
+            const uint8_t *g = L.h_gate + static_cast<size_t>(x) * gb, *u = L.h_up + static_cast<size_t>(x) * gb,
+                          *d = L.h_down + static_cast<size_t>(x) * db;
+            e->copy_pool->submit([=] {
+                memcpy(pin, g, gb);
+                memcpy(pin + gb, u, gb);
+                memcpy(pin + 2 * gb, d, db);
+            });
+        }
+    }
+    if (!L.host_pinned) e->copy_pool->wait_all();
+    cudaStream_t cs = e->copy_stream;
+    for (size_t m = 0; m < missing.size(); ++m) {
+        uint8_t *st = e->miss_staging + m * one;
+        if (L.host_pinned) {
+            const int x = missing[m];
+            WD_CUDA(cudaMemcpyAsync(st, L.h_gate + static_cast<size_t>(x) * gb, gb, cudaMemcpyHostToDevice, cs));
+            WD_CUDA(cudaMemcpyAsync(st + gb, L.h_up + static_cast<size_t>(x) * gb, gb, cudaMemcpyHostToDevice, cs));
+            WD_CUDA(cudaMemcpyAsync(st + 2 * gb, L.h_down + static_cast<size_t>(x) * db, db, cudaMemcpyHostToDevice, cs));
+        } else {
+            WD_CUDA(cudaMemcpyAsync(st, e->miss_pinned + m * one, one, cudaMemcpyHostToDevice, cs));
+        }
+        int rc = repack_expert_into_slot(e, st, st + gb, st + 2 * gb, slots[m], cs);
+        if (rc) return rc;
+    }
+    for (int l : changed_layers) {
+        Layer &C = e->layers[l];      // pageable source: the runtime stages it before the call returns
+        WD_CUDA(cudaMemcpyAsync(C.slot_of_expert, C.h_slot.data(), C.h_slot.size() * sizeof(int), cudaMemcpyHostToDevice, cs));
+    }
+    WD_CUDA(cudaEventRecord(e->fill_done, cs));
+    WD_CUDA(cudaStreamWaitEvent(s, e->fill_done, 0));
+    return WD_OK;
+}
+
+int forward_capped(wd_engine *e, int layer, const float *x, float *residual, float *out, cudaStream_t s) {
+    int rc = launch_layers(e, layer, layer + 1, x, residual, out, s, true);
+    if (rc) return rc;
+    if ((rc = acquire_selected(e, layer, s))) return rc;
+    return launch_layers(e, layer, layer + 1, x, residual, out, s, false);
 }
 
 int check_device_status(wd_engine *e) {
@@ -367,6 +525,14 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     WD_TRY(cudaMalloc(&e->staging, e->staging_bytes));
     e->pinned_bytes = align_up(std::max<size_t>(one_expert, static_cast<size_t>(H) * 8), 256);
     WD_TRY(cudaMallocHost(&e->pinned, e->pinned_bytes));
+    if (!e->resident) {
+        WD_TRY(cudaStreamCreateWithFlags(&e->copy_stream, cudaStreamNonBlocking));
+        WD_TRY(cudaEventCreateWithFlags(&e->fill_done, cudaEventDisableTiming));
+        WD_TRY(cudaMallocHost(&e->miss_pinned, one_expert * K));
+        WD_TRY(cudaMalloc(&e->miss_staging, one_expert * K));
+        WD_TRY(cudaMallocHost(&e->pinned_ids, sizeof(int) * K));
+        e->copy_pool = new CopyPool(std::max(1, std::min(8, static_cast<int>(std::thread::hardware_concurrency()))));
+    }
 #undef WD_TRY
 
     wd::MoeParams &p = e->base;
@@ -415,6 +581,12 @@ void wd_engine_destroy(wd_engine *e) {
     void *bufs[] = {e->pool, e->grid_packed, e->synth_lut, e->sync, e->tagged, e->ids, e->weights, e->routed,
                     e->x_buf, e->out_buf, e->residual_buf, e->staging, e->stamps, e->layer_table};
     for (void *b : bufs) cudaFree(b);
+    delete e->copy_pool;
+    cudaFree(e->miss_staging);
+    if (e->miss_pinned) cudaFreeHost(e->miss_pinned);
+    if (e->pinned_ids) cudaFreeHost(e->pinned_ids);
+    if (e->fill_done) cudaEventDestroy(e->fill_done);
+    if (e->copy_stream) cudaStreamDestroy(e->copy_stream);
     if (e->pinned) cudaFreeHost(e->pinned);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
@@ -512,6 +684,14 @@ int wd_set_experts(wd_engine *e, int layer, const void *gate, const void *up, co
     L.h_up = static_cast<const uint8_t *>(up);
     L.h_down = static_cast<const uint8_t *>(down);
     L.have_experts = true;
+    {
+        cudaPointerAttributes at{};
+        L.host_pinned = true;
+        for (const void *q : {gate, up, down}) {
+            if (cudaPointerGetAttributes(&at, q) != cudaSuccess || at.type != cudaMemoryTypeHost) L.host_pinned = false;
+        }
+        cudaGetLastError();
+    }
     if (e->resident) {
         for (int x = 0; x < e->e_count; ++x) {
             const int expert = e->e_first + x;
@@ -598,9 +778,9 @@ int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, 
     if (rc) return rc;
     if (n_tokens != 1) return fail(WD_E_INVALID, "n_tokens must be 1 in this build");
     if (!x_dev || !out_dev) return fail(WD_E_INVALID, "null buffer");
-    if (!e->resident) return fail(WD_E_STATE, "a capped expert cache is not supported by this build");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
+    if (!e->resident) return forward_capped(e, layer, x_dev, nullptr, out_dev, s);
     return launch_layer(e, layer, x_dev, nullptr, out_dev, s);
 }
 
@@ -622,9 +802,15 @@ int wd_moe_forward_host(wd_engine *e, int layer, const float *x_host, float *out
 
 int wd_stack_step(wd_engine *e, float *residual_dev, void *stream) {
     if (!e || !residual_dev) return fail(WD_E_INVALID, "null argument");
-    if (!e->resident) return fail(WD_E_STATE, "a capped expert cache is not supported by this build");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
+    if (!e->resident) {     // layer by layer: the host places the selected experts between the two passes
+        for (int l = 0; l < e->cfg.n_layers; ++l) {
+            int rc = forward_capped(e, l, nullptr, residual_dev, e->out_buf, s);
+            if (rc) return rc;
+        }
+        return WD_OK;
+    }
     return launch_layers(e, 0, e->cfg.n_layers, nullptr, residual_dev, e->out_buf, s);
 }
 

@@ -49,6 +49,7 @@ struct MoeParams {
     const LayerDev *layers;      // device array, one entry per layer of the stack
     int layer_begin, layer_end;
     int stamp_layer;             // the layer whose phase timestamps are recorded
+    int select_only;             // 1: stop after the selection (ids and weights written); nothing else changes
     const uint8_t *pool;         // slot pool base
     unsigned long long slot_bytes;
     unsigned gate_off, up_off, down_off;        // offsets of the three matrices inside a slot
@@ -121,7 +122,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     const int nbh = P.H >> 5, nbs = P.SF >> 5;
     const uint32_t lane4x2 = static_cast<uint32_t>(lane * 4) * 0x0101u;
     float *scr = reinterpret_cast<float *>(sm + P.off_scr + warp * P.scr_bytes);
-    float *rows_a = scr + P.scr_rows, *rows_b = rows_a + 32;       // per-warp row results of a tile
+    float *rows_a = scr + P.scr_rows;                               // per-warp row results of a tile
 
     float *xf = misc;                                               // [H], phases 0 and 1 only
     int *sel_ids = reinterpret_cast<int *>(misc + kMiscIds);
