@@ -30,6 +30,10 @@ CFG = dict(hidden=2048, expert_ffn=512, n_experts=512, top_k=10, shared_ffn=512,
 SEED, SIGMA = 3, 0.02
 EXPERT_BYTES = 3 * 450560
 LAYER_BYTES = 10 * EXPERT_BYTES + 3 * 1114112 + 8192 + 1114112     # routed + shared + gate vec + router
+# dram__bytes_read + dram__bytes_write of moe_layer_kernel per layer, from an ncu capture of a two-layer
+# launch of the same shape (36.18 MB + 0.09 MB for two layers); every layer reads its own weights once,
+# so a launch of n layers moves n times this.
+TRAFFIC_PER_LAYER = 18_137_000
 METRIC = "batch-1 decode tok/s (48L 512-expert IQ3_S MoE)"
 WORKLOAD = ("cfg2 MoE stack: 48 layers x (router top-10 of 512 IQ3_S experts + Q8_0 shared expert), "
             "hidden 2048, all experts resident; per token x=RMSNorm(residual), residual+=moe(x); "
@@ -241,7 +245,7 @@ def main():
                 "d2h_bytes_per_step": H * 4},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "kernel": "moe_layer_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None,
+                     "frac": achieved / peak, "traffic": TRAFFIC_PER_LAYER * args.layers if world == 1 else None,
                      "peak_source": "measured" if peaks else "fallback",
                      "bytes_per_launch": token_bytes, "us_per_launch": launch_s * 1e6,
                      "us_per_layer": launch_s * 1e6 / args.layers},
