@@ -167,10 +167,7 @@ def main():
     torch.cuda.synchronize()
     gen_s = time.perf_counter() - t0
     if world > 1:
-        handles = [None] * world
-        dist.all_gather_object(handles, eng.ep_export())
-        eng.ep_connect([h for r, h in enumerate(handles) if r != rank])
-        dist.barrier()
+        wd.ep_connect_all(eng, dist, rank, world)
     stream = torch.cuda.Stream()
     sp = stream.cuda_stream
     g = torch.Generator(device="cpu").manual_seed(SEED)

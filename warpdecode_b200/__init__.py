@@ -267,6 +267,25 @@ class Engine:
         return tuple(st)
 
 
+# -- expert-parallel host helpers --------------------------------------------------------------
+def ep_range(n_experts, rank, size):
+    """Experts [first, first + count) that rank `rank` of `size` owns (contiguous, equal shares)."""
+    if size < 1 or not 0 <= rank < size or n_experts % size:
+        raise ValueError("ep_rank/ep_size must partition n_experts evenly")
+    count = n_experts // size
+    return rank * count, count
+
+
+def ep_connect_all(engine, dist, rank, world):
+    """Exchanges the ranks' exchange-buffer handles over an initialised torch.distributed group (any
+    backend) and connects `engine` to every other rank. Collective: every rank must call it."""
+    handles = [None] * world
+    dist.all_gather_object(handles, engine.ep_export())
+    engine.ep_connect([h for r, h in enumerate(handles) if r != rank])
+    dist.barrier()
+    return handles
+
+
 # -- stand-alone pieces ------------------------------------------------------------------------
 def router_topk(logits, k, w_scale=1.0):
     logits = np.ascontiguousarray(logits, np.float32)
