@@ -182,6 +182,19 @@ int wd_ep_disconnect(wd_engine *e);
  * forward: the ranks' tag epochs must agree. (wd_device_status does it for the reporting engine only.) */
 int wd_reset_exchange(wd_engine *e);
 
+/* ---- dense Q4_0 matvec (the plain decoder path) ------------------------------------------ */
+/* y = W x for a Q4_0 matrix [rows][cols] against the Q8_0-quantised activation, the operator of
+ * q4_0_q8_0_gemv_kernel + q8_0_quantize_half_kernel (src/warodecode.cu:1535-1562, :1504). The matrix is
+ * packed once (planarize_q4, src/warodecode.cu:1027-1098, here: 32-row tiles, 16-byte quants then f16
+ * scales; 18 bytes per 32 weights) from ggml blocks on the host or on the device; the returned device
+ * pointer belongs to the caller until wd_dense_free. x_dev [cols] and y_dev [rows] are F32 device buffers;
+ * the call enqueues one kernel on `stream`. rows % 32 == 0, cols % 256 == 0, cols <= 32768.
+ * Float order: ggml's ggml_vec_dot_q4_0_q8_0 (eight lanes, one fmaf per block, 8-lane tree). */
+int wd_dense_pack_q4_0(const void *w_ggml_host, int rows, int cols, void **packed_dev);
+int wd_dense_pack_q4_0_device(const void *w_ggml_dev, int rows, int cols, void **packed_dev, void *stream);
+int wd_dense_matvec_q4_0(const void *packed_dev, int rows, int cols, const float *x_dev, float *y_dev, void *stream);
+int wd_dense_free(void *packed_dev);
+
 /* Has no counterpart in the reference. y = W x for one IQ3_S matrix like wd_matvec_host, for callers
  * that must not allocate device memory (HBM already handed to the expert pool, a latency-critical
  * token loop where cudaMalloc's device-wide synchronisation is unacceptable, memory owned by another

@@ -286,22 +286,31 @@ float wdo_row_iq4_nl_q8_0(const uint8_t *w_row, const uint8_t *y, int cols) {
 
 /* Q4_0 weights x Q8_0 activation for the dense matvec (src/warodecode.cu:1535-1562
  * computes (q - 8) * d against Q8_0 activations; that kernel carries no exact
- * float order, so this oracle fixes one: a single fmaf per block, blocks ascending). */
+ * float order and the reference has no host twin, so this oracle takes ggml's:
+ * ggml_vec_dot_q4_0_q8_0 (AVX2) unpacks the low nibbles of the 16 bytes to values
+ * 0..15 and the high nibbles to values 16..31, sums four consecutive products per
+ * lane, and does one fmaf(d_w * d_x, (float)p_lane, acc_lane) per block for the
+ * eight lanes, blocks ascending, then the same 8-lane tree as the Q8_0 row.
+ * Parity unpinned for this function: no golden vector of the reference covers it. */
 float wdo_row_q4_0_q8_0(const uint8_t *w_row, const uint8_t *y, int cols) {
     const int nb = cols / 32;
-    float acc = 0.0f;
+    float lane[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     for (int b = 0; b < nb; ++b) {
         const uint8_t *wb = w_row + (size_t)b * WDO_Q4_0_BYTES;
         const uint8_t *yb = y + (size_t)b * WDO_Q8_0_BYTES;
         const int8_t *yq = (const int8_t *)(yb + 2);
-        int32_t p = 0;
-        for (int j = 0; j < 16; ++j) {
-            p += ((int)(wb[2 + j] & 15) - 8) * (int)yq[j];
-            p += ((int)(wb[2 + j] >> 4) - 8) * (int)yq[j + 16];
+        const float d = half_at(wb) * half_at(yb);
+        for (int l = 0; l < 8; ++l) {
+            int32_t p = 0;
+            for (int j = 0; j < 4; ++j) {
+                const int v = 4 * l + j;        /* value index inside the block */
+                const int q = v < 16 ? (wb[2 + v] & 15) : (wb[2 + v - 16] >> 4);
+                p += (q - 8) * (int)yq[v];
+            }
+            lane[l] = fmaf(d, (float)p, lane[l]);
         }
-        acc = fmaf(half_at(wb) * half_at(yb), (float)p, acc);
     }
-    return acc;
+    return hsum8(lane);
 }
 
 /* ------------------------------------------------------------------------- */

@@ -16,7 +16,7 @@ ROOT = os.path.dirname(HERE)
 LIB_PATH = os.path.join(HERE, "libwarpdecode_b200.so")
 SOURCES = [os.path.join(HERE, "csrc", f) for f in
            ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_moe_kernel_phases.inc", "wd_blocks.cuh", "wd_router.cuh",
-            "wd_formats.cuh", "wd_device.cuh",
+            "wd_formats.cuh", "wd_device.cuh", "wd_dense.cuh",
             "wd_grids.h")] + [os.path.join(ROOT, "include", "warpdecode_b200.h")]
 
 TYPE_F32, TYPE_Q4_0, TYPE_Q8_0, TYPE_IQ3_S, TYPE_IQ2_S = 0, 2, 8, 21, 22
@@ -100,6 +100,10 @@ def lib():
         L.wd_ep_connect_local.argtypes = [vp, i, C.POINTER(vp)]
         L.wd_ep_disconnect.argtypes = [vp]
         L.wd_reset_exchange.argtypes = [vp]
+        L.wd_dense_pack_q4_0.argtypes = [vp, i, i, C.POINTER(vp)]
+        L.wd_dense_pack_q4_0_device.argtypes = [vp, i, i, C.POINTER(vp), vp]
+        L.wd_dense_matvec_q4_0.argtypes = [vp, i, i, vp, vp, vp]
+        L.wd_dense_free.argtypes = [vp]
         _lib = L
     return _lib
 
@@ -284,6 +288,34 @@ def ep_connect_all(engine, dist, rank, world):
     engine.ep_connect([h for r, h in enumerate(handles) if r != rank])
     dist.barrier()
     return handles
+
+
+# -- dense Q4_0 matvec -------------------------------------------------------------------------
+class DenseQ4_0:
+    """A Q4_0 matrix [rows][cols] packed on the device (wd_dense_pack_q4_0*); y = W x on device buffers."""
+
+    def __init__(self, rows, cols, ggml_host=None, ggml_dev_ptr=None, stream=None):
+        self.rows, self.cols, self.p = rows, cols, C.c_void_p()
+        if ggml_host is not None:
+            w = np.ascontiguousarray(ggml_host, np.uint8)
+            assert w.size == rows * (cols // 32) * 18
+            _check(lib().wd_dense_pack_q4_0(_ptr(w), rows, cols, C.byref(self.p)))
+        else:
+            _check(lib().wd_dense_pack_q4_0_device(ggml_dev_ptr, rows, cols, C.byref(self.p), stream))
+
+    def matvec(self, x_ptr, y_ptr, stream=None):
+        _check(lib().wd_dense_matvec_q4_0(self.p, self.rows, self.cols, x_ptr, y_ptr, stream))
+
+    def close(self):
+        if self.p:
+            lib().wd_dense_free(self.p)
+            self.p = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 # -- stand-alone pieces ------------------------------------------------------------------------

@@ -16,6 +16,7 @@
 #include <vector>
 
 #include "wd_aux_kernels.cuh"
+#include "wd_dense.cuh"
 #include "wd_grids.h"
 
 namespace {
@@ -1082,10 +1083,108 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
         WD_CUDA(cudaGetLastError());
         WD_CUDA(cudaDeviceSynchronize());
         WD_CUDA(cudaMemcpy(y, d_y, rows * 4, cudaMemcpyDeviceToHost));
+    } else if (type == WD_TYPE_Q4_0) {
+        void *packed = nullptr;
+        int rc = wd_dense_pack_q4_0(w, rows, cols, &packed);
+        if (rc) return rc;
+        WD_CUDA(cudaMalloc(&d_x, cols * 4));
+        WD_CUDA(cudaMalloc(&d_y, rows * 4));
+        WD_CUDA(cudaMemcpy(d_x, x, cols * 4, cudaMemcpyHostToDevice));
+        rc = wd_dense_matvec_q4_0(packed, rows, cols, d_x, d_y, nullptr);
+        if (rc == WD_OK) {
+            WD_CUDA(cudaDeviceSynchronize());
+            WD_CUDA(cudaMemcpy(y, d_y, rows * 4, cudaMemcpyDeviceToHost));
+        }
+        wd_dense_free(packed);
+        if (rc) {
+            cudaFree(d_x); cudaFree(d_y);
+            return rc;
+        }
     } else {
-        return fail(WD_E_INVALID, "matvec supports IQ3_S and Q8_0");
+        return fail(WD_E_INVALID, "matvec supports IQ3_S, Q8_0 and Q4_0");
     }
     cudaFree(d_x); cudaFree(d_y); cudaFree(d_src); cudaFree(d_dst); cudaFree(d_p); cudaFree(d_grid);
+    return WD_OK;
+}
+
+// ---- dense Q4_0 path ---------------------------------------------------------------------------------
+static int dense_check(int rows, int cols) {
+    if (rows <= 0 || cols <= 0 || rows % 32 || cols % (32 * wd::kDenseUnroll) || cols > 32768)
+        return fail(WD_E_INVALID, "Q4_0 matvec: rows must be a multiple of 32, cols a multiple of 256 up to 32768");
+    return WD_OK;
+}
+
+int wd_dense_pack_q4_0_device(const void *w_ggml_dev, int rows, int cols, void **packed_dev, void *stream) {
+    if (!w_ggml_dev || !packed_dev) return fail(WD_E_INVALID, "null argument");
+    int rc = dense_check(rows, cols);
+    if (rc) return rc;
+    const int nb = cols / 32;
+    uint8_t *dst = nullptr;
+    WD_CUDA(cudaMalloc(&dst, static_cast<size_t>(rows) * nb * 18));
+    const long long n = static_cast<long long>(rows) * nb;
+    wd::repack_q4_0_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t *>(w_ggml_dev), dst, rows, nb);
+    cudaError_t ce = cudaGetLastError();
+    if (ce != cudaSuccess) {
+        cudaFree(dst);
+        return fail(WD_E_CUDA, std::string("repack_q4_0_kernel: ") + cudaGetErrorString(ce));
+    }
+    *packed_dev = dst;
+    return WD_OK;
+}
+
+int wd_dense_pack_q4_0(const void *w_ggml_host, int rows, int cols, void **packed_dev) {
+    if (!w_ggml_host || !packed_dev) return fail(WD_E_INVALID, "null argument");
+    int rc = dense_check(rows, cols);
+    if (rc) return rc;
+    const size_t bytes = static_cast<size_t>(rows) * (cols / 32) * 18;
+    uint8_t *src = nullptr;
+    WD_CUDA(cudaMalloc(&src, bytes));
+    cudaError_t ce = cudaMemcpy(src, w_ggml_host, bytes, cudaMemcpyHostToDevice);
+    if (ce == cudaSuccess) {
+        rc = wd_dense_pack_q4_0_device(src, rows, cols, packed_dev, nullptr);
+        cudaDeviceSynchronize();
+    }
+    cudaFree(src);
+    if (ce != cudaSuccess) return fail(WD_E_CUDA, std::string("cudaMemcpy: ") + cudaGetErrorString(ce));
+    return rc;
+}
+
+int wd_dense_free(void *packed_dev) {
+    if (packed_dev) cudaFree(packed_dev);
+    return WD_OK;
+}
+
+int wd_dense_matvec_q4_0(const void *packed_dev, int rows, int cols, const float *x_dev, float *y_dev, void *stream) {
+    if (!packed_dev || !x_dev || !y_dev) return fail(WD_E_INVALID, "null argument");
+    int rc = dense_check(rows, cols);
+    if (rc) return rc;
+    const int nb = cols / 32;
+    const size_t smem = static_cast<size_t>(cols) + static_cast<size_t>(nb) * 4;
+    const size_t smem_tile = ((static_cast<size_t>(nb) * 36 + 15) & ~static_cast<size_t>(15)) + wd::kDenseSegSmem;
+    static bool attr_set = false;
+    if (!attr_set) {
+        WD_CUDA(cudaFuncSetAttribute(wd::q4_0_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 40 * 1024));
+        WD_CUDA(cudaFuncSetAttribute(wd::q4_0_gemv_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        attr_set = true;
+    }
+    int dev = 0, n_sm = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    const int warps = wd::kDenseThreads / 32;
+    const int tiles = rows / 32;
+    if (tiles <= n_sm * 4) {        // few rows: one CTA per tile, blocks of a row spread over the CTA's warps
+        wd::q4_0_gemv_tile_kernel<<<tiles, wd::kDenseThreads, smem_tile, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint8_t *>(packed_dev), rows, nb, x_dev, y_dev);
+        WD_CUDA(cudaGetLastError());
+        return WD_OK;
+    }
+    // one tile per warp while every CTA can be resident at once (8 per SM); beyond that, whole waves
+    int grid = (tiles + warps - 1) / warps;
+    if (grid > n_sm * 8) grid = n_sm * 8;
+    wd::q4_0_gemv_kernel<<<grid, wd::kDenseThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t *>(packed_dev), rows, nb, x_dev, y_dev);
+    WD_CUDA(cudaGetLastError());
     return WD_OK;
 }
 
