@@ -109,8 +109,10 @@ int wd_cache_stats(const wd_engine *e, int64_t stats[3]);
 /* One MoE block on device buffers: x [n_tokens][hidden] F32 -> out [n_tokens][hidden] F32
  * (router select, selected experts, ordered weighted combine, shared expert, finish).
  * Replaces run_qwen38_routed_moe_separate_f32_x + run_qwen38_shared_expert_f32_x +
- * q38_finish_moe_f32 (src/qwen38_moe.cuh:3761, :3963, :2442). Enqueues on `stream` and
- * returns without synchronising when every selected expert can be resident. */
+ * q38_finish_moe_f32 (src/qwen38_moe.cuh:3761, :3963, :2442) and, for n_tokens in 2..max_tokens,
+ * Qwen38MoeTokenBatch::run (:2955): pair (t, j) = expert ids[t][j] on the activation of token t, each
+ * token combined in its own rank order. Enqueues on `stream` and returns without synchronising when
+ * every selected expert is resident; with a capped cache it synchronises once per token. */
 int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, int n_tokens,
                    void *stream);
 /* Same through HOST buffers: copies x in, runs the block, copies out back, synchronises. */
@@ -133,6 +135,8 @@ int wd_stack_step_host(wd_engine *e, const float *residual_in_host, float *resid
 #define WD_TAP_SHARED_ACT 8   /* F32 [shared_ffn] */
 #define WD_TAP_STAMPS 9       /* U64 [sm_count][16] phase timestamps (ns), see wd_set_profiling */
 /* Copies a tap of the most recent forward of token `token` to host memory (synchronises).
+ * token = -1 means the last token of that call. After a batch of several tokens, ids and weights
+ * are kept for every token; the other taps show the last token only (earlier ones: WD_E_STATE).
  * The post-conditions the reference's callers read from Qwen38MoeScratch
  * (d_logits/h_ids/h_weights/d_accum/down_f32/d_shared_gate, src/qwen38_moe.cuh:1804-1830). */
 int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes);

@@ -125,9 +125,9 @@ class Engine:
     """One MoE stack on one GPU (wd_engine)."""
 
     def __init__(self, hidden, expert_ffn, n_experts, top_k, shared_ffn=0, n_layers=1, expert_type=TYPE_IQ3_S,
-                 w_scale=1.0, ep_rank=0, ep_size=1, device=0, cache_mib=0, rms_eps=1e-6):
+                 w_scale=1.0, ep_rank=0, ep_size=1, device=0, cache_mib=0, rms_eps=1e-6, max_tokens=1):
         self.cfg = Config(hidden, expert_ffn, shared_ffn, n_experts, top_k, n_layers, expert_type, expert_type,
-                          expert_type, w_scale, ep_rank, ep_size, 1, device, cache_mib, rms_eps)
+                          expert_type, w_scale, ep_rank, ep_size, max_tokens, device, cache_mib, rms_eps)
         self.h = C.c_void_p()
         _check(lib().wd_engine_create(C.byref(self.cfg), C.byref(self.h)))
         self._keep = []
@@ -189,9 +189,11 @@ class Engine:
 
     # -- forward -----------------------------------------------------------------------------
     def forward_host(self, layer, x):
+        """x: [hidden], or [n_tokens][hidden] for a batch of up to max_tokens tokens."""
         x = np.ascontiguousarray(x, np.float32)
-        out = np.zeros(self.cfg.hidden, np.float32)
-        _check(lib().wd_moe_forward_host(self.h, layer, _ptr(x), _ptr(out), 1))
+        n = 1 if x.ndim == 1 else x.shape[0]
+        out = np.zeros_like(x)
+        _check(lib().wd_moe_forward_host(self.h, layer, _ptr(x), _ptr(out), n))
         return out
 
     def forward_device(self, layer, x_ptr, out_ptr, stream=None):
@@ -234,13 +236,16 @@ class Engine:
         _check(lib().wd_device_status(self.h, C.byref(st)))
         return st.value
 
-    def tap(self, name):
+    def tap(self, name, token=None):
+        """Intermediate of the last forward call; `token` picks a token of a batch (default: its last)."""
         c = self.cfg
         shapes = dict(logits=(c.n_experts,), ids=(c.top_k,), weights=(c.top_k,), act=(c.top_k, c.expert_ffn),
                       expert_out=(c.top_k, c.hidden), routed=(c.hidden,), shared=(c.hidden,), shared_gate=(1,),
                       shared_act=(max(c.shared_ffn, 1),))
         a = np.zeros(shapes[name], np.int32 if name == "ids" else np.float32)
-        _check(lib().wd_read_tap(self.h, TAPS[name], 0, _ptr(a), a.nbytes))
+        if token is None:
+            token = -1
+        _check(lib().wd_read_tap(self.h, TAPS[name], token, _ptr(a), a.nbytes))
         return a
 
     def set_profiling(self, on):

@@ -144,6 +144,9 @@ struct wd_engine {
     wd::tagged_t *tagged = nullptr;
     size_t tagged_words = 0;
     int last_parity = 0;                    // half that holds the last launch's last layer (for the taps)
+    int last_tokens = 1;                    // tokens of the last forward call
+    int *tok_ids = nullptr;                 // [max_tokens][top_k] selection of every token of the last call
+    float *tok_weights = nullptr;
     size_t tagged_eo_offset = 0;            // word offset of the expert-output buffer inside `tagged`
     // expert-parallel peers
     int n_peers = 0;
@@ -299,6 +302,7 @@ int launch_layers(wd_engine *e, int begin, int end, const float *x, float *resid
     WD_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(wd::moe_layer_kernel), dim3(e->n_sm),
                                         dim3(wd::kThreads), args, e->smem_bytes, s));
     e->last_parity = (end - begin - 1) & 1;
+    e->last_tokens = 1;
     return WD_OK;
 }
 
@@ -442,7 +446,7 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
         return fail(WD_E_INVALID, "only IQ3_S expert tensors are supported by this build");
     if (c.ep_size < 1 || c.ep_rank < 0 || c.ep_rank >= c.ep_size || c.n_experts % c.ep_size)
         return fail(WD_E_INVALID, "ep_rank/ep_size must partition n_experts evenly");
-    if (c.max_tokens != 1) return fail(WD_E_INVALID, "max_tokens must be 1 in this build");
+    if (c.max_tokens < 1 || c.max_tokens > 4) return fail(WD_E_INVALID, "max_tokens must be 1..4");
     int ndev = 0;
     WD_CUDA(cudaGetDeviceCount(&ndev));
     if (c.device < 0 || c.device >= ndev) return fail(WD_E_INVALID, "no such CUDA device");
@@ -508,8 +512,10 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     WD_TRY(cudaMalloc(&e->ids, K * 4));
     WD_TRY(cudaMalloc(&e->weights, K * 4));
     WD_TRY(cudaMalloc(&e->routed, H * 4));
-    WD_TRY(cudaMalloc(&e->x_buf, H * 4));
-    WD_TRY(cudaMalloc(&e->out_buf, H * 4));
+    WD_TRY(cudaMalloc(&e->x_buf, static_cast<size_t>(c.max_tokens) * H * 4));
+    WD_TRY(cudaMalloc(&e->out_buf, static_cast<size_t>(c.max_tokens) * H * 4));
+    WD_TRY(cudaMalloc(&e->tok_ids, static_cast<size_t>(c.max_tokens) * K * 4));
+    WD_TRY(cudaMalloc(&e->tok_weights, static_cast<size_t>(c.max_tokens) * K * 4));
     WD_TRY(cudaMalloc(&e->residual_buf, H * 4));
     // tagged exchange words: logits, shared act, shared gate, act, expert out, shared down, residual (x2), progress
     const size_t tw_logits = 0, tw_shact = tw_logits + 2 * static_cast<size_t>(E), tw_shgate = tw_shact + 2 * static_cast<size_t>(SF),
@@ -524,7 +530,7 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     const size_t one_expert = 2 * e->gate_bytes + e->down_bytes;
     e->staging_bytes = align_up(std::max(dense, one_expert * 8), 256);
     WD_TRY(cudaMalloc(&e->staging, e->staging_bytes));
-    e->pinned_bytes = align_up(std::max<size_t>(one_expert, static_cast<size_t>(H) * 8), 256);
+    e->pinned_bytes = align_up(std::max<size_t>(one_expert, static_cast<size_t>(c.max_tokens) * H * 8), 256);
     WD_TRY(cudaMallocHost(&e->pinned, e->pinned_bytes));
     if (!e->resident) {
         WD_TRY(cudaStreamCreateWithFlags(&e->copy_stream, cudaStreamNonBlocking));
@@ -579,7 +585,7 @@ void wd_engine_destroy(wd_engine *e) {
         cudaFree(L.router); cudaFree(L.bias); cudaFree(L.gate_vec); cudaFree(L.sh_gate); cudaFree(L.sh_up);
         cudaFree(L.sh_down); cudaFree(L.norm); cudaFree(L.slot_of_expert);
     }
-    void *bufs[] = {e->pool, e->grid_packed, e->synth_lut, e->sync, e->tagged, e->ids, e->weights, e->routed,
+    void *bufs[] = {e->pool, e->grid_packed, e->synth_lut, e->sync, e->tagged, e->ids, e->weights, e->routed, e->tok_ids, e->tok_weights,
                     e->x_buf, e->out_buf, e->residual_buf, e->staging, e->stamps, e->layer_table};
     for (void *b : bufs) cudaFree(b);
     delete e->copy_pool;
@@ -774,30 +780,44 @@ int wd_cache_stats(const wd_engine *e, int64_t stats[3]) {
     return WD_OK;
 }
 
+// A batch of tokens (speculative verify, Qwen38MoeTokenBatch::run, src/qwen38_moe.cuh:2955) runs token by
+// token through the same layer kernel: pair (t, j) uses expert ids[t][j] on the activation of token t and
+// each token's rows are combined in its own rank order, exactly as a single-token call. The tokens of one
+// call read the same layer, so router, shared expert and repeated experts of tokens 1.. come from L2.
 int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, int n_tokens, void *stream) {
     int rc = check_layer(e, layer);
     if (rc) return rc;
-    if (n_tokens != 1) return fail(WD_E_INVALID, "n_tokens must be 1 in this build");
+    if (n_tokens < 1 || n_tokens > e->cfg.max_tokens) return fail(WD_E_INVALID, "n_tokens must be 1..max_tokens");
     if (!x_dev || !out_dev) return fail(WD_E_INVALID, "null buffer");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
-    if (!e->resident) return forward_capped(e, layer, x_dev, nullptr, out_dev, s);
-    return launch_layer(e, layer, x_dev, nullptr, out_dev, s);
+    const int H = e->cfg.hidden, K = e->cfg.top_k;
+    for (int t = 0; t < n_tokens; ++t) {
+        const float *x = x_dev + static_cast<size_t>(t) * H;
+        float *out = out_dev + static_cast<size_t>(t) * H;
+        rc = e->resident ? launch_layer(e, layer, x, nullptr, out, s) : forward_capped(e, layer, x, nullptr, out, s);
+        if (rc) return rc;
+        WD_CUDA(cudaMemcpyAsync(e->tok_ids + t * K, e->ids, K * 4, cudaMemcpyDeviceToDevice, s));
+        WD_CUDA(cudaMemcpyAsync(e->tok_weights + t * K, e->weights, K * 4, cudaMemcpyDeviceToDevice, s));
+    }
+    e->last_tokens = n_tokens;
+    return WD_OK;
 }
 
 int wd_moe_forward_host(wd_engine *e, int layer, const float *x_host, float *out_host, int n_tokens) {
     int rc = check_layer(e, layer);
     if (rc) return rc;
-    if (n_tokens != 1) return fail(WD_E_INVALID, "n_tokens must be 1 in this build");
-    const size_t bytes = static_cast<size_t>(e->cfg.hidden) * 4;
+    if (n_tokens < 1 || n_tokens > e->cfg.max_tokens) return fail(WD_E_INVALID, "n_tokens must be 1..max_tokens");
+    if (!x_host || !out_host) return fail(WD_E_INVALID, "null buffer");
+    const size_t n = static_cast<size_t>(e->cfg.hidden) * n_tokens, bytes = n * 4;
     WD_CUDA(cudaSetDevice(e->cfg.device));
     float *pin = static_cast<float *>(e->pinned);
     memcpy(pin, x_host, bytes);
     WD_CUDA(cudaMemcpyAsync(e->x_buf, pin, bytes, cudaMemcpyHostToDevice, e->stream));
-    if ((rc = wd_moe_forward(e, layer, e->x_buf, e->out_buf, 1, e->stream))) return rc;
-    WD_CUDA(cudaMemcpyAsync(pin + e->cfg.hidden, e->out_buf, bytes, cudaMemcpyDeviceToHost, e->stream));
+    if ((rc = wd_moe_forward(e, layer, e->x_buf, e->out_buf, n_tokens, e->stream))) return rc;
+    WD_CUDA(cudaMemcpyAsync(pin + n, e->out_buf, bytes, cudaMemcpyDeviceToHost, e->stream));
     WD_CUDA(cudaStreamSynchronize(e->stream));
-    memcpy(out_host, pin + e->cfg.hidden, bytes);
+    memcpy(out_host, pin + n, bytes);
     return check_device_status(e);
 }
 
@@ -832,7 +852,10 @@ int wd_stack_step_host(wd_engine *e, const float *in_host, float *out_host) {
 
 int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
     if (!e || !dst) return fail(WD_E_INVALID, "null argument");
-    if (token != 0) return fail(WD_E_INVALID, "token out of range");
+    if (token == -1) token = e->last_tokens - 1;     // the last token of the last call
+    if (token < 0 || token >= e->last_tokens) return fail(WD_E_INVALID, "token out of range");
+    if (token != e->last_tokens - 1 && tap != WD_TAP_IDS && tap != WD_TAP_WEIGHTS)
+        return fail(WD_E_STATE, "only the ids and weights of earlier tokens of a batch are kept; other taps show its last token");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     const wd_config &c = e->cfg;
     const wd::MoeParams &p = e->base;
@@ -842,8 +865,14 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
     size_t n = 0;
     switch (tap) {
         case WD_TAP_LOGITS: tsrc = p.t_logits + par * c.n_experts; n = c.n_experts * 4; break;
-        case WD_TAP_IDS: src = e->ids; n = c.top_k * 4; break;
-        case WD_TAP_WEIGHTS: src = e->weights; n = c.top_k * 4; break;
+        case WD_TAP_IDS:
+            src = e->last_tokens > 1 ? e->tok_ids + token * c.top_k : e->ids;
+            n = c.top_k * 4;
+            break;
+        case WD_TAP_WEIGHTS:
+            src = e->last_tokens > 1 ? e->tok_weights + token * c.top_k : e->weights;
+            n = c.top_k * 4;
+            break;
         case WD_TAP_ACT:
             n = static_cast<size_t>(c.top_k) * c.expert_ffn * 4;
             tsrc = p.t_act + par * (n / 4);
