@@ -252,9 +252,10 @@ class Engine:
         _check(lib().wd_set_profiling(self.h, int(on)))
 
     def stamps(self):
-        """[sm_count, 16] uint64 global-timer values of the last launch (profiling on)."""
+        """[sm_count, 32] uint64 global-timer values of the last launch (profiling on): 0..15 the layer's phases,
+        16..21 the stages of the selection, 24/25 the SM clock counter at stamps 0 and 10."""
         n = lib().wd_sm_count(self.h)
-        a = np.zeros((n, 16), np.uint64)
+        a = np.zeros((n, 32), np.uint64)
         _check(lib().wd_read_tap(self.h, 9, 0, _ptr(a), a.nbytes))
         return a
 

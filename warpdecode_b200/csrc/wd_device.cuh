@@ -65,7 +65,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Bounded wait; on timeout raises kErrCopyTimeout and returns false (the caller carries on with
 // whatever is in shared memory so that the kernel still terminates).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsigned *err) {
-    for (unsigned i = 0; i < kSpinLimit; ++i) {
+#pragma unroll 1
+    for (unsigned i = 0; i < kSpinLimit; ++i) {      // not unrolled: every copy of this loop is code that is fetched once per layer
         if (mbar_try_wait(bar, parity)) return true;
     }
     atomicOr(err, kErrCopyTimeout);

@@ -506,8 +506,8 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     WD_TRY(cudaMalloc(&e->sync, 8192));
     WD_TRY(cudaMemset(e->sync, 0, 8192));
     const int H = c.hidden, F = c.expert_ffn, K = c.top_k, E = c.n_experts, SF = std::max(c.shared_ffn, 1);
-    WD_TRY(cudaMalloc(&e->stamps, static_cast<size_t>(e->n_sm) * 16 * 8));
-    WD_TRY(cudaMemset(e->stamps, 0, static_cast<size_t>(e->n_sm) * 16 * 8));
+    WD_TRY(cudaMalloc(&e->stamps, static_cast<size_t>(e->n_sm) * wd::kStampStride * 8));
+    WD_TRY(cudaMemset(e->stamps, 0, static_cast<size_t>(e->n_sm) * wd::kStampStride * 8));
     WD_TRY(cudaMalloc(&e->layer_table, sizeof(wd::LayerDev) * c.n_layers));
     WD_TRY(cudaMalloc(&e->ids, K * 4));
     WD_TRY(cudaMalloc(&e->weights, K * 4));
@@ -888,7 +888,7 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
             tsrc = p.t_shared_act + par * std::max(c.shared_ffn, 1);
             n = static_cast<size_t>(c.shared_ffn) * 4;
             break;
-        case WD_TAP_STAMPS: src = e->stamps; n = static_cast<size_t>(e->n_sm) * 16 * 8; break;
+        case WD_TAP_STAMPS: src = e->stamps; n = static_cast<size_t>(e->n_sm) * wd::kStampStride * 8; break;
         default: return fail(WD_E_INVALID, "unknown tap");
     }
     if (bytes < n) return fail(WD_E_INVALID, "tap buffer too small");

@@ -25,6 +25,7 @@
 namespace wd {
 
 constexpr int kMaxBars = 96;
+constexpr int kStampStride = 32;    // profiling stamps per CTA: 0..15 phases of the layer, 16..23 stages of the selection
 
 // Weights of one layer (device pointers, repacked layouts).
 struct LayerDev {
@@ -74,7 +75,7 @@ struct MoeParams {
     int *ids;                    // [K]   (plain copies for inspection, written by CTA 0)
     float *weights;              // [K]
     float *routed;               // [H]
-    unsigned long long *stamps;  // nullable: [cta][16] globaltimer values at phase boundaries (profiling)
+    unsigned long long *stamps;  // nullable: [cta][kStampStride] globaltimer values at phase boundaries (profiling)
     unsigned *sync;              // [2] error word, [8] tag epoch (tag of layer `layer_begin` is epoch + 1; the
                                  // last CTA to leave advances it by the layers run), [9] count of CTAs that left
     // shared memory plan (byte offsets from the dynamic shared base; all 128-byte aligned)
@@ -135,7 +136,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     if (stamp_on) {                                                                            \
         unsigned long long t__;                                                                \
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                \
-        P.stamps[cta * 16 + (i)] = t__;                                                        \
+        P.stamps[cta * kStampStride + (i)] = t__;                                                        \
+        if ((i) == 0 || (i) == 10) P.stamps[cta * kStampStride + 24 + (i) / 10] = clock64();   /* SM clock rate */ \
     }
     if (tid < kMaxBars) {       // the last two belong to the shared gate vector and the slot table
         mbar_init(&bars[tid], 1);
@@ -162,7 +164,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     if (P.stamps != nullptr && tid == 0 && layer == P.stamp_layer + 1) {   // start of the next layer: the layer period
         unsigned long long t__;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));
-        P.stamps[cta * 16 + 14] = t__;
+        P.stamps[cta * kStampStride + 14] = t__;
     }
 
     // ---- issue phase-1 copies: router tasks and shared gate/up tasks of this CTA --------------
@@ -173,11 +175,13 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     if (tid == 0) {
         fence_proxy_async();        // the staging buffers were last read by ordinary loads (previous layer)
         int s = 0;
+#pragma unroll 1
         for (int t = cta; t < n_rt; t += ncta, ++s) {
             mbar_expect_tx(&bars[s], rt_bytes);
             bulk_load(stage_a + s * a1_slot, L.router_w + static_cast<size_t>(t) * rt_bytes, rt_bytes, &bars[s]);
         }
         s = P.n1r;
+#pragma unroll 1
         for (int t = ncta - 1 - cta; t < n_st; t += ncta, ++s) {
             mbar_expect_tx(&bars[s], 2u * rt_bytes);
             bulk_load(stage_a + s * a1_slot, L.sh_gate + static_cast<size_t>(t) * rt_bytes, rt_bytes, &bars[s]);
@@ -260,11 +264,13 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         }
     } else {
         if (layer >= P.layer_begin + 2 && tid < ncta) wait_tag_reached(P.t_progress + tid, tag - 2u, err);
+#pragma unroll 1
         for (int i = tid; i < P.H; i += kThreads) xf[i] = P.x[i];
     }
     const float *gate_vec_s = reinterpret_cast<const float *>(stage_b);
     __syncthreads();
     quantize_q8_0_cta(xf, P.H, xq0, xd0);
+#pragma unroll 1
     for (int sb = warp; sb < P.nsb_h; sb += kWarps)
         quantize_q8_K_warp(xf + sb * 256, lane, xk + sb * kActSbStride, &xdk[sb]);
     __syncthreads();

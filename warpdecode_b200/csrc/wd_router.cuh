@@ -33,7 +33,14 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {
 }
 
 __device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K, float w_scale, const RouterScratch &S,
-                                                  int *ids_out, float *w_out) {
+                                                  int *ids_out, float *w_out, unsigned long long *stage_stamps = nullptr) {
+    // profiling only: thread 0 leaves a global-timer value after each stage
+#define WD_RSTAMP(i)                                                       \
+    if (stage_stamps != nullptr && threadIdx.x == 0) {                     \
+        unsigned long long t__;                                            \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));            \
+        stage_stamps[i] = t__;                                             \
+    }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int e0 = tid, e1 = tid + kThreads;
     const bool h0 = e0 < E, h1 = e1 < E;
@@ -48,6 +55,7 @@ __device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K,
 #pragma unroll
     for (int s = 1; s < kWarps; s <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
     mx = __shfl_sync(0xffffffffu, mx, 0);
+    WD_RSTAMP(0)
     float p0 = h0 ? exp_ggml(__fsub_rn(l0, mx)) : 0.0f;
     float p1 = h1 ? exp_ggml(__fsub_rn(l1, mx)) : 0.0f;
     const float g0 = hsum8_lanes(p0), g1 = hsum8_lanes(p1);   // the reference's 8-lane tree
@@ -56,6 +64,7 @@ __device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K,
         if (h1) S.gsum[e1 >> 3] = g1;
     }
     __syncthreads();
+    WD_RSTAMP(1)
     {
         // The reference adds the group sums one by one, ascending, into a double. When every partial
         // sum is exactly representable the order cannot matter, and a shuffle tree gives the same bits:
@@ -67,6 +76,7 @@ __device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K,
         const int ng = E >> 3;
         double part = 0.0;
         int min_exp = 0x7fffffff, bad = 0;
+#pragma unroll 1
         for (int g = lane; g < ng; g += 32) {
             const float v = S.gsum[g];
             const int ex = static_cast<int>((__float_as_uint(v) >> 23) & 0xffu);
@@ -84,6 +94,7 @@ __device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K,
         double sum = part;
         if (bad || (min_exp != 0x7fffffff && tot_exp + 1 - (min_exp - 23) > 52)) {
             sum = 0.0;
+#pragma unroll 1
             for (int g = 0; g < ng; ++g) sum = __dadd_rn(sum, static_cast<double>(S.gsum[g]));
         }
         if (sum == 0.0) {
@@ -94,6 +105,7 @@ __device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K,
             p1 = __fmul_rn(p1, inv);
         }
     }
+    WD_RSTAMP(2)
     if (S.probs) {
         if (h0) S.probs[e0] = p0;
         if (h1) S.probs[e1] = p1;
@@ -102,6 +114,7 @@ __device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K,
     // stage 1: this warp's k best, in rung order
     uint32_t k0 = h0 ? order_key(p0) : 0u, k1 = h1 ? order_key(p1) : 0u;
     uint32_t *ck = S.cand, *ci = S.cand + kWarps * kMaxK;
+#pragma unroll 1
     for (int j = 0; j < K; ++j) {
         const uint32_t m = __reduce_max_sync(0xffffffffu, max(k0, k1));
         const uint32_t cand = (k0 == m) ? static_cast<uint32_t>(e0) : ((k1 == m) ? static_cast<uint32_t>(e1) : 0xffffffffu);
@@ -112,6 +125,7 @@ __device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K,
         }
         if (m <= kKeyNegInf) {          // nothing selectable is left in this warp: the rest of its list is empty
             if (lane == 0)
+#pragma unroll 1
                 for (int q = j + 1; q < K; ++q) ck[warp * kMaxK + q] = 0u;
             break;
         }
@@ -119,12 +133,14 @@ __device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K,
         if (mi == static_cast<uint32_t>(e1)) k1 = 0u;
     }
     __syncthreads();
+    WD_RSTAMP(3)
     // stage 2: warp 0 merges the lists; lane w holds the head of warp w's list
     if (warp == 0) {
         int ptr = 0;
         uint32_t my_id = 0u;
         float my_p = 0.0f;
         const float p_first = *S.first;
+#pragma unroll 1
         for (int j = 0; j < K; ++j) {
             const bool live = lane < kWarps && ptr < K;
             const uint32_t hk = live ? ck[lane * kMaxK + ptr] : 0u;
@@ -144,8 +160,23 @@ __device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K,
                 my_p = p;
             }
         }
-        double wsum = 0.0;
-        for (int j = 0; j < K; ++j) wsum = __dadd_rn(wsum, static_cast<double>(__shfl_sync(0xffffffffu, my_p, j)));
+        if (lane == 0) { WD_RSTAMP(4) }
+        // the reference adds the picked probabilities one by one into a double; as for the softmax sum, a
+        // shuffle tree gives the same bits whenever every partial sum is exact, else the serial order is replayed
+        const float tp = lane < K ? my_p : 0.0f;
+        const int ex = static_cast<int>((__float_as_uint(tp) >> 23) & 0xffu);
+        const bool nz = tp != 0.0f;
+        const int bad = __any_sync(0xffffffffu, nz && (ex == 0 || ex == 255 || tp < 0.0f));
+        const int min_exp = __reduce_min_sync(0xffffffffu, nz ? ex : 0x7fffffff);
+        double wsum = static_cast<double>(tp);
+#pragma unroll
+        for (int sft = 1; sft < 32; sft <<= 1) wsum = __dadd_rn(wsum, __shfl_xor_sync(0xffffffffu, wsum, sft));
+        const int tot_exp = static_cast<int>((__double_as_longlong(wsum) >> 52) & 0x7ff) - 1023 + 127;
+        if (bad || (min_exp != 0x7fffffff && tot_exp + 1 - (min_exp - 23) > 52)) {
+            wsum = 0.0;
+#pragma unroll 1
+            for (int j = 0; j < K; ++j) wsum = __dadd_rn(wsum, static_cast<double>(__shfl_sync(0xffffffffu, my_p, j)));
+        }
         const float denom = fmaxf(__double2float_rn(wsum), 6.103515625e-5f);
         if (lane < K) {
             float w = __fdiv_rn(my_p, denom);
@@ -155,6 +186,8 @@ __device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K,
         }
     }
     __syncthreads();
+    WD_RSTAMP(5)
+#undef WD_RSTAMP
 }
 
 }  // namespace wd
