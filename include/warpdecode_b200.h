@@ -111,7 +111,8 @@ int wd_cache_stats(const wd_engine *e, int64_t stats[3]);
  * Replaces run_qwen38_routed_moe_separate_f32_x + run_qwen38_shared_expert_f32_x +
  * q38_finish_moe_f32 (src/qwen38_moe.cuh:3761, :3963, :2442) and, for n_tokens in 2..max_tokens,
  * Qwen38MoeTokenBatch::run (:2955): pair (t, j) = expert ids[t][j] on the activation of token t, each
- * token combined in its own rank order. Enqueues on `stream` and returns without synchronising when
+ * token combined in its own rank order. Enqueues on `stream` (NULL: the engine's own non-blocking stream,
+ * which does not synchronise with the legacy default stream) and returns without synchronising when
  * every selected expert is resident; with a capped cache it synchronises once per token. */
 int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, int n_tokens,
                    void *stream);
@@ -198,6 +199,21 @@ int wd_dense_pack_q4_0(const void *w_ggml_host, int rows, int cols, void **packe
 int wd_dense_pack_q4_0_device(const void *w_ggml_dev, int rows, int cols, void **packed_dev, void *stream);
 int wd_dense_matvec_q4_0(const void *packed_dev, int rows, int cols, const float *x_dev, float *y_dev, void *stream);
 int wd_dense_free(void *packed_dev);
+/* Output head: token = arg-max over the finite logits of W x, W a Q8_0 matrix [rows = vocab][cols = hidden]
+ * packed like the Q4_0 one (wd_dense_pack_q8_0*; free with wd_dense_free). The operator of the head GEMV
+ * plus q38_argmax_kernel (src/qwen38_forward.cuh:450-486): largest value, ties to the lowest index,
+ * non-finite logits skipped and reported in *nonfinite_dev (nullable), token 0 when nothing is finite.
+ * logits_dev (nullable) receives the F32 logits [rows]. One matvec kernel with the arg-max fused
+ * (64-bit monotone key + atomicMax, as src/warodecode.cu:1603-1632) and a one-thread finish kernel on
+ * `stream`; calls on the same packed matrix must not overlap (its arg-max state sits behind the matrix). */
+int wd_dense_pack_q8_0(const void *w_ggml_host, int rows, int cols, void **packed_dev);
+int wd_dense_pack_q8_0_device(const void *w_ggml_dev, int rows, int cols, void **packed_dev, void *stream);
+/* out_dev[cols] = row *token_dev of a Q8_0 embedding table [rows][cols] in ggml layout on the device
+ * (d * q per value; the token is clamped to the table). With wd_stack_step and wd_head_argmax_q8_0 a greedy
+ * decode loop of the MoE stack stays on the device: embed -> layers -> head -> token. */
+int wd_embed_q8_0(const void *table_ggml_dev, int rows, int cols, const int *token_dev, float *out_dev, void *stream);
+int wd_head_argmax_q8_0(void *packed_dev, int rows, int cols, const float *x_dev, float *logits_dev, int *token_dev,
+                        int *nonfinite_dev, void *stream);
 
 /* Has no counterpart in the reference. y = W x for one IQ3_S matrix like wd_matvec_host, for callers
  * that must not allocate device memory (HBM already handed to the expert pool, a latency-critical

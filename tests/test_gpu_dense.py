@@ -52,3 +52,4 @@ def test_q4_0_matvec_quantised_weights_and_edge_inputs(wd, oracle):
 def test_q4_0_matvec_refuses_odd_shapes(wd):
     with pytest.raises(wd.WdError, match="multiple of 32"):
         wd.matvec(ol.TYPE_Q4_0, np.zeros(33 * 8 * 18, np.uint8), 33, 256, np.zeros(256, np.float32))
+

@@ -104,6 +104,10 @@ def lib():
         L.wd_dense_pack_q4_0_device.argtypes = [vp, i, i, C.POINTER(vp), vp]
         L.wd_dense_matvec_q4_0.argtypes = [vp, i, i, vp, vp, vp]
         L.wd_dense_free.argtypes = [vp]
+        L.wd_dense_pack_q8_0.argtypes = [vp, i, i, C.POINTER(vp)]
+        L.wd_dense_pack_q8_0_device.argtypes = [vp, i, i, C.POINTER(vp), vp]
+        L.wd_head_argmax_q8_0.argtypes = [vp, i, i, vp, vp, vp, vp, vp]
+        L.wd_embed_q8_0.argtypes = [vp, i, i, vp, vp, vp]
         _lib = L
     return _lib
 
@@ -322,6 +326,37 @@ class DenseQ4_0:
             self.close()
         except Exception:
             pass
+
+
+class HeadQ8_0:
+    """Output head: a Q8_0 matrix [vocab][hidden] packed on the device; token = arg-max(W x) (wd_head_argmax_q8_0)."""
+
+    def __init__(self, rows, cols, ggml_host=None, ggml_dev_ptr=None, stream=None):
+        self.rows, self.cols, self.p = rows, cols, C.c_void_p()
+        if ggml_host is not None:
+            w = np.ascontiguousarray(ggml_host, np.uint8)
+            assert w.size == rows * (cols // 32) * 34
+            _check(lib().wd_dense_pack_q8_0(_ptr(w), rows, cols, C.byref(self.p)))
+        else:
+            _check(lib().wd_dense_pack_q8_0_device(ggml_dev_ptr, rows, cols, C.byref(self.p), stream))
+
+    def argmax(self, x_ptr, token_ptr, logits_ptr=None, nonfinite_ptr=None, stream=None):
+        _check(lib().wd_head_argmax_q8_0(self.p, self.rows, self.cols, x_ptr, logits_ptr, token_ptr, nonfinite_ptr, stream))
+
+    def close(self):
+        if self.p:
+            lib().wd_dense_free(self.p)
+            self.p = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def embed_q8_0(table_dev_ptr, rows, cols, token_ptr, out_ptr, stream=None):
+    _check(lib().wd_embed_q8_0(table_dev_ptr, rows, cols, token_ptr, out_ptr, stream))
 
 
 # -- stand-alone pieces ------------------------------------------------------------------------

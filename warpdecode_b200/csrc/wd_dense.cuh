@@ -193,4 +193,121 @@ __global__ void __launch_bounds__(kDenseThreads) q4_0_gemv_tile_kernel(const uin
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Output head: logits = W x for a Q8_0 matrix [vocab][hidden] fused with the arg-max over the finite
+// logits (largest value, ties to the lowest index, non-finite values skipped and reported, token 0 when
+// nothing is finite): q38_argmax_kernel (src/qwen38_forward.cuh:450-486) over the Q8_0 GEMV of
+// src/qwen38_hc.cuh:1020; the multi-block reduction uses a monotone 64-bit key and atomicMax like
+// dense_argmax_reduce_kernel (src/warodecode.cu:1603-1632). Row order of the float operations: ggml's
+// Q8_0 x Q8_0 (src/qwen38_cpu_moe.cuh:424-440), the same as q8_task_row.
+// Planar layout: tiles of 32 rows; quants of block b of the tile's row r at q[((t * nb + b) * 32 + r) * 2]
+// (two 16-byte words), f16 scales after all quants in the same order.
+// ---------------------------------------------------------------------------------------------
+__global__ void repack_q8_0_planar_kernel(const uint8_t *src, uint8_t *dst, int rows, int nb) {
+    const long long n = static_cast<long long>(rows) * nb;
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= n) return;
+    const int row = static_cast<int>(i / nb), b = static_cast<int>(i % nb);
+    const uint8_t *blk = src + i * 34;
+    const long long o = (static_cast<long long>(row >> 5) * nb + b) * 32 + (row & 31);
+    uint32_t w[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        w[k] = blk[2 + 4 * k] | (blk[3 + 4 * k] << 8) | (blk[4 + 4 * k] << 16) | (static_cast<uint32_t>(blk[5 + 4 * k]) << 24);
+    uint4 *q = reinterpret_cast<uint4 *>(dst + o * 32);
+    q[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    q[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    uint16_t *d = reinterpret_cast<uint16_t *>(dst + n * 32);
+    d[o] = static_cast<uint16_t>(blk[0] | (blk[1] << 8));
+}
+
+constexpr int kHeadUnroll = 4;       // blocks in flight per lane (128 bytes of quants)
+
+// key: one u64, zeroed before the launch; flags: [0] set when a non-finite logit was seen
+__global__ void __launch_bounds__(kDenseThreads) q8_0_head_kernel(const uint8_t *wp, int rows, int nb, const float *x,
+                                                                   float *y, unsigned long long *key, int *flags) {
+    extern __shared__ __align__(16) uint8_t dsm[];
+    uint8_t *xq = dsm;
+    float *xd = reinterpret_cast<float *>(dsm + nb * 32);
+    quantize_q8_0_plain_cta(x, nb * 32, xq, xd);
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int n_tiles = rows >> 5;
+    const uint4 *q_all = reinterpret_cast<const uint4 *>(wp);
+    const uint16_t *d_all = reinterpret_cast<const uint16_t *>(wp + static_cast<size_t>(rows) * nb * 32);
+    const uint4 *a4 = reinterpret_cast<const uint4 *>(xq);
+    unsigned long long best = 0ull;
+    int nonfinite = 0;
+    for (int tile = blockIdx.x * nwarps + warp; tile < n_tiles; tile += gridDim.x * nwarps) {
+        const uint4 *q = q_all + (static_cast<size_t>(tile) * nb * 32 + lane) * 2;
+        const uint16_t *d = d_all + static_cast<size_t>(tile) * nb * 32 + lane;
+        float acc[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[c] = 0.0f;
+#pragma unroll 1
+        for (int b0 = 0; b0 < nb; b0 += kHeadUnroll) {
+            uint4 w0[kHeadUnroll], w1[kHeadUnroll];
+            uint16_t dw[kHeadUnroll];
+#pragma unroll
+            for (int u = 0; u < kHeadUnroll; ++u) {
+                w0[u] = __ldg(q + (b0 + u) * 64);
+                w1[u] = __ldg(q + (b0 + u) * 64 + 1);
+                dw[u] = __ldg(d + (b0 + u) * 32);
+            }
+#pragma unroll
+            for (int u = 0; u < kHeadUnroll; ++u) {
+                const int b = b0 + u;
+                const uint4 lo = a4[2 * b], hi = a4[2 * b + 1];
+                const float dd = __fmul_rn(half_bits_to_float(dw[u]), xd[b]);
+                const uint32_t ww[8] = {w0[u].x, w0[u].y, w0[u].z, w0[u].w, w1[u].x, w1[u].y, w1[u].z, w1[u].w};
+                const uint32_t aa[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    acc[c] = __fmaf_rn(dd, static_cast<float>(dp4a_s8(static_cast<int>(ww[c]), static_cast<int>(aa[c]), 0)), acc[c]);
+            }
+        }
+        const float r0 = __fadd_rn(acc[0], acc[4]), r1 = __fadd_rn(acc[1], acc[5]);
+        const float r2 = __fadd_rn(acc[2], acc[6]), r3 = __fadd_rn(acc[3], acc[7]);
+        const float v = __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
+        const int row = tile * 32 + lane;
+        if (y) y[row] = v;
+        if (isfinite(v)) {
+            const uint32_t u = __float_as_uint(v + 0.0f);       // -0 and +0 compare equal: one key for both
+            const uint32_t mono = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+            const unsigned long long k = (static_cast<unsigned long long>(mono) << 32) | static_cast<uint32_t>(~static_cast<uint32_t>(row));
+            best = k > best ? k : best;
+        } else {
+            nonfinite = 1;
+        }
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) {
+        const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, s);
+        best = o > best ? o : best;
+    }
+    nonfinite = __any_sync(0xffffffffu, nonfinite);
+    if (lane == 0) {
+        if (best != 0ull) atomicMax(key, best);
+        if (nonfinite) atomicOr(flags, 1);
+    }
+}
+
+// Embedding row of a Q8_0 table in ggml layout: out[i] = d(block) * q[i] for the row *token
+// (token_embd lookup of the decoder, src/qwen38_forward.cuh: embedding gather before layer 0).
+__global__ void embed_q8_0_kernel(const uint8_t *table, int rows, int nb, const int *token, float *out) {
+    int t = *token;
+    t = t < 0 ? 0 : (t >= rows ? rows - 1 : t);
+    const uint8_t *row = table + static_cast<size_t>(t) * nb * 34;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < nb * 32; i += gridDim.x * blockDim.x) {
+        const uint8_t *blk = row + (i >> 5) * 34;
+        const float d = half_bits_to_float(static_cast<uint16_t>(blk[0] | (blk[1] << 8)));
+        out[i] = __fmul_rn(d, static_cast<float>(static_cast<int8_t>(blk[2 + (i & 31)])));
+    }
+}
+
+__global__ void head_finish_kernel(const unsigned long long *key, int *token) {
+    const unsigned long long k = *key;
+    *token = k == 0ull ? 0 : static_cast<int>(~static_cast<uint32_t>(k & 0xffffffffull));
+}
+
 }  // namespace wd

@@ -1217,6 +1217,91 @@ int wd_dense_matvec_q4_0(const void *packed_dev, int rows, int cols, const float
     return WD_OK;
 }
 
+// ---- output head: Q8_0 matvec + arg-max ------------------------------------------------------------------
+static int head_check(int rows, int cols) {
+    if (rows <= 0 || cols <= 0 || rows % 32 || cols % (32 * wd::kHeadUnroll) || cols > 32768)
+        return fail(WD_E_INVALID, "Q8_0 head: rows must be a multiple of 32, cols a multiple of 128 up to 32768");
+    return WD_OK;
+}
+
+int wd_dense_pack_q8_0_device(const void *w_ggml_dev, int rows, int cols, void **packed_dev, void *stream) {
+    if (!w_ggml_dev || !packed_dev) return fail(WD_E_INVALID, "null argument");
+    int rc = head_check(rows, cols);
+    if (rc) return rc;
+    const int nb = cols / 32;
+    uint8_t *dst = nullptr;
+    // the packed matrix, then 16 bytes of arg-max state (key, flags)
+    WD_CUDA(cudaMalloc(&dst, static_cast<size_t>(rows) * nb * 34 + 16 + 16));
+    const long long n = static_cast<long long>(rows) * nb;
+    wd::repack_q8_0_planar_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t *>(w_ggml_dev), dst, rows, nb);
+    cudaError_t ce = cudaGetLastError();
+    if (ce != cudaSuccess) {
+        cudaFree(dst);
+        return fail(WD_E_CUDA, std::string("repack_q8_0_planar_kernel: ") + cudaGetErrorString(ce));
+    }
+    *packed_dev = dst;
+    return WD_OK;
+}
+
+int wd_dense_pack_q8_0(const void *w_ggml_host, int rows, int cols, void **packed_dev) {
+    if (!w_ggml_host || !packed_dev) return fail(WD_E_INVALID, "null argument");
+    int rc = head_check(rows, cols);
+    if (rc) return rc;
+    const size_t bytes = static_cast<size_t>(rows) * (cols / 32) * 34;
+    uint8_t *src = nullptr;
+    WD_CUDA(cudaMalloc(&src, bytes));
+    cudaError_t ce = cudaMemcpy(src, w_ggml_host, bytes, cudaMemcpyHostToDevice);
+    if (ce == cudaSuccess) {
+        rc = wd_dense_pack_q8_0_device(src, rows, cols, packed_dev, nullptr);
+        cudaDeviceSynchronize();
+    }
+    cudaFree(src);
+    if (ce != cudaSuccess) return fail(WD_E_CUDA, std::string("cudaMemcpy: ") + cudaGetErrorString(ce));
+    return rc;
+}
+
+int wd_head_argmax_q8_0(void *packed_dev, int rows, int cols, const float *x_dev, float *logits_dev, int *token_dev,
+                        int *nonfinite_dev, void *stream) {
+    if (!packed_dev || !x_dev || !token_dev) return fail(WD_E_INVALID, "null argument");
+    int rc = head_check(rows, cols);
+    if (rc) return rc;
+    const int nb = cols / 32;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // state behind the packed matrix (16-byte aligned): u64 key, then the flags word
+    uint8_t *state = static_cast<uint8_t *>(packed_dev) + ((static_cast<size_t>(rows) * nb * 34 + 15) & ~static_cast<size_t>(15));
+    unsigned long long *key = reinterpret_cast<unsigned long long *>(state);
+    int *flags = reinterpret_cast<int *>(state + 8);
+    WD_CUDA(cudaMemsetAsync(state, 0, 16, s));
+    static bool attr_set = false;
+    if (!attr_set) {
+        WD_CUDA(cudaFuncSetAttribute(wd::q8_0_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 40 * 1024));
+        attr_set = true;
+    }
+    int dev = 0, n_sm = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+    const int warps = wd::kDenseThreads / 32, tiles = rows / 32;
+    int grid = (tiles + warps - 1) / warps;
+    if (grid > n_sm * 8) grid = n_sm * 8;
+    const size_t smem = static_cast<size_t>(cols) + static_cast<size_t>(nb) * 4;
+    wd::q8_0_head_kernel<<<grid, wd::kDenseThreads, smem, s>>>(static_cast<const uint8_t *>(packed_dev), rows, nb, x_dev,
+                                                             logits_dev, key, flags);
+    wd::head_finish_kernel<<<1, 1, 0, s>>>(key, token_dev);
+    WD_CUDA(cudaGetLastError());
+    if (nonfinite_dev) WD_CUDA(cudaMemcpyAsync(nonfinite_dev, flags, sizeof(int), cudaMemcpyDeviceToDevice, s));
+    return WD_OK;
+}
+
+int wd_embed_q8_0(const void *table_ggml_dev, int rows, int cols, const int *token_dev, float *out_dev, void *stream) {
+    if (!table_ggml_dev || !token_dev || !out_dev) return fail(WD_E_INVALID, "null argument");
+    if (rows <= 0 || cols <= 0 || cols % 32) return fail(WD_E_INVALID, "embedding: cols must be a multiple of 32");
+    wd::embed_q8_0_kernel<<<(cols + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t *>(table_ggml_dev), rows, cols / 32, token_dev, out_dev);
+    WD_CUDA(cudaGetLastError());
+    return WD_OK;
+}
+
 // ---- synthetic model ----------------------------------------------------------------------------------
 static int ensure_lut(wd_engine *e, cudaStream_t s) {
     if (e->synth_lut) return WD_OK;
