@@ -37,6 +37,33 @@ __global__ void repack_iq3s_kernel(const uint8_t *__restrict__ src, uint8_t *__r
     for (int k = 0; k < 4; ++k) tile[kIq3OffSC + lane * 4 + k] = s[106 + k];
 }
 
+// repack: ggml IQ2_S blocks (82 B) -> tiles of 32 blocks
+__global__ void repack_iq2s_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, long long nblocks,
+                                   long long src_stride, long long dst_stride) {
+    const long long b = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (b >= nblocks) return;
+    src += blockIdx.y * src_stride;
+    dst += blockIdx.y * dst_stride;
+    const uint8_t *s = src + b * 82;
+    uint8_t *tile = dst + (b >> 5) * kIq2TileBytes;
+    const int lane = static_cast<int>(b & 31);
+    tile[kIq2OffD + lane * 2] = s[0];
+    tile[kIq2OffD + lane * 2 + 1] = s[1];
+    const uint8_t *qs = s + 2, *sg = s + 34, *qh = s + 66, *sc = s + 74;
+    for (int i = 0; i < 8; ++i) {
+        for (int k = 0; k < 4; ++k) tile[i * 128 + lane * 4 + k] = qs[i * 4 + k];
+        uint32_t word = 0;
+        for (int c = 0; c < 8; ++c) {
+            const uint32_t nib = (sg[i * 4 + (c >> 1)] >> (4 * (c & 1))) & 15u;
+            for (int j = 0; j < 4; ++j)
+                if ((nib >> j) & 1u) word |= 1u << (8 * j + 7 - c);
+        }
+        *reinterpret_cast<uint32_t *>(tile + kIq2OffSG + i * 128 + lane * 4) = word;
+        tile[kIq2OffQH + lane * 8 + i] = qh[i];
+        tile[kIq2OffSC + lane * 8 + i] = sc[i];
+    }
+}
+
 // repack: ggml Q8_0 [rows][nb] blocks (34 B) -> 4-row tasks
 __global__ void repack_q8_0_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int rows, int nb) {
     const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -231,7 +258,7 @@ __global__ void test_quantize_kernel(const float *x, int n, uint8_t *q80_blocks,
 // loads (no bulk copy), same decode and float chain as the fused kernel. x is quantised to Q8_K by
 // the same routine. partials (optional): [rows][nsb][8] int32.
 __global__ void test_matvec_iq3s_kernel(const uint8_t *tiles, int rows, int nsb, const float *x, float *y,
-                                        int *partials, const uint16_t *grid_packed) {
+                                        int *partials, const uint16_t *grid_packed, int type = kTypeIq3s) {
     extern __shared__ __align__(128) uint8_t tsm[];
     uint8_t *tab = tsm;
     uint8_t *xk = tab + kGridTableBytes;
@@ -239,7 +266,8 @@ __global__ void test_matvec_iq3s_kernel(const uint8_t *tiles, int rows, int nsb,
     uint8_t *tile_s = reinterpret_cast<uint8_t *>(xdk + 32);
     float *scr_all = reinterpret_cast<float *>(tile_s + (blockDim.x / 32) * kIq3TileBytes);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x / 32;
-    build_grid_table(tab, grid_packed);
+    if (type == kTypeIq2s) build_iq2_table(tab, grid_packed);     // grid_packed is the codebook of `type`
+    else build_grid_table(tab, grid_packed);
     for (int sb = warp; sb < nsb; sb += nw) quantize_q8_K_warp(x + sb * 256, lane, xk + sb * kActSbStride, &xdk[sb]);
     __syncthreads();
     const int R = 32 / nsb, ntiles = rows / R;
@@ -248,12 +276,13 @@ __global__ void test_matvec_iq3s_kernel(const uint8_t *tiles, int rows, int nsb,
     float *scr = scr_all + warp * 640;          // 544 floats of chain scratch, then 32 row results
     float *rows_out = scr + 576;
     for (int t = blockIdx.x * nw + warp; t < ntiles; t += gridDim.x * nw) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(tiles + static_cast<size_t>(t) * kIq3TileBytes);
-        for (int i = lane; i < kIq3TileBytes / 16; i += 32) reinterpret_cast<uint4 *>(ts)[i] = src[i];
+        const int tb = iq_tile_bytes(type);
+        const uint4 *src = reinterpret_cast<const uint4 *>(tiles + static_cast<size_t>(t) * tb);
+        for (int i = lane; i < tb / 16; i += 32) reinterpret_cast<uint4 *>(ts)[i] = src[i];
         __syncwarp();
         const int sb = lane % nsb, rl = lane / nsb;
         int *dump = partials ? partials + (static_cast<size_t>(t * R + rl) * nsb + sb) * 8 : nullptr;
-        iq3_tile_to_rows(ts, xk + sb * kActSbStride, xdk[sb], nsb, lane, lane4x2, tab, scr, rows_out, dump);
+        iq_tile_to_rows_any(type, ts, xk + sb * kActSbStride, xdk[sb], nsb, lane, lane4x2, tab, tab, scr, rows_out, dump);
         for (int rr = lane; rr < R; rr += 32) y[t * R + rr] = rows_out[rr];
         __syncwarp();
     }

@@ -126,7 +126,7 @@ __device__ __noinline__ float dot_f32_warp(const float *a, const float *b, int n
 // nsb*8+8 floats plus 32 scales.
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void iq_tile_rows(const int partial[8], float scale, int nsb, int lane, float *scr,
-                                             float *rows_out) {
+                                             float *rows_out, float post = 1.0f) {
     const int R = 32 / nsb;
     const int stripe = nsb * 8 + 8;
     const int r = lane / nsb, sb = lane % nsb;
@@ -149,7 +149,7 @@ __device__ __forceinline__ void iq_tile_rows(const int partial[8], float scale, 
             for (int s = 0; s < nsb; ++s) acc = __fmaf_rn(sc[rr * nsb + s], scr[rr * stripe + s * 8 + c], acc);
         }
         acc = hsum8_lanes(acc);
-        if (rr < R && c == 0) rows_out[rr] = acc;
+        if (rr < R && c == 0) rows_out[rr] = __fmul_rn(post, acc);       // post is 1 (exact) or IQ2_S's 0.125
     }
     __syncwarp();
 }
@@ -169,6 +169,27 @@ __device__ __noinline__ void iq3_tile_to_rows(const uint8_t *tile, const uint8_t
     }
     const float dw = half_bits_to_float(*reinterpret_cast<const uint16_t *>(tile + kIq3OffD + lane * 2));
     iq_tile_rows(p, __fmul_rn(dw, dx), nsb, lane, scr, rows_out);
+}
+
+// The IQ2_S twin.
+__device__ __noinline__ void iq2_tile_to_rows(const uint8_t *tile, const uint8_t *a, float dx, int nsb, int lane,
+                                              const uint8_t *tab2, float *scr, float *rows_out, int *partial_dump) {
+    int p[8];
+    iq2_block_partials_range(tile, lane, a, tab2, p, 0, 8);
+    if (partial_dump) {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) partial_dump[c] = p[c];
+    }
+    const float dw = half_bits_to_float(*reinterpret_cast<const uint16_t *>(tile + kIq2OffD + lane * 2));
+    iq_tile_rows(p, __fmul_rn(dw, dx), nsb, lane, scr, rows_out, 0.125f);
+}
+
+// Either type (a warp-uniform branch). tab3: lane-private IQ3_S table, tab2: IQ2_S table.
+__device__ __forceinline__ void iq_tile_to_rows_any(int type, const uint8_t *tile, const uint8_t *a, float dx, int nsb,
+                                                    int lane, uint32_t lane4x2, const uint8_t *tab3, const uint8_t *tab2,
+                                                    float *scr, float *rows_out, int *partial_dump) {
+    if (type == kTypeIq2s) iq2_tile_to_rows(tile, a, dx, nsb, lane, tab2, scr, rows_out, partial_dump);
+    else iq3_tile_to_rows(tile, a, dx, nsb, lane, lane4x2, tab3, scr, rows_out, partial_dump);
 }
 
 }  // namespace wd

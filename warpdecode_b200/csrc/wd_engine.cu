@@ -1069,26 +1069,29 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
     uint8_t *d_src = nullptr, *d_dst = nullptr;
     int *d_p = nullptr;
     uint16_t *d_grid = nullptr;
-    if (type == WD_TYPE_IQ3_S) {
+    if (type == WD_TYPE_IQ3_S || type == WD_TYPE_IQ2_S) {
         const int nsb = cols / 256;
         if (cols % 256 || !pow2(nsb) || nsb > 32 || rows % (32 / nsb))
-            return fail(WD_E_INVALID, "IQ3_S matvec: cols must be 256*2^n (n<=5), rows a multiple of 32/(cols/256)");
-        const size_t bytes = static_cast<size_t>(rows) * nsb * 110;
+            return fail(WD_E_INVALID, "IQ3_S / IQ2_S matvec: cols must be 256*2^n (n<=5), rows a multiple of 32/(cols/256)");
+        const bool iq2 = type == WD_TYPE_IQ2_S;
+        const size_t bytes = static_cast<size_t>(rows) * nsb * wd::iq_block_bytes(type);
         WD_CUDA(cudaMalloc(&d_src, bytes));
         WD_CUDA(cudaMalloc(&d_dst, bytes));
         WD_CUDA(cudaMalloc(&d_x, cols * 4));
         WD_CUDA(cudaMalloc(&d_y, rows * 4));
-        WD_CUDA(cudaMalloc(&d_grid, sizeof(wd_iq3s_grid_packed)));
-        WD_CUDA(cudaMemcpy(d_grid, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
+        WD_CUDA(cudaMalloc(&d_grid, sizeof(wd_iq2s_grid_packed)));      // the larger of the two codebooks
+        if (iq2) WD_CUDA(cudaMemcpy(d_grid, wd_iq2s_grid_packed, sizeof(wd_iq2s_grid_packed), cudaMemcpyHostToDevice));
+        else WD_CUDA(cudaMemcpy(d_grid, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
         if (partials) WD_CUDA(cudaMalloc(&d_p, static_cast<size_t>(rows) * nsb * 8 * 4));
         WD_CUDA(cudaMemcpy(d_src, w, bytes, cudaMemcpyHostToDevice));
         WD_CUDA(cudaMemcpy(d_x, x, cols * 4, cudaMemcpyHostToDevice));
         const long long nblocks = static_cast<long long>(rows) * nsb;
-        wd::repack_iq3s_kernel<<<static_cast<unsigned>((nblocks + 127) / 128), 128>>>(d_src, d_dst, nblocks, 0, 0);
+        if (iq2) wd::repack_iq2s_kernel<<<static_cast<unsigned>((nblocks + 127) / 128), 128>>>(d_src, d_dst, nblocks, 0, 0);
+        else wd::repack_iq3s_kernel<<<static_cast<unsigned>((nblocks + 127) / 128), 128>>>(d_src, d_dst, nblocks, 0, 0);
         const int nw = 8;
         const size_t smem = wd::kGridTableBytes + nsb * wd::kActSbStride + 32 * 4 + nw * wd::kIq3TileBytes + nw * 640 * 4 + 256;
         WD_CUDA(cudaFuncSetAttribute(wd::test_matvec_iq3s_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        wd::test_matvec_iq3s_kernel<<<64, nw * 32, smem>>>(d_dst, rows, nsb, d_x, d_y, d_p, d_grid);
+        wd::test_matvec_iq3s_kernel<<<64, nw * 32, smem>>>(d_dst, rows, nsb, d_x, d_y, d_p, d_grid, type);
         WD_CUDA(cudaGetLastError());
         WD_CUDA(cudaDeviceSynchronize());
         WD_CUDA(cudaMemcpy(y, d_y, rows * 4, cudaMemcpyDeviceToHost));
@@ -1130,7 +1133,7 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
             return rc;
         }
     } else {
-        return fail(WD_E_INVALID, "matvec supports IQ3_S, Q8_0 and Q4_0");
+        return fail(WD_E_INVALID, "matvec supports IQ3_S, IQ2_S, Q8_0 and Q4_0");
     }
     cudaFree(d_x); cudaFree(d_y); cudaFree(d_src); cudaFree(d_dst); cudaFree(d_p); cudaFree(d_grid);
     return WD_OK;
