@@ -129,9 +129,10 @@ class Engine:
     """One MoE stack on one GPU (wd_engine)."""
 
     def __init__(self, hidden, expert_ffn, n_experts, top_k, shared_ffn=0, n_layers=1, expert_type=TYPE_IQ3_S,
-                 w_scale=1.0, ep_rank=0, ep_size=1, device=0, cache_mib=0, rms_eps=1e-6, max_tokens=1):
+                 w_scale=1.0, ep_rank=0, ep_size=1, device=0, cache_mib=0, rms_eps=1e-6, max_tokens=1, down_type=None):
         self.cfg = Config(hidden, expert_ffn, shared_ffn, n_experts, top_k, n_layers, expert_type, expert_type,
-                          expert_type, w_scale, ep_rank, ep_size, max_tokens, device, cache_mib, rms_eps)
+                          expert_type if down_type is None else down_type, w_scale, ep_rank, ep_size, max_tokens,
+                          device, cache_mib, rms_eps)
         self.h = C.c_void_p()
         _check(lib().wd_engine_create(C.byref(self.cfg), C.byref(self.h)))
         self._keep = []

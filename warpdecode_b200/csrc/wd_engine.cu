@@ -132,7 +132,8 @@ struct wd_engine {
     int *pinned_ids = nullptr;
     CopyPool *copy_pool = nullptr;
     // device scratch
-    uint16_t *grid_packed = nullptr;
+    uint16_t *grid_packed = nullptr;        // IQ3_S codebook, packed
+    uint16_t *grid2_packed = nullptr;       // IQ2_S codebook, packed
     uint16_t *synth_lut = nullptr;
     unsigned *sync = nullptr;
     unsigned long long *stamps = nullptr;   // [n_sm][16] phase timestamps when profiling is on
@@ -174,7 +175,10 @@ int plan_shared_memory(wd_engine *e) {
         off = align_up(off + bytes, 128);
         return static_cast<unsigned>(o);
     };
-    p.off_tab = take(wd::kGridTableBytes);
+    const bool any3 = c.gate_type == WD_TYPE_IQ3_S || c.down_type == WD_TYPE_IQ3_S;
+    const bool any2 = c.gate_type == WD_TYPE_IQ2_S || c.down_type == WD_TYPE_IQ2_S;
+    p.off_tab = take(any3 ? wd::kGridTableBytes : 128);
+    p.off_tab2 = take(any2 ? wd::kIq2TableBytes : 128);
     p.off_xq0 = take(c.hidden);
     p.off_xd0 = take(nbh * 4);
     p.off_xk = take(e->nsb_h * wd::kActSbStride);
@@ -206,11 +210,11 @@ int plan_shared_memory(wd_engine *e) {
     const size_t rt_bytes = static_cast<size_t>(nbh) * 136;
     // stage A: phase-1 tasks, then gate/up tile pairs, then the selected experts' activations as floats
     const size_t stage_a = std::max(std::max(static_cast<size_t>(p.n1r + p.n1s) * 2 * rt_bytes,
-                                             static_cast<size_t>(p.n2) * 2 * wd::kIq3TileBytes),
+                                             static_cast<size_t>(p.n2) * 2 * p.gu_tile),
                                     static_cast<size_t>(c.top_k) * c.expert_ffn * 4);
     p.off_stage_a = take(stage_a);
     // stage B also holds the F32 shared gate vector during phase 1
-    p.off_stage_b = take(std::max(static_cast<size_t>(p.n3) * wd::kIq3TileBytes + static_cast<size_t>(p.nsd) * nbs * 136,
+    p.off_stage_b = take(std::max(static_cast<size_t>(p.n3) * p.d_tile + static_cast<size_t>(p.nsd) * nbs * 136,
                                   static_cast<size_t>(c.hidden) * 4));
     e->smem_bytes = off;
     if (e->smem_bytes > 227 * 1024)
@@ -239,15 +243,23 @@ int upload_f32(wd_engine *e, const float *host, size_t n, float **dev_out) {
     return WD_OK;
 }
 
+// ggml blocks -> tiles for either expert format (grid.y batches of `src_stride` / `dst_stride` bytes)
+static void launch_repack_iq(int type, const uint8_t *src, uint8_t *dst, long long nblocks, long long src_stride,
+                             long long dst_stride, unsigned batches, cudaStream_t s) {
+    const dim3 grid(static_cast<unsigned>((nblocks + 127) / 128), batches);
+    if (type == WD_TYPE_IQ2_S) wd::repack_iq2s_kernel<<<grid, 128, 0, s>>>(src, dst, nblocks, src_stride, dst_stride);
+    else wd::repack_iq3s_kernel<<<grid, 128, 0, s>>>(src, dst, nblocks, src_stride, dst_stride);
+}
+
 // Repack one expert's three ggml tensors (device pointers) into slot `slot`.
 int repack_expert_into_slot(wd_engine *e, const uint8_t *g, const uint8_t *u, const uint8_t *d, int slot,
                             cudaStream_t s) {
     uint8_t *dst = e->pool + static_cast<size_t>(slot) * e->slot_bytes;
     const long long nb_gu = static_cast<long long>(e->cfg.expert_ffn) * e->nsb_h;
     const long long nb_d = static_cast<long long>(e->cfg.hidden) * e->nsb_f;
-    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_gu + 127) / 128), 128, 0, s>>>(g, dst, nb_gu, 0, 0);
-    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_gu + 127) / 128), 128, 0, s>>>(u, dst + e->gate_bytes, nb_gu, 0, 0);
-    wd::repack_iq3s_kernel<<<static_cast<unsigned>((nb_d + 127) / 128), 128, 0, s>>>(d, dst + 2 * e->gate_bytes, nb_d, 0, 0);
+    launch_repack_iq(e->cfg.gate_type, g, dst, nb_gu, 0, 0, 1, s);
+    launch_repack_iq(e->cfg.gate_type, u, dst + e->gate_bytes, nb_gu, 0, 0, 1, s);
+    launch_repack_iq(e->cfg.down_type, d, dst + 2 * e->gate_bytes, nb_d, 0, 0, 1, s);
     WD_CUDA(cudaGetLastError());
     return WD_OK;
 }
@@ -442,8 +454,9 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
         return fail(WD_E_INVALID, "n_experts must be a multiple of 8, at most 1024");
     if (c.top_k < 1 || c.top_k > wd::kMaxK || c.top_k > c.n_experts) return fail(WD_E_INVALID, "top_k must be 1..16");
     if (c.n_layers < 1) return fail(WD_E_INVALID, "n_layers must be positive");
-    if (c.gate_type != WD_TYPE_IQ3_S || c.up_type != WD_TYPE_IQ3_S || c.down_type != WD_TYPE_IQ3_S)
-        return fail(WD_E_INVALID, "only IQ3_S expert tensors are supported by this build");
+    auto iq = [](int t) { return t == WD_TYPE_IQ3_S || t == WD_TYPE_IQ2_S; };
+    if (!iq(c.gate_type) || !iq(c.down_type) || c.up_type != c.gate_type)
+        return fail(WD_E_INVALID, "expert tensors must be IQ3_S or IQ2_S, gate and up of the same type");
     if (c.ep_size < 1 || c.ep_rank < 0 || c.ep_rank >= c.ep_size || c.n_experts % c.ep_size)
         return fail(WD_E_INVALID, "ep_rank/ep_size must partition n_experts evenly");
     if (c.max_tokens < 1 || c.max_tokens > 4) return fail(WD_E_INVALID, "max_tokens must be 1..4");
@@ -462,8 +475,8 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     e->nsb_f = c.expert_ffn / 256;
     e->e_count = c.n_experts / c.ep_size;
     e->e_first = c.ep_rank * e->e_count;
-    e->gate_bytes = static_cast<size_t>(c.expert_ffn) * e->nsb_h * 110;
-    e->down_bytes = static_cast<size_t>(c.hidden) * e->nsb_f * 110;
+    e->gate_bytes = static_cast<size_t>(c.expert_ffn) * e->nsb_h * wd::iq_block_bytes(c.gate_type);
+    e->down_bytes = static_cast<size_t>(c.hidden) * e->nsb_f * wd::iq_block_bytes(c.down_type);
     e->slot_bytes = align_up(2 * e->gate_bytes + e->down_bytes, 256);
     const int64_t owned = static_cast<int64_t>(e->e_count) * c.n_layers;
     if (c.cache_mib <= 0) {
@@ -503,6 +516,8 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     }
     WD_TRY(cudaMalloc(&e->grid_packed, sizeof(wd_iq3s_grid_packed)));
     WD_TRY(cudaMemcpy(e->grid_packed, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
+    WD_TRY(cudaMalloc(&e->grid2_packed, sizeof(wd_iq2s_grid_packed)));
+    WD_TRY(cudaMemcpy(e->grid2_packed, wd_iq2s_grid_packed, sizeof(wd_iq2s_grid_packed), cudaMemcpyHostToDevice));
     WD_TRY(cudaMalloc(&e->sync, 8192));
     WD_TRY(cudaMemset(e->sync, 0, 8192));
     const int H = c.hidden, F = c.expert_ffn, K = c.top_k, E = c.n_experts, SF = std::max(c.shared_ffn, 1);
@@ -551,6 +566,9 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     p.pool = e->pool; p.slot_bytes = e->slot_bytes;
     p.gate_off = 0; p.up_off = static_cast<unsigned>(e->gate_bytes); p.down_off = static_cast<unsigned>(2 * e->gate_bytes);
     p.grid_packed = e->grid_packed;
+    p.grid2_packed = e->grid2_packed;
+    p.gu_type = c.gate_type; p.d_type = c.down_type;
+    p.gu_tile = wd::iq_tile_bytes(c.gate_type); p.d_tile = wd::iq_tile_bytes(c.down_type);
     p.ids = e->ids; p.weights = e->weights; p.routed = e->routed;
     p.t_logits = e->tagged + tw_logits; p.t_shared_act = e->tagged + tw_shact; p.t_shared_gate = e->tagged + tw_shgate;
     p.t_act = e->tagged + tw_act; p.t_expert_out = e->tagged + tw_eo; p.t_shared_down = e->tagged + tw_shdown;
@@ -585,7 +603,7 @@ void wd_engine_destroy(wd_engine *e) {
         cudaFree(L.router); cudaFree(L.bias); cudaFree(L.gate_vec); cudaFree(L.sh_gate); cudaFree(L.sh_up);
         cudaFree(L.sh_down); cudaFree(L.norm); cudaFree(L.slot_of_expert);
     }
-    void *bufs[] = {e->pool, e->grid_packed, e->synth_lut, e->sync, e->tagged, e->ids, e->weights, e->routed, e->tok_ids, e->tok_weights,
+    void *bufs[] = {e->pool, e->grid_packed, e->grid2_packed, e->synth_lut, e->sync, e->tagged, e->ids, e->weights, e->routed, e->tok_ids, e->tok_weights,
                     e->x_buf, e->out_buf, e->residual_buf, e->staging, e->stamps, e->layer_table};
     for (void *b : bufs) cudaFree(b);
     delete e->copy_pool;
@@ -728,10 +746,9 @@ int wd_set_experts_device(wd_engine *e, int layer, const void *gate, const void 
         const long long nb_d = static_cast<long long>(e->cfg.hidden) * e->nsb_f;
         const long long gb = static_cast<long long>(e->gate_bytes), db = static_cast<long long>(e->down_bytes);
         const long long sb = static_cast<long long>(e->slot_bytes);
-        const dim3 grid_gu(static_cast<unsigned>((nb_gu + 127) / 128), e->e_count), grid_d(static_cast<unsigned>((nb_d + 127) / 128), e->e_count);
-        wd::repack_iq3s_kernel<<<grid_gu, 128, 0, e->stream>>>(g + e->e_first * gb, dst, nb_gu, gb, sb);
-        wd::repack_iq3s_kernel<<<grid_gu, 128, 0, e->stream>>>(u + e->e_first * gb, dst + gb, nb_gu, gb, sb);
-        wd::repack_iq3s_kernel<<<grid_d, 128, 0, e->stream>>>(d + e->e_first * db, dst + 2 * gb, nb_d, db, sb);
+        launch_repack_iq(e->cfg.gate_type, g + e->e_first * gb, dst, nb_gu, gb, sb, e->e_count, e->stream);
+        launch_repack_iq(e->cfg.gate_type, u + e->e_first * gb, dst + gb, nb_gu, gb, sb, e->e_count, e->stream);
+        launch_repack_iq(e->cfg.down_type, d + e->e_first * db, dst + 2 * gb, nb_d, db, sb, e->e_count, e->stream);
         WD_CUDA(cudaGetLastError());
     }
     for (int x = 0; x < e->e_count; ++x) {
@@ -1350,6 +1367,8 @@ static uint64_t sid(int layer, int which) { return static_cast<uint64_t>(layer) 
 int wd_synth_model(wd_engine *e, uint64_t seed, float sigma, float bias_sigma) {
     if (!e) return fail(WD_E_INVALID, "null engine");
     e->layer_table_dirty = true;
+    if (e->cfg.gate_type != WD_TYPE_IQ3_S || e->cfg.down_type != WD_TYPE_IQ3_S)
+        return fail(WD_E_STATE, "the device-side generator writes IQ3_S experts only");
     if (!e->resident) return fail(WD_E_STATE, "the device-side generator needs a pool that holds every owned expert");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     const wd_config &c = e->cfg;

@@ -54,7 +54,10 @@ struct MoeParams {
     const uint8_t *pool;         // slot pool base
     unsigned long long slot_bytes;
     unsigned gate_off, up_off, down_off;        // offsets of the three matrices inside a slot
-    const uint16_t *grid_packed; // packed codebook in global memory
+    const uint16_t *grid_packed; // packed IQ3_S codebook in global memory
+    const uint16_t *grid2_packed;// packed IQ2_S codebook
+    int gu_type, d_type;         // ggml type of the gate/up tensors and of the down tensor (IQ3_S or IQ2_S)
+    unsigned gu_tile, d_tile;    // bytes of one tile of 32 blocks of each
     // activations
     const float *x;              // [H] (used when residual == nullptr)
     float *residual;             // nullable: x = RMSNorm(residual) * norm_w, residual += out
@@ -79,7 +82,7 @@ struct MoeParams {
     unsigned *sync;              // [2] error word, [8] tag epoch (tag of layer `layer_begin` is epoch + 1; the
                                  // last CTA to leave advances it by the layers run), [9] count of CTAs that left
     // shared memory plan (byte offsets from the dynamic shared base; all 128-byte aligned)
-    unsigned off_tab, off_xq0, off_xd0, off_xk, off_xdk, off_actk, off_actd, off_shq, off_shd,
+    unsigned off_tab, off_tab2, off_xq0, off_xd0, off_xk, off_xdk, off_actk, off_actd, off_shq, off_shd,
         off_misc, off_scr, off_bar, off_slots, off_rowbuf, off_stage_a, off_stage_b;
     unsigned scr_bytes;          // per-warp transposition scratch
     unsigned scr_rows;           // float offset of the two 32-float row buffers inside it
@@ -97,7 +100,8 @@ extern __shared__ __align__(128) uint8_t wd_smem[];
 
 __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_constant__ MoeParams P) {
     uint8_t *sm = wd_smem;
-    uint8_t *tab = sm + P.off_tab;
+    uint8_t *tab = sm + P.off_tab;                                   // IQ3_S codebook, lane-private copies
+    uint8_t *tab2 = sm + P.off_tab2;                                 // IQ2_S codebook
     uint8_t *xq0 = sm + P.off_xq0;                                   // Q8_0 quants of x
     float *xd0 = reinterpret_cast<float *>(sm + P.off_xd0);          // Q8_0 scales of x
     uint8_t *xk = sm + P.off_xk;                                     // Q8_K quants of x, kActSbStride per superblock
@@ -143,7 +147,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         mbar_init(&bars[tid], 1);
         mbar_fence_init();
     }
-    build_grid_table(tab, P.grid_packed);          // first needed in phase 2
+    if (P.gu_type == kTypeIq3s || P.d_type == kTypeIq3s) build_grid_table(tab, P.grid_packed);   // first needed in phase 2
+    if (P.gu_type == kTypeIq2s || P.d_type == kTypeIq2s) build_iq2_table(tab2, P.grid2_packed);
     __syncthreads();
 
 #pragma unroll 1
