@@ -164,6 +164,25 @@ int wd_quantize_q8_K_host(const float *x, int n, void *blocks);
  * engine uses. `partials`, if not NULL, receives the int32 sums [rows][cols/256][8] (IQ types). */
 int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, float *y,
                    int32_t *partials);
+/* ---- model load from GGUF ------------------------------------------------------------------ */
+/* Read-only mapping of a GGUF file (v2/v3) with its metadata and tensor directory parsed: the part of
+ * GgufFile (src/gguf.hpp) and load_qwen38_runtime (src/qwen38_runtime.cuh:117-265) that the MoE path
+ * needs. wd_gguf_config fills the geometry fields of *cfg (hidden, expert_ffn, shared_ffn, n_experts,
+ * top_k, n_layers, the three expert tensor types, w_scale, rms_eps) from the qwen4exp.* keys
+ * (src/qwen38_layout.hpp:102-142) and the tensors' own extents, and leaves ep_rank, ep_size, max_tokens,
+ * device and cache_mib to the caller. wd_engine_load_gguf hands every layer's tensors
+ * (blk.N.ffn_gate_inp.weight [+ .bias], ffn_{gate,up,down}_exps.weight, ffn_gate_inp_shexp.weight,
+ * ffn_{gate,up,down}_shexp.weight, optional ffn_norm.weight; src/qwen38_moe.cuh:569-573, :601-612) to an
+ * engine created from that config. Expert tensors are used in place (a capped cache streams its misses
+ * straight from the mapping): close the file only after the engine is destroyed.
+ * wd_gguf_tensor returns a pointer into the mapping plus ggml type id and extents (GGUF order). */
+typedef struct wd_gguf wd_gguf;
+int wd_gguf_open(const char *path, wd_gguf **out);
+void wd_gguf_close(wd_gguf *g);
+int wd_gguf_config(const wd_gguf *g, wd_config *cfg);
+int wd_gguf_tensor(const wd_gguf *g, const char *name, const void **data, int *type, int64_t dims[4], int *n_dims);
+int wd_engine_load_gguf(wd_engine *e, const wd_gguf *g);
+
 /* ---- expert parallelism ------------------------------------------------------------------ */
 /* The reference runs on one GPU; its expert tables (src/expert_cache.cuh:2116-2146) shard by expert, and
  * these calls add that. An engine created with ep_size > 1 holds and computes only the experts of its

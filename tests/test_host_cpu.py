@@ -95,3 +95,74 @@ def test_gguf_writer_round_trip(tmp_path):
     assert int(t.tensor_type) == ol.TYPE_IQ3_S
     assert np.array_equal(np.asarray(t.data).reshape(-1).view(np.uint8), m["gate"])
     assert np.array_equal(np.asarray(names["blk.0.ffn_gate_inp_shexp.weight"].data).reshape(-1), m["shared_gate_vec"])
+
+
+def _tiny_gguf(tmp_path, layers=2, expert_type=None, bias=True, name="m.gguf"):
+    from warpdecode_b200 import synth
+    kw = {} if expert_type is None else {"expert_type": expert_type}
+    ms = [synth.make_moe_block(60 + l, 256, 256, 8, 2, 128, bias_sigma=1.0 if bias else 0.0, w_scale=2.5, **kw)
+          for l in range(layers)]
+    meta = {"general.architecture": "qwen4exp", "qwen4exp.block_count": layers, "qwen4exp.expert_count": 8,
+            "qwen4exp.expert_used_count": 2, "qwen4exp.embedding_length": 256,
+            "qwen4exp.expert_feed_forward_length": 256, "qwen4exp.expert_shared_feed_forward_length": 128,
+            "qwen4exp.expert_weights_scale": 2.5, "qwen4exp.attention.layer_norm_rms_epsilon": 1e-5,
+            "general.name": "tiny", "qwen4exp.rope.dimension_sections": [1, 2, 3]}
+    tensors = []
+    for l, m in enumerate(ms):
+        tensors += synth.moe_block_tensors(m, l)
+        tensors.append((f"blk.{l}.ffn_norm.weight", [256], ol.TYPE_F32, np.full(256, 1.0 + l, np.float32)))
+    path = str(tmp_path / name)
+    synth.write_gguf(path, meta, tensors)
+    return path, ms
+
+
+def test_gguf_reader_geometry_and_tensors_without_a_gpu(tmp_path):
+    """The C++ GGUF reader of the library (no CUDA call involved): geometry from keys and tensors, tensor
+    pointers into the mapping equal to the bytes that were written."""
+    import warpdecode_b200 as wd
+    path, ms = _tiny_gguf(tmp_path)
+    g = wd.Gguf(path)
+    c = g.config()
+    assert (c.hidden, c.expert_ffn, c.shared_ffn, c.n_experts, c.top_k, c.n_layers) == (256, 256, 128, 8, 2, 2)
+    assert (c.gate_type, c.up_type, c.down_type) == (ol.TYPE_IQ3_S,) * 3
+    assert c.w_scale == 2.5 and abs(c.rms_eps - 1e-5) < 1e-12
+    for l, m in enumerate(ms):
+        data, t, dims = g.tensor(f"blk.{l}.ffn_down_exps.weight")
+        assert (t, dims) == (ol.TYPE_IQ3_S, [256, 256, 8]) and np.array_equal(data, m["down"])
+        data, t, dims = g.tensor(f"blk.{l}.ffn_gate_inp.weight")
+        assert (t, dims) == (ol.TYPE_Q8_0, [256, 8]) and np.array_equal(data, m["router"])
+        data, t, dims = g.tensor(f"blk.{l}.ffn_gate_inp.bias")
+        assert t == ol.TYPE_F32 and np.array_equal(data.view(np.float32), m["router_bias"])
+    with pytest.raises(wd.WdError, match="no tensor"):
+        g.tensor("blk.9.ffn_gate_inp.weight")
+    g.close()
+    # IQ2_S experts are recognised by their tensor type
+    path2, _ = _tiny_gguf(tmp_path, layers=1, expert_type=ol.TYPE_IQ2_S, name="iq2.gguf")
+    g2 = wd.Gguf(path2)
+    assert g2.config().gate_type == ol.TYPE_IQ2_S and g2.config().n_layers == 1
+    g2.close()
+
+
+def test_gguf_reader_refuses_broken_files(tmp_path):
+    import warpdecode_b200 as wd
+    path, _ = _tiny_gguf(tmp_path, layers=1)
+    blob = open(path, "rb").read()
+    cases = {"magic": b"GGXX" + blob[4:], "version": blob[:4] + (9).to_bytes(4, "little") + blob[8:],
+             "short": blob[:200], "data": blob[:len(blob) // 2]}
+    for name, b in cases.items():
+        p = str(tmp_path / (name + ".gguf"))
+        open(p, "wb").write(b)
+        with pytest.raises(wd.WdError, match="GGUF|too short"):
+            wd.Gguf(p)
+    with pytest.raises(wd.WdError, match="cannot open"):
+        wd.Gguf(str(tmp_path / "missing.gguf"))
+    # a key that disagrees with the tensors
+    from warpdecode_b200 import synth
+    m = synth.make_moe_block(5, 256, 256, 8, 2, 128)
+    p = str(tmp_path / "liar.gguf")
+    synth.write_gguf(p, {"general.architecture": "qwen4exp", "qwen4exp.expert_used_count": 2,
+                         "qwen4exp.expert_count": 16}, synth.moe_block_tensors(m, 0))
+    g = wd.Gguf(p)
+    with pytest.raises(wd.WdError, match="disagrees"):
+        g.config()
+    g.close()

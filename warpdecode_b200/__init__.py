@@ -16,7 +16,7 @@ ROOT = os.path.dirname(HERE)
 LIB_PATH = os.path.join(HERE, "libwarpdecode_b200.so")
 SOURCES = [os.path.join(HERE, "csrc", f) for f in
            ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_moe_kernel_phases.inc", "wd_blocks.cuh", "wd_router.cuh",
-            "wd_formats.cuh", "wd_device.cuh", "wd_dense.cuh",
+            "wd_formats.cuh", "wd_device.cuh", "wd_dense.cuh", "wd_gguf.inc",
             "wd_grids.h")] + [os.path.join(ROOT, "include", "warpdecode_b200.h")]
 
 TYPE_F32, TYPE_Q4_0, TYPE_Q8_0, TYPE_IQ3_S, TYPE_IQ2_S = 0, 2, 8, 21, 22
@@ -108,6 +108,12 @@ def lib():
         L.wd_dense_pack_q8_0_device.argtypes = [vp, i, i, C.POINTER(vp), vp]
         L.wd_head_argmax_q8_0.argtypes = [vp, i, i, vp, vp, vp, vp, vp]
         L.wd_embed_q8_0.argtypes = [vp, i, i, vp, vp, vp]
+        L.wd_gguf_open.argtypes = [C.c_char_p, C.POINTER(vp)]
+        L.wd_gguf_close.argtypes = [vp]
+        L.wd_gguf_close.restype = None
+        L.wd_gguf_config.argtypes = [vp, C.POINTER(Config)]
+        L.wd_gguf_tensor.argtypes = [vp, C.c_char_p, C.POINTER(vp), C.POINTER(i), C.POINTER(C.c_int64), C.POINTER(i)]
+        L.wd_engine_load_gguf.argtypes = [vp, vp]
         _lib = L
     return _lib
 
@@ -125,8 +131,49 @@ def _ptr(a):
     return None if a is None else a.ctypes.data
 
 
+class Gguf:
+    """A mapped GGUF file (wd_gguf): geometry and tensor lookup without a GPU; Engine.from_gguf loads it."""
+
+    def __init__(self, path):
+        self.h = C.c_void_p()
+        _check(lib().wd_gguf_open(os.fsencode(path), C.byref(self.h)))
+
+    def config(self):
+        cfg = Config()
+        cfg.ep_size, cfg.max_tokens = 1, 1
+        _check(lib().wd_gguf_config(self.h, C.byref(cfg)))
+        return cfg
+
+    def tensor(self, name):
+        """(numpy uint8 view into the mapping, ggml type id, dims in GGUF order)."""
+        data, t, nd = C.c_void_p(), C.c_int(), C.c_int()
+        dims = (C.c_int64 * 4)()
+        _check(lib().wd_gguf_tensor(self.h, name.encode(), C.byref(data), C.byref(t), dims, C.byref(nd)))
+        dims = list(dims)[:nd.value]
+        n = int(np.prod(dims))
+        per = {0: (4, 1), 1: (2, 1), 2: (18, 32), 8: (34, 32), 20: (18, 32), 21: (110, 256), 22: (82, 256)}[t.value]
+        nbytes = n // per[1] * per[0]
+        buf = (C.c_uint8 * nbytes).from_address(data.value)
+        return np.frombuffer(buf, np.uint8), t.value, dims
+
+    def close(self):
+        if self.h:
+            lib().wd_gguf_close(self.h)
+            self.h = C.c_void_p()
+
+
 class Engine:
     """One MoE stack on one GPU (wd_engine)."""
+
+    @classmethod
+    def from_gguf(cls, gguf, **kw):
+        """Engine with the file's geometry, every layer loaded (the Gguf must outlive the engine)."""
+        c = gguf.config()
+        eng = cls(c.hidden, c.expert_ffn, c.n_experts, c.top_k, c.shared_ffn, c.n_layers, expert_type=c.gate_type,
+                  down_type=c.down_type, w_scale=c.w_scale, rms_eps=c.rms_eps, **kw)
+        _check(lib().wd_engine_load_gguf(eng.h, gguf.h))
+        eng._keep.append(gguf)
+        return eng
 
     def __init__(self, hidden, expert_ffn, n_experts, top_k, shared_ffn=0, n_layers=1, expert_type=TYPE_IQ3_S,
                  w_scale=1.0, ep_rank=0, ep_size=1, device=0, cache_mib=0, rms_eps=1e-6, max_tokens=1, down_type=None):

@@ -1555,3 +1555,5 @@ extern "C" int wd_matvec_iq3s_noalloc(const void *w_dev, int rows, int cols, con
     WD_CUDA(cudaGetLastError());
     return WD_OK;
 }
+
+#include "wd_gguf.inc"
