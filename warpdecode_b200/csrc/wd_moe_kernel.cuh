@@ -207,7 +207,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         // sum of squares as a perfect binary tree over consecutive elements, in double
         const int epl = P.H >= kThreads ? P.H / kThreads : 1;
         double ss = 0.0;
-        float rv[16];
+        float rv[16], nw[16];
+        // the norm weights do not depend on the residual: fetched before the wait, used after it
+#pragma unroll
+        for (int i = 0; i < 16; ++i) nw[i] = (L.norm_w && i < epl && tid * epl < P.H) ? L.norm_w[tid * epl + i] : 1.0f;
         if (tid * epl < P.H) {
             double loc[16];
             if (layer == P.layer_begin) {
@@ -262,7 +265,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
             for (int i = 0; i < 16; ++i) {
                 if (i < epl) {
                     float v = __fmul_rn(rv[i], scale);
-                    if (L.norm_w) v = __fmul_rn(v, L.norm_w[tid * epl + i]);
+                    if (L.norm_w) v = __fmul_rn(v, nw[i]);
                     xf[tid * epl + i] = v;
                 }
             }
