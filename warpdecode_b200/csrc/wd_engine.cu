@@ -2,6 +2,8 @@
 // and repack, the expert slot cache, launches, CUDA-graph capture of the per-token stack.
 #include "../../include/warpdecode_b200.h"
 
+#include <unistd.h>
+
 #include <algorithm>
 #include <condition_variable>
 #include <cstdio>
@@ -50,6 +52,10 @@ struct Layer {
     const uint8_t *h_gate = nullptr, *h_up = nullptr, *h_down = nullptr;   // retained host tensors
     bool have_router = false, have_shared = false, have_experts = false;
     bool host_pinned = false;                   // the retained host tensors are page-locked: no bounce copy
+    // When the tensors came from a mapped file, misses are read with pread at these offsets instead of through the
+    // mapping (no page faults on the copy threads; ExpertFileMap + ExpertPreadPool, src/expert_cache.cuh:204-508).
+    int fd = -1;
+    uint64_t file_gate = 0, file_up = 0, file_down = 0;
 };
 
 // A few host threads that copy missed experts from the caller's (pageable or mapped) tensors into the
@@ -374,10 +380,23 @@ int acquire_selected(wd_engine *e, int layer, cudaStream_t s) {
             uint8_t *pin = e->miss_pinned + m * one;
             const uint8_t *g = L.h_gate + static_cast<size_t>(x) * gb, *u = L.h_up + static_cast<size_t>(x) * gb,
                           *d = L.h_down + static_cast<size_t>(x) * db;
+            const int fd = L.fd;
+            const uint64_t fg = L.file_gate + static_cast<uint64_t>(x) * gb, fu = L.file_up + static_cast<uint64_t>(x) * gb,
+                           fdn = L.file_down + static_cast<uint64_t>(x) * db;
             e->copy_pool->submit([=] {
-                memcpy(pin, g, gb);
-                memcpy(pin + gb, u, gb);
-                memcpy(pin + 2 * gb, d, db);
+                // file-backed tensors: positional reads; a short or failed read falls back to the mapping
+                auto fetch = [&](uint8_t *to, const uint8_t *from, uint64_t off, size_t n) {
+                    size_t done = 0;
+                    while (fd >= 0 && done < n) {
+                        const ssize_t r = pread(fd, to + done, n - done, static_cast<off_t>(off + done));
+                        if (r <= 0) break;
+                        done += static_cast<size_t>(r);
+                    }
+                    if (done < n) memcpy(to + done, from + done, n - done);
+                };
+                fetch(pin, g, fg, gb);
+                fetch(pin + gb, u, fu, gb);
+                fetch(pin + 2 * gb, d, fdn, db);
             });
         }
     }
