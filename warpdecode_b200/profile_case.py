@@ -20,7 +20,8 @@ PHASES = ["issue_p1", "x_wait_quant", "q8_rows", "gather_logits", "select.router
 
 
 def phase_row(st, with_period):
-    d = [(st[:, ORDER[i + 1]] - st[:, ORDER[i]]).mean() for i in range(len(ORDER) - 1)]
+    ok = st[:, 11] >= st[:, 6]          # CTAs without a gate/up tile in this layer leave stamp 11 unset
+    d = [(st[ok, ORDER[i + 1]] - st[ok, ORDER[i]]).mean() for i in range(len(ORDER) - 1)]
     d.append((st[:, 10] - st[:, 0]).mean())                         # a CTA's time inside the layer
     d.append((st[:, 14] - st[:, 0]).mean() if with_period else 0)   # start of this layer to start of the next
     return d
