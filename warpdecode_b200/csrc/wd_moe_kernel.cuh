@@ -79,6 +79,7 @@ struct MoeParams {
     float *weights;              // [K]
     float *routed;               // [H]
     unsigned long long *stamps;  // nullable: [cta][kStampStride] globaltimer values at phase boundaries (profiling)
+    unsigned *host_status;       // nullable, host memory: receives the error word when the launch ends
     unsigned *sync;              // [2] error word, [8] tag epoch (tag of layer `layer_begin` is epoch + 1; the
                                  // last CTA to leave advances it by the layers run), [9] count of CTAs that left
     // shared memory plan (byte offsets from the dynamic shared base; all 128-byte aligned)
@@ -296,6 +297,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         if (atomicAdd(P.sync + 9, 1u) == static_cast<unsigned>(ncta) - 1u) {
             P.sync[9] = 0u;
             P.sync[8] = epoch + static_cast<uint32_t>(P.layer_end - P.layer_begin);
+            if (P.host_status) *P.host_status = *reinterpret_cast<volatile unsigned *>(err);
         }
     }
 }
