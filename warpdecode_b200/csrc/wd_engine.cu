@@ -136,6 +136,9 @@ struct wd_engine {
     cudaEvent_t fill_done = nullptr;
     uint8_t *miss_pinned = nullptr, *miss_staging = nullptr;
     int *pinned_ids = nullptr;
+    // model load (all experts resident): two half-rings of kLoadBatch experts each, pinned and on the device
+    uint8_t *load_pinned = nullptr, *load_staging = nullptr;
+    cudaEvent_t load_done[2] = {nullptr, nullptr};
     unsigned *host_status = nullptr;  // pinned, device-visible: the last CTA of a launch leaves the status word here
     CopyPool *copy_pool = nullptr;
     // device scratch
@@ -637,6 +640,10 @@ void wd_engine_destroy(wd_engine *e) {
     if (e->copy_stream) cudaStreamDestroy(e->copy_stream);
     if (e->pinned) cudaFreeHost(e->pinned);
     if (e->host_status) cudaFreeHost(e->host_status);
+    if (e->load_pinned) cudaFreeHost(e->load_pinned);
+    cudaFree(e->load_staging);
+    for (cudaEvent_t ev : e->load_done)
+        if (ev) cudaEventDestroy(ev);
     if (e->stream) cudaStreamDestroy(e->stream);
     delete e;
 }
@@ -723,7 +730,87 @@ static int bind_slot(wd_engine *e, int layer, int expert, int slot) {
     return WD_OK;
 }
 
+// Every owned expert of a layer from host tensors (memory or file) into its slots, pipelined: host threads fill one
+// pinned half-ring (memcpy, or pread for file-backed tensors) while the GPU copies and repacks the other
+// (ExpertPreadPool + ExpertStagePath of the reference's load path, src/expert_cache.cuh:357-508, :1166-1254).
+static constexpr int kLoadBatch = 8;
+
+static int load_layer_resident(wd_engine *e, int layer) {
+    Layer &L = e->layers[layer];
+    const size_t gb = e->gate_bytes, db = e->down_bytes, one = 2 * gb + db;
+    if (!e->load_pinned) {
+        WD_CUDA(cudaMallocHost(&e->load_pinned, 2 * kLoadBatch * one));
+        WD_CUDA(cudaMalloc(&e->load_staging, 2 * kLoadBatch * one));
+        for (cudaEvent_t &ev : e->load_done) WD_CUDA(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        if (!e->copy_pool) e->copy_pool = new CopyPool(std::max(1, std::min(8, static_cast<int>(std::thread::hardware_concurrency()))));
+    }
+    cudaStream_t s = e->stream;
+    const long long nb_gu = static_cast<long long>(e->cfg.expert_ffn) * e->nsb_h, nb_d = static_cast<long long>(e->cfg.hidden) * e->nsb_f;
+    bool used[2] = {false, false};
+    for (int x0 = 0, half = 0; x0 < e->e_count; x0 += kLoadBatch, half ^= 1) {
+        const int n = std::min(kLoadBatch, e->e_count - x0);
+        uint8_t *pin = e->load_pinned + static_cast<size_t>(half) * kLoadBatch * one;
+        uint8_t *st = e->load_staging + static_cast<size_t>(half) * kLoadBatch * one;
+        if (used[half]) WD_CUDA(cudaEventSynchronize(e->load_done[half]));     // the GPU is done with this half
+        for (int m = 0; m < n; ++m) {
+            const int x = e->e_first + x0 + m;
+            uint8_t *to = pin + static_cast<size_t>(m) * one;
+            const uint8_t *g = L.h_gate + static_cast<size_t>(x) * gb, *u = L.h_up + static_cast<size_t>(x) * gb,
+                          *d = L.h_down + static_cast<size_t>(x) * db;
+            const int fd = L.fd;
+            const uint64_t fg = L.file_gate + static_cast<uint64_t>(x) * gb, fu = L.file_up + static_cast<uint64_t>(x) * gb,
+                           fdn = L.file_down + static_cast<uint64_t>(x) * db;
+            e->copy_pool->submit([=] {
+                auto fetch = [&](uint8_t *dst, const uint8_t *from, uint64_t off, size_t bytes) {
+                    size_t done = 0;
+                    while (fd >= 0 && done < bytes) {
+                        const ssize_t r = pread(fd, dst + done, bytes - done, static_cast<off_t>(off + done));
+                        if (r <= 0) break;
+                        done += static_cast<size_t>(r);
+                    }
+                    if (done < bytes) memcpy(dst + done, from + done, bytes - done);
+                };
+                fetch(to, g, fg, gb);
+                fetch(to + gb, u, fu, gb);
+                fetch(to + 2 * gb, d, fdn, db);
+            });
+        }
+        e->copy_pool->wait_all();
+        WD_CUDA(cudaMemcpyAsync(st, pin, static_cast<size_t>(n) * one, cudaMemcpyHostToDevice, s));
+        uint8_t *dst = e->pool + static_cast<size_t>(layer * e->e_count + x0) * e->slot_bytes;
+        const long long so = static_cast<long long>(one), sb = static_cast<long long>(e->slot_bytes);
+        launch_repack_iq(e->cfg.gate_type, st, dst, nb_gu, so, sb, n, s);
+        launch_repack_iq(e->cfg.gate_type, st + gb, dst + gb, nb_gu, so, sb, n, s);
+        launch_repack_iq(e->cfg.down_type, st + 2 * gb, dst + 2 * gb, nb_d, so, sb, n, s);
+        WD_CUDA(cudaGetLastError());
+        WD_CUDA(cudaEventRecord(e->load_done[half], s));
+        used[half] = true;
+    }
+    std::vector<int> slots(e->cfg.n_experts, -1);
+    for (int x = 0; x < e->e_count; ++x) {
+        const int expert = e->e_first + x, slot = layer * e->e_count + x;
+        slots[expert] = slot;
+        const int64_t key = (static_cast<int64_t>(layer) << 32) | static_cast<uint32_t>(expert);
+        e->slot_key[slot] = key;
+        e->key_slot[key] = slot;
+    }
+    L.h_slot = slots;
+    WD_CUDA(cudaMemcpyAsync(L.slot_of_expert, slots.data(), slots.size() * sizeof(int), cudaMemcpyHostToDevice, s));
+    WD_CUDA(cudaStreamSynchronize(s));
+    return WD_OK;
+}
+
+static int set_experts_from(wd_engine *e, int layer, const void *gate, const void *up, const void *down, int fd,
+                            uint64_t file_gate, uint64_t file_up, uint64_t file_down);
+
 int wd_set_experts(wd_engine *e, int layer, const void *gate, const void *up, const void *down) {
+    return set_experts_from(e, layer, gate, up, down, -1, 0, 0, 0);
+}
+
+// fd >= 0: the tensors are also readable from that file at the given offsets (positional reads instead of copies
+// out of a mapping)
+static int set_experts_from(wd_engine *e, int layer, const void *gate, const void *up, const void *down, int fd,
+                            uint64_t file_gate, uint64_t file_up, uint64_t file_down) {
     int rc = check_layer(e, layer);
     if (rc) return rc;
     if (!gate || !up || !down) return fail(WD_E_INVALID, "null expert tensor");
@@ -733,6 +820,10 @@ int wd_set_experts(wd_engine *e, int layer, const void *gate, const void *up, co
     L.h_up = static_cast<const uint8_t *>(up);
     L.h_down = static_cast<const uint8_t *>(down);
     L.have_experts = true;
+    L.fd = fd;
+    L.file_gate = file_gate;
+    L.file_up = file_up;
+    L.file_down = file_down;
     {
         cudaPointerAttributes at{};
         L.host_pinned = true;
@@ -741,15 +832,8 @@ int wd_set_experts(wd_engine *e, int layer, const void *gate, const void *up, co
         }
         cudaGetLastError();
     }
-    if (e->resident) {
-        for (int x = 0; x < e->e_count; ++x) {
-            const int expert = e->e_first + x;
-            const int slot = layer * e->e_count + x;
-            if ((rc = fill_slot_from_host(e, layer, expert, slot))) return rc;
-            if ((rc = bind_slot(e, layer, expert, slot))) return rc;
-            touch_slot(e, slot);
-        }
-    }
+    e->layer_table_dirty = true;
+    if (e->resident) return load_layer_resident(e, layer);
     return WD_OK;
 }
 
