@@ -86,7 +86,7 @@ __device__ __noinline__ float q8_task_row(const uint8_t *task, int nb, const uin
     const uint8_t *wq = task + r * 128 + l * 16;
     const uint8_t *wd = task + nb * 128 + r * nb * 2;
     float acc = 0.0f;
-#pragma unroll 2
+#pragma unroll 4
     for (int g = 0; g < (nb >> 2); ++g) {
         const uint4 w = *reinterpret_cast<const uint4 *>(wq + g * 512);
         const uint4 a = *reinterpret_cast<const uint4 *>(xq + (g * 8 + l) * 16);
@@ -102,6 +102,39 @@ __device__ __noinline__ float q8_task_row(const uint8_t *task, int nb, const uin
         acc = __fmaf_rn(s3, static_cast<float>(dp4a_s8(w.w, a.w, 0)), acc);
     }
     return hsum8_lanes(acc);
+}
+
+// Two row tasks against the same activation in one pass (the shared expert's gate and up rows): the two fmaf
+// chains are independent, so their loads and integer dots overlap. Same operations as two q8_task_row calls.
+__device__ __noinline__ void q8_task_row2(const uint8_t *task_a, const uint8_t *task_b, int nb, const uint8_t *xq,
+                                          const float *xd, int lane, float &out_a, float &out_b) {
+    const int r = lane >> 3, l = lane & 7;
+    const uint8_t *wqa = task_a + r * 128 + l * 16, *wqb = task_b + r * 128 + l * 16;
+    const uint8_t *wda = task_a + nb * 128 + r * nb * 2, *wdb = task_b + nb * 128 + r * nb * 2;
+    float acc_a = 0.0f, acc_b = 0.0f;
+#pragma unroll 2
+    for (int g = 0; g < (nb >> 2); ++g) {
+        const uint4 wa = *reinterpret_cast<const uint4 *>(wqa + g * 512);
+        const uint4 wb = *reinterpret_cast<const uint4 *>(wqb + g * 512);
+        const uint4 a = *reinterpret_cast<const uint4 *>(xq + (g * 8 + l) * 16);
+        const uint2 da = *reinterpret_cast<const uint2 *>(wda + g * 8);
+        const uint2 db = *reinterpret_cast<const uint2 *>(wdb + g * 8);
+        const float4 dx = *reinterpret_cast<const float4 *>(xd + g * 4);
+        const float sa0 = __fmul_rn(half_bits_to_float(da.x & 0xffffu), dx.x), sb0 = __fmul_rn(half_bits_to_float(db.x & 0xffffu), dx.x);
+        const float sa1 = __fmul_rn(half_bits_to_float(da.x >> 16), dx.y), sb1 = __fmul_rn(half_bits_to_float(db.x >> 16), dx.y);
+        const float sa2 = __fmul_rn(half_bits_to_float(da.y & 0xffffu), dx.z), sb2 = __fmul_rn(half_bits_to_float(db.y & 0xffffu), dx.z);
+        const float sa3 = __fmul_rn(half_bits_to_float(da.y >> 16), dx.w), sb3 = __fmul_rn(half_bits_to_float(db.y >> 16), dx.w);
+        acc_a = __fmaf_rn(sa0, static_cast<float>(dp4a_s8(wa.x, a.x, 0)), acc_a);
+        acc_b = __fmaf_rn(sb0, static_cast<float>(dp4a_s8(wb.x, a.x, 0)), acc_b);
+        acc_a = __fmaf_rn(sa1, static_cast<float>(dp4a_s8(wa.y, a.y, 0)), acc_a);
+        acc_b = __fmaf_rn(sb1, static_cast<float>(dp4a_s8(wb.y, a.y, 0)), acc_b);
+        acc_a = __fmaf_rn(sa2, static_cast<float>(dp4a_s8(wa.z, a.z, 0)), acc_a);
+        acc_b = __fmaf_rn(sb2, static_cast<float>(dp4a_s8(wb.z, a.z, 0)), acc_b);
+        acc_a = __fmaf_rn(sa3, static_cast<float>(dp4a_s8(wa.w, a.w, 0)), acc_a);
+        acc_b = __fmaf_rn(sb3, static_cast<float>(dp4a_s8(wb.w, a.w, 0)), acc_b);
+    }
+    out_a = hsum8_lanes(acc_a);
+    out_b = hsum8_lanes(acc_b);
 }
 
 // ggml_vec_dot_f32 in its AVX2 order by one warp: lane t owns elements = t (mod 32)
