@@ -97,6 +97,44 @@ constexpr int kMiscLogits = 0, kMiscProbs = 1024, kMiscGsum = 2048, kMiscRed = 2
               kMiscChamp = 2208, kMiscDsum = 2272, kMiscIds = 2288, kMiscW = 2304, kMiscLocJ = 2320,
               kMiscLocSlot = 2336, kMiscLocN = 2352, kMiscSlots = 2368, kMiscSharedAct = 2400;
 
+// Phase 0 of one thread: its EPL consecutive residual values (plain memory in the first layer of a launch, the
+// previous layer's tagged words otherwise, polled together with the progress word), the norm weights, and the
+// binary-tree sum of their squares in double.
+template <int EPL>
+__device__ __forceinline__ double p0_gather(const float *plain, const float *norm_w, const tagged_t *src, const tagged_t *progress,
+                                            bool mine, bool first, bool chk, uint32_t tag, unsigned *err, float rv[16],
+                                            float nw[16]) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) nw[i] = (norm_w && mine) ? norm_w[i] : 1.0f;      // fetched before the wait, used after it
+    if (!mine) return 0.0;
+    if (first) {
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) rv[i] = plain[i];
+    } else {
+        tagged_t w[EPL];
+        for (unsigned it = 0;; ++it) {
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) w[i] = ld_tagged(src + i);
+            const tagged_t wp = chk ? ld_tagged(progress) : 0;
+            unsigned bad = chk & (static_cast<int32_t>(static_cast<uint32_t>(wp >> 32) - (tag - 2u)) < 0);
+#pragma unroll
+            for (int i = 0; i < EPL; ++i) bad |= static_cast<uint32_t>(w[i] >> 32) != tag - 1u;
+            if (!bad) break;
+            if (wait_expired(it, err)) break;
+        }
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) rv[i] = __uint_as_float(static_cast<uint32_t>(w[i]));
+    }
+    double loc[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) loc[i] = __dmul_rn(static_cast<double>(rv[i]), static_cast<double>(rv[i]));
+#pragma unroll
+    for (int w = 1; w < EPL; w <<= 1)
+#pragma unroll
+        for (int i = 0; i + w < EPL; i += 2 * w) loc[i] = __dadd_rn(loc[i], loc[i + w]);
+    return loc[0];
+}
+
 extern __shared__ __align__(128) uint8_t wd_smem[];
 
 __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_constant__ MoeParams P) {
@@ -206,44 +244,21 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     // ---- phase 0: x -> shared (with the optional RMSNorm prologue), then both quantisations --
     if (P.residual != nullptr) {
         // sum of squares as a perfect binary tree over consecutive elements, in double
-        const int epl = P.H >= kThreads ? P.H / kThreads : 1;
-        double ss = 0.0;
+        const int epl = P.H >= kThreads ? P.H / kThreads : 1;       // 1, 2, 4, 8 or 16 (H = 256 * 2^n)
+        const bool mine = tid * epl < P.H;
+        const bool first = layer == P.layer_begin;
+        // the previous layer's combine publishes the updated residual row by row; the same round trips check that
+        // no CTA is still inside the layer whose exchange buffers this layer overwrites
+        const bool chk = layer >= P.layer_begin + 2 && tid < ncta;
+        const tagged_t *src = P.t_residual + (par ^ 1u) * P.H + tid * epl;
         float rv[16], nw[16];
-        // the norm weights do not depend on the residual: fetched before the wait, used after it
-#pragma unroll
-        for (int i = 0; i < 16; ++i) nw[i] = (L.norm_w && i < epl && tid * epl < P.H) ? L.norm_w[tid * epl + i] : 1.0f;
-        if (tid * epl < P.H) {
-            double loc[16];
-            if (layer == P.layer_begin) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) rv[i] = i < epl ? P.residual[tid * epl + i] : 0.0f;
-            } else {
-                // the previous layer's combine publishes the updated residual row by row; the same round trips
-                // check that no CTA is still inside the layer whose exchange buffers this layer overwrites
-                const bool chk = layer >= P.layer_begin + 2 && tid < ncta;
-                tagged_t w[16] = {};
-                const tagged_t *src = P.t_residual + (par ^ 1u) * P.H + tid * epl;
-                for (unsigned it = 0;; ++it) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        if (i < epl) w[i] = ld_tagged(src + i);
-                    const tagged_t wp = chk ? ld_tagged(P.t_progress + tid) : 0;
-                    unsigned bad = chk & (static_cast<int32_t>(static_cast<uint32_t>(wp >> 32) - (tag - 2u)) < 0);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) bad |= (i < epl) & (static_cast<uint32_t>(w[i] >> 32) != tag - 1u);
-                    if (!bad) break;
-                    if (wait_expired(it, err)) break;
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i) rv[i] = i < epl ? __uint_as_float(static_cast<uint32_t>(w[i])) : 0.0f;
-            }
-#pragma unroll
-            for (int i = 0; i < 16; ++i) loc[i] = __dmul_rn(static_cast<double>(rv[i]), static_cast<double>(rv[i]));
-#pragma unroll
-            for (int w = 1; w < 16; w <<= 1)
-#pragma unroll
-                for (int i = 0; i + w < 16; i += 2 * w) loc[i] = __dadd_rn(loc[i], loc[i + w]);
-            ss = loc[0];
+        double ss;
+        switch (epl) {      // the element count per thread as a compile-time constant: no predicated-off work
+            case 1: ss = p0_gather<1>(P.residual + tid * epl, L.norm_w ? L.norm_w + tid * epl : nullptr, src, P.t_progress + tid, mine, first, chk, tag, err, rv, nw); break;
+            case 2: ss = p0_gather<2>(P.residual + tid * epl, L.norm_w ? L.norm_w + tid * epl : nullptr, src, P.t_progress + tid, mine, first, chk, tag, err, rv, nw); break;
+            case 4: ss = p0_gather<4>(P.residual + tid * epl, L.norm_w ? L.norm_w + tid * epl : nullptr, src, P.t_progress + tid, mine, first, chk, tag, err, rv, nw); break;
+            case 8: ss = p0_gather<8>(P.residual + tid * epl, L.norm_w ? L.norm_w + tid * epl : nullptr, src, P.t_progress + tid, mine, first, chk, tag, err, rv, nw); break;
+            default: ss = p0_gather<16>(P.residual + tid * epl, L.norm_w ? L.norm_w + tid * epl : nullptr, src, P.t_progress + tid, mine, first, chk, tag, err, rv, nw); break;
         }
 #pragma unroll
         for (int s = 1; s < 32; s <<= 1) ss = __dadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, s));
@@ -261,14 +276,13 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
             __ddiv_rn(1.0, __dsqrt_rn(__dadd_rn(P.inv_h != 0.0 ? __dmul_rn(tot[0], P.inv_h)
                                                                : __ddiv_rn(tot[0], static_cast<double>(P.H)),
                                                 static_cast<double>(P.eps)))));
-        if (tid * epl < P.H) {
+        if (mine) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                if (i < epl) {
-                    float v = __fmul_rn(rv[i], scale);
-                    if (L.norm_w) v = __fmul_rn(v, nw[i]);
-                    xf[tid * epl + i] = v;
-                }
+                if (i >= epl) break;
+                float v = __fmul_rn(rv[i], scale);
+                if (L.norm_w) v = __fmul_rn(v, nw[i]);
+                xf[tid * epl + i] = v;
             }
         }
     } else {
