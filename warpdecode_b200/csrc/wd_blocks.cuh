@@ -112,7 +112,7 @@ __device__ __noinline__ void q8_task_row2(const uint8_t *task_a, const uint8_t *
     const uint8_t *wqa = task_a + r * 128 + l * 16, *wqb = task_b + r * 128 + l * 16;
     const uint8_t *wda = task_a + nb * 128 + r * nb * 2, *wdb = task_b + nb * 128 + r * nb * 2;
     float acc_a = 0.0f, acc_b = 0.0f;
-#pragma unroll 2
+#pragma unroll 8
     for (int g = 0; g < (nb >> 2); ++g) {
         const uint4 wa = *reinterpret_cast<const uint4 *>(wqa + g * 512);
         const uint4 wb = *reinterpret_cast<const uint4 *>(wqb + g * 512);

@@ -216,27 +216,50 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     const int n_st = P.SF >> 2;                    // shared gate/up tasks (4 row pairs each)
     const unsigned rt_bytes = static_cast<unsigned>(nbh) * 136u;
     const unsigned a1_slot = 2u * rt_bytes;        // staging slot of phase 1
-    if (tid == 0) {
+    if (warp == 0) {
+        // lanes issue together: 0-7 router tasks, 8-15 shared gate tasks, 16-23 their up halves (same barrier),
+        // 24 the slot table, 25 the shared gate vector (one CTA); eight slots of each kind per round
         fence_proxy_async();        // the staging buffers were last read by ordinary loads (previous layer)
-        int s = 0;
+        const int k = lane & 7, grp = lane >> 3;
+        const int rounds = (max(static_cast<int>(P.n1r), static_cast<int>(P.n1s)) + 7) >> 3;
 #pragma unroll 1
-        for (int t = cta; t < n_rt; t += ncta, ++s) {
-            mbar_expect_tx(&bars[s], rt_bytes);
-            bulk_load(stage_a + s * a1_slot, L.router_w + static_cast<size_t>(t) * rt_bytes, rt_bytes, &bars[s]);
-        }
-        s = P.n1r;
-#pragma unroll 1
-        for (int t = ncta - 1 - cta; t < n_st; t += ncta, ++s) {
-            mbar_expect_tx(&bars[s], 2u * rt_bytes);
-            bulk_load(stage_a + s * a1_slot, L.sh_gate + static_cast<size_t>(t) * rt_bytes, rt_bytes, &bars[s]);
-            bulk_load(stage_a + s * a1_slot + rt_bytes, L.sh_up + static_cast<size_t>(t) * rt_bytes, rt_bytes, &bars[s]);
-        }
-        mbar_expect_tx(&bars[kMaxBars - 2], static_cast<unsigned>(P.E) * 4u);
-        bulk_load(slot_tab, L.slot_of_expert, static_cast<unsigned>(P.E) * 4u, &bars[kMaxBars - 2]);
-        // the one CTA that computes the shared gate scalar brings the F32 gate vector into stage B
-        if (P.SF > 0 && cta == ncta / 2) {
-            mbar_expect_tx(&bars[kMaxBars - 1], static_cast<unsigned>(P.H) * 4u);
-            bulk_load(stage_b, L.sh_gate_vec, static_cast<unsigned>(P.H) * 4u, &bars[kMaxBars - 1]);
+        for (int r = 0; r < max(rounds, 1); ++r) {
+            const int s = r * 8 + k;
+            bool copy = false, expect = false;
+            uint8_t *dst = stage_a;
+            const uint8_t *src = L.router_w;
+            unsigned bytes = rt_bytes, tx = rt_bytes;
+            uint64_t *bar = bars;
+            if (grp == 0) {
+                const int t = cta + s * ncta;
+                copy = expect = s < static_cast<int>(P.n1r) && t < n_rt;
+                dst = stage_a + s * a1_slot;
+                src = L.router_w + static_cast<size_t>(copy ? t : 0) * rt_bytes;
+                bar = &bars[s];
+            } else if (grp <= 2) {
+                const int t = ncta - 1 - cta + s * ncta;
+                copy = s < static_cast<int>(P.n1s) && t < n_st;
+                expect = copy && grp == 1;
+                dst = stage_a + (P.n1r + s) * a1_slot + (grp == 2 ? rt_bytes : 0u);
+                src = (grp == 1 ? L.sh_gate : L.sh_up) + static_cast<size_t>(copy ? t : 0) * rt_bytes;
+                tx = 2u * rt_bytes;
+                bar = &bars[P.n1r + s];
+            } else if (r == 0 && k == 0) {
+                copy = expect = true;
+                dst = reinterpret_cast<uint8_t *>(slot_tab);
+                src = reinterpret_cast<const uint8_t *>(L.slot_of_expert);
+                bytes = tx = static_cast<unsigned>(P.E) * 4u;
+                bar = &bars[kMaxBars - 2];
+            } else if (r == 0 && k == 1) {
+                // the one CTA that computes the shared gate scalar brings the F32 gate vector into stage B
+                copy = expect = P.SF > 0 && cta == ncta / 2;
+                dst = stage_b;
+                src = reinterpret_cast<const uint8_t *>(L.sh_gate_vec);
+                bytes = tx = static_cast<unsigned>(P.H) * 4u;
+                bar = &bars[kMaxBars - 1];
+            }
+            if (expect) mbar_expect_tx(bar, tx);
+            if (copy) bulk_load(dst, src, bytes, bar);
         }
     }
     WD_STAMP(1);
