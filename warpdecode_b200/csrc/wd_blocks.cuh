@@ -2,9 +2,10 @@
 // F32 dot and the float side of an IQ3_S tile.
 //
 // Code size matters here as much as instruction count: the layer kernel runs each instruction only a
-// few times per launch, so it is bound by instruction fetch unless its code stays small. The helpers
-// that are used from several places are therefore real functions (__noinline__) and loops that do not
-// need unrolling carry `#pragma unroll 1`.
+// few times per launch, so instruction fetch is part of its critical path. Which helpers are real
+// functions (__noinline__: the tile decoders, used from three places) and which are inlined, and how far
+// each loop is unrolled, was settled by same-device A/B timing of the whole layer stack, not by rule;
+// loops that do not need unrolling carry `#pragma unroll 1`.
 #pragma once
 
 #include "wd_formats.cuh"
@@ -21,7 +22,7 @@ constexpr int kMaxExperts = 1024;
 // ---------------------------------------------------------------------------------------------
 // Q8_0 of n floats (n multiple of 128) held in shared `xf`; output: quants in task layout
 // [g][l][16 B] (word i = values 4l..4l+3 of block 4g+i) and per-block scales as the f16-rounded float.
-__device__ __noinline__ void quantize_q8_0_cta(const float *xf, int n, uint8_t *q_out, float *d_out) {
+__device__ __forceinline__ void quantize_q8_0_cta(const float *xf, int n, uint8_t *q_out, float *d_out) {
     const int nchunks = n >> 2;    // groups of four values; 8 chunks form a block
 #pragma unroll 1
     for (int ch = threadIdx.x; ch < ((nchunks + 31) & ~31); ch += blockDim.x) {
@@ -51,7 +52,7 @@ __device__ __noinline__ void quantize_q8_0_cta(const float *xf, int n, uint8_t *
 }
 
 // Q8_K of one 256-value superblock by one warp: lane quantises src[8*lane .. 8*lane+7].
-__device__ __noinline__ void quantize_q8_K_warp(const float *src, int lane, uint8_t *q_out_sb, float *d_out) {
+__device__ __forceinline__ void quantize_q8_K_warp(const float *src, int lane, uint8_t *q_out_sb, float *d_out) {
     const float4 a = *reinterpret_cast<const float4 *>(src + lane * 8);
     const float4 b = *reinterpret_cast<const float4 *>(src + lane * 8 + 4);
     const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
@@ -81,7 +82,7 @@ __device__ __noinline__ void quantize_q8_K_warp(const float *src, int lane, uint
 // One fmaf(d_w * d_x, int_dot, lane_acc) per block, blocks ascending, then the 8-lane reduction
 // (src/qwen38_cpu_moe.cuh:424-440, device twin src/qwen38_hc.cuh:420).
 // ---------------------------------------------------------------------------------------------
-__device__ __noinline__ float q8_task_row(const uint8_t *task, int nb, const uint8_t *xq, const float *xd, int lane) {
+__device__ __forceinline__ float q8_task_row(const uint8_t *task, int nb, const uint8_t *xq, const float *xd, int lane) {
     const int r = lane >> 3, l = lane & 7;
     const uint8_t *wq = task + r * 128 + l * 16;
     const uint8_t *wd = task + nb * 128 + r * nb * 2;
@@ -106,7 +107,7 @@ __device__ __noinline__ float q8_task_row(const uint8_t *task, int nb, const uin
 
 // Two row tasks against the same activation in one pass (the shared expert's gate and up rows): the two fmaf
 // chains are independent, so their loads and integer dots overlap. Same operations as two q8_task_row calls.
-__device__ __noinline__ void q8_task_row2(const uint8_t *task_a, const uint8_t *task_b, int nb, const uint8_t *xq,
+__device__ __forceinline__ void q8_task_row2(const uint8_t *task_a, const uint8_t *task_b, int nb, const uint8_t *xq,
                                           const float *xd, int lane, float &out_a, float &out_b) {
     const int r = lane >> 3, l = lane & 7;
     const uint8_t *wqa = task_a + r * 128 + l * 16, *wqb = task_b + r * 128 + l * 16;

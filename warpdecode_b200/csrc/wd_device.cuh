@@ -167,7 +167,7 @@ constexpr uint32_t kKeyNegInf = 0x007fffffu;   // order_key(-inf): nothing at or
 // scalar math in the reference's order
 // ---------------------------------------------------------------------------------------------
 // One lane of ggml's AVX2 ggml_v_expf (src/qwen38_exact_math.cuh:94-115, src/qwen38_cpu_moe.cuh:816-834).
-__device__ __noinline__ float exp_ggml(float x) {
+__device__ __forceinline__ float exp_ggml(float x) {
     const float r = 0x1.8p23f;
     const float z = __fmaf_rn(x, 0x1.715476p+0f, r);
     const float n = __fsub_rn(z, r);

@@ -32,7 +32,7 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {
     return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
 }
 
-__device__ __noinline__ void router_select_cta(float l0, float l1, int E, int K, float w_scale, const RouterScratch &S,
+__device__ __forceinline__ void router_select_cta(float l0, float l1, int E, int K, float w_scale, const RouterScratch &S,
                                                   int *ids_out, float *w_out, unsigned long long *stage_stamps = nullptr) {
     // profiling only: thread 0 leaves a global-timer value after each stage
 #define WD_RSTAMP(i)                                                       \
