@@ -92,6 +92,10 @@ struct MoeParams {
 };
 
 // float offsets inside the `misc` region once phase 1 is over (before that it holds x as floats)
+#ifndef WD_MAX_SLICES
+#define WD_MAX_SLICES 2
+#endif
+constexpr int kMaxSlices = WD_MAX_SLICES;   // slices per gate/up tile left over after a whole round (measured: 2 beats 4 beats 8)
 constexpr int kLeftInts = 2048;     // = kMiscGsum: the x floats / router candidates region, reused in phase 2
 constexpr int kMiscLogits = 0, kMiscProbs = 1024, kMiscGsum = 2048, kMiscRed = 2176, kMiscTop = 2192,
               kMiscChamp = 2208, kMiscDsum = 2272, kMiscIds = 2288, kMiscW = 2304, kMiscLocJ = 2320,
