@@ -139,6 +139,57 @@ __device__ __forceinline__ double p0_gather(const float *plain, const float *nor
     return loc[0];
 }
 
+// The bulk copies of phase 1 of one layer, issued by the lanes of one warp together: lanes 0-7 router tasks,
+// 8-15 shared gate tasks, 16-23 their up halves (same barrier), 24 the slot table, 25 the shared gate vector (one
+// CTA); eight slots of each kind per round. `tasks` / `tables` select the two groups.
+__device__ __forceinline__ void issue_phase1_copies(const MoeParams &P, const LayerDev &L, int lane, int cta, int ncta,
+                                                    unsigned rt_bytes, uint8_t *stage_a, uint8_t *stage_b, int *slot_tab,
+                                                    uint64_t *bars, bool tasks, bool tables) {
+    const int n_rt = P.E >> 2, n_st = P.SF >> 2;
+    const unsigned a1_slot = 2u * rt_bytes;
+    const int k = lane & 7, grp = lane >> 3;
+    const int rounds = tasks ? (max(static_cast<int>(P.n1r), static_cast<int>(P.n1s)) + 7) >> 3 : 1;
+#pragma unroll 1
+    for (int r = 0; r < max(rounds, 1); ++r) {
+        const int s = r * 8 + k;
+        bool copy = false, expect = false;
+        uint8_t *dst = stage_a;
+        const uint8_t *src = L.router_w;
+        unsigned bytes = rt_bytes, tx = rt_bytes;
+        uint64_t *bar = bars;
+        if (grp == 0) {
+            const int t = cta + s * ncta;
+            copy = expect = tasks && s < static_cast<int>(P.n1r) && t < n_rt;
+            dst = stage_a + s * a1_slot;
+            src = L.router_w + static_cast<size_t>(copy ? t : 0) * rt_bytes;
+            bar = &bars[s];
+        } else if (grp <= 2) {
+            const int t = ncta - 1 - cta + s * ncta;
+            copy = tasks && s < static_cast<int>(P.n1s) && t < n_st;
+            expect = copy && grp == 1;
+            dst = stage_a + (P.n1r + s) * a1_slot + (grp == 2 ? rt_bytes : 0u);
+            src = (grp == 1 ? L.sh_gate : L.sh_up) + static_cast<size_t>(copy ? t : 0) * rt_bytes;
+            tx = 2u * rt_bytes;
+            bar = &bars[P.n1r + s];
+        } else if (r == 0 && k == 0) {
+            copy = expect = tables;
+            dst = reinterpret_cast<uint8_t *>(slot_tab);
+            src = reinterpret_cast<const uint8_t *>(L.slot_of_expert);
+            bytes = tx = static_cast<unsigned>(P.E) * 4u;
+            bar = &bars[kMaxBars - 2];
+        } else if (r == 0 && k == 1) {
+            // the one CTA that computes the shared gate scalar brings the F32 gate vector into stage B
+            copy = expect = tables && P.SF > 0 && cta == ncta / 2;
+            dst = stage_b;
+            src = reinterpret_cast<const uint8_t *>(L.sh_gate_vec);
+            bytes = tx = static_cast<unsigned>(P.H) * 4u;
+            bar = &bars[kMaxBars - 1];
+        }
+        if (expect) mbar_expect_tx(bar, tx);
+        if (copy) bulk_load(dst, src, bytes, bar);
+    }
+}
+
 extern __shared__ __align__(128) uint8_t wd_smem[];
 
 __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_constant__ MoeParams P) {
@@ -220,51 +271,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     const int n_st = P.SF >> 2;                    // shared gate/up tasks (4 row pairs each)
     const unsigned rt_bytes = static_cast<unsigned>(nbh) * 136u;
     const unsigned a1_slot = 2u * rt_bytes;        // staging slot of phase 1
+    // Phase-1 weights do not depend on data: from the second layer of a launch on they were requested by the
+    // previous layer (see the down phase), so only the first layer asks for them here.
     if (warp == 0) {
-        // lanes issue together: 0-7 router tasks, 8-15 shared gate tasks, 16-23 their up halves (same barrier),
-        // 24 the slot table, 25 the shared gate vector (one CTA); eight slots of each kind per round
         fence_proxy_async();        // the staging buffers were last read by ordinary loads (previous layer)
-        const int k = lane & 7, grp = lane >> 3;
-        const int rounds = (max(static_cast<int>(P.n1r), static_cast<int>(P.n1s)) + 7) >> 3;
-#pragma unroll 1
-        for (int r = 0; r < max(rounds, 1); ++r) {
-            const int s = r * 8 + k;
-            bool copy = false, expect = false;
-            uint8_t *dst = stage_a;
-            const uint8_t *src = L.router_w;
-            unsigned bytes = rt_bytes, tx = rt_bytes;
-            uint64_t *bar = bars;
-            if (grp == 0) {
-                const int t = cta + s * ncta;
-                copy = expect = s < static_cast<int>(P.n1r) && t < n_rt;
-                dst = stage_a + s * a1_slot;
-                src = L.router_w + static_cast<size_t>(copy ? t : 0) * rt_bytes;
-                bar = &bars[s];
-            } else if (grp <= 2) {
-                const int t = ncta - 1 - cta + s * ncta;
-                copy = s < static_cast<int>(P.n1s) && t < n_st;
-                expect = copy && grp == 1;
-                dst = stage_a + (P.n1r + s) * a1_slot + (grp == 2 ? rt_bytes : 0u);
-                src = (grp == 1 ? L.sh_gate : L.sh_up) + static_cast<size_t>(copy ? t : 0) * rt_bytes;
-                tx = 2u * rt_bytes;
-                bar = &bars[P.n1r + s];
-            } else if (r == 0 && k == 0) {
-                copy = expect = true;
-                dst = reinterpret_cast<uint8_t *>(slot_tab);
-                src = reinterpret_cast<const uint8_t *>(L.slot_of_expert);
-                bytes = tx = static_cast<unsigned>(P.E) * 4u;
-                bar = &bars[kMaxBars - 2];
-            } else if (r == 0 && k == 1) {
-                // the one CTA that computes the shared gate scalar brings the F32 gate vector into stage B
-                copy = expect = P.SF > 0 && cta == ncta / 2;
-                dst = stage_b;
-                src = reinterpret_cast<const uint8_t *>(L.sh_gate_vec);
-                bytes = tx = static_cast<unsigned>(P.H) * 4u;
-                bar = &bars[kMaxBars - 1];
-            }
-            if (expect) mbar_expect_tx(bar, tx);
-            if (copy) bulk_load(dst, src, bytes, bar);
-        }
+        issue_phase1_copies(P, L, lane, cta, ncta, rt_bytes, stage_a, stage_b, slot_tab, bars, layer == P.layer_begin, true);
     }
     WD_STAMP(1);
 
