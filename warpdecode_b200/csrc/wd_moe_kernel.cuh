@@ -141,10 +141,11 @@ __device__ __forceinline__ double p0_gather(const float *plain, const float *nor
 
 // The bulk copies of phase 1 of one layer, issued by the lanes of one warp together: lanes 0-7 router tasks,
 // 8-15 shared gate tasks, 16-23 their up halves (same barrier), 24 the slot table, 25 the shared gate vector (one
-// CTA); eight slots of each kind per round. `tasks` / `tables` select the two groups.
+// CTA); eight slots of each kind per round. `tasks`: the row tasks and the slot table (their buffers are free from
+// the previous layer's down phase on); `gate_vec`: the shared gate vector, whose buffer (stage B) is not.
 __device__ __forceinline__ void issue_phase1_copies(const MoeParams &P, const LayerDev &L, int lane, int cta, int ncta,
                                                     unsigned rt_bytes, uint8_t *stage_a, uint8_t *stage_b, int *slot_tab,
-                                                    uint64_t *bars, bool tasks, bool tables) {
+                                                    uint64_t *bars, bool tasks, bool gate_vec) {
     const int n_rt = P.E >> 2, n_st = P.SF >> 2;
     const unsigned a1_slot = 2u * rt_bytes;
     const int k = lane & 7, grp = lane >> 3;
@@ -172,14 +173,14 @@ __device__ __forceinline__ void issue_phase1_copies(const MoeParams &P, const La
             tx = 2u * rt_bytes;
             bar = &bars[P.n1r + s];
         } else if (r == 0 && k == 0) {
-            copy = expect = tables;
+            copy = expect = tasks;
             dst = reinterpret_cast<uint8_t *>(slot_tab);
             src = reinterpret_cast<const uint8_t *>(L.slot_of_expert);
             bytes = tx = static_cast<unsigned>(P.E) * 4u;
             bar = &bars[kMaxBars - 2];
         } else if (r == 0 && k == 1) {
             // the one CTA that computes the shared gate scalar brings the F32 gate vector into stage B
-            copy = expect = tables && P.SF > 0 && cta == ncta / 2;
+            copy = expect = gate_vec && P.SF > 0 && cta == ncta / 2;
             dst = stage_b;
             src = reinterpret_cast<const uint8_t *>(L.sh_gate_vec);
             bytes = tx = static_cast<unsigned>(P.H) * 4u;
