@@ -249,9 +249,16 @@ def main():
         "cpu_baseline": cpu,
         "clocks": clocks_summary(samples),
     }
-    print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+    # the JSON line must be the LAST line on stdout: native libraries (NCCL's version banner) write through C stdio,
+    # which is block-buffered on a pipe, so that buffer is emptied first
+    import ctypes
+    try:
+        ctypes.CDLL(None).fflush(None)
+    except Exception:
+        pass
+    print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":
