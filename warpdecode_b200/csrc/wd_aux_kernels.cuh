@@ -198,7 +198,7 @@ __global__ void test_router_kernel(const float *logits, int E, int K, float w_sc
     __shared__ float pr[kMaxExperts];
     __shared__ float gsum[kMaxExperts / 8];
     __shared__ float red[kWarps];
-    __shared__ float first[1];
+    __shared__ float first[2];
     __shared__ uint32_t cand[2 * kWarps * kMaxK];
     __shared__ int sid[kMaxK];
     __shared__ float sw[kMaxK];

@@ -24,8 +24,10 @@ struct RouterScratch {
     float *gsum;        // [E/8]
     uint32_t *cand;     // [2][kWarps][kMaxK]: keys, then indices
     float *red;         // [kWarps]
-    float *first;       // [1] probability of expert 0 (what a rung reports when nothing is selectable)
+    float *first;       // [2] probability of expert 0 (what a rung reports when nothing is selectable); repeat flag
 };
+
+constexpr int kShortList = 4;    // entries per warp list in the first attempt of the rungs
 
 // inverse of order_key for keys above kKeyNegInf
 __device__ __forceinline__ float key_to_float(uint32_t key) {
@@ -111,55 +113,76 @@ __device__ __forceinline__ void router_select_cta(float l0, float l1, int E, int
         if (h1) S.probs[e1] = p1;
     }
     if (tid == 0) *S.first = p0;
-    // stage 1: this warp's k best, in rung order
-    uint32_t k0 = h0 ? order_key(p0) : 0u, k1 = h1 ? order_key(p1) : 0u;
+    // stage 1: this warp's best, in rung order. The lists are first cut at kShortList entries: ten rungs over 512
+    // experts rarely take more than that from one warp, and the merge notices when it would have needed more
+    // (then everything is repeated with full lists).
+    const uint32_t key0 = h0 ? order_key(p0) : 0u, key1 = h1 ? order_key(p1) : 0u;
     uint32_t *ck = S.cand, *ci = S.cand + kWarps * kMaxK;
+    uint32_t my_id = 0u;
+    float my_p = 0.0f;
+    int depth = min(K, kShortList);
 #pragma unroll 1
-    for (int j = 0; j < K; ++j) {
-        const uint32_t m = __reduce_max_sync(0xffffffffu, max(k0, k1));
-        const uint32_t cand = (k0 == m) ? static_cast<uint32_t>(e0) : ((k1 == m) ? static_cast<uint32_t>(e1) : 0xffffffffu);
-        const uint32_t mi = __reduce_min_sync(0xffffffffu, cand);
-        if (lane == 0) {
-            ck[warp * kMaxK + j] = m;
-            ci[warp * kMaxK + j] = mi;
-        }
-        if (m <= kKeyNegInf) {          // nothing selectable is left in this warp: the rest of its list is empty
-            if (lane == 0)
+    for (;;) {
+        uint32_t k0 = key0, k1 = key1;
 #pragma unroll 1
-                for (int q = j + 1; q < K; ++q) ck[warp * kMaxK + q] = 0u;
-            break;
+        for (int j = 0; j < depth; ++j) {
+            const uint32_t m = __reduce_max_sync(0xffffffffu, max(k0, k1));
+            const uint32_t cand = (k0 == m) ? static_cast<uint32_t>(e0) : ((k1 == m) ? static_cast<uint32_t>(e1) : 0xffffffffu);
+            const uint32_t mi = __reduce_min_sync(0xffffffffu, cand);
+            if (lane == 0) {
+                ck[warp * kMaxK + j] = m;
+                ci[warp * kMaxK + j] = mi;
+            }
+            if (m <= kKeyNegInf) {          // nothing selectable is left in this warp: the rest of its list is empty
+                if (lane == 0)
+#pragma unroll 1
+                    for (int q = j + 1; q < depth; ++q) ck[warp * kMaxK + q] = 0u;
+                break;
+            }
+            if (mi == static_cast<uint32_t>(e0)) k0 = 0u;
+            if (mi == static_cast<uint32_t>(e1)) k1 = 0u;
         }
-        if (mi == static_cast<uint32_t>(e0)) k0 = 0u;
-        if (mi == static_cast<uint32_t>(e1)) k1 = 0u;
+        __syncthreads();
+        WD_RSTAMP(3)
+        // stage 2: warp 0 merges the lists; lane w holds the head of warp w's list
+        if (warp == 0) {
+            int ptr = 0;
+            bool starved = false;       // a rung was decided while this lane's (cut) list had run out
+            const float p_first = *S.first;
+            // key of the last entry of a list that was cut while it still had selectable entries (else 0): what
+            // the warp did not list is at most this
+            const uint32_t last_key = (lane < kWarps && depth < K) ? ck[lane * kMaxK + depth - 1] : 0u;
+            const bool cut = last_key > kKeyNegInf;
+#pragma unroll 1
+            for (int j = 0; j < K; ++j) {
+                const bool live = lane < kWarps && ptr < depth;
+                const uint32_t hk = live ? ck[lane * kMaxK + ptr] : 0u;
+                const uint32_t hi = live ? ci[lane * kMaxK + ptr] : 0xffffffffu;
+                const uint32_t M = __reduce_max_sync(0xffffffffu, hk);
+                uint32_t win = __reduce_min_sync(0xffffffffu, hk == M ? hi : 0xffffffffu);
+                starved = starved || (cut && ptr == depth && M <= last_key);    // an unlisted entry could have won
+                float p;
+                if (M <= kKeyNegInf) {      // nothing selectable: the rung keeps expert 0
+                    win = 0u;
+                    p = p_first;
+                } else {
+                    p = key_to_float(M);
+                    if (static_cast<uint32_t>(lane) == ((win & (kThreads - 1)) >> 5)) ++ptr;
+                }
+                if (lane == j) {
+                    my_id = win;
+                    my_p = p;
+                }
+            }
+            const int again = __any_sync(0xffffffffu, starved);
+            if (lane == 0) S.first[1] = again ? 1.0f : 0.0f;
+        }
+        __syncthreads();
+        if (depth == K || S.first[1] == 0.0f) break;
+        depth = K;
+        __syncthreads();        // everyone has read the flag before the lists are rewritten
     }
-    __syncthreads();
-    WD_RSTAMP(3)
-    // stage 2: warp 0 merges the lists; lane w holds the head of warp w's list
     if (warp == 0) {
-        int ptr = 0;
-        uint32_t my_id = 0u;
-        float my_p = 0.0f;
-        const float p_first = *S.first;
-#pragma unroll 1
-        for (int j = 0; j < K; ++j) {
-            const bool live = lane < kWarps && ptr < K;
-            const uint32_t hk = live ? ck[lane * kMaxK + ptr] : 0u;
-            const uint32_t hi = live ? ci[lane * kMaxK + ptr] : 0xffffffffu;
-            const uint32_t M = __reduce_max_sync(0xffffffffu, hk);
-            uint32_t win = __reduce_min_sync(0xffffffffu, hk == M ? hi : 0xffffffffu);
-            float p;
-            if (M <= kKeyNegInf) {      // nothing selectable: the rung keeps expert 0
-                win = 0u;
-                p = p_first;
-            } else {
-                p = key_to_float(M);
-                if (static_cast<uint32_t>(lane) == ((win & (kThreads - 1)) >> 5)) ++ptr;
-            }
-            if (lane == j) {
-                my_id = win;
-                my_p = p;
-            }
-        }
         if (lane == 0) { WD_RSTAMP(4) }
         // the reference adds the picked probabilities one by one into a double; as for the softmax sum, a
         // shuffle tree gives the same bits whenever every partial sum is exact, else the serial order is replayed
