@@ -62,6 +62,29 @@ def test_router_topk_many_seeds(wd, oracle):
             assert np.array_equal(ids, io) and np.array_equal(bits(w), bits(wo)), (kind, rep)
 
 
+def test_router_topk_when_one_warp_holds_most_of_the_winners(wd, oracle):
+    """The selection first lists four candidates per 32 consecutive experts and repeats with full lists when
+    the merge would have needed a fifth: rows whose winners crowd into one such group (0..k of them, with and
+    without ties) must give the oracle's ids and weights either way."""
+    for e in (512, 256, 1024):
+        for rep in range(40):
+            rng = np.random.Generator(np.random.PCG64(77000 + rep))
+            k = [10, 8, 16, 5, 3][rep % 5]
+            logits = rng.standard_normal(e).astype(np.float32)
+            group = int(rng.integers(0, e // 32))
+            crowd = rep % (k + 1)                                   # how many winners sit in the group
+            lanes = rng.choice(32, size=min(crowd, 32), replace=False)
+            boost = 6.0 + rng.standard_normal(len(lanes)).astype(np.float32)
+            if rep % 4 == 3:
+                boost[:] = 6.0                                       # equal winners: the lower index first
+            logits[group * 32 + lanes] = boost
+            if rep % 7 == 6:                                         # and the same value once outside the group
+                logits[(group * 32 + 40) % e] = 6.0
+            p, ids, w = wd.router_topk(logits, k, 1.0)
+            po, io, wo = oracle.router(logits, k, 1.0)
+            assert np.array_equal(ids, io) and np.array_equal(bits(w), bits(wo)), (e, rep)
+
+
 @pytest.mark.parametrize("cols", [256, 512, 1024, 2048])
 def test_iq3s_matvec_partials_and_rows(wd, oracle, cols):
     rng = np.random.Generator(np.random.PCG64(300 + cols))
