@@ -48,15 +48,13 @@ __device__ __forceinline__ void router_select_cta(float l0, float l1, int E, int
     const bool h0 = e0 < E, h1 = e1 < E;
     if (!h0) l0 = -INFINITY;
     if (!h1) l1 = -INFINITY;
-    float mx = fmaxf(l0, l1);
-#pragma unroll
-    for (int s = 1; s < 32; s <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
-    if (lane == 0) S.red[warp] = mx;
+    // running max through the order-preserving integer key (one redux per level instead of a shuffle tree). NaN maps
+    // to key 0 and is passed over as fmaxf would; if every logit is NaN the result is a NaN, as with fmaxf.
+    uint32_t mk = __reduce_max_sync(0xffffffffu, max(order_key(l0), order_key(l1)));
+    if (lane == 0) S.cand[warp] = mk;
     __syncthreads();
-    mx = lane < kWarps ? S.red[lane] : -INFINITY;
-#pragma unroll
-    for (int s = 1; s < kWarps; s <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
-    mx = __shfl_sync(0xffffffffu, mx, 0);
+    mk = __reduce_max_sync(0xffffffffu, lane < kWarps ? S.cand[lane] : 0u);
+    const float mx = __uint_as_float((mk & 0x80000000u) ? (mk ^ 0x80000000u) : ~mk);
     WD_RSTAMP(0)
     float p0 = h0 ? exp_ggml(__fsub_rn(l0, mx)) : 0.0f;
     float p1 = h1 ? exp_ggml(__fsub_rn(l1, mx)) : 0.0f;
