@@ -15,8 +15,10 @@ namespace wd {
 // The rungs run in two stages with one __syncthreads between them: every warp lists its own k best
 // (key, index) pairs in rung order with two redux steps per rung; warp 0 then merges the 16 sorted
 // lists, one head per lane. The order (larger key, then lower index) is total, so the merged rungs are
-// exactly the rungs over all experts.
-// Shared scratch: gsum[E/8], red[kWarps], cand[2][kWarps][kMaxK] u32, first[1];
+// exactly the rungs over all experts. The lists are first cut at kShortList entries; when the merge decides a
+// rung while a cut list has run out and something that list left out could have won, both stages are repeated
+// with lists of k entries.
+// Shared scratch: gsum[E/8], red[kWarps] (unused), cand[2][kWarps][kMaxK] u32, first[2];
 // probs[E] is optional (nullptr: not stored).
 // ---------------------------------------------------------------------------------------------
 struct RouterScratch {
