@@ -148,6 +148,8 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes);
 int wd_set_profiling(wd_engine *e, int on);
 /* Number of SMs = CTAs of the layer kernel. */
 int wd_sm_count(const wd_engine *e);
+/* Name of the kernel a stack step of this engine launches (for bench records). */
+const char *wd_kernel_name(const wd_engine *e);
 /* Device error word of the last forward (0 = none) and a reset of the barrier state. */
 int wd_device_status(wd_engine *e, int *status);
 
@@ -240,7 +242,8 @@ int wd_head_argmax_q8_0(void *packed_dev, int rows, int cols, const float *x_dev
  * allocator): w_dev (ggml layout), x_dev, y_dev are DEVICE buffers of the caller; the only scratch is
  * a fixed 8 MiB array inside the library that every GPU loading it holds until exit, so rows*cols/256*110
  * must not exceed 8 MiB - 1 KiB (larger is refused with a message). Work is enqueued on `stream`.
- * The first call on each device looks up the array's device address; make that call before any stream
+ * The first call on each device looks up the array's device address and uploads the 1 KiB codebook into
+ * its front with a blocking copy (later calls only enqueue kernels); make that call before any stream
  * capture. All calls share the array, which keeps the last call's contents (nothing needs clearing:
  * every byte read is first rewritten); calls that overlap on the GPU race on it. */
 int wd_matvec_iq3s_noalloc(const void *w_dev, int rows, int cols, const float *x_dev, float *y_dev,

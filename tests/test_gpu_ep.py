@@ -84,6 +84,47 @@ def test_two_ranks_reproduce_one_gpu_bit_for_bit(wd, oracle, torch2):
         e.close()
 
 
+def test_a_rank_that_owns_nothing_and_launches_late_is_waited_for(wd, oracle, torch2):
+    """Every selected expert belongs to rank 0 (router bias), so nothing rank 0 computes depends on rank 1: without
+    flow control it would run layers and whole launches ahead and overwrite rows in rank 1's buffer that rank 1 has
+    not combined yet. Rank 1 starts each step late (a host-side sleep, well under the one-second wait limit); both
+    ranks must still produce the single-GPU bits, with no status raised."""
+    import time
+    torch = torch2
+    ms, norms, rng = _blocks_and_norms()
+    for m in ms:
+        b = np.zeros(E, np.float32)
+        b[:E // 2] = 100.0                                  # the top-k all come from rank 0's half
+        m["router_bias"] = b
+    single = _engine(wd, ms, norms, 0, 1, 0)
+    ranks = [_engine(wd, ms, norms, r, 2, r) for r in range(2)]
+    ranks[0].ep_connect_local([ranks[1]])
+    ranks[1].ep_connect_local([ranks[0]])
+    res = rng.standard_normal(H).astype(np.float32)
+    n_steps = 3
+    want = []
+    cur = res
+    for step in range(n_steps):
+        cur = single.stack_step_host(cur)
+        assert max(single.tap("ids")) < E // 2
+        want.append(cur)
+    dev = [torch.from_numpy(res).to(f"cuda:{r}") for r in range(2)]
+    torch.cuda.synchronize(0), torch.cuda.synchronize(1)
+    # rank 0 is given all its launches at once; rank 1 follows late, launch by launch
+    for step in range(n_steps):
+        ranks[0].stack_step_device(dev[0].data_ptr())
+    for step in range(n_steps):
+        time.sleep(0.15)
+        ranks[1].stack_step_device(dev[1].data_ptr())
+    torch.cuda.synchronize(0), torch.cuda.synchronize(1)
+    for r in range(2):
+        assert ranks[r].device_status() == 0
+        assert np.array_equal(bits(dev[r].cpu().numpy()), bits(want[-1])), r
+    for e in ranks + [single]:
+        e.ep_disconnect()
+        e.close()
+
+
 def test_unconnected_ranks_return_partial_sums(wd, oracle, torch2):
     ms, norms, rng = _blocks_and_norms()
     single = _engine(wd, ms, norms, 0, 1, 0)

@@ -4,8 +4,9 @@ It exists for callers that cannot call cudaMalloc while decoding: when the exper
 nearly all of HBM an allocation can fail, and even a successful one synchronises the device in the
 middle of a token. Its scratch is a fixed array inside the library, shared by every call, so the
 test makes two calls in a row with different matrices and checks each result, bit for bit, against
-the ordinary entry point (wd_matvec_host), which allocates its own buffers: stale contents of the
-shared array must never leak into a later result. The file name keeps it last in collection order.
+the ordinary entry point (wd_matvec_host), which allocates its own buffers, and against the CPU oracle's
+row dot on the same block bytes: stale contents of the shared array must never leak into a later
+result. The file name keeps it last in collection order.
 """
 import ctypes as C
 
@@ -17,7 +18,7 @@ import oracle_lib as ol
 pytestmark = pytest.mark.gpu
 
 
-def test_no_alloc_matvec_matches_allocating_entry_point_twice():
+def test_no_alloc_matvec_matches_allocating_entry_point_twice(oracle):
     import torch
     import warpdecode_b200 as wd
     lib = wd.lib()
@@ -37,6 +38,11 @@ def test_no_alloc_matvec_matches_allocating_entry_point_twice():
         torch.cuda.synchronize()
         got = y_d.cpu().numpy()
         assert np.array_equal(ol.fbits(got), ol.fbits(want)), (rows, cols)
+        # and the oracle itself, row by row, on the same bytes (not only the sibling entry point)
+        xk = oracle.quantize_q8_K(x)
+        rb = cols // 256 * 110
+        ref = np.array([oracle.row(ol.TYPE_IQ3_S, w[r * rb:(r + 1) * rb], xk, cols) for r in range(rows)], np.float32)
+        assert np.array_equal(ol.fbits(got), ol.fbits(ref)), (rows, cols)
 
 
 def test_no_alloc_matvec_refuses_more_than_its_fixed_scratch():

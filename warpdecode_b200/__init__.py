@@ -93,6 +93,9 @@ def lib():
         L.wd_quantize_q8_K_host.argtypes = [vp, i, vp]
         L.wd_matvec_host.argtypes = [i, vp, i, i, vp, vp, vp]
         L.wd_synth_model.argtypes = [vp, C.c_uint64, C.c_float, C.c_float]
+        L.wd_synth_tensor_device.argtypes = [i, i, i, C.c_float, C.c_uint64, C.c_uint64, vp, vp]
+        L.wd_kernel_name.argtypes = [vp]
+        L.wd_kernel_name.restype = C.c_char_p
         L.wd_synth_expert_host.argtypes = [vp, C.c_uint64, C.c_float, i, i, vp, vp, vp]
         L.wd_synth_dense_host.argtypes = [vp, C.c_uint64, C.c_float, C.c_float, i, vp, vp, vp, vp, vp, vp]
         L.wd_ep_export.argtypes = [vp, vp]
@@ -300,6 +303,10 @@ class Engine:
         _check(lib().wd_read_tap(self.h, TAPS[name], token, _ptr(a), a.nbytes))
         return a
 
+    def kernel_name(self):
+        """Name of the kernel that this engine's stack step launches."""
+        return lib().wd_kernel_name(self.h).decode()
+
     def set_profiling(self, on):
         _check(lib().wd_set_profiling(self.h, int(on)))
 
@@ -405,6 +412,11 @@ class HeadQ8_0:
 
 def embed_q8_0(table_dev_ptr, rows, cols, token_ptr, out_ptr, stream=None):
     _check(lib().wd_embed_q8_0(table_dev_ptr, rows, cols, token_ptr, out_ptr, stream))
+
+
+def synth_tensor_device(t, rows, cols, sigma, seed, stream_id, dst_ptr, stream=None):
+    """rows x cols N(0, sigma) weights quantised to ggml type `t`, written to device memory at dst_ptr."""
+    _check(lib().wd_synth_tensor_device(t, rows, cols, sigma, seed, stream_id, dst_ptr, stream))
 
 
 # -- stand-alone pieces ------------------------------------------------------------------------

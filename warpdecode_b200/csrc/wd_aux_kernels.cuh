@@ -257,7 +257,7 @@ __global__ void test_quantize_kernel(const float *x, int n, uint8_t *q80_blocks,
 // y = W x for a repacked IQ3_S matrix; one warp per tile, tile copied to shared memory with plain
 // loads (no bulk copy), same decode and float chain as the fused kernel. x is quantised to Q8_K by
 // the same routine. partials (optional): [rows][nsb][8] int32.
-__global__ void test_matvec_iq3s_kernel(const uint8_t *tiles, int rows, int nsb, const float *x, float *y,
+__global__ void iq_matvec_tiles_kernel(const uint8_t *tiles, int rows, int nsb, const float *x, float *y,
                                         int *partials, const uint16_t *grid_packed, int type = kTypeIq3s) {
     extern __shared__ __align__(128) uint8_t tsm[];
     uint8_t *tab = tsm;

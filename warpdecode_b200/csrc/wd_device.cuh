@@ -18,9 +18,17 @@ enum : unsigned {
     kErrCopyTimeout = 2u,      // a bulk copy never completed
     kErrExpertMiss = 4u,       // a selected expert has no slot
     kErrGeometry = 8u,         // launch geometry does not match the parameters
+    kErrOverrun = 16u,         // a polled word carried a LATER layer's tag: it was overwritten before it was read
 };
 
-constexpr unsigned kSpinLimit = 1u << 20;   // polls before a wait gives up (about a second)
+constexpr unsigned kSpinLimit = 1u << 20;   // polls before a copy wait gives up
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;   // a wait for another CTA or GPU gives up after one second
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -80,16 +88,34 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsign
 // ---------------------------------------------------------------------------------------------
 typedef unsigned long long tagged_t;
 
-// True when a polling loop should give up: its own limit ran out, or some other wait of this launch
-// already failed (then the remaining waits end after 1024 polls instead of the full limit, so that a
-// broken launch still terminates quickly). Raises kErrBarrierTimeout.
-__device__ __forceinline__ bool wait_expired(unsigned it, unsigned *err) {
+// True when a polling loop should give up: one second of the global timer has passed since its 1024th
+// poll (a time limit, so that it does not depend on how long one poll takes: local L2 or another GPU
+// over NVLink), or some other wait of this launch already failed (then the remaining waits end after
+// 1024 polls, so that a broken launch still terminates quickly). Raises kErrBarrierTimeout. `t0` is
+// the caller's loop-local start time, 0 before the loop.
+__device__ __forceinline__ bool wait_expired(unsigned it, unsigned long long &t0, unsigned *err) {
     if ((it & 0x3ffu) != 0x3ffu) return false;
-    if (it >= kSpinLimit || (*reinterpret_cast<volatile unsigned *>(err) & (kErrBarrierTimeout | kErrCopyTimeout)) != 0u) {
+    const unsigned long long now = global_timer_ns();
+    if (t0 == 0ull) t0 = now;
+    if (now - t0 > kWaitLimitNs || it >= 0xfffffc00u ||
+        (*reinterpret_cast<volatile unsigned *>(err) & (kErrBarrierTimeout | kErrCopyTimeout)) != 0u) {
         atomicOr(err, kErrBarrierTimeout);
         return true;
     }
     return false;
+}
+
+// Tags are compared as a wrapping sequence. A word whose tag is still behind the wanted one has not been
+// written yet; one whose tag is ahead was overwritten by a later layer before this reader got to it,
+// which the exchange protocol must never allow: it is reported (kErrOverrun) instead of waited for.
+__device__ __forceinline__ unsigned tag_behind(tagged_t w, uint32_t tag) {
+    return static_cast<int32_t>(static_cast<uint32_t>(w >> 32) - tag) < 0;
+}
+__device__ __forceinline__ unsigned tag_ahead(tagged_t w, uint32_t tag) {
+    return static_cast<int32_t>(static_cast<uint32_t>(w >> 32) - tag) > 0;
+}
+__device__ __forceinline__ void report_overrun(unsigned over, unsigned *err) {
+    if (over) atomicOr(err, kErrOverrun);
 }
 
 __device__ __forceinline__ tagged_t make_tagged(float v, uint32_t tag) {
@@ -102,17 +128,23 @@ __device__ __forceinline__ void st_tagged(tagged_t *p, float v, uint32_t tag) {
 __device__ __forceinline__ void st_tagged_sys(tagged_t *p, float v, uint32_t tag) {
     asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(make_tagged(v, tag)) : "memory");
 }
+// same, ordered after this thread's earlier loads and stores (a progress word that tells another GPU that
+// this one has finished READING something must not pass those reads)
+__device__ __forceinline__ void st_tagged_sys_release(tagged_t *p, float v, uint32_t tag) {
+    asm volatile("st.release.sys.global.b64 [%0], %1;" ::"l"(p), "l"(make_tagged(v, tag)) : "memory");
+}
 __device__ __forceinline__ tagged_t ld_tagged(const tagged_t *p) {
     tagged_t w;
     asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
     return w;
 }
-// Polls up to N words (word i at p[i * stride], i < n) until every tag matches; values to out[].
-// Bounded: on timeout raises kErrBarrierTimeout and returns what it has.
+// Polls up to N words (word i at p[i * stride], i < n) until every tag has reached `tag`; values to out[].
+// Bounded: on timeout raises kErrBarrierTimeout and returns what it has; a tag beyond `tag` raises kErrOverrun.
 template <int N>
 __device__ __forceinline__ void wait_tagged(const tagged_t *p, int stride, int n, uint32_t tag, float out[N],
                                             unsigned *err) {
     tagged_t w[N] = {};
+    unsigned long long t0 = 0ull;
     for (unsigned it = 0;; ++it) {
         // all loads first, then the checks, so that the loads are in flight together
 #pragma unroll
@@ -120,10 +152,14 @@ __device__ __forceinline__ void wait_tagged(const tagged_t *p, int stride, int n
             if (i < n) w[i] = ld_tagged(p + static_cast<size_t>(i) * stride);
         unsigned bad = 0;
 #pragma unroll
-        for (int i = 0; i < N; ++i) bad |= (i < n) & (static_cast<uint32_t>(w[i] >> 32) != tag);
+        for (int i = 0; i < N; ++i) bad |= (i < n) & tag_behind(w[i], tag);
         if (!bad) break;
-        if (wait_expired(it, err)) break;
+        if (wait_expired(it, t0, err)) break;
     }
+    unsigned over = 0;
+#pragma unroll
+    for (int i = 0; i < N; ++i) over |= (i < n) & tag_ahead(w[i], tag);
+    report_overrun(over, err);
 #pragma unroll
     for (int i = 0; i < N; ++i) out[i] = i < n ? __uint_as_float(static_cast<uint32_t>(w[i])) : 0.0f;
 }
@@ -133,25 +169,31 @@ template <int N>
 __device__ __forceinline__ void wait_tagged_at(const tagged_t *const p[N], int n, uint32_t tag, float out[N],
                                                unsigned *err) {
     tagged_t w[N] = {};
+    unsigned long long t0 = 0ull;
     for (unsigned it = 0;; ++it) {
 #pragma unroll
         for (int i = 0; i < N; ++i)
             if (i < n) w[i] = ld_tagged(p[i]);
         unsigned bad = 0;
 #pragma unroll
-        for (int i = 0; i < N; ++i) bad |= (i < n) & (static_cast<uint32_t>(w[i] >> 32) != tag);
+        for (int i = 0; i < N; ++i) bad |= (i < n) & tag_behind(w[i], tag);
         if (!bad) break;
-        if (wait_expired(it, err)) break;
+        if (wait_expired(it, t0, err)) break;
     }
+    unsigned over = 0;
+#pragma unroll
+    for (int i = 0; i < N; ++i) over |= (i < n) & tag_ahead(w[i], tag);
+    report_overrun(over, err);
 #pragma unroll
     for (int i = 0; i < N; ++i) out[i] = i < n ? __uint_as_float(static_cast<uint32_t>(w[i])) : 0.0f;
 }
 // Waits until the tag of *p has reached `tag` (tags compared as a wrapping sequence).
 __device__ __forceinline__ void wait_tag_reached(const tagged_t *p, uint32_t tag, unsigned *err) {
+    unsigned long long t0 = 0ull;
     for (unsigned it = 0;; ++it) {
         const uint32_t t = static_cast<uint32_t>(ld_tagged(p) >> 32);
         if (static_cast<int32_t>(t - tag) >= 0) break;
-        if (wait_expired(it, err)) break;
+        if (wait_expired(it, t0, err)) break;
     }
 }
 

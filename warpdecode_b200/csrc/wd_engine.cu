@@ -5,6 +5,7 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <atomic>
 #include <condition_variable>
 #include <cstdio>
 #include <cstdlib>
@@ -40,6 +41,20 @@ int fail(int code, const std::string &msg) {
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
+
+// Device buffers of a stand-alone entry point: released when the function returns, on every path.
+struct ScopedDev {
+    std::vector<void *> held;
+    template <class T>
+    cudaError_t alloc(T **out, size_t bytes) {
+        const cudaError_t ce = cudaMalloc(reinterpret_cast<void **>(out), bytes);
+        if (ce == cudaSuccess) held.push_back(*out);
+        return ce;
+    }
+    ~ScopedDev() {
+        for (void *q : held) cudaFree(q);
+    }
+};
 
 struct Layer {
     uint8_t *router = nullptr;
@@ -155,10 +170,12 @@ struct wd_engine {
     wd::tagged_t *tagged = nullptr;
     size_t tagged_words = 0;
     int last_parity = 0;                    // half that holds the last launch's last layer (for the taps)
+    uint32_t epoch = 0;                     // host mirror of the device's tag epoch (sync[8]): tags issued so far
     int last_tokens = 1;                    // tokens of the last forward call
     int *tok_ids = nullptr;                 // [max_tokens][top_k] selection of every token of the last call
     float *tok_weights = nullptr;
     size_t tagged_eo_offset = 0;            // word offset of the expert-output buffer inside `tagged`
+    size_t tagged_left_offset = 0;          // word offset of the peers' "left layer" words
     // expert-parallel peers
     int n_peers = 0;
     void *peer_mapped[8] = {};              // bases opened from IPC handles (closed on disconnect); null for local peers
@@ -323,7 +340,8 @@ int launch_layers(wd_engine *e, int begin, int end, const float *x, float *resid
     void *args[] = {&p};
     WD_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(wd::moe_layer_kernel), dim3(e->n_sm),
                                         dim3(wd::kThreads), args, e->smem_bytes, s));
-    e->last_parity = (end - begin - 1) & 1;
+    e->epoch += static_cast<uint32_t>(end - begin);     // the kernel advances the device's epoch by the same amount
+    e->last_parity = static_cast<int>(e->epoch & 1u);   // the last layer's tag is the new epoch; halves follow the tag
     e->last_tokens = 1;
     return WD_OK;
 }
@@ -442,8 +460,10 @@ int check_device_status(wd_engine *e) {
         // an interrupted launch leaves the tag epoch and the exchange words undefined: start over
         cudaMemset(e->sync, 0, 8192);
         cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t));
+        e->epoch = 0;
         return fail(WD_E_DEVICE, "kernel raised status " + std::to_string(st) +
-                                     " (1 wait timeout, 2 copy timeout, 4 expert without slot, 8 geometry)");
+                                     " (1 wait timeout, 2 copy timeout, 4 expert without slot, 8 geometry, "
+                                     "16 exchange word overwritten before it was read)");
     }
     return WD_OK;
 }
@@ -559,8 +579,8 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     const size_t tw_logits = 0, tw_shact = tw_logits + 2 * static_cast<size_t>(E), tw_shgate = tw_shact + 2 * static_cast<size_t>(SF),
                  tw_act = tw_shgate + 2, tw_eo = tw_act + 2 * static_cast<size_t>(K) * F,
                  tw_shdown = tw_eo + 2 * static_cast<size_t>(K) * H, tw_res = tw_shdown + 2 * static_cast<size_t>(H),
-                 tw_prog = tw_res + 2 * static_cast<size_t>(H);
-    e->tagged_words = tw_prog + static_cast<size_t>(e->n_sm);
+                 tw_prog = tw_res + 2 * static_cast<size_t>(H), tw_left = tw_prog + static_cast<size_t>(e->n_sm);
+    e->tagged_words = tw_left + 8;
     WD_TRY(cudaMalloc(&e->tagged, e->tagged_words * sizeof(wd::tagged_t)));
     WD_TRY(cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t)));
     // staging: one layer's routed experts in ggml layout (or a dense tensor, whichever is larger)
@@ -599,6 +619,8 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     p.t_act = e->tagged + tw_act; p.t_expert_out = e->tagged + tw_eo; p.t_shared_down = e->tagged + tw_shdown;
     p.t_residual = e->tagged + tw_res; p.t_progress = e->tagged + tw_prog;
     e->tagged_eo_offset = tw_eo;
+    e->tagged_left_offset = tw_left;
+    p.t_peer_left = e->tagged + tw_left;
     p.n_peers = 0;
     p.sync = e->sync;
     p.host_status = e->host_status;
@@ -1042,6 +1064,7 @@ int wd_set_profiling(wd_engine *e, int on) {
 }
 
 int wd_sm_count(const wd_engine *e) { return e ? e->n_sm : 0; }
+const char *wd_kernel_name(const wd_engine *) { return "moe_layer_kernel"; }
 
 // ---- expert parallelism ----------------------------------------------------------------------------
 int wd_ep_handle_bytes(void) { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
@@ -1082,6 +1105,9 @@ int wd_ep_connect(wd_engine *e, int n_peers, const void *handles) {
         }
         e->peer_mapped[p] = base;
         e->base.peer_expert_out[p] = static_cast<wd::tagged_t *>(base) + e->tagged_eo_offset;
+        // peers are the other ranks in rank order; each peer keeps one "left layer" word per global rank
+        e->base.peer_rank[p] = p < e->cfg.ep_rank ? p : p + 1;
+        e->base.peer_left_out[p] = static_cast<wd::tagged_t *>(base) + e->tagged_left_offset + e->cfg.ep_rank;
     }
     e->n_peers = e->base.n_peers = n_peers;
     return WD_OK;
@@ -1106,6 +1132,8 @@ int wd_ep_connect_local(wd_engine *e, int n_peers, wd_engine *const *peers) {
         }
         e->peer_mapped[p] = nullptr;
         e->base.peer_expert_out[p] = o->tagged + o->tagged_eo_offset;
+        e->base.peer_rank[p] = o->cfg.ep_rank;
+        e->base.peer_left_out[p] = o->tagged + o->tagged_left_offset + e->cfg.ep_rank;
     }
     e->n_peers = e->base.n_peers = n_peers;
     return WD_OK;
@@ -1120,6 +1148,7 @@ int wd_ep_disconnect(wd_engine *e) {
         if (e->peer_mapped[p]) cudaIpcCloseMemHandle(e->peer_mapped[p]);
         e->peer_mapped[p] = nullptr;
         e->base.peer_expert_out[p] = nullptr;
+        e->base.peer_left_out[p] = nullptr;
     }
     e->n_peers = e->base.n_peers = 0;
     return WD_OK;
@@ -1131,6 +1160,7 @@ int wd_reset_exchange(wd_engine *e) {
     WD_CUDA(cudaDeviceSynchronize());
     WD_CUDA(cudaMemset(e->sync, 0, 8192));
     WD_CUDA(cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t)));
+    e->epoch = 0;
     return WD_OK;
 }
 
@@ -1144,6 +1174,7 @@ int wd_device_status(wd_engine *e, int *status) {
     if (st) {
         WD_CUDA(cudaMemset(e->sync, 0, 8192));
         WD_CUDA(cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t)));
+        e->epoch = 0;
     }
     return WD_OK;
 }
@@ -1154,12 +1185,13 @@ int wd_router_topk_host(const float *logits, int n_experts, int k, float w_scale
     if (!logits || !ids || !weights) return fail(WD_E_INVALID, "null argument");
     if (n_experts <= 0 || n_experts % 8 || n_experts > wd::kMaxExperts || k < 1 || k > wd::kMaxK)
         return fail(WD_E_INVALID, "n_experts must be a multiple of 8 up to 1024, k 1..16");
+    ScopedDev bufs;
     float *d_l = nullptr, *d_w = nullptr, *d_p = nullptr;
     int *d_i = nullptr;
-    WD_CUDA(cudaMalloc(&d_l, n_experts * 4));
-    WD_CUDA(cudaMalloc(&d_p, n_experts * 4));
-    WD_CUDA(cudaMalloc(&d_w, wd::kMaxK * 4));
-    WD_CUDA(cudaMalloc(&d_i, wd::kMaxK * 4));
+    WD_CUDA(bufs.alloc(&d_l, n_experts * 4));
+    WD_CUDA(bufs.alloc(&d_p, n_experts * 4));
+    WD_CUDA(bufs.alloc(&d_w, wd::kMaxK * 4));
+    WD_CUDA(bufs.alloc(&d_i, wd::kMaxK * 4));
     WD_CUDA(cudaMemcpy(d_l, logits, n_experts * 4, cudaMemcpyHostToDevice));
     wd::test_router_kernel<<<1, wd::kThreads>>>(d_l, n_experts, k, w_scale, d_i, d_w, d_p);
     WD_CUDA(cudaGetLastError());
@@ -1167,18 +1199,18 @@ int wd_router_topk_host(const float *logits, int n_experts, int k, float w_scale
     WD_CUDA(cudaMemcpy(ids, d_i, k * 4, cudaMemcpyDeviceToHost));
     WD_CUDA(cudaMemcpy(weights, d_w, k * 4, cudaMemcpyDeviceToHost));
     if (probs) WD_CUDA(cudaMemcpy(probs, d_p, n_experts * 4, cudaMemcpyDeviceToHost));
-    cudaFree(d_l); cudaFree(d_p); cudaFree(d_w); cudaFree(d_i);
     return WD_OK;
 }
 
 static int quantize_host(const float *x, int n, void *q80, void *q8k) {
     if (!x || n <= 0 || n % 256 || n > 8192) return fail(WD_E_INVALID, "n must be a multiple of 256 up to 8192");
+    ScopedDev bufs;
     float *d_x = nullptr;
     uint8_t *d_0 = nullptr, *d_k = nullptr;
-    WD_CUDA(cudaMalloc(&d_x, n * 4));
+    WD_CUDA(bufs.alloc(&d_x, n * 4));
     WD_CUDA(cudaMemcpy(d_x, x, n * 4, cudaMemcpyHostToDevice));
-    if (q80) WD_CUDA(cudaMalloc(&d_0, n / 32 * 34));
-    if (q8k) WD_CUDA(cudaMalloc(&d_k, n / 256 * 292));
+    if (q80) WD_CUDA(bufs.alloc(&d_0, n / 32 * 34));
+    if (q8k) WD_CUDA(bufs.alloc(&d_k, n / 256 * 292));
     const size_t smem = n * 4 + n + n / 32 * 4 + (n / 256 + 1) * wd::kActSbStride + (n / 256 + 4) * 4 + 64;
     WD_CUDA(cudaFuncSetAttribute(wd::test_quantize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
     wd::test_quantize_kernel<<<1, 512, smem>>>(d_x, n, d_0, d_k);
@@ -1186,7 +1218,6 @@ static int quantize_host(const float *x, int n, void *q80, void *q8k) {
     WD_CUDA(cudaDeviceSynchronize());
     if (q80) WD_CUDA(cudaMemcpy(q80, d_0, n / 32 * 34, cudaMemcpyDeviceToHost));
     if (q8k) WD_CUDA(cudaMemcpy(q8k, d_k, n / 256 * 292, cudaMemcpyDeviceToHost));
-    cudaFree(d_x); cudaFree(d_0); cudaFree(d_k);
     return WD_OK;
 }
 int wd_quantize_q8_0_host(const float *x, int n, void *blocks) { return quantize_host(x, n, blocks, nullptr); }
@@ -1194,6 +1225,7 @@ int wd_quantize_q8_K_host(const float *x, int n, void *blocks) { return quantize
 
 int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, float *y, int32_t *partials) {
     if (!w || !x || !y) return fail(WD_E_INVALID, "null argument");
+    ScopedDev bufs;
     float *d_x = nullptr, *d_y = nullptr;
     uint8_t *d_src = nullptr, *d_dst = nullptr;
     int *d_p = nullptr;
@@ -1204,14 +1236,14 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
             return fail(WD_E_INVALID, "IQ3_S / IQ2_S matvec: cols must be 256*2^n (n<=5), rows a multiple of 32/(cols/256)");
         const bool iq2 = type == WD_TYPE_IQ2_S;
         const size_t bytes = static_cast<size_t>(rows) * nsb * wd::iq_block_bytes(type);
-        WD_CUDA(cudaMalloc(&d_src, bytes));
-        WD_CUDA(cudaMalloc(&d_dst, bytes));
-        WD_CUDA(cudaMalloc(&d_x, cols * 4));
-        WD_CUDA(cudaMalloc(&d_y, rows * 4));
-        WD_CUDA(cudaMalloc(&d_grid, sizeof(wd_iq2s_grid_packed)));      // the larger of the two codebooks
+        WD_CUDA(bufs.alloc(&d_src, bytes));
+        WD_CUDA(bufs.alloc(&d_dst, bytes));
+        WD_CUDA(bufs.alloc(&d_x, cols * 4));
+        WD_CUDA(bufs.alloc(&d_y, rows * 4));
+        WD_CUDA(bufs.alloc(&d_grid, sizeof(wd_iq2s_grid_packed)));      // the larger of the two codebooks
         if (iq2) WD_CUDA(cudaMemcpy(d_grid, wd_iq2s_grid_packed, sizeof(wd_iq2s_grid_packed), cudaMemcpyHostToDevice));
         else WD_CUDA(cudaMemcpy(d_grid, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
-        if (partials) WD_CUDA(cudaMalloc(&d_p, static_cast<size_t>(rows) * nsb * 8 * 4));
+        if (partials) WD_CUDA(bufs.alloc(&d_p, static_cast<size_t>(rows) * nsb * 8 * 4));
         WD_CUDA(cudaMemcpy(d_src, w, bytes, cudaMemcpyHostToDevice));
         WD_CUDA(cudaMemcpy(d_x, x, cols * 4, cudaMemcpyHostToDevice));
         const long long nblocks = static_cast<long long>(rows) * nsb;
@@ -1219,8 +1251,8 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
         else wd::repack_iq3s_kernel<<<static_cast<unsigned>((nblocks + 127) / 128), 128>>>(d_src, d_dst, nblocks, 0, 0);
         const int nw = 8;
         const size_t smem = wd::kGridTableBytes + nsb * wd::kActSbStride + 32 * 4 + nw * wd::kIq3TileBytes + nw * 640 * 4 + 256;
-        WD_CUDA(cudaFuncSetAttribute(wd::test_matvec_iq3s_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        wd::test_matvec_iq3s_kernel<<<64, nw * 32, smem>>>(d_dst, rows, nsb, d_x, d_y, d_p, d_grid, type);
+        WD_CUDA(cudaFuncSetAttribute(wd::iq_matvec_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        wd::iq_matvec_tiles_kernel<<<64, nw * 32, smem>>>(d_dst, rows, nsb, d_x, d_y, d_p, d_grid, type);
         WD_CUDA(cudaGetLastError());
         WD_CUDA(cudaDeviceSynchronize());
         WD_CUDA(cudaMemcpy(y, d_y, rows * 4, cudaMemcpyDeviceToHost));
@@ -1229,10 +1261,10 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
         const int nb = cols / 32;
         if (cols % 128 || rows % 4 || cols > 8192) return fail(WD_E_INVALID, "Q8_0 matvec: cols % 128, rows % 4");
         const size_t bytes = static_cast<size_t>(rows) * nb * 34;
-        WD_CUDA(cudaMalloc(&d_src, bytes));
-        WD_CUDA(cudaMalloc(&d_dst, bytes));
-        WD_CUDA(cudaMalloc(&d_x, cols * 4));
-        WD_CUDA(cudaMalloc(&d_y, rows * 4));
+        WD_CUDA(bufs.alloc(&d_src, bytes));
+        WD_CUDA(bufs.alloc(&d_dst, bytes));
+        WD_CUDA(bufs.alloc(&d_x, cols * 4));
+        WD_CUDA(bufs.alloc(&d_y, rows * 4));
         WD_CUDA(cudaMemcpy(d_src, w, bytes, cudaMemcpyHostToDevice));
         WD_CUDA(cudaMemcpy(d_x, x, cols * 4, cudaMemcpyHostToDevice));
         const long long n = static_cast<long long>(rows) * nb;
@@ -1248,8 +1280,8 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
         void *packed = nullptr;
         int rc = wd_dense_pack_q4_0(w, rows, cols, &packed);
         if (rc) return rc;
-        WD_CUDA(cudaMalloc(&d_x, cols * 4));
-        WD_CUDA(cudaMalloc(&d_y, rows * 4));
+        WD_CUDA(bufs.alloc(&d_x, cols * 4));
+        WD_CUDA(bufs.alloc(&d_y, rows * 4));
         WD_CUDA(cudaMemcpy(d_x, x, cols * 4, cudaMemcpyHostToDevice));
         rc = wd_dense_matvec_q4_0(packed, rows, cols, d_x, d_y, nullptr);
         if (rc == WD_OK) {
@@ -1257,14 +1289,10 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
             WD_CUDA(cudaMemcpy(y, d_y, rows * 4, cudaMemcpyDeviceToHost));
         }
         wd_dense_free(packed);
-        if (rc) {
-            cudaFree(d_x); cudaFree(d_y);
-            return rc;
-        }
+        if (rc) return rc;
     } else {
         return fail(WD_E_INVALID, "matvec supports IQ3_S, IQ2_S, Q8_0 and Q4_0");
     }
-    cudaFree(d_x); cudaFree(d_y); cudaFree(d_src); cudaFree(d_dst); cudaFree(d_p); cudaFree(d_grid);
     return WD_OK;
 }
 
@@ -1487,8 +1515,9 @@ int wd_synth_model(wd_engine *e, uint64_t seed, float sigma, float bias_sigma) {
     cudaStream_t s = e->stream;
     const size_t gb = e->gate_bytes, db = e->down_bytes;
     const size_t need = static_cast<size_t>(c.n_experts) * (2 * gb + db);
+    ScopedDev bufs;         // `big` is released on every path out of this function
     uint8_t *big = nullptr;
-    WD_CUDA(cudaMalloc(&big, need));
+    WD_CUDA(bufs.alloc(&big, need));
     int rc = WD_OK;
     for (int l = 0; l < c.n_layers && rc == WD_OK; ++l) {
         Layer &L = e->layers[l];
@@ -1531,7 +1560,6 @@ int wd_synth_model(wd_engine *e, uint64_t seed, float sigma, float bias_sigma) {
         if ((rc = wd_set_experts_device(e, l, g, u, d))) break;
     }
     cudaStreamSynchronize(s);
-    cudaFree(big);
     return rc;
 }
 
@@ -1606,8 +1634,9 @@ int wd_synth_dense_host(wd_engine *e, uint64_t seed, float sigma, float bias_sig
 // the fixed array below, which every GPU that loads this library holds until the process exits.
 //
 // The array's name is only a host-side handle; the device address the kernels need comes from
-// cudaGetSymbolAddress, looked up once per device by the first call made with that device current. That
-// first call should happen before any stream capture. All calls share the array: it keeps the previous
+// cudaGetSymbolAddress, looked up once per device by the first call made with that device current. The same
+// first call uploads the packed codebook into the front of the array with a blocking copy (later calls never
+// write that region), so it should happen before any stream capture. All calls share the array: it keeps the previous
 // call's tiles (each call overwrites every byte it later reads, so nothing has to be cleared), and two
 // calls that overlap on the GPU - different streams, or one stream re-entered from two host threads -
 // race on it.
@@ -1619,20 +1648,24 @@ constexpr size_t kNoAllocGridBytes = 1024;                   // packed codebook 
 static __device__ __align__(256) unsigned char wd_noalloc_scratch[kNoAllocScratchBytes];
 
 constexpr int kNoAllocMaxDevices = 64;
-void *g_noalloc_ptr[kNoAllocMaxDevices] = {};
+// Set once per device, after the codebook is in place. Two threads that race through the set-up of one device
+// both upload the same bytes and store the same address.
+std::atomic<void *> g_noalloc_ptr[kNoAllocMaxDevices];
 
 int noalloc_scratch_for_current_device(void **out) {
     int dev = -1;
     WD_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kNoAllocMaxDevices) return fail(WD_E_INVALID, "device ordinal out of range");
-    if (!g_noalloc_ptr[dev]) {
-        void *p = nullptr;
+    void *p = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+    if (!p) {
         const cudaError_t ce = cudaGetSymbolAddress(&p, wd_noalloc_scratch);
         if (ce != cudaSuccess || p == nullptr)
             return fail(WD_E_CUDA, std::string("cudaGetSymbolAddress(wd_noalloc_scratch): ") + cudaGetErrorString(ce));
-        g_noalloc_ptr[dev] = p;
+        static_assert(sizeof(wd_iq3s_grid_packed) == kNoAllocGridBytes, "packed codebook size");
+        WD_CUDA(cudaMemcpy(p, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
+        g_noalloc_ptr[dev].store(p, std::memory_order_release);
     }
-    *out = g_noalloc_ptr[dev];
+    *out = p;
     return WD_OK;
 }
 
@@ -1655,15 +1688,13 @@ extern "C" int wd_matvec_iq3s_noalloc(const void *w_dev, int rows, int cols, con
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     uint16_t *grid = static_cast<uint16_t *>(base);
     uint8_t *tiles = static_cast<uint8_t *>(base) + kNoAllocGridBytes;
-    static_assert(sizeof(wd_iq3s_grid_packed) == kNoAllocGridBytes, "packed codebook size");
-    WD_CUDA(cudaMemcpyAsync(grid, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice, s));
     const long long nblocks = static_cast<long long>(rows) * nsb;
     wd::repack_iq3s_kernel<<<static_cast<unsigned>((nblocks + 127) / 128), 128, 0, s>>>(
         static_cast<const uint8_t *>(w_dev), tiles, nblocks, 0, 0);
     const int nw = 8;
     const size_t smem = wd::kGridTableBytes + nsb * wd::kActSbStride + 32 * 4 + nw * wd::kIq3TileBytes + nw * 640 * 4 + 256;
-    WD_CUDA(cudaFuncSetAttribute(wd::test_matvec_iq3s_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    wd::test_matvec_iq3s_kernel<<<64, nw * 32, smem, s>>>(tiles, rows, nsb, x_dev, y_dev, nullptr, grid);
+    WD_CUDA(cudaFuncSetAttribute(wd::iq_matvec_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    wd::iq_matvec_tiles_kernel<<<64, nw * 32, smem, s>>>(tiles, rows, nsb, x_dev, y_dev, nullptr, grid);
     WD_CUDA(cudaGetLastError());
     return WD_OK;
 }

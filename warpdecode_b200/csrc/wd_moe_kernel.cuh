@@ -75,6 +75,13 @@ struct MoeParams {
     tagged_t *t_progress;        // [grid]   tag of the last layer each CTA has completely left
     tagged_t *peer_expert_out[8];// expert-parallel peers' t_expert_out buffers (n_peers entries)
     int n_peers;                 // 0: single GPU (or partial sums only); else every rank combines all K experts
+    // Flow control between ranks: word [r] of t_peer_left holds the tag of the last layer whose expert rows rank r
+    // has finished reading. Rank r writes it into every peer (peer_left_out[p] = that peer's word for this rank);
+    // a rank stores layer t's rows into a peer only after that peer has left layer t - 2, the previous user of the
+    // same half of its row buffer.
+    tagged_t *t_peer_left;       // [8]
+    tagged_t *peer_left_out[8];
+    int peer_rank[8];            // global rank of peer p
     int *ids;                    // [K]   (plain copies for inspection, written by CTA 0)
     float *weights;              // [K]
     float *routed;               // [H]
@@ -116,16 +123,21 @@ __device__ __forceinline__ double p0_gather(const float *plain, const float *nor
         for (int i = 0; i < EPL; ++i) rv[i] = plain[i];
     } else {
         tagged_t w[EPL];
+        unsigned long long t0 = 0ull;
         for (unsigned it = 0;; ++it) {
 #pragma unroll
             for (int i = 0; i < EPL; ++i) w[i] = ld_tagged(src + i);
             const tagged_t wp = chk ? ld_tagged(progress) : 0;
-            unsigned bad = chk & (static_cast<int32_t>(static_cast<uint32_t>(wp >> 32) - (tag - 2u)) < 0);
+            unsigned bad = chk & tag_behind(wp, tag - 2u);
 #pragma unroll
-            for (int i = 0; i < EPL; ++i) bad |= static_cast<uint32_t>(w[i] >> 32) != tag - 1u;
+            for (int i = 0; i < EPL; ++i) bad |= tag_behind(w[i], tag - 1u);
             if (!bad) break;
-            if (wait_expired(it, err)) break;
+            if (wait_expired(it, t0, err)) break;
         }
+        unsigned over = 0;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) over |= tag_ahead(w[i], tag - 1u);
+        report_overrun(over, err);
 #pragma unroll
         for (int i = 0; i < EPL; ++i) rv[i] = __uint_as_float(static_cast<uint32_t>(w[i]));
     }
@@ -249,8 +261,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
 #pragma unroll 1
     for (int layer = P.layer_begin; layer < P.layer_end; ++layer) {
     const LayerDev L = P.layers[layer];
-    const uint32_t par = static_cast<uint32_t>(layer - P.layer_begin) & 1u;   // every mbarrier completes once per layer
+    const uint32_t mpar = static_cast<uint32_t>(layer - P.layer_begin) & 1u;  // every mbarrier completes once per layer
     const uint32_t tag = epoch + static_cast<uint32_t>(layer - P.layer_begin) + 1u;
+    // The half of every exchange buffer follows the TAG, not the position in the launch: consecutive layers then
+    // alternate halves across launches too (a peer may still be one launch behind).
+    const uint32_t par = tag & 1u;
     const bool stamp_on = P.stamps != nullptr && tid == 0 && layer == P.stamp_layer;
     // this layer's halves of the exchange buffers
     tagged_t *t_logits = P.t_logits + par * P.E;
@@ -304,6 +319,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         double *redd = reinterpret_cast<double *>(sm + P.off_scr);
         if (lane == 0) redd[warp] = ss;
         __syncthreads();
+        // Every residual row of the previous layer is here, so every CTA of this rank has finished reading that
+        // layer's expert rows (a combine publishes its residual rows after it has read them): tell the peers.
+        if (cta == 0 && !first && tid < P.n_peers) st_tagged_sys_release(P.peer_left_out[tid], 0.0f, tag - 1u);
         double tot[kWarps];
 #pragma unroll
         for (int i = 0; i < kWarps; ++i) tot[i] = redd[i];
@@ -328,6 +346,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         if (layer >= P.layer_begin + 2 && tid < ncta) wait_tag_reached(P.t_progress + tid, tag - 2u, err);
 #pragma unroll 1
         for (int i = tid; i < P.H; i += kThreads) xf[i] = P.x[i];
+        if (P.n_peers > 0 && cta == 0 && layer >= P.layer_begin + 2) {      // every CTA has left layer tag - 2
+            __syncthreads();
+            if (tid < P.n_peers) st_tagged_sys_release(P.peer_left_out[tid], 0.0f, tag - 2u);
+        }
     }
     const float *gate_vec_s = reinterpret_cast<const float *>(stage_b);
     __syncthreads();
@@ -347,9 +369,14 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
 #undef WD_STAMP
     if (tid == 0) {
         // every CTA read the epoch before it got here, so the last one to leave may advance it
+        __threadfence();        // this CTA's reads of the last layers' rows come before its arrival below
         if (atomicAdd(P.sync + 9, 1u) == static_cast<unsigned>(ncta) - 1u) {
             P.sync[9] = 0u;
             P.sync[8] = epoch + static_cast<uint32_t>(P.layer_end - P.layer_begin);
+            // every CTA of this rank has left the launch: the peers may overwrite both halves of its row buffer
+            __threadfence();
+            for (int p = 0; p < P.n_peers; ++p)
+                st_tagged_sys_release(P.peer_left_out[p], 0.0f, epoch + static_cast<uint32_t>(P.layer_end - P.layer_begin));
             if (P.host_status) *P.host_status = *reinterpret_cast<volatile unsigned *>(err);
         }
     }
