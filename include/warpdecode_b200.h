@@ -135,6 +135,8 @@ int wd_stack_step_host(wd_engine *e, const float *residual_in_host, float *resid
 #define WD_TAP_SHARED_GATE 7  /* F32 [1] */
 #define WD_TAP_SHARED_ACT 8   /* F32 [shared_ffn] */
 #define WD_TAP_STAMPS 9       /* U64 [sm_count][32] phase timestamps (ns), see wd_set_profiling */
+#define WD_TAP_FALLBACKS 10   /* U32 [1] layers so far whose ids came from the exact rungs, not from the logit threshold
+                               * (engines that run the compiled kernel; 0 otherwise) */
 /* Copies a tap of the most recent forward of token `token` to host memory (synchronises).
  * token = -1 means the last token of that call. After a batch of several tokens, ids and weights
  * are kept for every token; the other taps show the last token only (earlier ones: WD_E_STATE).
@@ -251,7 +253,8 @@ int wd_matvec_iq3s_noalloc(const void *w_dev, int rows, int cols, const float *x
 
 /* ---- synthetic model generator (device side) ----------------------------------------------- */
 /* Fills `dst` (device) with `rows` x `cols` N(0, sigma) weights drawn from (seed, stream_id)
- * and quantised to `type` in ggml layout. Used to build full-size synthetic models in HBM. */
+ * and quantised to `type` (WD_TYPE_F32 or WD_TYPE_Q8_0; IQ3_S tensors come from wd_synth_model) in
+ * ggml layout. Used to build full-size synthetic tensors (embedding table, output head) in HBM. */
 int wd_synth_tensor_device(int type, int rows, int cols, float sigma, uint64_t seed,
                            uint64_t stream_id, void *dst_dev, void *stream);
 /* Builds every layer of the engine's model from `seed` directly on the device. */

@@ -15,7 +15,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 LIB_PATH = os.path.join(HERE, "libwarpdecode_b200.so")
 SOURCES = [os.path.join(HERE, "csrc", f) for f in
-           ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_moe_kernel_phases.inc", "wd_blocks.cuh", "wd_router.cuh",
+           ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_moe_kernel_phases.inc", "wd_moe_fast.cuh",
+            "wd_blocks.cuh", "wd_router.cuh",
             "wd_formats.cuh", "wd_device.cuh", "wd_dense.cuh", "wd_gguf.inc",
             "wd_grids.h")] + [os.path.join(ROOT, "include", "warpdecode_b200.h")]
 
@@ -302,6 +303,12 @@ class Engine:
             token = -1
         _check(lib().wd_read_tap(self.h, TAPS[name], token, _ptr(a), a.nbytes))
         return a
+
+    def fallbacks(self):
+        """Layers so far whose expert ids came from the exact rungs instead of the logit threshold."""
+        a = np.zeros(1, np.uint32)
+        _check(lib().wd_read_tap(self.h, 10, -1, _ptr(a), 4))
+        return int(a[0])
 
     def kernel_name(self):
         """Name of the kernel that this engine's stack step launches."""

@@ -2,7 +2,7 @@
 // generator, and single-purpose wrappers that expose pieces of the fused kernel to unit tests.
 #pragma once
 
-#include "wd_moe_kernel.cuh"
+#include "wd_moe_fast.cuh"
 
 namespace wd {
 
@@ -76,6 +76,20 @@ __global__ void repack_q8_0_kernel(const uint8_t *__restrict__ src, uint8_t *__r
     task[nb * 128 + (r * nb + b) * 2 + 1] = s[1];
     for (int l = 0; l < 8; ++l)
         for (int k = 0; k < 4; ++k) task[(b >> 2) * 512 + r * 128 + l * 16 + (b & 3) * 4 + k] = s[2 + 4 * l + k];
+}
+
+// repack: ggml Q8_0 [rows][nb] blocks (34 B) -> one row at a time (the layout q8_row_warp reads): quants
+// [g = b / 4][chunk-lane l][16 B] (word b & 3 = values 4l..4l+3 of block b), then the nb f16 scales
+__global__ void repack_q8_0_rows_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int rows, int nb) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= static_cast<long long>(rows) * nb) return;
+    const int row = static_cast<int>(i / nb), b = static_cast<int>(i % nb);
+    const uint8_t *s = src + i * 34;
+    uint8_t *r = dst + static_cast<long long>(row) * nb * 34;
+    r[nb * 32 + b * 2] = s[0];
+    r[nb * 32 + b * 2 + 1] = s[1];
+    for (int l = 0; l < 8; ++l)
+        for (int k = 0; k < 4; ++k) r[(b >> 2) * 128 + l * 16 + (b & 3) * 4 + k] = s[2 + 4 * l + k];
 }
 
 // ---------------------------------------------------------------------------------------------

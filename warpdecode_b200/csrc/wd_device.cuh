@@ -26,7 +26,7 @@ constexpr unsigned long long kWaitLimitNs = 1000000000ull;   // a wait for anoth
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t) : : "memory");
     return t;
 }
 
@@ -81,6 +81,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsign
     return false;
 }
 
+// Integer atomics on this CTA's shared memory, addressed in the shared window (an atomic through a generic
+// pointer has to find out at run time which memory it targets).
+__device__ __forceinline__ void red_add_shared(int *p, int v) {
+    asm volatile("red.shared.add.s32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_or_shared(uint32_t *p, uint32_t v) {
+    asm volatile("red.shared.or.b32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ int atom_add_shared(int *p, int v) {
+    int old;
+    asm volatile("atom.shared.add.s32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(p)), "r"(v) : "memory");
+    return old;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Tagged words: a float and the tag of the layer that produced it, published with ONE 8-byte store.
 // A consumer polls the word itself until the tag matches, so no fence and no separate flag is needed
@@ -93,8 +107,12 @@ typedef unsigned long long tagged_t;
 // over NVLink), or some other wait of this launch already failed (then the remaining waits end after
 // 1024 polls, so that a broken launch still terminates quickly). Raises kErrBarrierTimeout. `t0` is
 // the caller's loop-local start time, 0 before the loop.
+__device__ __noinline__ bool wait_expired_slow(unsigned it, unsigned long long &t0, unsigned *err);
 __device__ __forceinline__ bool wait_expired(unsigned it, unsigned long long &t0, unsigned *err) {
     if ((it & 0x3ffu) != 0x3ffu) return false;
+    return wait_expired_slow(it, t0, err);
+}
+__device__ __noinline__ bool wait_expired_slow(unsigned it, unsigned long long &t0, unsigned *err) {
     const unsigned long long now = global_timer_ns();
     if (t0 == 0ull) t0 = now;
     if (now - t0 > kWaitLimitNs || it >= 0xfffffc00u ||
@@ -114,8 +132,9 @@ __device__ __forceinline__ unsigned tag_behind(tagged_t w, uint32_t tag) {
 __device__ __forceinline__ unsigned tag_ahead(tagged_t w, uint32_t tag) {
     return static_cast<int32_t>(static_cast<uint32_t>(w >> 32) - tag) > 0;
 }
+__device__ __noinline__ void report_overrun_slow(unsigned *err) { atomicOr(err, kErrOverrun); }
 __device__ __forceinline__ void report_overrun(unsigned over, unsigned *err) {
-    if (over) atomicOr(err, kErrOverrun);
+    if (over) report_overrun_slow(err);
 }
 
 __device__ __forceinline__ tagged_t make_tagged(float v, uint32_t tag) {

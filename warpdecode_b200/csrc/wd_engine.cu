@@ -187,9 +187,92 @@ struct wd_engine {
     size_t pinned_bytes = 0;
     wd::MoeParams base{};
     size_t smem_bytes = 0;
+    // the kernel for geometries compiled in (wd_moe_fast.cuh); null: the generic kernel runs
+    const void *fast_fn = nullptr;
+    wd::FastParams fbase{};
+    size_t fast_smem = 0;
+    float *eo_plain = nullptr, *shdown_plain = nullptr;     // inspection copies the fast kernel writes
+    wd::tagged_t *xbuf = nullptr;                           // the compiled kernel's per-CTA mailboxes
+    size_t xbuf_words = 0;
+    unsigned *fallbacks = nullptr;                          // layers that took the exact rungs
 };
 
 namespace {
+
+// Geometries the fast kernel is compiled for (IQ3_S experts, a Q8_0 shared expert). The first is the 48-layer
+// model's block; the others are the small shapes the parity tests use, so that they exercise the same code.
+template <int H, int F, int E, int K, int SF>
+const void *fast_entry(const wd_config &c) {
+    if (c.hidden == H && c.expert_ffn == F && c.n_experts == E && c.top_k == K && c.shared_ffn == SF)
+        return reinterpret_cast<const void *>(&wd::moe_fast_kernel<wd::FastGeo<H, F, E, K, SF>>);
+    return nullptr;
+}
+
+const void *find_fast_kernel(const wd_config &c) {
+    if (c.gate_type != WD_TYPE_IQ3_S || c.down_type != WD_TYPE_IQ3_S) return nullptr;
+    if (const char *v = std::getenv("WD_GENERIC_KERNEL"))
+        if (v[0] == '1') return nullptr;
+    const void *f = nullptr;
+    if (!f) f = fast_entry<2048, 512, 512, 10, 512>(c);
+    if (!f) f = fast_entry<2048, 512, 32, 10, 512>(c);
+    if (!f) f = fast_entry<512, 256, 32, 6, 256>(c);
+    if (!f) f = fast_entry<512, 256, 64, 6, 256>(c);
+    if (!f) f = fast_entry<512, 256, 32, 4, 256>(c);
+    return f;
+}
+
+// Shared-memory plan and per-CTA shares of the fast kernel for this engine's grid.
+int plan_fast(wd_engine *e) {
+    wd::FastParams &p = e->fbase;
+    const wd_config &c = e->cfg;
+    const int ncta = e->n_sm;
+    const int H = c.hidden, F = c.expert_ffn, E = c.n_experts, K = c.top_k, SF = c.shared_ffn;
+    const int nsb_h = H / 256, nsb_f = F / 256, r2 = 32 / nsb_h, r3 = 32 / nsb_f;
+    const int t2 = F / r2, t3 = H / r3;
+    const size_t row_h = static_cast<size_t>(H / 32) * 34;
+    const int n_router_ctas = E / 16, n_pair_ctas = ncta - n_router_ctas;
+    if (n_pair_ctas < 1) return fail(WD_E_INVALID, "this grid is too small for the compiled layer kernel of this geometry");
+    p.n_sp = (SF + n_pair_ctas - 1) / n_pair_ctas;
+    p.p2_max = (K * t2 + ncta - 1) / ncta;
+    p.b3_max = (t3 + ncta - 1) / ncta;
+    p.act_pad = (p.p2_max * r2 + 15) / 16 * 16;
+    if (wd::kFbTiles + 2 * p.p2_max + p.b3_max * K > static_cast<unsigned>(wd::kMaxBars) || p.b3_max * r3 > 80 ||
+        p.n_sp > wd::kWarps || p.b3_max > 32)
+        return fail(WD_E_INVALID, "this grid is too small for the compiled layer kernel of this geometry");
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off = align_up(off + bytes, 128);
+        return static_cast<unsigned>(o);
+    };
+    p.off_tab = take(wd::kGridTableBytes);
+    p.off_xq0 = take(H);
+    p.off_xd0 = take(H / 32 * 4);
+    p.off_xk = take(static_cast<size_t>(nsb_h) * wd::kActSbStride);
+    p.off_xdk = take(nsb_h * 4);
+    p.off_actk = take(static_cast<size_t>(K) * nsb_f * wd::kActSbStride);
+    p.off_actd = take(static_cast<size_t>(K) * nsb_f * 4);
+    p.off_shq = take(SF);
+    p.off_shd = take(SF / 32 * 4);
+    p.off_misc = take(wd::kFmEnd * 4);
+    p.off_bar = take(wd::kMaxBars * 8);
+    p.off_slots = take(static_cast<size_t>(E) * 4);
+    // tile accumulator; the F32 copy of x that the shared gate dot needs lives there during phases 0 and 1
+    const size_t acc_tiles = std::max<size_t>(2 * p.p2_max, static_cast<size_t>(p.b3_max) * K);
+    p.off_acc = take(std::max<size_t>(acc_tiles * wd::kFastAccStride * 4, static_cast<size_t>(H) * 4));
+    p.off_xf = p.off_acc;
+    p.off_rowbuf = take(static_cast<size_t>(2) * p.p2_max * r2 * 4);
+    p.off_rows3 = take(static_cast<size_t>(p.b3_max) * (K + 1) * r3 * 4);
+    p.off_push = take(std::max<size_t>(std::max<size_t>(p.act_pad, static_cast<size_t>(p.b3_max) * r3), 16) * 8);
+    p.xstride = 2ull * E + 2ull * SF + 32 + 2ull * H + 2ull * K * F;
+    p.off_a = take(std::max<size_t>(std::max<size_t>(16, 2 * p.n_sp) * row_h + static_cast<size_t>(H) * 4,
+                                    static_cast<size_t>(2) * p.p2_max * wd::kIq3TileBytes));
+    p.off_b = take(static_cast<size_t>(p.b3_max) * K * wd::kIq3TileBytes);
+    p.off_c = take(static_cast<size_t>(p.b3_max) * r3 * (SF / 32) * 34);
+    e->fast_smem = off;
+    if (e->fast_smem > 227 * 1024) return fail(WD_E_INVALID, "the compiled layer kernel needs more shared memory than one SM has");
+    return WD_OK;
+}
 
 int plan_shared_memory(wd_engine *e) {
     wd::MoeParams &p = e->base;
@@ -250,14 +333,20 @@ int plan_shared_memory(wd_engine *e) {
     return WD_OK;
 }
 
+// ggml Q8_0 blocks -> the layout of the engine's layer kernel (4-row tasks, or single rows for the compiled kernel)
+void launch_repack_q8(const wd_engine *e, const uint8_t *src, uint8_t *dst, int rows, int nb, cudaStream_t s) {
+    const long long n = static_cast<long long>(rows) * nb;
+    const unsigned grid = static_cast<unsigned>((n + 255) / 256);
+    if (e->fast_fn) wd::repack_q8_0_rows_kernel<<<grid, 256, 0, s>>>(src, dst, rows, nb);
+    else wd::repack_q8_0_kernel<<<grid, 256, 0, s>>>(src, dst, rows, nb);
+}
+
 int upload_repacked_q8(wd_engine *e, const void *host_ggml, int rows, int cols, uint8_t **dev_out) {
     const size_t bytes = static_cast<size_t>(rows) * (cols / 32) * 34;
     if (bytes > e->staging_bytes) return fail(WD_E_STATE, "staging buffer too small for a Q8_0 tensor");
     if (!*dev_out) WD_CUDA(cudaMalloc(dev_out, bytes));
     WD_CUDA(cudaMemcpyAsync(e->staging, host_ggml, bytes, cudaMemcpyHostToDevice, e->stream));
-    const long long n = static_cast<long long>(rows) * (cols / 32);
-    wd::repack_q8_0_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, e->stream>>>(e->staging, *dev_out, rows,
-                                                                                         cols / 32);
+    launch_repack_q8(e, e->staging, *dev_out, rows, cols / 32, e->stream);
     WD_CUDA(cudaGetLastError());
     WD_CUDA(cudaStreamSynchronize(e->stream));
     return WD_OK;
@@ -327,19 +416,34 @@ int launch_layers(wd_engine *e, int begin, int end, const float *x, float *resid
     }
     int rc = sync_layer_table(e, s);
     if (rc) return rc;
-    wd::MoeParams p = e->base;
-    p.layers = e->layer_table;
-    p.layer_begin = begin;
-    p.layer_end = end;
-    p.stamp_layer = std::min(end - 1, begin + e->stamp_layer);
-    p.x = x;
-    p.residual = residual;
-    p.out = out;
-    p.stamps = e->profiling ? e->stamps : nullptr;
-    p.select_only = select_only ? 1 : 0;
-    void *args[] = {&p};
-    WD_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(wd::moe_layer_kernel), dim3(e->n_sm),
-                                        dim3(wd::kThreads), args, e->smem_bytes, s));
+    if (e->fast_fn) {
+        wd::FastParams p = e->fbase;
+        p.layers = e->layer_table;
+        p.layer_begin = begin;
+        p.layer_end = end;
+        p.stamp_layer = std::min(end - 1, begin + e->stamp_layer);
+        p.x = x;
+        p.residual = residual;
+        p.out = out;
+        p.stamps = e->profiling ? e->stamps : nullptr;
+        p.select_only = select_only ? 1 : 0;
+        void *args[] = {&p};
+        WD_CUDA(cudaLaunchCooperativeKernel(e->fast_fn, dim3(e->n_sm), dim3(wd::kThreads), args, e->fast_smem, s));
+    } else {
+        wd::MoeParams p = e->base;
+        p.layers = e->layer_table;
+        p.layer_begin = begin;
+        p.layer_end = end;
+        p.stamp_layer = std::min(end - 1, begin + e->stamp_layer);
+        p.x = x;
+        p.residual = residual;
+        p.out = out;
+        p.stamps = e->profiling ? e->stamps : nullptr;
+        p.select_only = select_only ? 1 : 0;
+        void *args[] = {&p};
+        WD_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(wd::moe_layer_kernel), dim3(e->n_sm),
+                                            dim3(wd::kThreads), args, e->smem_bytes, s));
+    }
     e->epoch += static_cast<uint32_t>(end - begin);     // the kernel advances the device's epoch by the same amount
     e->last_parity = static_cast<int>(e->epoch & 1u);   // the last layer's tag is the new epoch; halves follow the tag
     e->last_tokens = 1;
@@ -460,6 +564,7 @@ int check_device_status(wd_engine *e) {
         // an interrupted launch leaves the tag epoch and the exchange words undefined: start over
         cudaMemset(e->sync, 0, 8192);
         cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t));
+        if (e->xbuf) cudaMemset(e->xbuf, 0, e->xbuf_words * sizeof(wd::tagged_t));
         e->epoch = 0;
         return fail(WD_E_DEVICE, "kernel raised status " + std::to_string(st) +
                                      " (1 wait timeout, 2 copy timeout, 4 expert without slot, 8 geometry, "
@@ -576,11 +681,15 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     WD_TRY(cudaMalloc(&e->tok_weights, static_cast<size_t>(c.max_tokens) * K * 4));
     WD_TRY(cudaMalloc(&e->residual_buf, H * 4));
     // tagged exchange words: logits, shared act, shared gate, act, expert out, shared down, residual (x2), progress
-    const size_t tw_logits = 0, tw_shact = tw_logits + 2 * static_cast<size_t>(E), tw_shgate = tw_shact + 2 * static_cast<size_t>(SF),
-                 tw_act = tw_shgate + 2, tw_eo = tw_act + 2 * static_cast<size_t>(K) * F,
-                 tw_shdown = tw_eo + 2 * static_cast<size_t>(K) * H, tw_res = tw_shdown + 2 * static_cast<size_t>(H),
-                 tw_prog = tw_res + 2 * static_cast<size_t>(H), tw_left = tw_prog + static_cast<size_t>(e->n_sm);
-    e->tagged_words = tw_left + 8;
+    // every region starts on a 128-byte line (16 words): lines that one CTA writes are then never shared with another's
+    auto up16 = [](size_t w) { return (w + 15) / 16 * 16; };
+    const size_t tw_logits = 0, tw_shact = up16(tw_logits + 2 * static_cast<size_t>(E)),
+                 tw_shgate = up16(tw_shact + 2 * static_cast<size_t>(SF)), tw_act = tw_shgate + 32,
+                 tw_eo = up16(tw_act + 2 * static_cast<size_t>(K) * F),
+                 tw_shdown = up16(tw_eo + 2 * static_cast<size_t>(K) * H), tw_res = up16(tw_shdown + 2 * static_cast<size_t>(H)),
+                 tw_prog = up16(tw_res + 2 * static_cast<size_t>(H)), tw_left = up16(tw_prog + static_cast<size_t>(e->n_sm)),
+                 tw_end = tw_left + 16;
+    e->tagged_words = tw_end;
     WD_TRY(cudaMalloc(&e->tagged, e->tagged_words * sizeof(wd::tagged_t)));
     WD_TRY(cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t)));
     // staging: one layer's routed experts in ggml layout (or a dense tensor, whichever is larger)
@@ -638,6 +747,36 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
         fail(WD_E_INVALID, "the layer kernel does not fit one CTA per SM with this geometry");
         return bail(WD_E_INVALID);
     }
+    if (c.shared_ffn > 0 && (e->fast_fn = find_fast_kernel(c)) != nullptr) {
+        wd::FastParams &f = e->fbase;
+        if ((rc = plan_fast(e)) != WD_OK) {
+            e->fast_fn = nullptr;       // the generic kernel serves this grid
+        } else {
+            e->xbuf_words = static_cast<size_t>(e->n_sm) * f.xstride;
+            cudaError_t fe = cudaMalloc(&e->xbuf, e->xbuf_words * sizeof(wd::tagged_t));
+            if (fe == cudaSuccess) fe = cudaMemset(e->xbuf, 0, e->xbuf_words * sizeof(wd::tagged_t));
+            if (fe == cudaSuccess) fe = cudaMalloc(&e->eo_plain, static_cast<size_t>(K) * H * 4);
+            if (fe == cudaSuccess) fe = cudaMalloc(&e->shdown_plain, static_cast<size_t>(H) * 4);
+            if (fe == cudaSuccess) fe = cudaMalloc(&e->fallbacks, 64);
+            if (fe == cudaSuccess) fe = cudaMemset(e->fallbacks, 0, 64);
+            if (fe == cudaSuccess)
+                fe = cudaFuncSetAttribute(e->fast_fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(e->fast_smem));
+            if (fe != cudaSuccess) {
+                fail(WD_E_CUDA, std::string("setting up the compiled layer kernel: ") + cudaGetErrorString(fe));
+                return bail(WD_E_CUDA);
+            }
+            f.e_first = p.e_first; f.e_count = p.e_count; f.w_scale = p.w_scale; f.eps = p.eps;
+            f.pool = p.pool; f.slot_bytes = p.slot_bytes; f.gate_off = p.gate_off; f.up_off = p.up_off; f.down_off = p.down_off;
+            f.grid_packed = p.grid_packed;
+            f.xbuf = e->xbuf;
+            f.t_expert_out = p.t_expert_out; f.t_progress = p.t_progress;
+            f.t_peer_left = p.t_peer_left; f.n_peers = 0;
+            f.ids = p.ids; f.weights = p.weights; f.routed = p.routed;
+            f.expert_out = e->eo_plain; f.shared_down = e->shdown_plain;
+            f.sync = p.sync; f.host_status = p.host_status; f.fallbacks = e->fallbacks;
+        }
+        rc = WD_OK;
+    }
     *out = e;
     return WD_OK;
 }
@@ -652,7 +791,7 @@ void wd_engine_destroy(wd_engine *e) {
         cudaFree(L.sh_down); cudaFree(L.norm); cudaFree(L.slot_of_expert);
     }
     void *bufs[] = {e->pool, e->grid_packed, e->grid2_packed, e->synth_lut, e->sync, e->tagged, e->ids, e->weights, e->routed, e->tok_ids, e->tok_weights,
-                    e->x_buf, e->out_buf, e->residual_buf, e->staging, e->stamps, e->layer_table};
+                    e->x_buf, e->out_buf, e->residual_buf, e->staging, e->stamps, e->layer_table, e->eo_plain, e->shdown_plain, e->fallbacks, e->xbuf};
     for (void *b : bufs) cudaFree(b);
     delete e->copy_pool;
     cudaFree(e->miss_staging);
@@ -1001,6 +1140,33 @@ int wd_stack_step_host(wd_engine *e, const float *in_host, float *out_host) {
     return check_device_status(e);
 }
 
+// The compiled kernel's act values, from CTA 0's mailbox: row jl there is the jl-th OWNED selected expert. Rows of
+// experts another rank owns come back as zeros.
+static int read_fast_act(wd_engine *e, float *dst, size_t bytes) {
+    const wd_config &c = e->cfg;
+    const int K = c.top_k, F = c.expert_ffn;
+    if (bytes < static_cast<size_t>(K) * F * 4) return fail(WD_E_INVALID, "tap buffer too small");
+    WD_CUDA(cudaStreamSynchronize(e->stream));
+    WD_CUDA(cudaDeviceSynchronize());
+    const size_t words = static_cast<size_t>(K) * F;
+    std::vector<wd::tagged_t> w(words);
+    std::vector<int> ids(K);
+    const size_t o_act = 2ull * c.n_experts + 2ull * c.shared_ffn + 32 + 2ull * c.hidden;       // inside a mailbox
+    WD_CUDA(cudaMemcpy(w.data(), e->xbuf + o_act + static_cast<size_t>(e->last_parity) * words, words * sizeof(wd::tagged_t),
+                       cudaMemcpyDeviceToHost));
+    WD_CUDA(cudaMemcpy(ids.data(), e->ids, K * sizeof(int), cudaMemcpyDeviceToHost));
+    int jl = 0;
+    for (int j = 0; j < K; ++j) {
+        const bool owned = ids[j] >= e->e_first && ids[j] < e->e_first + e->e_count;
+        for (int f = 0; f < F; ++f) {
+            const uint32_t v = owned ? static_cast<uint32_t>(w[static_cast<size_t>(jl) * F + f]) : 0u;
+            memcpy(dst + static_cast<size_t>(j) * F + f, &v, 4);
+        }
+        jl += owned ? 1 : 0;
+    }
+    return WD_OK;
+}
+
 int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
     if (!e || !dst) return fail(WD_E_INVALID, "null argument");
     if (token == -1) token = e->last_tokens - 1;     // the last token of the last call
@@ -1015,7 +1181,10 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
     const wd::tagged_t *tsrc = nullptr;     // or tagged words of the last layer's half
     size_t n = 0;
     switch (tap) {
-        case WD_TAP_LOGITS: tsrc = p.t_logits + par * c.n_experts; n = c.n_experts * 4; break;
+        case WD_TAP_LOGITS:      // the compiled kernel: CTA 0's mailbox ([2][E] logits | [2][SF] shared act | [2][16] gate | ..)
+            tsrc = e->fast_fn ? e->xbuf + par * c.n_experts : p.t_logits + par * c.n_experts;
+            n = c.n_experts * 4;
+            break;
         case WD_TAP_IDS:
             src = e->last_tokens > 1 ? e->tok_ids + token * c.top_k : e->ids;
             n = c.top_k * 4;
@@ -1026,17 +1195,27 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
             break;
         case WD_TAP_ACT:
             n = static_cast<size_t>(c.top_k) * c.expert_ffn * 4;
+            if (e->fast_fn) return read_fast_act(e, static_cast<float *>(dst), bytes);
             tsrc = p.t_act + par * (n / 4);
             break;
         case WD_TAP_EXPERT_OUT:
             n = static_cast<size_t>(c.top_k) * c.hidden * 4;
-            tsrc = p.t_expert_out + par * (n / 4);
+            if (e->fast_fn) src = e->eo_plain;
+            else tsrc = p.t_expert_out + par * (n / 4);
             break;
         case WD_TAP_ROUTED: src = e->routed; n = c.hidden * 4; break;
-        case WD_TAP_SHARED: tsrc = p.t_shared_down + par * c.hidden; n = c.hidden * 4; break;
-        case WD_TAP_SHARED_GATE: tsrc = p.t_shared_gate + par; n = 4; break;
+        case WD_TAP_SHARED:
+            if (e->fast_fn) src = e->shdown_plain;
+            else tsrc = p.t_shared_down + par * c.hidden;
+            n = c.hidden * 4;
+            break;
+        case WD_TAP_FALLBACKS: src = e->fallbacks; n = 4; break;
+        case WD_TAP_SHARED_GATE:
+            tsrc = e->fast_fn ? e->xbuf + 2 * c.n_experts + 2 * c.shared_ffn + par * 16 : p.t_shared_gate + par;
+            n = 4;
+            break;
         case WD_TAP_SHARED_ACT:
-            tsrc = p.t_shared_act + par * std::max(c.shared_ffn, 1);
+            tsrc = e->fast_fn ? e->xbuf + 2 * c.n_experts + par * c.shared_ffn : p.t_shared_act + par * std::max(c.shared_ffn, 1);
             n = static_cast<size_t>(c.shared_ffn) * 4;
             break;
         case WD_TAP_STAMPS: src = e->stamps; n = static_cast<size_t>(e->n_sm) * wd::kStampStride * 8; break;
@@ -1064,7 +1243,7 @@ int wd_set_profiling(wd_engine *e, int on) {
 }
 
 int wd_sm_count(const wd_engine *e) { return e ? e->n_sm : 0; }
-const char *wd_kernel_name(const wd_engine *) { return "moe_layer_kernel"; }
+const char *wd_kernel_name(const wd_engine *e) { return e && e->fast_fn ? "moe_fast_kernel" : "moe_layer_kernel"; }
 
 // ---- expert parallelism ----------------------------------------------------------------------------
 int wd_ep_handle_bytes(void) { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
@@ -1079,6 +1258,16 @@ int wd_ep_export(wd_engine *e, void *handle_out) {
 }
 
 namespace {
+// the compiled kernel's parameter block carries the same peer pointers
+void mirror_peers(wd_engine *e) {
+    for (int p = 0; p < 8; ++p) {
+        e->fbase.peer_expert_out[p] = e->base.peer_expert_out[p];
+        e->fbase.peer_left_out[p] = e->base.peer_left_out[p];
+        e->fbase.peer_rank[p] = e->base.peer_rank[p];
+    }
+    e->fbase.n_peers = e->base.n_peers;
+}
+
 int ep_check_connect(wd_engine *e, int n_peers) {
     if (!e) return fail(WD_E_INVALID, "null engine");
     if (n_peers != e->cfg.ep_size - 1) return fail(WD_E_INVALID, "expected ep_size - 1 peers");
@@ -1110,6 +1299,7 @@ int wd_ep_connect(wd_engine *e, int n_peers, const void *handles) {
         e->base.peer_left_out[p] = static_cast<wd::tagged_t *>(base) + e->tagged_left_offset + e->cfg.ep_rank;
     }
     e->n_peers = e->base.n_peers = n_peers;
+    mirror_peers(e);
     return WD_OK;
 }
 
@@ -1136,6 +1326,7 @@ int wd_ep_connect_local(wd_engine *e, int n_peers, wd_engine *const *peers) {
         e->base.peer_left_out[p] = o->tagged + o->tagged_left_offset + e->cfg.ep_rank;
     }
     e->n_peers = e->base.n_peers = n_peers;
+    mirror_peers(e);
     return WD_OK;
 }
 
@@ -1151,6 +1342,7 @@ int wd_ep_disconnect(wd_engine *e) {
         e->base.peer_left_out[p] = nullptr;
     }
     e->n_peers = e->base.n_peers = 0;
+    mirror_peers(e);
     return WD_OK;
 }
 
@@ -1160,6 +1352,7 @@ int wd_reset_exchange(wd_engine *e) {
     WD_CUDA(cudaDeviceSynchronize());
     WD_CUDA(cudaMemset(e->sync, 0, 8192));
     WD_CUDA(cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t)));
+    if (e->xbuf) WD_CUDA(cudaMemset(e->xbuf, 0, e->xbuf_words * sizeof(wd::tagged_t)));
     e->epoch = 0;
     return WD_OK;
 }
@@ -1174,6 +1367,7 @@ int wd_device_status(wd_engine *e, int *status) {
     if (st) {
         WD_CUDA(cudaMemset(e->sync, 0, 8192));
         WD_CUDA(cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t)));
+        if (e->xbuf) WD_CUDA(cudaMemset(e->xbuf, 0, e->xbuf_words * sizeof(wd::tagged_t)));
         e->epoch = 0;
     }
     return WD_OK;
@@ -1496,8 +1690,12 @@ static int synth_into(wd_engine *e, int type, long long rows, int cols, float si
 
 int wd_synth_tensor_device(int type, int rows, int cols, float sigma, uint64_t seed, uint64_t stream_id,
                            void *dst_dev, void *stream) {
-    (void)type; (void)rows; (void)cols; (void)sigma; (void)seed; (void)stream_id; (void)dst_dev; (void)stream;
-    return fail(WD_E_STATE, "use wd_synth_model / wd_synth_expert_host (they own the codebook lookup table)");
+    if (!dst_dev || rows <= 0 || cols <= 0) return fail(WD_E_INVALID, "bad argument");
+    if (type == WD_TYPE_IQ3_S)
+        return fail(WD_E_STATE, "IQ3_S tensors come from wd_synth_model / wd_synth_expert_host (the engine owns the "
+                                "codebook lookup table of that encoder)");
+    if (type == WD_TYPE_Q8_0 && cols % 32) return fail(WD_E_INVALID, "Q8_0 needs cols % 32 == 0");
+    return synth_into(nullptr, type, rows, cols, sigma, seed, stream_id, dst_dev, static_cast<cudaStream_t>(stream));
 }
 
 // stream ids of the tensors of layer l: l*16 + {0 router, 1 bias, 2 gate vec, 3..5 shared gate/up/down,
@@ -1527,8 +1725,7 @@ int wd_synth_model(wd_engine *e, uint64_t seed, float sigma, float bias_sigma) {
             if (!*dst) WD_CUDA(cudaMalloc(dst, bytes));
             int r = synth_into(e, WD_TYPE_Q8_0, rows, cols, sigma, seed, sid(l, which), e->staging, s);
             if (r) return r;
-            const long long n = static_cast<long long>(rows) * (cols / 32);
-            wd::repack_q8_0_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(e->staging, *dst, rows, cols / 32);
+            launch_repack_q8(e, e->staging, *dst, rows, cols / 32, s);
             WD_CUDA(cudaGetLastError());
             return WD_OK;
         };

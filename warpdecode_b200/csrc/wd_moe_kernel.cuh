@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
 #define WD_STAMP(i)                                                                            \
     if (stamp_on) {                                                                            \
         unsigned long long t__;                                                                \
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));                                \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__) : : "memory");                                \
         P.stamps[cta * kStampStride + (i)] = t__;                                                        \
         if ((i) == 0 || (i) == 10) P.stamps[cta * kStampStride + 24 + (i) / 10] = clock64();   /* SM clock rate */ \
     }
@@ -278,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     WD_STAMP(0);
     if (P.stamps != nullptr && tid == 0 && layer == P.stamp_layer + 1) {   // start of the next layer: the layer period
         unsigned long long t__;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__) : : "memory");
         P.stamps[cta * kStampStride + 14] = t__;
     }
 

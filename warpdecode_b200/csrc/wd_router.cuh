@@ -36,13 +36,14 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {
     return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
 }
 
-__device__ __forceinline__ void router_select_cta(float l0, float l1, int E, int K, float w_scale, const RouterScratch &S,
-                                                  int *ids_out, float *w_out, unsigned long long *stage_stamps = nullptr) {
-    // profiling only: thread 0 leaves a global-timer value after each stage
+// Softmax of the whole row (the first half of router_select_cta): thread t holds the logits of experts t and
+// t + kThreads and receives their probabilities (-inf in every place when the sum is zero).
+__device__ __forceinline__ void router_softmax_cta(float l0, float l1, int E, const RouterScratch &S, float &p0_out,
+                                                   float &p1_out, unsigned long long *stage_stamps = nullptr) {
 #define WD_RSTAMP(i)                                                       \
     if (stage_stamps != nullptr && threadIdx.x == 0) {                     \
         unsigned long long t__;                                            \
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__));            \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__) : : "memory");            \
         stage_stamps[i] = t__;                                             \
     }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -107,6 +108,48 @@ __device__ __forceinline__ void router_select_cta(float l0, float l1, int E, int
             p1 = __fmul_rn(p1, inv);
         }
     }
+    p0_out = p0;
+    p1_out = p1;
+#undef WD_RSTAMP
+}
+
+// Closing step of the selection by one warp: lane j < K holds the j-th picked probability; returns its weight
+// = picked / max((float) sum of the K picked, 2^-14) (times w_scale unless it is 0 or 1). The reference adds the
+// picked probabilities one by one into a double; as for the softmax sum, a shuffle tree gives the same bits
+// whenever every partial sum is exact, else the serial order is replayed.
+__device__ __forceinline__ float router_weights_warp(float my_p, int K, float w_scale, int lane) {
+    const float tp = lane < K ? my_p : 0.0f;
+    const int ex = static_cast<int>((__float_as_uint(tp) >> 23) & 0xffu);
+    const bool nz = tp != 0.0f;
+    const int bad = __any_sync(0xffffffffu, nz && (ex == 0 || ex == 255 || tp < 0.0f));
+    const int min_exp = __reduce_min_sync(0xffffffffu, nz ? ex : 0x7fffffff);
+    double wsum = static_cast<double>(tp);
+#pragma unroll
+    for (int sft = 1; sft < 32; sft <<= 1) wsum = __dadd_rn(wsum, __shfl_xor_sync(0xffffffffu, wsum, sft));
+    const int tot_exp = static_cast<int>((__double_as_longlong(wsum) >> 52) & 0x7ff) - 1023 + 127;
+    if (bad || (min_exp != 0x7fffffff && tot_exp + 1 - (min_exp - 23) > 52)) {
+        wsum = 0.0;
+#pragma unroll 1
+        for (int j = 0; j < K; ++j) wsum = __dadd_rn(wsum, static_cast<double>(__shfl_sync(0xffffffffu, my_p, j)));
+    }
+    const float denom = fmaxf(__double2float_rn(wsum), 6.103515625e-5f);
+    float w = __fdiv_rn(my_p, denom);
+    if (w_scale != 0.0f && w_scale != 1.0f) w = __fmul_rn(w, w_scale);
+    return w;
+}
+
+// The k rungs over the probabilities (the second half of router_select_cta).
+__device__ __forceinline__ void router_rungs_cta(float p0, float p1, int E, int K, float w_scale, const RouterScratch &S,
+                                                 int *ids_out, float *w_out, unsigned long long *stage_stamps = nullptr) {
+#define WD_RSTAMP(i)                                                       \
+    if (stage_stamps != nullptr && threadIdx.x == 0) {                     \
+        unsigned long long t__;                                            \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__) : : "memory");            \
+        stage_stamps[i] = t__;                                             \
+    }
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int e0 = tid, e1 = tid + kThreads;
+    const bool h0 = e0 < E, h1 = e1 < E;
     WD_RSTAMP(2)
     if (S.probs) {
         if (h0) S.probs[e0] = p0;
@@ -184,26 +227,8 @@ __device__ __forceinline__ void router_select_cta(float l0, float l1, int E, int
     }
     if (warp == 0) {
         if (lane == 0) { WD_RSTAMP(4) }
-        // the reference adds the picked probabilities one by one into a double; as for the softmax sum, a
-        // shuffle tree gives the same bits whenever every partial sum is exact, else the serial order is replayed
-        const float tp = lane < K ? my_p : 0.0f;
-        const int ex = static_cast<int>((__float_as_uint(tp) >> 23) & 0xffu);
-        const bool nz = tp != 0.0f;
-        const int bad = __any_sync(0xffffffffu, nz && (ex == 0 || ex == 255 || tp < 0.0f));
-        const int min_exp = __reduce_min_sync(0xffffffffu, nz ? ex : 0x7fffffff);
-        double wsum = static_cast<double>(tp);
-#pragma unroll
-        for (int sft = 1; sft < 32; sft <<= 1) wsum = __dadd_rn(wsum, __shfl_xor_sync(0xffffffffu, wsum, sft));
-        const int tot_exp = static_cast<int>((__double_as_longlong(wsum) >> 52) & 0x7ff) - 1023 + 127;
-        if (bad || (min_exp != 0x7fffffff && tot_exp + 1 - (min_exp - 23) > 52)) {
-            wsum = 0.0;
-#pragma unroll 1
-            for (int j = 0; j < K; ++j) wsum = __dadd_rn(wsum, static_cast<double>(__shfl_sync(0xffffffffu, my_p, j)));
-        }
-        const float denom = fmaxf(__double2float_rn(wsum), 6.103515625e-5f);
+        const float w = router_weights_warp(my_p, K, w_scale, lane);
         if (lane < K) {
-            float w = __fdiv_rn(my_p, denom);
-            if (w_scale != 0.0f && w_scale != 1.0f) w = __fmul_rn(w, w_scale);
             ids_out[lane] = static_cast<int>(my_id);
             w_out[lane] = w;
         }
@@ -211,6 +236,13 @@ __device__ __forceinline__ void router_select_cta(float l0, float l1, int E, int
     __syncthreads();
     WD_RSTAMP(5)
 #undef WD_RSTAMP
+}
+
+__device__ __forceinline__ void router_select_cta(float l0, float l1, int E, int K, float w_scale, const RouterScratch &S,
+                                                  int *ids_out, float *w_out, unsigned long long *stage_stamps = nullptr) {
+    float p0, p1;
+    router_softmax_cta(l0, l1, E, S, p0, p1, stage_stamps);
+    router_rungs_cta(p0, p1, E, K, w_scale, S, ids_out, w_out, stage_stamps);
 }
 
 }  // namespace wd
