@@ -218,9 +218,11 @@ __device__ __noinline__ void q8k_from_regs(const float v[8], int lane, uint8_t *
 __device__ __noinline__ float silu_mul(float g, float u) { return __fmul_rn(silu_ggml(g), u); }
 
 // out-of-line copies of the two halves of the router (the second one is the rare, exact path)
-__device__ __noinline__ void fast_softmax(float l0, float l1, int E, const RouterScratch &S, float &p0, float &p1) {
-    router_softmax_cta(l0, l1, E, S, p0, p1);
+__device__ __noinline__ void fast_softmax(float l0, float l1, float mx, int E, const RouterScratch &S, float &p0, float &p1,
+                                          float *inv) {
+    router_softmax_given_max(l0, l1, mx, E, S, p0, p1, nullptr, inv);
 }
+__device__ __noinline__ float exp_noinline(float x) { return exp_ggml(x); }
 __device__ __noinline__ void fast_rungs(float p0, float p1, int E, int K, float w_scale, const RouterScratch &S, int *ids,
                                         float *w) {
     router_rungs_cta(p0, p1, E, K, w_scale, S, ids, w);
@@ -310,9 +312,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
 
     uint32_t *gm = reinterpret_cast<uint32_t *>(misc + kFmGm);
     int *cnt = reinterpret_cast<int *>(misc + kFmCnt);
-    uint32_t *cand_k = reinterpret_cast<uint32_t *>(misc + kFmCk), *cand_i = reinterpret_cast<uint32_t *>(misc + kFmCi);
+    uint2 *cand = reinterpret_cast<uint2 *>(misc + kFmCk);         // candidates above the threshold: (key, expert)
     int *sel_ids = reinterpret_cast<int *>(misc + kFmIds);
-    float *sel_w = misc + kFmW, *sel_p = misc + kFmSelP;
+    float *sel_w = misc + kFmW;
+    uint32_t *sel_keys = reinterpret_cast<uint32_t *>(misc + kFmSelP);   // order keys of the picked logits, rank order
     int *flags = reinterpret_cast<int *>(misc + kFmFlag);          // [0] order proven, [1] boundary id; floats: [2] boundary p
     int *loc_j = reinterpret_cast<int *>(misc + kFmLocJ), *loc_slot = reinterpret_cast<int *>(misc + kFmLocSlot);
     int *loc_n = reinterpret_cast<int *>(misc + kFmLocN);
@@ -414,8 +417,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
         asm volatile("mov.u64 %0, %%clock64;" : "=l"(c__) : : "memory");
         P.stamps[cta * kStampStride + 14] = static_cast<unsigned long long>(c__);
     }
+    // (No proxy fence anywhere in this kernel: a buffer that receives a bulk copy has only ever been READ by ordinary
+    // loads since its last copy, and those reads are complete before the block-wide synchronisation that precedes
+    // the new copy.)
     if (warp == kWarps - 1) {
-        fence_proxy_async();
         if (first) issue_phase1(L);         // later layers' copies were requested by the layer before
         issue_shared_down(L);
     }
@@ -544,8 +549,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
 
     // ---- phase 1: one row (or shared row pair) per warp -------------------------------------------------------------
     {
+        const int n_tasks = router_cta ? my_rr : 2 * my_sp;     // a pair CTA: gate rows [0, my_sp), then the up rows
+        float *rowres = shrow;                                   // row results of a pair CTA (free until phase 3)
 #pragma unroll 1
-        for (int t = warp; t < my_rr + my_sp; t += kWarps) {
+        for (int t = warp; t < n_tasks; t += kWarps) {
             if (router_cta) {
                 const int row = rr0 + t;
                 const float bias = L.router_bias ? L.router_bias[row] : 0.0f;      // fetched before the wait
@@ -557,9 +564,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
                 }
             } else {
                 mbar_wait(&bars[kFbShared], mpar, err);
-                const float g = q8_row_warp<G::NBH>(reg_a + t * G::ROW_H, xq0, xd0, lane);
-                const float u = q8_row_warp<G::NBH>(reg_a + (P.n_sp + t) * G::ROW_H, xq0, xd0, lane);
-                if (lane == 0) pushbuf[t] = make_tagged(silu_mul(g, u), tag);
+                const int r = t < my_sp ? t : static_cast<int>(P.n_sp) + t - my_sp;
+                const float v = q8_row_warp<G::NBH>(reg_a + r * G::ROW_H, xq0, xd0, lane);
+                if (lane == 0) rowres[t] = v;
             }
         }
         if (cta == gcta && warp == kWarps - 1) {
@@ -573,9 +580,21 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
                              : "memory");
         }
         __syncthreads();
-        // a router CTA's 16 logits are one line of every mailbox; a pair CTA's shared activations a run of the bands'
-        if (router_cta) push_words(pushbuf, my_rr, P.xbuf, P.xstride, o_logits + rr0, ncta, warp, lane);
-        else push_words(pushbuf, my_sp, P.xbuf, P.xstride, o_shact + sp0, n_band_ctas, warp, lane);
+        if (router_cta) {
+            // a router CTA's 16 logits are one line of every mailbox
+            push_words(pushbuf, my_rr, P.xbuf, P.xstride, o_logits + rr0, ncta, warp, lane);
+        } else {
+            // a pair CTA's shared activations: every warp forms them itself (lane = pair) and carries them to its share
+            // of the band CTAs' mailboxes
+            tagged_t w = 0ull;
+            if (lane < my_sp) w = make_tagged(silu_mul(rowres[lane], rowres[my_sp + lane]), tag);
+#pragma unroll 1
+            for (int d = warp; d < n_band_ctas; d += kWarps)
+                if (lane < my_sp)
+                    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(P.xbuf + static_cast<size_t>(d) * P.xstride + o_shact + sp0 + lane),
+                                 "l"(w)
+                                 : "memory");
+        }
     }
     WD_STAMP(2);
 
@@ -626,16 +645,16 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
     WD_DSTAMP(18, tid == 0);
     bool slow;
     {
-        // threshold: the K-th best group maximum (at least K experts reach it)
-        const uint32_t mine = lane < 16 ? gm[lane] : 0u;
+        // threshold: the K-th best group maximum (at least K experts reach it). Every lane ranks one of the 16 maxima
+        // against all of them, read from shared memory (no shuffle loops: the shuffle unit is one per SM).
+        const uint32_t mine = gm[lane & 15];
         int rank = 0;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const uint32_t o = __shfl_sync(0xffffffffu, mine, j);
-            rank += (o > mine) || (o == mine && j < lane);
+            const uint32_t o = gm[j];
+            rank += (o > mine) || (o == mine && j < (lane & 15));
         }
-        const uint32_t thr = __shfl_sync(0xffffffffu, mine, __ffs(__ballot_sync(0xffffffffu, lane < 16 && rank == K - 1)) - 1);
-        WD_DSTAMP(22, tid == 0);
+        const uint32_t thr = gm[__ffs(__ballot_sync(0xffffffffu, lane < 16 && rank == K - 1)) - 1];
         const bool c0 = h0 && key0 >= thr, c1 = h1 && key1 >= thr;
         const unsigned b0 = __ballot_sync(0xffffffffu, c0), b1 = __ballot_sync(0xffffffffu, c1);
         int base = 0;
@@ -644,69 +663,64 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
         const unsigned lt = (1u << lane) - 1u;
         if (c0) {
             const int pos = base + __popc(b0 & lt);
-            if (pos < kFastMaxCand) {
-                cand_k[pos] = key0;
-                cand_i[pos] = static_cast<uint32_t>(tid);
-            }
+            if (pos < kFastMaxCand) cand[pos] = make_uint2(key0, static_cast<uint32_t>(tid));
         }
         if (c1) {
             const int pos = base + __popc(b0) + __popc(b1 & lt);
-            if (pos < kFastMaxCand) {
-                cand_k[pos] = key1;
-                cand_i[pos] = static_cast<uint32_t>(tid + kThreads);
-            }
+            if (pos < kFastMaxCand) cand[pos] = make_uint2(key1, static_cast<uint32_t>(tid + kThreads));
         }
         slow = thr <= kKeyNegInf;      // fewer than K groups hold a finite logit: leave it to the exact rungs
-        WD_DSTAMP(23, tid == 0);
-        WD_DSTAMP(20, tid == kThreads - 1);
     }
     __syncthreads();
     WD_DSTAMP(19, tid == 0);
-    int n_loc = 0;
-    {
-        const int nc = *cnt;
-        slow = slow || nc > 32 || nc < K;
-        if (!slow) {
-            // every warp ranks the candidates for itself: (larger key, then lower index) is a total order
-            const uint32_t ck = lane < nc ? cand_k[lane] : 0u, ci = lane < nc ? cand_i[lane] : 0xffffffffu;
-            int rank = 0;
-#pragma unroll 1
-            for (int j = 0; j < nc; ++j) {
-                const uint32_t kj = __shfl_sync(0xffffffffu, ck, j), ij = __shfl_sync(0xffffffffu, ci, j);
-                rank += (kj > ck) || (kj == ck && ij < ci);
-            }
-            if (lane < nc && rank < K) {
-                sel_ids[rank] = static_cast<int>(ci);
-                if (warp == 0) red_or_shared(&selmask[ci >> 5], 1u << (ci & 31u));
-            }
-            __syncwarp();
-        }
-    }
-    WD_STAMP(4);
-
-    // The owned selected experts in rank order with their slots, per warp in registers (lane i < n_loc), then this
-    // warp's share of the tile copies. Also used after the exact rungs.
     const int p2_max = static_cast<int>(P.p2_max), n_dslots = static_cast<int>(P.b3_max) * K;
     uint64_t *bar_gu = bars + kFbTiles, *bar_dn = bars + kFbTiles + 2 * p2_max;
-    auto issue_tiles = [&]() {
+    // warp 0: the owned picked experts in rank order with their slots, from sel_ids
+    auto build_loc = [&]() {
         const int e = lane < K ? sel_ids[lane] : -1;
         const bool owned = lane < K && e >= P.e_first && e < P.e_first + P.e_count;
         int slot = owned ? slot_tab[e] : 0;
         if (owned && slot < 0) {
-            atomicOr(err, kErrExpertMiss);
+            if (!P.select_only) atomicOr(err, kErrExpertMiss);
             slot = 0;
         }
         const unsigned mask = __ballot_sync(0xffffffffu, owned);
-        const int nl = __popc(mask);
-        const int srcl = lane < nl ? static_cast<int>(__fns(mask, 0, lane + 1)) : 0;
-        const int cslot = __shfl_sync(0xffffffffu, slot, srcl);
-        if (warp == 0) {
-            if (lane < nl) {
-                loc_j[lane] = srcl;
-                loc_slot[lane] = cslot;
-            }
-            if (lane == 0) *loc_n = nl;
+        if (owned) {
+            const int pos = __popc(mask & ((1u << lane) - 1u));
+            loc_j[pos] = lane;
+            loc_slot[pos] = slot;
         }
+        if (lane == 0) *loc_n = __popc(mask);
+    };
+    {
+        const int nc = *cnt;
+        slow = slow || nc > 32 || nc < K;
+        if (!slow && warp == 0) {
+            // warp 0 ranks the candidates: (larger key, then lower index) is a total order
+            const uint2 me = lane < nc ? cand[lane] : make_uint2(0u, 0xffffffffu);
+            int rank = 0;
+#pragma unroll 8
+            for (int j = 0; j < nc; ++j) {      // the loads do not depend on one another
+                const uint2 o = cand[j];
+                rank += (o.x > me.x) || (o.x == me.x && o.y < me.y);
+            }
+            if (lane < nc && rank < K) {
+                sel_ids[rank] = static_cast<int>(me.y);
+                sel_keys[rank] = me.x;
+                red_or_shared(&selmask[me.y >> 5], 1u << (me.y & 31u));
+            }
+            __syncwarp();
+            mbar_wait(&bars[kFbSlots], mpar, err);
+            build_loc();
+        }
+    }
+    __syncthreads();
+    WD_STAMP(4);
+
+    int n_loc = 0;
+    // this warp's share of the tile copies of the owned picked experts (loc_*)
+    auto issue_tiles = [&]() {
+        const int nl = *loc_n;
         const int n_pairs = nl * T2;
 #pragma unroll 1
         for (int s = warp; s < max(p2_max, n_dslots); s += kWarps) {
@@ -716,7 +730,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
             const int jl = pair_live ? u / T2 : 0, t = u % T2;
             const int bi = s / K, jj = s % K;
             const bool dn_ok = s < n_dslots, dn_live = dn_ok && bi < my_b3 && jj < nl;
-            const int sl_p = __shfl_sync(0xffffffffu, cslot, jl), sl_d = __shfl_sync(0xffffffffu, cslot, dn_live ? jj : 0);
+            const int sl_p = loc_slot[jl], sl_d = loc_slot[dn_live ? jj : 0];
             if (lane <= 1 && pair_ok) {
                 uint64_t *bar = &bar_gu[2 * s + lane];
                 if (pair_live) {
@@ -744,9 +758,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
         return nl;
     };
     bool issued = false;
-    mbar_wait(&bars[kFbSlots], mpar, err);
     if (!slow && !P.select_only) {
-        fence_proxy_async();        // region A was read by ordinary loads in phase 1
         n_loc = issue_tiles();
         issued = true;
     }
@@ -760,53 +772,44 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
         rs.red = misc + kFmRed;
         rs.first = misc + kFmFirst;
         rs.cand = reinterpret_cast<uint32_t *>(misc + kFmCand);
-        float p0, p1;
-        fast_softmax(lg[0], lg[1], E, rs, p0, p1);               // two block-wide synchronisations inside
-        bool ok = !slow;
+        // the row maximum is the largest group maximum of the selection
+        uint32_t mk = __reduce_max_sync(0xffffffffu, lane < 16 ? gm[lane] : 0u);
+        const float mx = __uint_as_float((mk & 0x80000000u) ? (mk ^ 0x80000000u) : ~mk);
+        float p0, p1, inv = 0.0f;
+        fast_softmax(lg[0], lg[1], mx, E, rs, p0, p1, &inv);      // one block-wide synchronisation inside
+        bool bad = slow;
         if (!slow) {
+            // The picked set must be the rungs by PROBABILITY: nothing outside it may beat its weakest member (larger
+            // probability, or the same with a lower index), and inside it the probabilities must fall in exactly this
+            // order with every one an ordinary number. Every thread forms the weakest member's probability itself,
+            // with the operations its owner used.
+            const float pb = __fmul_rn(exp_noinline(__fsub_rn(key_to_float(sel_keys[K - 1]), mx)), inv);
+            const int eb = sel_ids[K - 1];
             const bool s0 = h0 && ((selmask[tid >> 5] >> (tid & 31)) & 1u);
             const bool s1 = h1 && ((selmask[(tid + kThreads) >> 5] >> (tid & 31)) & 1u);
-            if (s0 || s1) {
-#pragma unroll 1
-                for (int j = 0; j < K; ++j) {
-                    if (s0 && sel_ids[j] == tid) sel_p[j] = p0;
-                    if (s1 && sel_ids[j] == tid + kThreads) sel_p[j] = p1;
-                }
-            }
-            __syncthreads();
+            bad = (h0 && !s0 && (p0 > pb || (p0 == pb && tid < eb))) || (h1 && !s1 && (p1 > pb || (p1 == pb && tid + kThreads < eb)));
+            bad = bad || !(inv > 0.0f && inv < INFINITY);
             if (warp == 0) {
-                const float pj = lane < K ? sel_p[lane] : 0.0f;
+                const float pj = lane < K ? __fmul_rn(exp_noinline(__fsub_rn(key_to_float(sel_keys[lane]), mx)), inv) : 0.0f;
                 const int ej = lane < K ? sel_ids[lane] : 0x7fffffff;
-                int rank = 0;
-#pragma unroll 1
-                for (int j = 0; j < K; ++j) {
-                    const float po = __shfl_sync(0xffffffffu, pj, j);
-                    const int eo = __shfl_sync(0xffffffffu, ej, j);
-                    rank += (po > pj) || (po == pj && eo < ej);
-                }
-                // every picked probability must be an ordinary number above -inf, in exactly this order
-                const bool fine = lane >= K || (rank == lane && pj == pj && pj > -INFINITY);
-                const int all_fine = __all_sync(0xffffffffu, fine);
+                const float pn = __shfl_down_sync(0xffffffffu, pj, 1);
+                const int en = __shfl_down_sync(0xffffffffu, ej, 1);
+                const bool fine = lane >= K || (pj == pj && pj > -INFINITY && (lane == K - 1 || pj > pn || (pj == pn && ej < en)));
+                bad = bad || !__all_sync(0xffffffffu, fine);
                 const float w = router_weights_warp(pj, K, P.w_scale, lane);
                 if (lane < K) sel_w[lane] = w;
-                if (lane == K - 1) {
-                    flags[0] = all_fine;
-                    flags[1] = ej;
-                    misc[kFmFlag + 2] = pj;
-                }
             }
-            __syncthreads();
-            // nothing outside the picked set may beat its weakest member
-            const float pb = misc[kFmFlag + 2];
-            const int eb = flags[1];
-            const bool beat0 = h0 && !s0 && (p0 > pb || (p0 == pb && tid < eb));
-            const bool beat1 = h1 && !s1 && (p1 > pb || (p1 == pb && tid + kThreads < eb));
-            ok = !__syncthreads_or(beat0 || beat1) && flags[0] != 0;
         }
+        const bool ok = !__syncthreads_or(bad);
         if (!ok) {
             // the exact rungs (rare): ids and weights as the reference computes them, and the copies once more
             fast_rungs(p0, p1, E, K, P.w_scale, rs, sel_ids, sel_w);
             if (cta == 0 && tid == 0 && P.fallbacks != nullptr) atomicAdd(P.fallbacks, 1u);
+            if (warp == 0) {
+                mbar_wait(&bars[kFbSlots], mpar, err);
+                build_loc();
+            }
+            __syncthreads();
             if (!P.select_only) {
                 if (issued) {
                     // the copies issued from the first ids must land before their buffers and barriers are reused
@@ -814,9 +817,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
                     __syncthreads();
                     tflip ^= 1u;
                 }
-                fence_proxy_async();
                 n_loc = issue_tiles();
-                __syncthreads();        // loc_j / loc_slot / loc_n are warp 0's
             }
         }
         if (cta == 0 && tid < K) {
@@ -878,8 +879,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
         }
         const int n_t3 = my_b3 * n_loc;
         for (int i = tid; i < n_t3 * kFastAccStride; i += kThreads) acc[i] = 0;
-        fence_proxy_async();        // region A (read by ordinary loads) receives the next layer's phase-1 rows
-        __syncthreads();
+        __syncthreads();            // region A is free: it receives the next layer's phase-1 rows during the down phase
         // this CTA's act values into every band CTA's mailbox, each tile pair's rows at their place in [expert][F]
         {
             const int n_w = my_pairs * R2;
@@ -912,34 +912,79 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
             wait_tagged<1>(mbox + o_shgate, 1, 1, tag, one, err);
             sg = one[0];
         }
-        // every owned expert's activation -> Q8_K, one warp per superblock: 256 consecutive words of this CTA's mailbox
-#pragma unroll 1
-        for (int sbq = warp; sbq < n_loc * NSB_F; sbq += kWarps) {
-            const int jl = sbq / NSB_F, sb = sbq % NSB_F;
-            const tagged_t *src0 = mbox + o_act + static_cast<size_t>(jl) * F + sb * 256 + lane * 8;
+        // Every owned expert's activation -> Q8_K. A superblock is 256 consecutive words of this CTA's mailbox. Whole
+        // rounds take one superblock per warp; the superblocks left over are cut into equal runs over several warps each
+        // (their maxima meet in shared memory), so that no warp waits for a mostly empty second round.
+        const int n_sb = n_loc * NSB_F, n_full = n_sb & ~(kWarps - 1), rem = n_sb - n_full;
+        int wps = 1;
+        while (wps < 8 && 2 * wps * rem <= kWarps) wps <<= 1;       // warps per left-over superblock
+        const int vpl = 8 / wps;                                    // values per lane in a left-over superblock
+        // this warp's piece: superblock sbq, values [first, first + 32 * vpl) of it, vpl per lane
+        auto piece = [&](int sbq, int first, int n, float v[8]) {
+            const tagged_t *src0 = mbox + o_act + static_cast<size_t>(sbq / NSB_F) * F + (sbq % NSB_F) * 256 + first + lane * n;
             tagged_t w[8] = {};
             unsigned long long t0 = 0ull;
             for (unsigned it = 0;; ++it) {
                 unsigned bad = 0;
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                    if (it == 0 || tag_behind(w[i], tag)) w[i] = ld_tagged(src0 + i);
+                    if (i < n && (it == 0 || tag_behind(w[i], tag))) w[i] = ld_tagged(src0 + i);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) bad |= tag_behind(w[i], tag);
+                for (int i = 0; i < 8; ++i) bad |= (i < n) & tag_behind(w[i], tag);
                 if (!bad) break;
                 if (wait_expired(it, t0, err)) break;
             }
-            float v[8];
             unsigned over = 0;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                over |= tag_ahead(w[i], tag);
-                v[i] = __uint_as_float(static_cast<uint32_t>(w[i]));
+                over |= (i < n) & tag_ahead(w[i], tag);
+                v[i] = i < n ? __uint_as_float(static_cast<uint32_t>(w[i])) : 0.0f;
             }
             report_overrun(over, err);
+        };
+#pragma unroll 1
+        for (int sbq = warp; sbq < n_full + (wps == 1 ? rem : 0); sbq += kWarps) {
+            float v[8];
+            piece(sbq, 0, 8, v);
             WD_DSTAMP(24, tid == 0 && sbq == 0);
-            WD_DSTAMP(25, tid == 3 * 32 && sbq >= kWarps);
             q8k_from_regs(v, lane, actk + sbq * kActSbStride, &actd[sbq]);
+        }
+        if (rem > 0 && wps > 1) {           // uniform over the CTA
+            const int r = warp / wps, wi = warp % wps;
+            const bool live = r < rem;
+            const int sbq = n_full + (live ? r : 0), first = wi * (256 / wps);
+            float v[8];
+            float *amaxs = misc + kFmRed;
+            if (live) {
+                piece(sbq, first, vpl, v);
+                float amax = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+                for (int sft = 1; sft < 32; sft <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sft));
+                if (lane == 0) amaxs[warp] = amax;
+            }
+            __syncthreads();
+            if (live) {
+                float amax = 0.0f;
+                for (int k = 0; k < wps; ++k) amax = fmaxf(amax, amaxs[r * wps + k]);
+                uint32_t packed[2] = {0u, 0u};
+                float d = 0.0f;
+                if (amax != 0.0f) {             // the operations of quantize_q8_K (src/qwen38_cpu_moe.cuh:239)
+                    const float iscale = __fdiv_rn(-127.0f, amax);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int q = min(127, __float2int_rn(__fmul_rn(v[i], iscale)));
+                        if (i < vpl) packed[i >> 2] |= static_cast<uint32_t>(q & 0xff) << (8 * (i & 3));
+                    }
+                    d = __fdiv_rn(1.0f, iscale);
+                }
+                uint8_t *dst = actk + sbq * kActSbStride + first + lane * vpl;
+                if (vpl == 4) *reinterpret_cast<uint32_t *>(dst) = packed[0];
+                else if (vpl == 2) *reinterpret_cast<uint16_t *>(dst) = static_cast<uint16_t>(packed[0]);
+                else *dst = static_cast<uint8_t>(packed[0]);
+                if (wi == 0 && lane == 0) actd[sbq] = d;
+            }
         }
         WD_DSTAMP(26, tid == 0);
         __syncthreads();
@@ -964,6 +1009,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
         fast_float_stage<NSB_F, K>(n_t3, reg_b, acc, actd, n_loc, tid, [&](int, int bi, int jl, int rr, float a) {
             const int j = loc_j[jl], row = (cta + bi * ncta) * R3 + rr;
             rows3[(bi * K + j) * R3 + rr] = a;
+            P.expert_out[static_cast<size_t>(j) * H + row] = a;
 #pragma unroll 1
             for (int pr = 0; pr < P.n_peers; ++pr)
                 st_tagged_sys(P.peer_expert_out[pr] + static_cast<size_t>(par) * K * H + static_cast<size_t>(j) * H + row, a, tag);
@@ -972,9 +1018,24 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
         // ---- combine: one thread per row of the bands -------------------------------------------------------------------
         if (tid < my_b3 * R3) {
             const int bi = tid / R3, rr = tid % R3, row = (cta + bi * ncta) * R3 + rr;
-            float ev[K];
-            if (P.n_peers > 0) {
+            float accf = 0.0f;
+            if (P.n_peers == 0 && n_loc == K) {
+                // one GPU: every picked expert's row is in shared memory; rank-ordered add_rn(mul_rn())
+                float ev[K];
+#pragma unroll
+                for (int j = 0; j < K; ++j) ev[j] = rows3[(bi * K + j) * R3 + rr];
+#pragma unroll
+                for (int j = 0; j < K; ++j) accf = __fadd_rn(accf, __fmul_rn(ev[j], sel_w[j]));
+            } else if (P.n_peers == 0) {
+                // an unconnected rank's partial sum: its own experts, in rank order
+#pragma unroll 1
+                for (int q = 0; q < n_loc; ++q) {
+                    const int j = loc_j[q];
+                    accf = __fadd_rn(accf, __fmul_rn(rows3[(bi * K + j) * R3 + rr], sel_w[j]));
+                }
+            } else {
                 // rows of the experts other ranks own arrive in this rank's row buffer
+                float ev[K];
                 unsigned ownedmask = 0;
                 for (int q = 0; q < n_loc; ++q) ownedmask |= 1u << loc_j[q];
                 tagged_t w[K] = {};
@@ -996,28 +1057,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
                     const bool mine_j = (ownedmask >> j) & 1u;
                     over |= !mine_j & tag_ahead(w[j], tag);
                     ev[j] = mine_j ? rows3[(bi * K + j) * R3 + rr] : __uint_as_float(static_cast<uint32_t>(w[j]));
+                    if (!mine_j) P.expert_out[static_cast<size_t>(j) * H + row] = ev[j];
                 }
                 report_overrun(over, err);
-            } else {
-                // single GPU, or an unconnected rank's partial sum: the owned experts only
 #pragma unroll
-                for (int j = 0; j < K; ++j) ev[j] = 0.0f;
-                for (int q = 0; q < n_loc; ++q) {
-                    const int j = loc_j[q];
-#pragma unroll
-                    for (int jj = 0; jj < K; ++jj)
-                        if (jj == j) ev[jj] = rows3[(bi * K + j) * R3 + rr];
-                }
-            }
-            unsigned have = 0;
-            if (P.n_peers > 0) have = (1u << K) - 1u;
-            else
-                for (int q = 0; q < n_loc; ++q) have |= 1u << loc_j[q];
-            float accf = 0.0f;
-#pragma unroll
-            for (int j = 0; j < K; ++j) {
-                if ((have >> j) & 1u) accf = __fadd_rn(accf, __fmul_rn(ev[j], sel_w[j]));
-                P.expert_out[static_cast<size_t>(j) * H + row] = ((have >> j) & 1u) ? ev[j] : 0.0f;
+                for (int j = 0; j < K; ++j) accf = __fadd_rn(accf, __fmul_rn(ev[j], sel_w[j]));
             }
             const float sd = shrow[tid];
             P.routed[row] = accf;

@@ -36,6 +36,10 @@ __device__ __forceinline__ float key_to_float(uint32_t key) {
     return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
 }
 
+__device__ __forceinline__ void router_softmax_given_max(float l0, float l1, float mx, int E, const RouterScratch &S,
+                                                         float &p0_out, float &p1_out,
+                                                         unsigned long long *stage_stamps = nullptr, float *inv_out = nullptr);
+
 // Softmax of the whole row (the first half of router_select_cta): thread t holds the logits of experts t and
 // t + kThreads and receives their probabilities (-inf in every place when the sum is zero).
 __device__ __forceinline__ void router_softmax_cta(float l0, float l1, int E, const RouterScratch &S, float &p0_out,
@@ -58,6 +62,24 @@ __device__ __forceinline__ void router_softmax_cta(float l0, float l1, int E, co
     __syncthreads();
     mk = __reduce_max_sync(0xffffffffu, lane < kWarps ? S.cand[lane] : 0u);
     const float mx = __uint_as_float((mk & 0x80000000u) ? (mk ^ 0x80000000u) : ~mk);
+    router_softmax_given_max(l0, l1, mx, E, S, p0_out, p1_out, stage_stamps);
+#undef WD_RSTAMP
+}
+
+// The softmax once the row maximum is known (one block-wide synchronisation inside). `inv_out`, optional: the factor
+// (float)(1 / sum) every exponential was multiplied with, 0 when the sum was zero (then every probability is -inf).
+__device__ __forceinline__ void router_softmax_given_max(float l0, float l1, float mx, int E, const RouterScratch &S,
+                                                         float &p0_out, float &p1_out, unsigned long long *stage_stamps,
+                                                         float *inv_out) {
+#define WD_RSTAMP(i)                                                       \
+    if (stage_stamps != nullptr && threadIdx.x == 0) {                     \
+        unsigned long long t__;                                            \
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t__) : : "memory");            \
+        stage_stamps[i] = t__;                                             \
+    }
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int e0 = tid, e1 = tid + kThreads;
+    const bool h0 = e0 < E, h1 = e1 < E;
     WD_RSTAMP(0)
     float p0 = h0 ? exp_ggml(__fsub_rn(l0, mx)) : 0.0f;
     float p1 = h1 ? exp_ggml(__fsub_rn(l1, mx)) : 0.0f;
@@ -102,10 +124,12 @@ __device__ __forceinline__ void router_softmax_cta(float l0, float l1, int E, co
         }
         if (sum == 0.0) {
             p0 = p1 = -INFINITY;
+            if (inv_out) *inv_out = 0.0f;
         } else {
             const float inv = __double2float_rn(__ddiv_rn(1.0, sum));
             p0 = __fmul_rn(p0, inv);
             p1 = __fmul_rn(p1, inv);
+            if (inv_out) *inv_out = inv;
         }
     }
     p0_out = p0;
