@@ -905,6 +905,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
     // ---- phase 3: this CTA's row bands ----------------------------------------------------------------------------------
     if (my_b3 > 0) {
         const int n_t3 = my_b3 * n_loc;
+        // expert parallel: this layer's rows go into the half of every peer's row buffer that layer tag - 2 used; the
+        // peer must have left that layer (the synchronisation after the gather below hands the result to every warp)
+        if (warp == 1 && lane < P.n_peers) wait_tag_reached(P.t_peer_left + P.peer_rank[lane], tag - 2u, err);
         // the shared gate scalar (published in phase 1 by one CTA) for the combine threads
         float sg = 0.0f;
         if (tid < my_b3 * R3) {
