@@ -49,3 +49,41 @@ def test_batch_of_tokens_equals_single_token_calls_and_oracle(wd, oracle, cache_
 def test_max_tokens_out_of_range_is_refused(wd):
     with pytest.raises(wd.WdError, match="max_tokens"):
         wd.Engine(H, F, E, K, SF, 1, max_tokens=5)
+
+
+def test_batch_of_four_at_the_model_shape(wd, oracle):
+    """Four tokens x ten experts = forty (token, slot) pairs at the 48-layer model's block shape (hidden 2048, 512
+    experts, top-10), weights generated on the device. Token 3 repeats token 0, so ten of the pairs share their
+    experts. One call (one launch of the layer kernel) must give, for every token, the oracle's ids, weights and
+    output bit for bit, and the same bits as four single-token calls. The pair map follows the reference's batch
+    verify (p = t * k + j; tests/moe_batch_verify_host_test.cpp:137-186): swapping two tokens' activations must
+    change the result (negative control)."""
+    Hh, Fh, Eh, Kh, SFh = 2048, 512, 512, 10, 512
+    eng = wd.Engine(Hh, Fh, Eh, Kh, SFh, 1, max_tokens=4)
+    assert eng.kernel_name() == "moe_layer_kernel"
+    eng.synth_model(31, 0.02, 1.0)
+    dense = eng.synth_dense_host(31, 0.02, 1.0, 0)
+    gb = Fh * (Hh // 256) * 110
+    gate, up, down = np.zeros(Eh * gb, np.uint8), np.zeros(Eh * gb, np.uint8), np.zeros(Eh * gb, np.uint8)
+    x = np.random.Generator(np.random.PCG64(32)).standard_normal((4, Hh)).astype(np.float32)
+    x[3] = x[0]
+    out = eng.forward_host(0, x)
+    ids = [eng.tap("ids", t) for t in range(4)]
+    wts = [eng.tap("weights", t) for t in range(4)]
+    assert eng.device_status() == 0
+    for e in sorted({int(v) for t in range(4) for v in ids[t]}):
+        g, u, d = eng.synth_expert_host(31, 0.02, 0, e)
+        gate[e * gb:(e + 1) * gb], up[e * gb:(e + 1) * gb], down[e * gb:(e + 1) * gb] = g, u, d
+    m = dict(hidden=Hh, expert_ffn=Fh, shared_ffn=SFh, n_experts=Eh, top_k=Kh, gate_type=21, up_type=21, down_type=21,
+             w_scale=1.0, gate=gate, up=up, down=down, **dense)
+    for t in range(4):
+        r = oracle.moe_block(m, x[t])
+        assert np.array_equal(ids[t], r["ids"]), t
+        assert np.array_equal(bits(wts[t]), bits(r["weights"])), t
+        assert np.array_equal(bits(out[t]), bits(r["out"])), t
+        single = eng.forward_host(0, x[t])
+        assert np.array_equal(bits(single), bits(out[t])), t
+    assert np.array_equal(ids[0], ids[3]) and not np.array_equal(ids[0], ids[1])
+    swapped = eng.forward_host(0, x[[1, 0, 2, 3]])
+    assert np.array_equal(bits(swapped[0]), bits(out[1])) and not np.array_equal(bits(swapped[0]), bits(out[0]))
+    eng.close()

@@ -41,19 +41,32 @@ def _blocks_and_norms():
     return ms, norms, rng
 
 
-def _engine(wd, ms, norms, rank, size, device):
-    eng = wd.Engine(H, F, E, K, SF, L, ep_rank=rank, ep_size=size, device=device)
+def _engine(wd, ms, norms, rank, size, device, compiled=False):
+    """compiled: run the kernel compiled for this geometry instead of the generic one (WD_COMPILED_KERNEL is read
+    when an engine is created)."""
+    import os
+    old = os.environ.get("WD_COMPILED_KERNEL")
+    os.environ["WD_COMPILED_KERNEL"] = "1" if compiled else "0"
+    try:
+        eng = wd.Engine(H, F, E, K, SF, L, ep_rank=rank, ep_size=size, device=device)
+    finally:
+        if old is None:
+            os.environ.pop("WD_COMPILED_KERNEL", None)
+        else:
+            os.environ["WD_COMPILED_KERNEL"] = old
+    assert eng.kernel_name() == ("moe_fast_kernel" if compiled else "moe_layer_kernel")
     for l in range(L):
         eng.load_block(l, ms[l])
         eng.set_norm(l, norms[l])
     return eng
 
 
-def test_two_ranks_reproduce_one_gpu_bit_for_bit(wd, oracle, torch2):
+@pytest.mark.parametrize("compiled", [False, True])
+def test_two_ranks_reproduce_one_gpu_bit_for_bit(wd, oracle, torch2, compiled):
     torch = torch2
     ms, norms, rng = _blocks_and_norms()
     single = _engine(wd, ms, norms, 0, 1, 0)
-    ranks = [_engine(wd, ms, norms, r, 2, r) for r in range(2)]
+    ranks = [_engine(wd, ms, norms, r, 2, r, compiled) for r in range(2)]
     ranks[0].ep_connect_local([ranks[1]])
     ranks[1].ep_connect_local([ranks[0]])
     res = rng.standard_normal(H).astype(np.float32)
@@ -84,7 +97,8 @@ def test_two_ranks_reproduce_one_gpu_bit_for_bit(wd, oracle, torch2):
         e.close()
 
 
-def test_a_rank_that_owns_nothing_and_launches_late_is_waited_for(wd, oracle, torch2):
+@pytest.mark.parametrize("compiled", [False, True])
+def test_a_rank_that_owns_nothing_and_launches_late_is_waited_for(wd, oracle, torch2, compiled):
     """Every selected expert belongs to rank 0 (router bias), so nothing rank 0 computes depends on rank 1: without
     flow control it would run layers and whole launches ahead and overwrite rows in rank 1's buffer that rank 1 has
     not combined yet. Rank 1 starts each step late (a host-side sleep, well under the one-second wait limit); both
@@ -97,7 +111,7 @@ def test_a_rank_that_owns_nothing_and_launches_late_is_waited_for(wd, oracle, to
         b[:E // 2] = 100.0                                  # the top-k all come from rank 0's half
         m["router_bias"] = b
     single = _engine(wd, ms, norms, 0, 1, 0)
-    ranks = [_engine(wd, ms, norms, r, 2, r) for r in range(2)]
+    ranks = [_engine(wd, ms, norms, r, 2, r, compiled) for r in range(2)]
     ranks[0].ep_connect_local([ranks[1]])
     ranks[1].ep_connect_local([ranks[0]])
     res = rng.standard_normal(H).astype(np.float32)

@@ -5,7 +5,8 @@ exact rungs as the fallback. The adversarial router rows of the reference's test
 (tests/router_parallel_exact_test.cu:36-76, tests/qwen38_router_host_test.cpp:181-295) must come out bit for
 bit through either route: they are fed in through the router bias (a router of zero blocks gives logits =
 0 + bias), at the full shape (512 experts, top-10), against the oracle's router on the same logits.
-The same blocks also run through the generic kernel (WD_GENERIC_KERNEL=1 when the engine is created).
+An engine runs this kernel when WD_COMPILED_KERNEL=1 is set while it is created (the generic kernel is the
+default: it is the faster of the two on the 48-layer model); the stack test runs on both.
 """
 import os
 
@@ -29,11 +30,24 @@ def wd():
     return w
 
 
+def _engine(wd, compiled, *a, **kw):
+    old = os.environ.get("WD_COMPILED_KERNEL")
+    os.environ["WD_COMPILED_KERNEL"] = "1" if compiled else "0"
+    try:
+        eng = wd.Engine(*a, **kw)
+    finally:
+        if old is None:
+            os.environ.pop("WD_COMPILED_KERNEL", None)
+        else:
+            os.environ["WD_COMPILED_KERNEL"] = old
+    assert eng.kernel_name() == ("moe_fast_kernel" if compiled else "moe_layer_kernel")
+    return eng
+
+
 @pytest.fixture(scope="module")
 def head_engine(wd):
-    eng = wd.Engine(H, F, E, K, SF, 1)
+    eng = _engine(wd, True, H, F, E, K, SF, 1)
     eng.synth_model(11, 0.02, 0.0)
-    assert eng.kernel_name() == "moe_fast_kernel"
     yield eng
     eng.close()
 
@@ -99,16 +113,7 @@ def test_stack_at_the_model_shape_matches_the_oracle_chain(wd, oracle, generic):
     residual must equal the oracle chain bit for bit (the oracle needs the selected experts' bytes only). Runs on
     the compiled kernel and on the generic one."""
     L, n_tok, seed = 8, 4, 21
-    old = os.environ.get("WD_GENERIC_KERNEL")
-    os.environ["WD_GENERIC_KERNEL"] = "1" if generic else "0"
-    try:
-        eng = wd.Engine(H, F, E, K, SF, L)
-    finally:
-        if old is None:
-            os.environ.pop("WD_GENERIC_KERNEL", None)
-        else:
-            os.environ["WD_GENERIC_KERNEL"] = old
-    assert eng.kernel_name() == ("moe_layer_kernel" if generic else "moe_fast_kernel")
+    eng = _engine(wd, not generic, H, F, E, K, SF, L)
     eng.synth_model(seed, 0.02, 1.0)
     rng = np.random.Generator(np.random.PCG64(8))
     norms = [(1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32) for _ in range(L)]
@@ -137,3 +142,30 @@ def test_stack_at_the_model_shape_matches_the_oracle_chain(wd, oracle, generic):
             ref = (ref + oracle.moe_block(m, x)["out"]).astype(np.float32)
         assert np.array_equal(bits(res), bits(ref)), t
     eng.close()
+
+
+def test_small_block_and_taps_on_the_compiled_kernel(wd, oracle):
+    """One small block with every tap, and a capped expert cache (selection pass, fill, full pass), on the compiled
+    kernel: bit-equal to the oracle."""
+    from warpdecode_b200 import synth
+    h, f, e, k, sf = 512, 256, 32, 6, 256
+    m = synth.make_moe_block(4100, h, f, e, k, sf, bias_sigma=1.0, w_scale=2.5)
+    rng = np.random.Generator(np.random.PCG64(41))
+    for cache_mib in (0, 1):
+        eng = _engine(wd, True, h, f, e, k, sf, 1, w_scale=2.5, cache_mib=cache_mib)
+        eng.load_block(0, m)
+        for _ in range(3):
+            x = rng.standard_normal(h).astype(np.float32)
+            out = eng.forward_host(0, x)
+            ref = oracle.moe_block(m, x)
+            assert np.array_equal(eng.tap("ids"), ref["ids"])
+            assert np.array_equal(bits(eng.tap("weights")), bits(ref["weights"]))
+            assert np.array_equal(bits(eng.tap("logits")), bits(ref["logits"]))
+            assert np.array_equal(bits(eng.tap("act")), bits(ref["act"]))
+            assert np.array_equal(bits(eng.tap("expert_out")), bits(ref["expert_out"]))
+            assert np.array_equal(bits(eng.tap("routed")), bits(ref["routed"]))
+            assert np.array_equal(bits(eng.tap("shared")), bits(ref["shared"]))
+            assert np.array_equal(bits(eng.tap("shared_gate")), bits(ref["shared_gate"]))
+            assert np.array_equal(bits(out), bits(ref["out"]))
+            assert eng.device_status() == 0
+        eng.close()

@@ -210,8 +210,11 @@ const void *fast_entry(const wd_config &c) {
 
 const void *find_fast_kernel(const wd_config &c) {
     if (c.gate_type != WD_TYPE_IQ3_S || c.down_type != WD_TYPE_IQ3_S) return nullptr;
-    if (const char *v = std::getenv("WD_GENERIC_KERNEL"))
-        if (v[0] == '1') return nullptr;
+    // The compiled kernel is opt-in: on the 48-layer model it measures about 10 % behind the generic kernel (see the
+    // measurements beside its design notes), so engines run the generic one unless WD_COMPILED_KERNEL=1 is set when
+    // they are created.
+    const char *v = std::getenv("WD_COMPILED_KERNEL");
+    if (v == nullptr || v[0] != '1') return nullptr;
     const void *f = nullptr;
     if (!f) f = fast_entry<2048, 512, 512, 10, 512>(c);
     if (!f) f = fast_entry<2048, 512, 32, 10, 512>(c);
@@ -408,7 +411,7 @@ int sync_layer_table(wd_engine *e, cudaStream_t s) {
 
 // Layers [begin, end) in one cooperative launch.
 int launch_layers(wd_engine *e, int begin, int end, const float *x, float *residual, float *out, cudaStream_t s,
-                  bool select_only = false) {
+                  bool select_only = false, int n_tokens = 1) {
     for (int l = begin; l < end; ++l) {
         const Layer &L = e->layers[l];
         if (!L.have_router || !L.have_experts || (e->cfg.shared_ffn > 0 && !L.have_shared))
@@ -434,6 +437,11 @@ int launch_layers(wd_engine *e, int begin, int end, const float *x, float *resid
         p.layers = e->layer_table;
         p.layer_begin = begin;
         p.layer_end = end;
+        p.n_tokens = n_tokens;
+        if (n_tokens > 1) {         // the selection of every token of the batch is kept
+            p.ids = e->tok_ids;
+            p.weights = e->tok_weights;
+        }
         p.stamp_layer = std::min(end - 1, begin + e->stamp_layer);
         p.x = x;
         p.residual = residual;
@@ -444,7 +452,8 @@ int launch_layers(wd_engine *e, int begin, int end, const float *x, float *resid
         WD_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(wd::moe_layer_kernel), dim3(e->n_sm),
                                             dim3(wd::kThreads), args, e->smem_bytes, s));
     }
-    e->epoch += static_cast<uint32_t>(end - begin);     // the kernel advances the device's epoch by the same amount
+    // the kernel advances the device's epoch by the length of its sequence (layers, or the tokens of a batch)
+    e->epoch += static_cast<uint32_t>(n_tokens > 1 && !e->fast_fn ? n_tokens : end - begin);
     e->last_parity = static_cast<int>(e->epoch & 1u);   // the last layer's tag is the new epoch; halves follow the tag
     e->last_tokens = 1;
     return WD_OK;
@@ -1066,10 +1075,12 @@ int wd_cache_stats(const wd_engine *e, int64_t stats[3]) {
     return WD_OK;
 }
 
-// A batch of tokens (speculative verify, Qwen38MoeTokenBatch::run, src/qwen38_moe.cuh:2955) runs token by
-// token through the same layer kernel: pair (t, j) uses expert ids[t][j] on the activation of token t and
-// each token's rows are combined in its own rank order, exactly as a single-token call. The tokens of one
-// call read the same layer, so router, shared expert and repeated experts of tokens 1.. come from L2.
+// A batch of tokens (speculative verify, Qwen38MoeTokenBatch::run, src/qwen38_moe.cuh:2955): pair (t, j) uses expert
+// ids[t][j] on the activation of token t and each token's rows are combined in its own rank order, exactly as a
+// single-token call. With every expert resident the whole batch is ONE launch of the layer kernel, which walks the
+// tokens the way a stack launch walks layers (the next token's router and shared rows travel during the current
+// token's down phase; router, shared expert and repeated experts of tokens 1.. come from L2). A capped cache still
+// takes the tokens one at a time, because the host places each token's experts between its two passes.
 int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, int n_tokens, void *stream) {
     int rc = check_layer(e, layer);
     if (rc) return rc;
@@ -1078,6 +1089,12 @@ int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, 
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
     const int H = e->cfg.hidden, K = e->cfg.top_k;
+    if (e->resident && !e->fast_fn && n_tokens > 1) {
+        rc = launch_layers(e, layer, layer + 1, x_dev, nullptr, out_dev, s, false, n_tokens);
+        if (rc) return rc;
+        e->last_tokens = n_tokens;
+        return WD_OK;
+    }
     for (int t = 0; t < n_tokens; ++t) {
         const float *x = x_dev + static_cast<size_t>(t) * H;
         float *out = out_dev + static_cast<size_t>(t) * H;

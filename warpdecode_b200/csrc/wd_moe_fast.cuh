@@ -160,6 +160,9 @@ __device__ __noinline__ void fast_tile_units(int u0, int u1, const uint8_t *tile
     Iq3Head h;
     const uint8_t *tile = tiles;
     const uint4 *av = reinterpret_cast<const uint4 *>(act);
+#ifndef WD_FAST_PAIRED_UNITS
+#define WD_FAST_PAIRED_UNITS 1
+#endif
 #pragma unroll 1
     for (int u = u0; u < u1; ++u) {
         const int d = u >> 3, i = u & 7;
@@ -183,7 +186,14 @@ __device__ __noinline__ void fast_tile_units(int u0, int u1, const uint8_t *tile
 #pragma unroll
             for (int c = 0; c < 8; ++c) p[c] = 0;
         }
-        iq3_subblock(tile, h, i, lane, av[2 * i], av[2 * i + 1], lane4x2, tab, p);
+        if (WD_FAST_PAIRED_UNITS && i < 7 && u + 1 < u1) {
+            // two sub-blocks of the same tile at once: sixteen independent chunk chains in flight
+            iq3_subblock(tile, h, i, lane, av[2 * i], av[2 * i + 1], lane4x2, tab, p);
+            iq3_subblock(tile, h, i + 1, lane, av[2 * i + 2], av[2 * i + 3], lane4x2, tab, p);
+            ++u;
+        } else {
+            iq3_subblock(tile, h, i, lane, av[2 * i], av[2 * i + 1], lane4x2, tab, p);
+        }
     }
     if (cur >= 0) {
         int *dst = acc + cur * kFastAccStride + lane * 9;

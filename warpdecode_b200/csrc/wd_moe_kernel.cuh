@@ -49,6 +49,11 @@ struct MoeParams {
     // every instruction comes from the instruction cache
     const LayerDev *layers;      // device array, one entry per layer of the stack
     int layer_begin, layer_end;
+    // A batch of tokens through ONE layer (speculative verify): n_tokens > 1 runs layer_begin once per token inside one
+    // launch, token t reading x + t * H and writing out + t * H, ids + t * K, weights + t * K (no residual mode). The
+    // tokens take the place of the layers in the launch's sequence of tags and mbarrier phases, and the copies of the
+    // layer's phase-1 weights for token t + 1 travel during token t's down phase.
+    int n_tokens;
     int stamp_layer;             // the layer whose phase timestamps are recorded
     int select_only;             // 1: stop after the selection (ids and weights written); nothing else changes
     const uint8_t *pool;         // slot pool base
@@ -258,9 +263,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     if (P.gu_type == kTypeIq2s || P.d_type == kTypeIq2s) build_iq2_table(tab2, P.grid2_packed);
     __syncthreads();
 
+    const int seq_end = P.n_tokens > 1 ? P.layer_begin + P.n_tokens : P.layer_end;   // end of the launch's sequence
 #pragma unroll 1
-    for (int layer = P.layer_begin; layer < P.layer_end; ++layer) {
-    const LayerDev L = P.layers[layer];
+    for (int layer = P.layer_begin; layer < seq_end; ++layer) {     // position in the sequence: a layer, or a token
+    const int tok = P.n_tokens > 1 ? layer - P.layer_begin : 0;
+    const LayerDev L = P.layers[P.n_tokens > 1 ? P.layer_begin : layer];
     const uint32_t mpar = static_cast<uint32_t>(layer - P.layer_begin) & 1u;  // every mbarrier completes once per layer
     const uint32_t tag = epoch + static_cast<uint32_t>(layer - P.layer_begin) + 1u;
     // The half of every exchange buffer follows the TAG, not the position in the launch: consecutive layers then
@@ -345,7 +352,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     } else {
         if (layer >= P.layer_begin + 2 && tid < ncta) wait_tag_reached(P.t_progress + tid, tag - 2u, err);
 #pragma unroll 1
-        for (int i = tid; i < P.H; i += kThreads) xf[i] = P.x[i];
+        for (int i = tid; i < P.H; i += kThreads) xf[i] = P.x[static_cast<size_t>(tok) * P.H + i];
         if (P.n_peers > 0 && cta == 0 && layer >= P.layer_begin + 2) {      // every CTA has left layer tag - 2
             __syncthreads();
             if (tid < P.n_peers) st_tagged_sys_release(P.peer_left_out[tid], 0.0f, tag - 2u);
@@ -372,11 +379,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         __threadfence();        // this CTA's reads of the last layers' rows come before its arrival below
         if (atomicAdd(P.sync + 9, 1u) == static_cast<unsigned>(ncta) - 1u) {
             P.sync[9] = 0u;
-            P.sync[8] = epoch + static_cast<uint32_t>(P.layer_end - P.layer_begin);
+            P.sync[8] = epoch + static_cast<uint32_t>(seq_end - P.layer_begin);
             // every CTA of this rank has left the launch: the peers may overwrite both halves of its row buffer
             __threadfence();
             for (int p = 0; p < P.n_peers; ++p)
-                st_tagged_sys_release(P.peer_left_out[p], 0.0f, epoch + static_cast<uint32_t>(P.layer_end - P.layer_begin));
+                st_tagged_sys_release(P.peer_left_out[p], 0.0f, epoch + static_cast<uint32_t>(seq_end - P.layer_begin));
             if (P.host_status) *P.host_status = *reinterpret_cast<volatile unsigned *>(err);
         }
     }
