@@ -252,8 +252,8 @@ class Engine:
         _check(lib().wd_moe_forward_host(self.h, layer, _ptr(x), _ptr(out), n))
         return out
 
-    def forward_device(self, layer, x_ptr, out_ptr, stream=None):
-        _check(lib().wd_moe_forward(self.h, layer, x_ptr, out_ptr, 1, stream))
+    def forward_device(self, layer, x_ptr, out_ptr, stream=None, n_tokens=1):
+        _check(lib().wd_moe_forward(self.h, layer, x_ptr, out_ptr, n_tokens, stream))
 
     def stack_step_host(self, residual):
         r = np.ascontiguousarray(residual, np.float32)

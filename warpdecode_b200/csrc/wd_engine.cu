@@ -761,7 +761,11 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
         if ((rc = plan_fast(e)) != WD_OK) {
             e->fast_fn = nullptr;       // the generic kernel serves this grid
         } else {
-            e->xbuf_words = static_cast<size_t>(e->n_sm) * f.xstride;
+            // CTAs per mailbox, measured on the 48-layer model (tok/s): 1 -> 827, 2 -> 865, 4 -> 894, 8 -> 907, 16 -> 914,
+            // 37 -> 905, 148 (one shared copy that everybody polls) -> 845
+            f.mbox_group = 16;
+            if (const char *g = std::getenv("WD_MBOX_GROUP")) f.mbox_group = std::max(1, std::min(e->n_sm, std::atoi(g)));
+            e->xbuf_words = static_cast<size_t>((e->n_sm + f.mbox_group - 1) / f.mbox_group) * f.xstride;
             cudaError_t fe = cudaMalloc(&e->xbuf, e->xbuf_words * sizeof(wd::tagged_t));
             if (fe == cudaSuccess) fe = cudaMemset(e->xbuf, 0, e->xbuf_words * sizeof(wd::tagged_t));
             if (fe == cudaSuccess) fe = cudaMalloc(&e->eo_plain, static_cast<size_t>(K) * H * 4);

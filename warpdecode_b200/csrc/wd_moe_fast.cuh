@@ -66,13 +66,14 @@ struct FastParams {
     const float *x;              // [H] (used when residual == nullptr)
     float *residual;             // nullable: x = RMSNorm(residual) * norm_w, residual += out
     float *out;                  // [H]
-    // Exchange between CTAs: every CTA has a private mailbox, and a producer PUSHES its values (tagged words, in
-    // whole 128-byte lines) into the mailbox of every CTA that needs them. A consumer polls only its own mailbox, so no
-    // line is ever polled by more than one SM: a line that a hundred SMs poll while it is written comes back
-    // microseconds late. Mailbox of CTA d (words): [2][E] logits | [2][SF] shared act | [2][16] shared gate |
+    // Exchange between CTAs: a producer PUSHES its values (tagged words, in whole 128-byte lines) into every mailbox,
+    // and a consumer polls only the mailbox of its own group of `mbox_group` neighbouring CTAs. One copy that all
+    // 148 SMs poll while it is being written comes back microseconds late (the line is hot in L2); one copy per CTA
+    // costs 148 stores per line and producer. A mailbox per 16 CTAs measured best. Mailbox d (words): [2][E] logits | [2][SF] shared act | [2][16] shared gate |
     // [2][H] residual | [2][K][F] act values (row jl = the jl-th owned selected expert).
     tagged_t *xbuf;
     unsigned long long xstride;  // words per mailbox
+    int mbox_group;              // CTAs per mailbox: a mailbox is shared by this many neighbouring CTAs (they all poll it)
     tagged_t *t_expert_out;      // [2][K][H]  rows that expert-parallel peers push (unused on one GPU)
     tagged_t *t_progress;        // [grid]   tag of the last layer each CTA has left
     tagged_t *peer_expert_out[8];
@@ -242,14 +243,15 @@ __device__ __noinline__ void fast_rungs(float p0, float p1, int E, int K, float 
 // fmaf(d_w * d_x, (float) partial, acc) ascending, then ggml's 8-lane tree (src/qwen38_cpu_moe.cuh:337-375).
 // Chains are spread over the whole CTA. List index d -> staging slot and expert as in fast_tile_units; the
 // activation scales of d are dx + (d % nl) * NSB (nl == 0: dx). Returns this thread's chains through `emit`.
+// The chains of list indices [d0, d1) are spread over `nthr` threads (a whole number of warps), this one being `t`.
 template <int NSB, int K, class Emit>
-__device__ __forceinline__ void fast_float_stage(int n_tiles, const uint8_t *tiles, const int *acc, const float *dx, int nl,
-                                                 int tid, Emit emit) {
+__device__ __forceinline__ void fast_float_stage(int d0, int d1, const uint8_t *tiles, const int *acc, const float *dx, int nl,
+                                                 int t, int nthr, Emit emit) {
     constexpr int R = 32 / NSB;
 #pragma unroll 1
-    for (int ch = tid; ch < ((n_tiles * R * 8 + 31) & ~31); ch += kThreads) {
-        const int d = ch / (R * 8), rr = (ch >> 3) % R, c = ch & 7;
-        const bool live = d < n_tiles;
+    for (int ch = t; ch < (((d1 - d0) * R * 8 + 31) & ~31); ch += nthr) {
+        const int d = d0 + ch / (R * 8), rr = (ch >> 3) % R, c = ch & 7;
+        const bool live = d < d1;
         float a = 0.0f;
         int bi = 0, jl = 0;
         if (live) {
@@ -416,8 +418,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
     const size_t o_logits = par * E, o_shact = 2 * E + par * SF, o_shgate = 2 * E + 2 * SF + par * 16,
                  o_res = 2 * E + 2 * SF + 32 + par * H, o_res_prev = 2 * E + 2 * SF + 32 + (par ^ 1u) * H,
                  o_act = 2 * E + 2 * SF + 32 + 2 * H + static_cast<size_t>(par) * K * F;
-    tagged_t *mbox = P.xbuf + static_cast<size_t>(cta) * P.xstride;
+    tagged_t *mbox = P.xbuf + static_cast<size_t>(cta / P.mbox_group) * P.xstride;
     const int n_band_ctas = min(T3, ncta);          // the CTAs that own row bands (the first ones)
+    const int n_mbox = (ncta + P.mbox_group - 1) / P.mbox_group;                 // mailboxes in all
+    const int n_band_mbox = (n_band_ctas + P.mbox_group - 1) / P.mbox_group;     // mailboxes that band CTAs read
     tagged_t *t_eo = P.t_expert_out + static_cast<size_t>(par) * K * H;
     WD_GSTAMP(30);
     WD_DSTAMP(31, tid == 0);
@@ -585,21 +589,21 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
             // the gate scalar goes to the CTAs that combine: one word each
             const tagged_t w = make_tagged(sigmoid_ggml(d), tag);
 #pragma unroll 1
-            for (int dd = lane; dd < n_band_ctas; dd += 32)
+            for (int dd = lane; dd < n_band_mbox; dd += 32)
                 asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(P.xbuf + static_cast<size_t>(dd) * P.xstride + o_shgate), "l"(w)
                              : "memory");
         }
         __syncthreads();
         if (router_cta) {
             // a router CTA's 16 logits are one line of every mailbox
-            push_words(pushbuf, my_rr, P.xbuf, P.xstride, o_logits + rr0, ncta, warp, lane);
+            push_words(pushbuf, my_rr, P.xbuf, P.xstride, o_logits + rr0, n_mbox, warp, lane);
         } else {
             // a pair CTA's shared activations: every warp forms them itself (lane = pair) and carries them to its share
             // of the band CTAs' mailboxes
             tagged_t w = 0ull;
             if (lane < my_sp) w = make_tagged(silu_mul(rowres[lane], rowres[my_sp + lane]), tag);
 #pragma unroll 1
-            for (int d = warp; d < n_band_ctas; d += kWarps)
+            for (int d = warp; d < n_band_mbox; d += kWarps)
                 if (lane < my_sp)
                     asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(P.xbuf + static_cast<size_t>(d) * P.xstride + o_shact + sp0 + lane),
                                  "l"(w)
@@ -870,14 +874,30 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
 
     // ---- phase 2: gate and up tiles in sub-block units, evenly over the warps ---------------------------------------
     {
-        const int n_units = n_t2 * 8, per = (n_units + kWarps - 1) / kWarps;
-        const int u0 = min(warp * per, n_units), u1 = min(u0 + per, n_units);
-        fast_tile_units<K>(u0, u1, reg_a, bar_gu, acc, xk + (lane % NSB_H) * kActSbStride, 0, 0, lane, tab, tpar, err);
-        // barriers of pair slots this CTA does not use complete by themselves (arrive at issue)
-        __syncthreads();
-        WD_STAMP(7);
-        fast_float_stage<NSB_H, K>(n_t2, reg_a, acc, xdk, 0, tid,
-                                   [&](int d, int, int, int rr, float a) { rowbuf[d * R2 + rr] = a; });
+        const uint8_t *a_lane = xk + (lane % NSB_H) * kActSbStride;
+        auto to_rowbuf = [&](int d, int, int, int rr, float a) { rowbuf[d * R2 + rr] = a; };
+        if (n_t2 >= kWarps) {
+            // A whole tile per warp first: its partials never leave the warp (they pass through the warp's own slot of
+            // the accumulator only to change hands between lanes), and the warp runs the tile's float chains at once.
+            // The tiles beyond 16 are cut into sub-block units, one or two per warp.
+            fast_tile_units<K>(warp * 8, warp * 8 + 8, reg_a, bar_gu, acc, a_lane, 0, 0, lane, tab, tpar, err);
+            __syncwarp();
+            fast_float_stage<NSB_H, K>(warp, warp + 1, reg_a, acc, xdk, 0, lane, 32, to_rowbuf);
+            const int n_left = (n_t2 - kWarps) * 8, per = (n_left + kWarps - 1) / kWarps;
+            const int u0 = kWarps * 8 + min(warp * per, n_left), u1 = min(u0 + per, kWarps * 8 + n_left);
+            fast_tile_units<K>(u0, u1, reg_a, bar_gu, acc, a_lane, 0, 0, lane, tab, tpar, err);
+            __syncthreads();
+            WD_STAMP(7);
+            fast_float_stage<NSB_H, K>(kWarps, n_t2, reg_a, acc, xdk, 0, tid, kThreads, to_rowbuf);
+        } else {
+            // less than one tile per warp (few owned experts): everything in sub-block units, evenly over the warps
+            const int n_units = n_t2 * 8, per = (n_units + kWarps - 1) / kWarps;
+            const int u0 = min(warp * per, n_units), u1 = min(u0 + per, n_units);
+            fast_tile_units<K>(u0, u1, reg_a, bar_gu, acc, a_lane, 0, 0, lane, tab, tpar, err);
+            __syncthreads();
+            WD_STAMP(7);
+            fast_float_stage<NSB_H, K>(0, n_t2, reg_a, acc, xdk, 0, tid, kThreads, to_rowbuf);
+        }
         __syncthreads();
         if (tid < my_pairs * R2) {
             const int s2 = tid / R2, rr = tid % R2;
@@ -901,7 +921,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
                 const size_t off = o_act + static_cast<size_t>(u / T2) * F + (u % T2) * R2 + i % R2;
                 const tagged_t w = live ? pushbuf[i] : 0ull;
 #pragma unroll 1
-                for (int d = warp; d < n_band_ctas; d += kWarps)
+                for (int d = warp; d < n_band_mbox; d += kWarps)
                     if (live)
                         asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(P.xbuf + static_cast<size_t>(d) * P.xstride + off), "l"(w)
                                      : "memory");
@@ -925,78 +945,46 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
             wait_tagged<1>(mbox + o_shgate, 1, 1, tag, one, err);
             sg = one[0];
         }
-        // Every owned expert's activation -> Q8_K. A superblock is 256 consecutive words of this CTA's mailbox. Whole
-        // rounds take one superblock per warp; the superblocks left over are cut into equal runs over several warps each
-        // (their maxima meet in shared memory), so that no warp waits for a mostly empty second round.
-        const int n_sb = n_loc * NSB_F, n_full = n_sb & ~(kWarps - 1), rem = n_sb - n_full;
-        int wps = 1;
-        while (wps < 8 && 2 * wps * rem <= kWarps) wps <<= 1;       // warps per left-over superblock
-        const int vpl = 8 / wps;                                    // values per lane in a left-over superblock
-        // this warp's piece: superblock sbq, values [first, first + 32 * vpl) of it, vpl per lane
-        auto piece = [&](int sbq, int first, int n, float v[8]) {
-            const tagged_t *src0 = mbox + o_act + static_cast<size_t>(sbq / NSB_F) * F + (sbq % NSB_F) * 256 + first + lane * n;
-            tagged_t w[8] = {};
+        // Every owned expert's activation -> Q8_K, one warp per superblock (256 consecutive words of the mailbox). A warp
+        // with two superblocks (more than 16 in all) polls both at once, so that the second costs no round trip.
+        const int n_sb = n_loc * NSB_F;
+#pragma unroll 1
+        for (int sb0 = warp; sb0 < n_sb; sb0 += 2 * kWarps) {
+            const int sb1 = sb0 + kWarps;
+            const bool two = sb1 < n_sb;
+            const tagged_t *src0 = mbox + o_act + static_cast<size_t>(sb0 / NSB_F) * F + (sb0 % NSB_F) * 256 + lane * 8;
+            const tagged_t *src1 = mbox + o_act + static_cast<size_t>((two ? sb1 : sb0) / NSB_F) * F + ((two ? sb1 : sb0) % NSB_F) * 256 + lane * 8;
+            tagged_t w[16] = {};
             unsigned long long t0 = 0ull;
             for (unsigned it = 0;; ++it) {
                 unsigned bad = 0;
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
-                    if (i < n && (it == 0 || tag_behind(w[i], tag))) w[i] = ld_tagged(src0 + i);
+                    if (it == 0 || tag_behind(w[i], tag)) w[i] = ld_tagged(src0 + i);
+                if (two) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) bad |= (i < n) & tag_behind(w[i], tag);
+                    for (int i = 0; i < 8; ++i)
+                        if (it == 0 || tag_behind(w[8 + i], tag)) w[8 + i] = ld_tagged(src1 + i);
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) bad |= tag_behind(w[i], tag) | (two & tag_behind(w[8 + i], tag));
                 if (!bad) break;
                 if (wait_expired(it, t0, err)) break;
             }
+            float v[8];
             unsigned over = 0;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                over |= (i < n) & tag_ahead(w[i], tag);
-                v[i] = i < n ? __uint_as_float(static_cast<uint32_t>(w[i])) : 0.0f;
+                over |= tag_ahead(w[i], tag) | (two & tag_ahead(w[8 + i], tag));
+                v[i] = __uint_as_float(static_cast<uint32_t>(w[i]));
             }
             report_overrun(over, err);
-        };
-#pragma unroll 1
-        for (int sbq = warp; sbq < n_full + (wps == 1 ? rem : 0); sbq += kWarps) {
-            float v[8];
-            piece(sbq, 0, 8, v);
-            WD_DSTAMP(24, tid == 0 && sbq == 0);
-            q8k_from_regs(v, lane, actk + sbq * kActSbStride, &actd[sbq]);
-        }
-        if (rem > 0 && wps > 1) {           // uniform over the CTA
-            const int r = warp / wps, wi = warp % wps;
-            const bool live = r < rem;
-            const int sbq = n_full + (live ? r : 0), first = wi * (256 / wps);
-            float v[8];
-            float *amaxs = misc + kFmRed;
-            if (live) {
-                piece(sbq, first, vpl, v);
-                float amax = 0.0f;
+            WD_DSTAMP(24, tid == 0 && sb0 == 0);
+            q8k_from_regs(v, lane, actk + sb0 * kActSbStride, &actd[sb0]);
+            if (two) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-                for (int sft = 1; sft < 32; sft <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sft));
-                if (lane == 0) amaxs[warp] = amax;
-            }
-            __syncthreads();
-            if (live) {
-                float amax = 0.0f;
-                for (int k = 0; k < wps; ++k) amax = fmaxf(amax, amaxs[r * wps + k]);
-                uint32_t packed[2] = {0u, 0u};
-                float d = 0.0f;
-                if (amax != 0.0f) {             // the operations of quantize_q8_K (src/qwen38_cpu_moe.cuh:239)
-                    const float iscale = __fdiv_rn(-127.0f, amax);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int q = min(127, __float2int_rn(__fmul_rn(v[i], iscale)));
-                        if (i < vpl) packed[i >> 2] |= static_cast<uint32_t>(q & 0xff) << (8 * (i & 3));
-                    }
-                    d = __fdiv_rn(1.0f, iscale);
-                }
-                uint8_t *dst = actk + sbq * kActSbStride + first + lane * vpl;
-                if (vpl == 4) *reinterpret_cast<uint32_t *>(dst) = packed[0];
-                else if (vpl == 2) *reinterpret_cast<uint16_t *>(dst) = static_cast<uint16_t>(packed[0]);
-                else *dst = static_cast<uint8_t>(packed[0]);
-                if (wi == 0 && lane == 0) actd[sbq] = d;
+                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(static_cast<uint32_t>(w[8 + i]));
+                q8k_from_regs(v, lane, actk + sb1 * kActSbStride, &actd[sb1]);
             }
         }
         WD_DSTAMP(26, tid == 0);
@@ -1019,7 +1007,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
         __syncthreads();
         WD_STAMP(10);
         // float chains of the down tiles; expert parallel: the peers combine these rows too
-        fast_float_stage<NSB_F, K>(n_t3, reg_b, acc, actd, n_loc, tid, [&](int, int bi, int jl, int rr, float a) {
+        fast_float_stage<NSB_F, K>(0, n_t3, reg_b, acc, actd, n_loc, tid, kThreads, [&](int, int bi, int jl, int rr, float a) {
             const int j = loc_j[jl], row = (cta + bi * ncta) * R3 + rr;
             rows3[(bi * K + j) * R3 + rr] = a;
             P.expert_out[static_cast<size_t>(j) * H + row] = a;
@@ -1095,7 +1083,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
             __syncthreads();
 #pragma unroll 1
             for (int bi = 0; bi < my_b3; ++bi)
-                push_words(pushbuf + bi * R3, R3, P.xbuf, P.xstride, o_res + static_cast<size_t>(cta + bi * ncta) * R3, ncta, warp, lane);
+                push_words(pushbuf + bi * R3, R3, P.xbuf, P.xstride, o_res + static_cast<size_t>(cta + bi * ncta) * R3, n_mbox, warp, lane);
         }
     }
     WD_STAMP(11);
