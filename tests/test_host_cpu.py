@@ -166,3 +166,26 @@ def test_gguf_reader_refuses_broken_files(tmp_path):
     with pytest.raises(wd.WdError, match="disagrees"):
         g.config()
     g.close()
+
+
+def test_cpp_wrappers_with_the_reference_signatures_compile_link_and_report_errors(tmp_path):
+    """include/warpdecode_b200.hpp (the reference's C++ entry points over the C ABI) meets a compiler: the call sites
+    of tests/boundary_check.cpp, written like the reference decoder's, compile with -Wall -Wextra against stand-ins
+    for the CUDA names, link against the built library, and a load that cannot succeed here (no file, or no GPU)
+    ends in std::runtime_error with the library's message, as the reference's callers expect."""
+    import shutil
+    import subprocess
+    import warpdecode_b200 as wd
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    wd.build()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "boundary_check")
+    libdir = os.path.dirname(wd.LIB_PATH)
+    r = subprocess.run(["g++", "-std=c++17", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(root, "include"), "-o", exe,
+                        os.path.join(root, "tests", "boundary_check.cpp"), "-L", libdir, "-lwarpdecode_b200",
+                        f"-Wl,-rpath,{libdir}"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "runtime_error: warpdecode_b200: cannot open" in r.stdout
