@@ -104,6 +104,10 @@ int64_t wd_cache_slot_bytes(const wd_engine *e);
 int wd_cache_acquire(wd_engine *e, int layer, int expert, int *slot);
 /* hits / misses / evictions since creation (ExpertCacheMonitor counters, :1671). */
 int wd_cache_stats(const wd_engine *e, int64_t stats[3]);
+/* Miss stream since creation: bytes sent host -> device, nanoseconds of host time spent placing missed experts
+ * (reads, enqueueing the copies), number of layers that went through the placement
+ * (the per-stage timings of ExpertStagePath, src/expert_cache.cuh:1166-1273). */
+int wd_cache_stream_stats(const wd_engine *e, int64_t stats[3]);
 
 /* ---- forward --------------------------------------------------------------------------- */
 /* One MoE block on device buffers: x [n_tokens][hidden] F32 -> out [n_tokens][hidden] F32

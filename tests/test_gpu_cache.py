@@ -118,3 +118,38 @@ def test_capped_cache_reads_pinned_host_tensors_without_a_bounce_copy(wd):
 def test_cache_smaller_than_one_selection_is_refused(wd):
     with pytest.raises(wd.WdError, match="smaller than one layer"):
         wd.Engine(2048, 512, 512, 10, 512, 2, cache_mib=8)     # 8 MiB < 10 slots of 1.35 MB
+
+
+def test_capped_cache_at_the_model_shape_streams_misses_and_matches_resident(wd):
+    """Hidden 2048, 512 experts, top-10, three layers generated on the device, the cache capped at 64 MiB (49 slots
+    for 1,536 experts): a stack launch runs on while the selected experts are resident and stops at the first layer
+    that misses; the host streams that layer's experts in from page-locked memory and the stack resumes there.
+    Different inputs keep the routing moving, so the cache misses and evicts all the time; every token's residual must
+    equal, bit for bit, what an engine with every expert resident computes."""
+    Hh, Fh, Eh, Kh, SFh, Lh = 2048, 512, 512, 10, 512, 3
+    full = wd.Engine(Hh, Fh, Eh, Kh, SFh, Lh)
+    capped = wd.Engine(Hh, Fh, Eh, Kh, SFh, Lh, cache_mib=64)
+    assert capped.slot_count() == 64 * 2 ** 20 // capped.slot_bytes() and capped.slot_count() < Lh * Eh
+    rng = np.random.Generator(np.random.PCG64(77))
+    for eng in (full, capped):
+        eng.synth_model(41, 0.02, 0.0)
+    norms = [(1.0 + 0.1 * rng.standard_normal(Hh)).astype(np.float32) for _ in range(Lh)]
+    for eng in (full, capped):
+        for l in range(Lh):
+            eng.set_norm(l, norms[l])
+    for t in range(12):
+        res = (rng.standard_normal(Hh) * (1.0 + t % 3)).astype(np.float32)
+        a, b = full.stack_step_host(res), capped.stack_step_host(res)
+        assert np.array_equal(bits(a), bits(b)), t
+        # the same token again: now every expert is resident and the token is a single launch
+        before = capped.cache_stats()
+        assert np.array_equal(bits(capped.stack_step_host(res)), bits(a)), t
+        after = capped.cache_stats()
+        assert after[1] == before[1] and after[0] == before[0] + Lh * Kh
+    hits, misses, evictions = capped.cache_stats()
+    sent, host_ns, placed = capped.cache_stream_stats()
+    assert misses > 100 and evictions > 50 and hits > 0
+    assert sent == misses * 3 * 450560 and placed > 0
+    assert capped.device_status() == 0 and full.device_status() == 0
+    full.close()
+    capped.close()

@@ -81,6 +81,7 @@ def lib():
         L.wd_set_experts_device.argtypes = [vp, i, vp, vp, vp]
         L.wd_cache_acquire.argtypes = [vp, i, i, C.POINTER(C.c_int)]
         L.wd_cache_stats.argtypes = [vp, C.POINTER(C.c_int64)]
+        L.wd_cache_stream_stats.argtypes = [vp, C.POINTER(C.c_int64)]
         L.wd_moe_forward.argtypes = [vp, i, vp, vp, i, vp]
         L.wd_moe_forward_host.argtypes = [vp, i, vp, vp, i]
         L.wd_stack_step.argtypes = [vp, vp, vp]
@@ -335,6 +336,12 @@ class Engine:
         slot = C.c_int()
         _check(lib().wd_cache_acquire(self.h, layer, expert, C.byref(slot)))
         return slot.value
+
+    def cache_stream_stats(self):
+        """(bytes sent host -> device, host nanoseconds spent placing misses, layers placed) since creation."""
+        st = (C.c_int64 * 3)()
+        _check(lib().wd_cache_stream_stats(self.h, st))
+        return tuple(st)
 
     def cache_stats(self):
         """(hits, misses, evictions) since creation."""

@@ -6,6 +6,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <condition_variable>
 #include <cstdio>
 #include <cstdlib>
@@ -71,6 +72,7 @@ struct Layer {
     // mapping (no page faults on the copy threads; ExpertFileMap + ExpertPreadPool, src/expert_cache.cuh:204-508).
     int fd = -1;
     uint64_t file_gate = 0, file_up = 0, file_down = 0;
+    uint8_t *owned_host = nullptr;              // page-locked copy of a generated layer's experts (capped cache only)
 };
 
 // A few host threads that copy missed experts from the caller's (pageable or mapped) tensors into the
@@ -146,11 +148,13 @@ struct wd_engine {
     std::vector<std::list<int>::iterator> lru_pos;
     std::unordered_map<int64_t, int> key_slot;
     int64_t hits = 0, misses = 0, evictions = 0;
+    int64_t h2d_bytes = 0, fill_host_ns = 0, acquires = 0;      // miss stream: bytes sent, host time spent placing experts
     // miss path of a capped cache: pinned ring and device staging of top_k experts, a copy stream
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t fill_done = nullptr;
     uint8_t *miss_pinned = nullptr, *miss_staging = nullptr;
     int *pinned_ids = nullptr;
+    int *miss_info = nullptr;               // page-locked: [0] layer a launch stopped at (-1 none), then [layer][top_k] picks
     // model load (all experts resident): two half-rings of kLoadBatch experts each, pinned and on the device
     uint8_t *load_pinned = nullptr, *load_staging = nullptr;
     cudaEvent_t load_done[2] = {nullptr, nullptr};
@@ -411,7 +415,7 @@ int sync_layer_table(wd_engine *e, cudaStream_t s) {
 
 // Layers [begin, end) in one cooperative launch.
 int launch_layers(wd_engine *e, int begin, int end, const float *x, float *residual, float *out, cudaStream_t s,
-                  bool select_only = false, int n_tokens = 1) {
+                  bool select_only = false, int n_tokens = 1, bool stop_on_miss = false) {
     for (int l = begin; l < end; ++l) {
         const Layer &L = e->layers[l];
         if (!L.have_router || !L.have_experts || (e->cfg.shared_ffn > 0 && !L.have_shared))
@@ -438,6 +442,8 @@ int launch_layers(wd_engine *e, int begin, int end, const float *x, float *resid
         p.layer_begin = begin;
         p.layer_end = end;
         p.n_tokens = n_tokens;
+        p.stop_on_miss = stop_on_miss ? 1 : 0;
+        p.miss_info = e->miss_info;
         if (n_tokens > 1) {         // the selection of every token of the batch is kept
             p.ids = e->tok_ids;
             p.weights = e->tok_weights;
@@ -467,11 +473,15 @@ int launch_layer(wd_engine *e, int layer, const float *x, float *residual, float
 // the copy stream, then the full layer (which repeats the selection bit for bit and finds every slot).
 // The flow of q38_moe_select_experts_f32_x + GpuExpertCache::acquire + ExpertStagePath
 // (src/qwen38_moe.cuh:2323-2380, src/expert_cache.cuh:2252, :1166-1273).
-int acquire_selected(wd_engine *e, int layer, cudaStream_t s) {
+int acquire_selected(wd_engine *e, int layer, cudaStream_t s, const int *host_ids = nullptr) {
     const wd_config &c = e->cfg;
     Layer &L = e->layers[layer];
-    WD_CUDA(cudaMemcpyAsync(e->pinned_ids, e->ids, sizeof(int) * c.top_k, cudaMemcpyDeviceToHost, s));
-    WD_CUDA(cudaStreamSynchronize(s));
+    if (host_ids) {         // the picks are on the host already (a stopped launch left them there)
+        memcpy(e->pinned_ids, host_ids, sizeof(int) * c.top_k);
+    } else {
+        WD_CUDA(cudaMemcpyAsync(e->pinned_ids, e->ids, sizeof(int) * c.top_k, cudaMemcpyDeviceToHost, s));
+        WD_CUDA(cudaStreamSynchronize(s));
+    }
     if (!L.h_gate) return fail(WD_E_STATE, "no host tensors to fill the slots from");
     std::vector<int> owned;
     for (int j = 0; j < c.top_k; ++j) {
@@ -492,8 +502,23 @@ int acquire_selected(wd_engine *e, int layer, cudaStream_t s) {
     }
     if (missing.empty()) return WD_OK;
     const size_t gb = e->gate_bytes, db = e->down_bytes, one = 2 * gb + db;
+    const auto t_begin = std::chrono::steady_clock::now();
+    ++e->acquires;
     std::vector<int> changed_layers{layer};
     std::vector<int> slots(missing.size());
+    // Pageable or file-backed sources: three read tasks per missed expert (gate, up, down) go to the copy threads at
+    // once; each expert's DMA and repack are enqueued as soon as ITS three reads are done, while the threads keep
+    // reading the next ones (ExpertPreadPool + ExpertStagePath::submit, src/expert_cache.cuh:357-508, :1166-1273).
+    // A ring entry is free here because the previous layer's launch, which waited for its DMAs, has completed
+    // (the ids this function works from were read after it).
+    std::vector<std::atomic<int>> reads_left(missing.size());
+    // whatever way this function is left, the read tasks (which point into this frame) have finished by then
+    struct Drain {
+        CopyPool *pool;
+        ~Drain() {
+            if (pool) pool->wait_all();
+        }
+    } drain{L.host_pinned ? nullptr : e->copy_pool};
     for (size_t m = 0; m < missing.size(); ++m) {
         const int x = missing[m], slot = e->lru.back();
         ++e->misses;
@@ -511,16 +536,22 @@ int acquire_selected(wd_engine *e, int layer, cudaStream_t s) {
         L.h_slot[x] = slot;
         touch_slot(e, slot);
         slots[m] = slot;
+        reads_left[m].store(L.host_pinned ? 0 : 3, std::memory_order_relaxed);
         if (!L.host_pinned) {
             uint8_t *pin = e->miss_pinned + m * one;
-            const uint8_t *g = L.h_gate + static_cast<size_t>(x) * gb, *u = L.h_up + static_cast<size_t>(x) * gb,
-                          *d = L.h_down + static_cast<size_t>(x) * db;
             const int fd = L.fd;
-            const uint64_t fg = L.file_gate + static_cast<uint64_t>(x) * gb, fu = L.file_up + static_cast<uint64_t>(x) * gb,
-                           fdn = L.file_down + static_cast<uint64_t>(x) * db;
-            e->copy_pool->submit([=] {
-                // file-backed tensors: positional reads; a short or failed read falls back to the mapping
-                auto fetch = [&](uint8_t *to, const uint8_t *from, uint64_t off, size_t n) {
+            std::atomic<int> *left = &reads_left[m];
+            const struct { uint8_t *to; const uint8_t *from; uint64_t off; size_t n; } parts[3] = {
+                {pin, L.h_gate + static_cast<size_t>(x) * gb, L.file_gate + static_cast<uint64_t>(x) * gb, gb},
+                {pin + gb, L.h_up + static_cast<size_t>(x) * gb, L.file_up + static_cast<uint64_t>(x) * gb, gb},
+                {pin + 2 * gb, L.h_down + static_cast<size_t>(x) * db, L.file_down + static_cast<uint64_t>(x) * db, db}};
+            for (const auto &pt : parts) {
+                uint8_t *to = pt.to;
+                const uint8_t *from = pt.from;
+                const uint64_t off = pt.off;
+                const size_t n = pt.n;
+                e->copy_pool->submit([=] {
+                    // file-backed tensors: positional reads; a short or failed read falls back to the mapping
                     size_t done = 0;
                     while (fd >= 0 && done < n) {
                         const ssize_t r = pread(fd, to + done, n - done, static_cast<off_t>(off + done));
@@ -528,14 +559,11 @@ int acquire_selected(wd_engine *e, int layer, cudaStream_t s) {
                         done += static_cast<size_t>(r);
                     }
                     if (done < n) memcpy(to + done, from + done, n - done);
-                };
-                fetch(pin, g, fg, gb);
-                fetch(pin + gb, u, fu, gb);
-                fetch(pin + 2 * gb, d, fdn, db);
-            });
+                    left->fetch_sub(1, std::memory_order_release);
+                });
+            }
         }
     }
-    if (!L.host_pinned) e->copy_pool->wait_all();
     cudaStream_t cs = e->copy_stream;
     for (size_t m = 0; m < missing.size(); ++m) {
         uint8_t *st = e->miss_staging + m * one;
@@ -545,8 +573,10 @@ int acquire_selected(wd_engine *e, int layer, cudaStream_t s) {
             WD_CUDA(cudaMemcpyAsync(st + gb, L.h_up + static_cast<size_t>(x) * gb, gb, cudaMemcpyHostToDevice, cs));
             WD_CUDA(cudaMemcpyAsync(st + 2 * gb, L.h_down + static_cast<size_t>(x) * db, db, cudaMemcpyHostToDevice, cs));
         } else {
+            while (reads_left[m].load(std::memory_order_acquire) > 0) std::this_thread::yield();
             WD_CUDA(cudaMemcpyAsync(st, e->miss_pinned + m * one, one, cudaMemcpyHostToDevice, cs));
         }
+        e->h2d_bytes += static_cast<int64_t>(one);
         int rc = repack_expert_into_slot(e, st, st + gb, st + 2 * gb, slots[m], cs);
         if (rc) return rc;
     }
@@ -556,10 +586,53 @@ int acquire_selected(wd_engine *e, int layer, cudaStream_t s) {
     }
     WD_CUDA(cudaEventRecord(e->fill_done, cs));
     WD_CUDA(cudaStreamWaitEvent(s, e->fill_done, 0));
+    e->fill_host_ns += std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t_begin).count();
+    return WD_OK;
+}
+
+// Capped cache, optimistic: layers [begin, end) in ONE launch as long as every selected expert is resident. A launch
+// that meets a missing expert stops at that layer; the host touches the finished layers' picks (recency order),
+// places the stopped layer's experts and launches again from there. With a warm cache a token is one launch and one
+// synchronisation, as with every expert resident. (The flow of GpuExpertCache::acquire + ExpertStagePath,
+// src/expert_cache.cuh:2252, :1166-1273, without the per-layer host round trip of q38_moe_select_experts_f32_x,
+// src/qwen38_moe.cuh:2363-2379.) Synchronises the stream.
+int run_capped_optimistic(wd_engine *e, int begin, int end, const float *x, float *residual, float *out, cudaStream_t s) {
+    const int K = e->cfg.top_k;
+    int l = begin;
+    bool relaunch = false;      // layer l was counted when its experts were placed
+    while (l < end) {
+        e->miss_info[0] = -1;
+        int rc = launch_layers(e, l, end, x, residual, out, s, false, 1, true);
+        if (rc) return rc;
+        WD_CUDA(cudaStreamSynchronize(s));
+        const int stopped = e->miss_info[0];
+        const int done_end = stopped >= 0 ? stopped : end;       // layers [l, done_end) ran completely
+        if (stopped >= 0) {
+            // launch_layers counted end - l tags; the launch used stopped - l + 1
+            e->epoch -= static_cast<uint32_t>(end - l);
+            e->epoch += static_cast<uint32_t>(stopped - l + 1);
+            e->last_parity = static_cast<int>(e->epoch & 1u);
+        }
+        for (int d = l; d < done_end; ++d) {                     // every pick of a finished layer was a hit
+            for (int j = 0; j < K; ++j) {
+                const int x_id = e->miss_info[1 + d * K + j];
+                if (x_id >= e->e_first && x_id < e->e_first + e->e_count && e->layers[d].h_slot[x_id] >= 0) {
+                    if (!(relaunch && d == l)) ++e->hits;
+                    touch_slot(e, e->layers[d].h_slot[x_id]);
+                }
+            }
+        }
+        if (stopped < 0) break;
+        if (stopped < l || stopped >= end) return fail(WD_E_DEVICE, "a stopped launch reported a layer outside its range");
+        if ((rc = acquire_selected(e, stopped, s, e->miss_info + 1 + stopped * K))) return rc;
+        l = stopped;
+        relaunch = true;
+    }
     return WD_OK;
 }
 
 int forward_capped(wd_engine *e, int layer, const float *x, float *residual, float *out, cudaStream_t s) {
+    if (!e->fast_fn && e->n_peers == 0) return run_capped_optimistic(e, layer, layer + 1, x, residual, out, s);
     int rc = launch_layers(e, layer, layer + 1, x, residual, out, s, true);
     if (rc) return rc;
     if ((rc = acquire_selected(e, layer, s))) return rc;
@@ -716,6 +789,7 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
         WD_TRY(cudaMallocHost(&e->miss_pinned, one_expert * K));
         WD_TRY(cudaMalloc(&e->miss_staging, one_expert * K));
         WD_TRY(cudaMallocHost(&e->pinned_ids, sizeof(int) * K));
+        WD_TRY(cudaMallocHost(&e->miss_info, sizeof(int) * (1 + static_cast<size_t>(c.n_layers) * K)));
         e->copy_pool = new CopyPool(std::max(1, std::min(8, static_cast<int>(std::thread::hardware_concurrency()))));
     }
 #undef WD_TRY
@@ -802,6 +876,7 @@ void wd_engine_destroy(wd_engine *e) {
     for (Layer &L : e->layers) {
         cudaFree(L.router); cudaFree(L.bias); cudaFree(L.gate_vec); cudaFree(L.sh_gate); cudaFree(L.sh_up);
         cudaFree(L.sh_down); cudaFree(L.norm); cudaFree(L.slot_of_expert);
+        if (L.owned_host) cudaFreeHost(L.owned_host);
     }
     void *bufs[] = {e->pool, e->grid_packed, e->grid2_packed, e->synth_lut, e->sync, e->tagged, e->ids, e->weights, e->routed, e->tok_ids, e->tok_weights,
                     e->x_buf, e->out_buf, e->residual_buf, e->staging, e->stamps, e->layer_table, e->eo_plain, e->shdown_plain, e->fallbacks, e->xbuf};
@@ -810,6 +885,7 @@ void wd_engine_destroy(wd_engine *e) {
     cudaFree(e->miss_staging);
     if (e->miss_pinned) cudaFreeHost(e->miss_pinned);
     if (e->pinned_ids) cudaFreeHost(e->pinned_ids);
+    if (e->miss_info) cudaFreeHost(e->miss_info);
     if (e->fill_done) cudaEventDestroy(e->fill_done);
     if (e->copy_stream) cudaStreamDestroy(e->copy_stream);
     if (e->pinned) cudaFreeHost(e->pinned);
@@ -1073,6 +1149,12 @@ int wd_cache_acquire(wd_engine *e, int layer, int expert, int *slot_out) {
     return WD_OK;
 }
 
+int wd_cache_stream_stats(const wd_engine *e, int64_t stats[3]) {
+    if (!e || !stats) return fail(WD_E_INVALID, "null argument");
+    stats[0] = e->h2d_bytes; stats[1] = e->fill_host_ns; stats[2] = e->acquires;
+    return WD_OK;
+}
+
 int wd_cache_stats(const wd_engine *e, int64_t stats[3]) {
     if (!e || !stats) return fail(WD_E_INVALID, "null argument");
     stats[0] = e->hits; stats[1] = e->misses; stats[2] = e->evictions;
@@ -1132,6 +1214,8 @@ int wd_stack_step(wd_engine *e, float *residual_dev, void *stream) {
     if (!e || !residual_dev) return fail(WD_E_INVALID, "null argument");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
+    if (!e->resident && !e->fast_fn && e->n_peers == 0)
+        return run_capped_optimistic(e, 0, e->cfg.n_layers, nullptr, residual_dev, e->out_buf, s);
     if (!e->resident) {     // layer by layer: the host places the selected experts between the two passes
         for (int l = 0; l < e->cfg.n_layers; ++l) {
             int rc = forward_capped(e, l, nullptr, residual_dev, e->out_buf, s);
@@ -1728,7 +1812,6 @@ int wd_synth_model(wd_engine *e, uint64_t seed, float sigma, float bias_sigma) {
     e->layer_table_dirty = true;
     if (e->cfg.gate_type != WD_TYPE_IQ3_S || e->cfg.down_type != WD_TYPE_IQ3_S)
         return fail(WD_E_STATE, "the device-side generator writes IQ3_S experts only");
-    if (!e->resident) return fail(WD_E_STATE, "the device-side generator needs a pool that holds every owned expert");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     const wd_config &c = e->cfg;
     cudaStream_t s = e->stream;
@@ -1775,7 +1858,16 @@ int wd_synth_model(wd_engine *e, uint64_t seed, float sigma, float bias_sigma) {
         if ((rc = synth_into(e, WD_TYPE_IQ3_S, static_cast<long long>(c.n_experts) * c.hidden, c.expert_ffn, sigma, seed,
                              sid(l, 10), d, s)))
             break;
-        if ((rc = wd_set_experts_device(e, l, g, u, d))) break;
+        if (e->resident) {
+            if ((rc = wd_set_experts_device(e, l, g, u, d))) break;
+        } else {
+            // a capped cache streams its misses from host memory: keep a page-locked copy of the layer's experts
+            if (!L.owned_host) WD_CUDA(cudaMallocHost(&L.owned_host, need));
+            WD_CUDA(cudaMemcpyAsync(L.owned_host, big, need, cudaMemcpyDeviceToHost, s));
+            WD_CUDA(cudaStreamSynchronize(s));
+            const size_t ge = static_cast<size_t>(c.n_experts) * gb;
+            if ((rc = wd_set_experts(e, l, L.owned_host, L.owned_host + ge, L.owned_host + 2 * ge))) break;
+        }
     }
     cudaStreamSynchronize(s);
     return rc;

@@ -56,6 +56,14 @@ struct MoeParams {
     int n_tokens;
     int stamp_layer;             // the layer whose phase timestamps are recorded
     int select_only;             // 1: stop after the selection (ids and weights written); nothing else changes
+    // Capped expert cache, optimistic: layers run on as long as every selected expert has a slot. A layer that meets
+    // an expert without one stops the launch there (every CTA computes the same selection, so all of them stop at
+    // the same layer without talking to one another): the residual as of that layer's input goes back to `residual`,
+    // miss_info[0] receives the layer's index (-1: the launch ran through) and the host places the experts and
+    // launches again from that layer. miss_info[1 + l * K + j] logs every finished layer's picks (for the cache's
+    // recency order); miss_info lives in page-locked host memory.
+    int stop_on_miss;
+    int *miss_info;
     const uint8_t *pool;         // slot pool base
     unsigned long long slot_bytes;
     unsigned gate_off, up_off, down_off;        // offsets of the three matrices inside a slot
@@ -111,7 +119,7 @@ constexpr int kMaxSlices = WD_MAX_SLICES;   // slices per gate/up tile left over
 constexpr int kLeftInts = 2048;     // = kMiscGsum: the x floats / router candidates region, reused in phase 2
 constexpr int kMiscLogits = 0, kMiscProbs = 1024, kMiscGsum = 2048, kMiscRed = 2176, kMiscTop = 2192,
               kMiscChamp = 2208, kMiscDsum = 2272, kMiscIds = 2288, kMiscW = 2304, kMiscLocJ = 2320,
-              kMiscLocSlot = 2336, kMiscLocN = 2352, kMiscSlots = 2368, kMiscSharedAct = 2400;
+              kMiscLocSlot = 2336, kMiscLocN = 2352, kMiscMiss = 2353, kMiscSlots = 2368, kMiscSharedAct = 2400;
 
 // Phase 0 of one thread: its EPL consecutive residual values (plain memory in the first layer of a launch, the
 // previous layer's tagged words otherwise, polled together with the progress word), the norm weights, and the
@@ -264,6 +272,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     __syncthreads();
 
     const int seq_end = P.n_tokens > 1 ? P.layer_begin + P.n_tokens : P.layer_end;   // end of the launch's sequence
+    int seq_done = seq_end - P.layer_begin;             // positions that consumed a tag (less when a miss stops the launch)
+    int *miss_flag = reinterpret_cast<int *>(misc + kMiscMiss);
 #pragma unroll 1
     for (int layer = P.layer_begin; layer < seq_end; ++layer) {     // position in the sequence: a layer, or a token
     const int tok = P.n_tokens > 1 ? layer - P.layer_begin : 0;
@@ -379,11 +389,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         __threadfence();        // this CTA's reads of the last layers' rows come before its arrival below
         if (atomicAdd(P.sync + 9, 1u) == static_cast<unsigned>(ncta) - 1u) {
             P.sync[9] = 0u;
-            P.sync[8] = epoch + static_cast<uint32_t>(seq_end - P.layer_begin);
+            P.sync[8] = epoch + static_cast<uint32_t>(seq_done);
             // every CTA of this rank has left the launch: the peers may overwrite both halves of its row buffer
             __threadfence();
             for (int p = 0; p < P.n_peers; ++p)
-                st_tagged_sys_release(P.peer_left_out[p], 0.0f, epoch + static_cast<uint32_t>(seq_end - P.layer_begin));
+                st_tagged_sys_release(P.peer_left_out[p], 0.0f, epoch + static_cast<uint32_t>(seq_done));
             if (P.host_status) *P.host_status = *reinterpret_cast<volatile unsigned *>(err);
         }
     }
