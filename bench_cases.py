@@ -1,0 +1,238 @@
+"""Small, self-ending measurement cases beside bench.py: the workloads that the profile summaries under profiles/
+were captured from (ncu wants a short program with few launches), and the kernel's own phase stamps.
+
+    python bench_cases.py profile [--layers 2] [--iters 4] [--stamps] [--stack] [--compiled]
+        a few forward calls of the MoE layer kernel at the 48-layer model's block shape, direct launches, about
+        0.7 GB per layer on the device; --stamps prints the kernel's per-phase timestamps (mean over CTAs)
+        instead (generic kernel), which needs no profiler; --compiled runs the kernel compiled for the geometry
+    python bench_cases.py dense [--rows 128256] [--cols 2048] [--mats 2] [--iters 20]
+        streams Q4_0 matrices of the plain decoder's output-head size through the dense matvec kernel
+    python bench_cases.py head [--rows 151936] [--cols 2048] [--iters 20]
+        the Q8_0 output head with fused arg-max
+    python bench_cases.py load [--layers 2] [--dir /tmp]
+        model load from a GGUF file: open + engine create + load for a few layers of the model's shape
+"""
+import argparse
+import json
+import os
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import warpdecode_b200 as wd          # noqa: E402
+
+
+def measured_peak():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+# ---- profile: the MoE layer kernel ---------------------------------------------------------------------------------
+
+
+# stamp indices in the order the kernel passes them, and the name of the span that ends at each
+ORDER = [0, 1, 2, 3, 4, 13, 5, 6, 11, 7, 9, 8, 10]
+PHASES = ["issue_p1", "x_wait_quant", "q8_rows", "gather_logits", "select.router", "select.rest",
+          "issue_tiles", "first_tile_wait", "gate_up", "gather_act_quant", "down", "combine"]
+
+
+def phase_row(st, with_period):
+    ok = st[:, 11] >= st[:, 6]          # CTAs without a gate/up tile in this layer leave stamp 11 unset
+    d = [(st[ok, ORDER[i + 1]] - st[ok, ORDER[i]]).mean() for i in range(len(ORDER) - 1)]
+    d.append((st[:, 10] - st[:, 0]).mean())                         # a CTA's time inside the layer
+    d.append((st[:, 14] - st[:, 0]).mean() if with_period else 0)   # start of this layer to start of the next
+    return d
+
+
+def profile_case(a):
+    if a.compiled:
+        os.environ["WD_COMPILED_KERNEL"] = "1"
+    eng = wd.Engine(2048, 512, 512, 10, 512, a.layers)
+    print("kernel:", eng.kernel_name())
+    eng.synth_model(3, 0.02, 0.0)
+    rng = np.random.Generator(np.random.PCG64(1))
+    rows = []
+    if a.stack:
+        # all layers in one launch; the profiled layer sits in the middle, where the code is cache-warm
+        eng.set_profiling(1 + a.layers // 2 if a.stamps else 0)
+        res = rng.standard_normal(2048).astype(np.float32)
+        for it in range(a.iters + 1):
+            t0 = time.perf_counter()
+            res = eng.stack_step_host(res)
+            wall = time.perf_counter() - t0
+            if a.stamps:
+                rows.append(phase_row(eng.stamps().astype(np.int64), a.layers // 2 + 1 < a.layers))
+        print("last stack step, host wall clock: %.1f us per layer" % (wall * 1e6 / a.layers))
+        skip = 1
+    else:
+        eng.set_profiling(a.stamps)
+        for it in range(a.iters):
+            for layer in range(a.layers):
+                eng.forward_host(layer, rng.standard_normal(2048).astype(np.float32))
+                if a.stamps:
+                    rows.append(phase_row(eng.stamps().astype(np.int64), False))
+        skip = a.layers
+    assert eng.device_status() == 0
+    if a.stamps:
+        m = np.array(rows[skip:]).mean(0)          # skip the first pass (cold)
+        names = PHASES + ["cta_in_layer", "layer_period"]
+        print("mean ns per phase:", {n: int(v) for n, v in zip(names, m)})
+    print("done")
+
+
+# ---- dense: Q4_0 matvec and the Q8_0 head ---------------------------------------------------------------------------
+
+
+def head_case(a):
+    """Q8_0 matrix [rows][cols] (default: the 48-layer decoder's head, 151936 x 2048 = 331 MB) + arg-max."""
+    import torch
+    nb = a.cols // 32
+    g = torch.Generator(device="cuda").manual_seed(7)
+    blocks = torch.randint(0, 256, (a.rows * nb, 34), dtype=torch.uint8, device="cuda", generator=g)
+    scale = (torch.rand(a.rows * nb, device="cuda", generator=g) * 0.01 + 0.001).to(torch.float16)
+    blocks[:, 0:2] = scale.view(torch.uint8).reshape(-1, 2)
+    torch.cuda.synchronize()
+    head = wd.HeadQ8_0(a.rows, a.cols, ggml_dev_ptr=blocks.data_ptr())
+    torch.cuda.synchronize()
+    del blocks
+    x = torch.randn(a.cols, device="cuda", generator=g)
+    tok = torch.zeros(1, dtype=torch.int32, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(3):
+        head.argmax(x.data_ptr(), tok.data_ptr(), None, None, s)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.iters):
+        head.argmax(x.data_ptr(), tok.data_ptr(), None, None, s)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / a.iters
+    nbytes = a.rows * nb * 34
+    peak = measured_peak()
+    gbs = nbytes / us / 1e3
+    print(json.dumps({"kernel": "q8_0_head_kernel (+ memset, finish)", "rows": a.rows, "cols": a.cols,
+                      "bytes_per_call": nbytes, "us_per_call": us, "achieved_gbs": gbs, "peak_gbs": peak,
+                      "frac": gbs / peak, "token": int(tok[0])}))
+
+
+def dense_case(a):
+    import torch
+    wd.lib()
+    nb = a.cols // 32
+    g = torch.Generator(device="cuda").manual_seed(7)
+    mats = []
+    for m in range(a.mats):
+        blocks = torch.randint(0, 256, (a.rows * nb, 18), dtype=torch.uint8, device="cuda", generator=g)
+        scale = (torch.rand(a.rows * nb, device="cuda", generator=g) * 0.01 + 0.001).to(torch.float16)
+        blocks[:, 0:2] = scale.view(torch.uint8).reshape(-1, 2)
+        torch.cuda.synchronize()
+        mats.append(wd.DenseQ4_0(a.rows, a.cols, ggml_dev_ptr=blocks.data_ptr()))
+        torch.cuda.synchronize()
+        del blocks
+    x = torch.randn(a.cols, device="cuda", generator=g)
+    y = torch.zeros(a.rows, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    for i in range(3 * a.mats):
+        mats[i % a.mats].matvec(x.data_ptr(), y.data_ptr(), s)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(a.iters * a.mats):
+        mats[i % a.mats].matvec(x.data_ptr(), y.data_ptr(), s)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (a.iters * a.mats)
+    nbytes = a.rows * nb * 18
+    peak = measured_peak()
+    gbs = nbytes / us / 1e3
+    print(json.dumps({"kernel": "q4_0_gemv_kernel", "rows": a.rows, "cols": a.cols, "bytes_per_launch": nbytes,
+                      "us_per_launch": us, "achieved_gbs": gbs, "peak_gbs": peak, "frac": gbs / peak,
+                      "finite": bool(torch.isfinite(y).all())}))
+
+
+# ---- load: GGUF file -> repacked HBM slots --------------------------------------------------------------------------
+
+
+def load_case(a):
+    from warpdecode_b200 import synth
+    H, F, E, K, SF = 2048, 512, 512, 10, 512
+    rng = np.random.Generator(np.random.PCG64(9))
+    gb = F * (H // 256) * 110
+    meta = {"general.architecture": "qwen4exp", "qwen4exp.block_count": a.layers, "qwen4exp.expert_count": E,
+            "qwen4exp.expert_used_count": K, "qwen4exp.embedding_length": H, "qwen4exp.expert_feed_forward_length": F,
+            "qwen4exp.expert_shared_feed_forward_length": SF}
+    tensors = []
+    for l in range(a.layers):
+        m = dict(hidden=H, expert_ffn=F, n_experts=E, shared_ffn=SF, gate_type=21, up_type=21, down_type=21,
+                 router=rng.integers(0, 256, E * (H // 32) * 34, dtype=np.uint8),
+                 gate=rng.integers(0, 256, E * gb, dtype=np.uint8), up=rng.integers(0, 256, E * gb, dtype=np.uint8),
+                 down=rng.integers(0, 256, E * gb, dtype=np.uint8),
+                 shared_gate_vec=rng.standard_normal(H).astype(np.float32),
+                 shared_gate=rng.integers(0, 256, SF * (H // 32) * 34, dtype=np.uint8),
+                 shared_up=rng.integers(0, 256, SF * (H // 32) * 34, dtype=np.uint8),
+                 shared_down=rng.integers(0, 256, H * (SF // 32) * 34, dtype=np.uint8))
+        tensors += synth.moe_block_tensors(m, l)
+    path = os.path.join(a.dir, "wd_load_case.gguf")
+    synth.write_gguf(path, meta, tensors)
+    del tensors
+    size = os.path.getsize(path)
+    with open(path, "rb") as f:                  # page-cache warm, as the reference's own protocol does
+        while f.read(1 << 26):
+            pass
+    wd.lib()
+    wd.Engine(256, 256, 8, 2, 0, 1).close()      # CUDA context and module load happen here, outside the timing
+    t0 = time.perf_counter()
+    g = wd.Gguf(path)
+    c = g.config()
+    eng = wd.Engine(c.hidden, c.expert_ffn, c.n_experts, c.top_k, c.shared_ffn, c.n_layers, expert_type=c.gate_type,
+                    down_type=c.down_type, w_scale=c.w_scale, rms_eps=c.rms_eps)
+    t1 = time.perf_counter()
+    wd._check(wd.lib().wd_engine_load_gguf(eng.h, g.h))
+    t2 = time.perf_counter()
+    expert_bytes = a.layers * E * 3 * gb
+    print(json.dumps({"layers": a.layers, "file_bytes": size, "expert_bytes": expert_bytes, "open_create_s": t1 - t0,
+                      "load_s": t2 - t1, "expert_gb_per_s": expert_bytes / (t2 - t1) / 1e9,
+                      "status": eng.device_status()}))
+    eng.close()
+    g.close()
+    os.remove(path)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="case", required=True)
+    p = sub.add_parser("profile")
+    p.add_argument("--layers", type=int, default=2)
+    p.add_argument("--iters", type=int, default=4)
+    p.add_argument("--stamps", action="store_true")
+    p.add_argument("--stack", action="store_true", help="run every layer in one launch (wd_stack_step)")
+    p.add_argument("--compiled", action="store_true", help="the kernel compiled for the geometry (WD_COMPILED_KERNEL=1)")
+    p.set_defaults(fn=profile_case)
+    p = sub.add_parser("dense")
+    p.add_argument("--rows", type=int, default=128256)
+    p.add_argument("--cols", type=int, default=2048)
+    p.add_argument("--mats", type=int, default=2)
+    p.add_argument("--iters", type=int, default=20)
+    p.set_defaults(fn=dense_case)
+    p = sub.add_parser("head")
+    p.add_argument("--rows", type=int, default=151936)
+    p.add_argument("--cols", type=int, default=2048)
+    p.add_argument("--iters", type=int, default=20)
+    p.set_defaults(fn=head_case)
+    p = sub.add_parser("load")
+    p.add_argument("--layers", type=int, default=2)
+    p.add_argument("--dir", default="/tmp")
+    p.set_defaults(fn=load_case)
+    a = ap.parse_args()
+    a.fn(a)
+
+
+if __name__ == "__main__":
+    main()

@@ -169,6 +169,23 @@ float wdo_row_q8_0_q8_0(const uint8_t *w_row, const uint8_t *y, int cols) {
     return hsum8(lane);
 }
 
+/* The Q8_0 row dot above for `rows` consecutive rows (an output head of 151,936 rows is too many calls for a Python
+ * loop); also returns the index of the largest finite logit, lowest index first, which is the greedy token. */
+int wdo_matvec_q8_0_argmax(const uint8_t *w, int rows, int cols, const uint8_t *y, float *out) {
+    const size_t rb = (size_t)(cols / 32) * WDO_Q8_0_BYTES;
+    int best = 0;
+    float best_v = -INFINITY;
+    for (int r = 0; r < rows; ++r) {
+        const float v = wdo_row_q8_0_q8_0(w + (size_t)r * rb, y, cols);
+        if (out) out[r] = v;
+        if (v == v && v > best_v && v <= 3.402823466e38f) {
+            best_v = v;
+            best = r;
+        }
+    }
+    return best;
+}
+
 /* IQ3_S weights x Q8_K activation (src/qwen38_cpu_moe.cuh:337-375). Block layout:
  * d(2) qs(64) qh(8) signs(32) scales(4). Chunk-lane c of sub-block ib32 uses grid
  * index qs[8*ib32 + c] | bit (c) of qh[ib32] << 8, sign nibble (c & 1) of

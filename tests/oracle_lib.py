@@ -84,6 +84,7 @@ class Oracle:
         for name in ("wdo_row_q8_0_q8_0", "wdo_row_iq4_nl_q8_0", "wdo_row_q4_0_q8_0"):
             getattr(L, name).restype = C.c_float
             getattr(L, name).argtypes = [C.c_void_p, C.c_void_p, C.c_int]
+        L.wdo_matvec_q8_0_argmax.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         for name in ("wdo_row_iq3_s_q8_K", "wdo_row_iq2_s_q8_K"):
             getattr(L, name).restype = C.c_float
             getattr(L, name).argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
@@ -141,6 +142,15 @@ class Oracle:
         f = {TYPE_Q8_0: self.lib.wdo_row_q8_0_q8_0, TYPE_IQ4_NL: self.lib.wdo_row_iq4_nl_q8_0,
              TYPE_Q4_0: self.lib.wdo_row_q4_0_q8_0}[t]
         return np.float32(f(w_row.ctypes.data, y.ctypes.data, cols))
+
+    def head_argmax_q8_0(self, w, rows, cols, y, logits=False):
+        """Greedy token of a Q8_0 head [rows][cols] (ggml blocks) for the Q8_0-quantised activation y:
+        the row dot of every row, then the largest finite logit, lowest index first."""
+        w = np.ascontiguousarray(w, np.uint8)
+        y = np.ascontiguousarray(y, np.uint8)
+        out = np.zeros(rows, np.float32) if logits else None
+        tok = self.lib.wdo_matvec_q8_0_argmax(w.ctypes.data, rows, cols, y.ctypes.data, out.ctypes.data if logits else None)
+        return (tok, out) if logits else tok
 
     def dot_f32(self, a, b):
         a = np.ascontiguousarray(a, np.float32)

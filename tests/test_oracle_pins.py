@@ -174,3 +174,38 @@ def test_live_block_against_reference_any_thread_count(oracle, reference):
     for th in (1, 3, 8):
         r = reference.moe_block(m, xs[1], threads=th)
         assert np.array_equal(r["ids"], o["ids"]) and np.array_equal(bits(r["out"]), bits(o["out"]))
+
+
+def test_q4_0_row_dot_against_gguf_py_decoder_and_exact_integers(oracle):
+    """The reference has no host twin and no golden vector for its plain Q4_0 matvec (src/warodecode.cu:1535-1562),
+    so the oracle's Q4_0 row is pinned against an independent decoder instead: gguf-py dequantises the same block
+    bytes, the integer side (sum of (q - 8) * q_x per chunk of four values) is rebuilt in int64, and the float side
+    replays ggml's order (one fmaf per block and chunk-lane, then the 8-lane tree) with every step rounded once."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    rng = np.random.Generator(np.random.PCG64(404))
+    cols, rows = 2048, 48
+    nb = cols // 32
+    w = rng.integers(0, 256, (rows * nb, 18), dtype=np.uint8)
+    w[:, 0:2] = (rng.random(rows * nb) * 0.01 + 0.001).astype(np.float16).view(np.uint8).reshape(-1, 2)
+    x = rng.standard_normal(cols).astype(np.float32)
+    xq = oracle.quantize_q8_0(x).reshape(nb, 34)
+    wf = quants.dequantize(w.reshape(rows, nb * 18), gguf.GGMLQuantizationType.Q4_0).reshape(rows, nb, 32)
+    xf = quants.dequantize(xq.reshape(1, nb * 34), gguf.GGMLQuantizationType.Q8_0).reshape(nb, 32)
+    d_w = w[:, 0:2].copy().view(np.float16).astype(np.float32).reshape(rows, nb)
+    d_x = xq[:, 0:2].copy().view(np.float16).astype(np.float32).reshape(nb)
+    qw = np.rint(wf.astype(np.float64) / d_w[:, :, None]).astype(np.int64)          # (q - 8), exact
+    qx = xq[:, 2:].view(np.int8).astype(np.int64)
+    assert np.array_equal(np.rint(xf.astype(np.float64) / np.where(d_x == 0, 1, d_x)[:, None]).astype(np.int64) * (d_x != 0)[:, None],
+                          qx * (d_x != 0)[:, None])
+    assert qw.min() >= -8 and qw.max() <= 7
+    part = (qw.reshape(rows, nb, 8, 4) * qx.reshape(1, nb, 8, 4)).sum(-1)           # [row][block][chunk-lane], int64
+    for r in range(rows):
+        lane = np.zeros(8, np.float32)
+        for b in range(nb):
+            d = np.float32(d_w[r, b] * d_x[b])
+            lane = (d.astype(np.float64) * part[r, b].astype(np.float64) + lane.astype(np.float64)).astype(np.float32)   # fmaf
+        s = [np.float32(lane[i] + lane[i + 4]) for i in range(4)]
+        want = np.float32(np.float32(s[0] + s[2]) + np.float32(s[1] + s[3]))
+        got = oracle.row(ol.TYPE_Q4_0, w[r * nb:(r + 1) * nb].reshape(-1), xq.reshape(-1), cols)
+        assert ol.fbits(np.array([got]))[0] == ol.fbits(np.array([want]))[0], r
