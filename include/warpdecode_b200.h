@@ -139,8 +139,8 @@ int wd_stack_step_host(wd_engine *e, const float *residual_in_host, float *resid
 #define WD_TAP_SHARED_GATE 7  /* F32 [1] */
 #define WD_TAP_SHARED_ACT 8   /* F32 [shared_ffn] */
 #define WD_TAP_STAMPS 9       /* U64 [sm_count][32] phase timestamps (ns), see wd_set_profiling */
-#define WD_TAP_FALLBACKS 10   /* U32 [1] layers so far whose ids came from the exact rungs, not from the logit threshold
-                               * (engines that run the compiled kernel; 0 otherwise) */
+#define WD_TAP_FALLBACKS 10   /* U32 [1] rows so far whose ids came from the exact rungs because the proof of the
+                               * threshold pick failed (0 for engines created with WD_THRESHOLD_SELECT=0) */
 /* Copies a tap of the most recent forward of token `token` to host memory (synchronises).
  * token = -1 means the last token of that call. After a batch of several tokens, ids and weights
  * are kept for every token; the other taps show the last token only (earlier ones: WD_E_STATE).

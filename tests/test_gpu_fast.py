@@ -44,9 +44,11 @@ def _engine(wd, compiled, *a, **kw):
     return eng
 
 
-@pytest.fixture(scope="module")
-def head_engine(wd):
-    eng = _engine(wd, True, H, F, E, K, SF, 1)
+@pytest.fixture(scope="module", params=["compiled", "generic"])
+def head_engine(wd, request):
+    """One block at the model shape on the compiled kernel, and on the generic kernel (whose ids come from the same
+    threshold on the logits with the same proof)."""
+    eng = _engine(wd, request.param == "compiled", H, F, E, K, SF, 1)
     eng.synth_model(11, 0.02, 0.0)
     yield eng
     eng.close()

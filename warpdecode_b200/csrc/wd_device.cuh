@@ -70,15 +70,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait; on timeout raises kErrCopyTimeout and returns false (the caller carries on with
-// whatever is in shared memory so that the kernel still terminates).
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsigned *err) {
+// Bounded wait: one second of the global timer (checked every 64 polls; a poll can itself suspend the thread for a
+// while), or 64 more polls once another wait of this launch has failed, so that a broken launch ends quickly. On
+// timeout raises kErrCopyTimeout, leaves the barrier's shared-memory address in err[2] (first failure only, for
+// diagnosis) and returns false; the caller carries on with whatever is in shared memory so that the kernel terminates.
+__device__ __noinline__ bool mbar_wait_slow(uint64_t *bar, uint32_t parity, unsigned *err) {
+    const unsigned long long t0 = global_timer_ns();
 #pragma unroll 1
-    for (unsigned i = 0; i < kSpinLimit; ++i) {      // not unrolled: every copy of this loop is code that is fetched once per layer
+    for (unsigned i = 0;; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u) {
+            const bool others = (*reinterpret_cast<volatile unsigned *>(err) & (kErrBarrierTimeout | kErrCopyTimeout)) != 0u;
+            if (others || global_timer_ns() - t0 > kWaitLimitNs) break;
+        }
     }
-    atomicOr(err, kErrCopyTimeout);
+    if ((atomicOr(err, kErrCopyTimeout) & kErrCopyTimeout) == 0u) err[2] = smem_u32(bar);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, unsigned *err) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, err);
 }
 
 // Integer atomics on this CTA's shared memory, addressed in the shared window (an atomic through a generic

@@ -199,6 +199,7 @@ struct wd_engine {
     wd::tagged_t *xbuf = nullptr;                           // the compiled kernel's per-CTA mailboxes
     size_t xbuf_words = 0;
     unsigned *fallbacks = nullptr;                          // layers that took the exact rungs
+    bool threshold_select = true;   // the generic kernel: ids from a threshold on the logits (WD_THRESHOLD_SELECT=0: the rungs)
 };
 
 namespace {
@@ -444,6 +445,8 @@ int launch_layers(wd_engine *e, int begin, int end, const float *x, float *resid
         p.n_tokens = n_tokens;
         p.stop_on_miss = stop_on_miss ? 1 : 0;
         p.miss_info = e->miss_info;
+        p.threshold_select = e->threshold_select ? 1 : 0;
+        p.fallbacks = e->fallbacks;
         if (n_tokens > 1) {         // the selection of every token of the batch is kept
             p.ids = e->tok_ids;
             p.weights = e->tok_weights;
@@ -600,7 +603,10 @@ int run_capped_optimistic(wd_engine *e, int begin, int end, const float *x, floa
     const int K = e->cfg.top_k;
     int l = begin;
     bool relaunch = false;      // layer l was counted when its experts were placed
+    int launches = 0;
     while (l < end) {
+        // every launch either ends the range or places one more layer's experts: more launches than that is a fault
+        if (++launches > 2 * (end - begin) + 2) return fail(WD_E_DEVICE, "the capped cache keeps stopping at the same layer");
         e->miss_info[0] = -1;
         int rc = launch_layers(e, l, end, x, residual, out, s, false, 1, true);
         if (rc) return rc;
@@ -624,6 +630,7 @@ int run_capped_optimistic(wd_engine *e, int begin, int end, const float *x, floa
         }
         if (stopped < 0) break;
         if (stopped < l || stopped >= end) return fail(WD_E_DEVICE, "a stopped launch reported a layer outside its range");
+        if (relaunch && stopped == l) return fail(WD_E_DEVICE, "a layer missed again right after its experts were placed");
         if ((rc = acquire_selected(e, stopped, s, e->miss_info + 1 + stopped * K))) return rc;
         l = stopped;
         relaunch = true;
@@ -643,6 +650,9 @@ int check_device_status(wd_engine *e) {
     unsigned st = 0;
     WD_CUDA(cudaMemcpy(&st, e->sync + 2, sizeof(st), cudaMemcpyDeviceToHost));
     if (st != 0) {
+        unsigned where[2] = {0, 0};     // shared-memory address of the first copy barrier that timed out, and of barrier 0
+        cudaMemcpy(where, e->sync + 4, sizeof(where), cudaMemcpyDeviceToHost);
+        const std::string bar = (st & 2u) ? " [copy barrier " + std::to_string((static_cast<long long>(where[0]) - where[1]) / 8) + "]" : "";
         // an interrupted launch leaves the tag epoch and the exchange words undefined: start over
         cudaMemset(e->sync, 0, 8192);
         cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t));
@@ -650,7 +660,7 @@ int check_device_status(wd_engine *e) {
         e->epoch = 0;
         return fail(WD_E_DEVICE, "kernel raised status " + std::to_string(st) +
                                      " (1 wait timeout, 2 copy timeout, 4 expert without slot, 8 geometry, "
-                                     "16 exchange word overwritten before it was read)");
+                                     "16 exchange word overwritten before it was read)" + bar);
     }
     return WD_OK;
 }
@@ -719,6 +729,7 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
         }
     }
     e->resident = e->n_slots == owned;
+    if (const char *v = std::getenv("WD_THRESHOLD_SELECT")) e->threshold_select = v[0] != '0';
     int rc = WD_OK;
     auto bail = [&](int code) {
         wd_engine_destroy(e);
@@ -762,6 +773,8 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     WD_TRY(cudaMalloc(&e->tok_ids, static_cast<size_t>(c.max_tokens) * K * 4));
     WD_TRY(cudaMalloc(&e->tok_weights, static_cast<size_t>(c.max_tokens) * K * 4));
     WD_TRY(cudaMalloc(&e->residual_buf, H * 4));
+    WD_TRY(cudaMalloc(&e->fallbacks, 64));
+    WD_TRY(cudaMemset(e->fallbacks, 0, 64));
     // tagged exchange words: logits, shared act, shared gate, act, expert out, shared down, residual (x2), progress
     // every region starts on a 128-byte line (16 words): lines that one CTA writes are then never shared with another's
     auto up16 = [](size_t w) { return (w + 15) / 16 * 16; };
@@ -844,8 +857,7 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
             if (fe == cudaSuccess) fe = cudaMemset(e->xbuf, 0, e->xbuf_words * sizeof(wd::tagged_t));
             if (fe == cudaSuccess) fe = cudaMalloc(&e->eo_plain, static_cast<size_t>(K) * H * 4);
             if (fe == cudaSuccess) fe = cudaMalloc(&e->shdown_plain, static_cast<size_t>(H) * 4);
-            if (fe == cudaSuccess) fe = cudaMalloc(&e->fallbacks, 64);
-            if (fe == cudaSuccess) fe = cudaMemset(e->fallbacks, 0, 64);
+
             if (fe == cudaSuccess)
                 fe = cudaFuncSetAttribute(e->fast_fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(e->fast_smem));
             if (fe != cudaSuccess) {

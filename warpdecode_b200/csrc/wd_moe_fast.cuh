@@ -369,6 +369,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
         mbar_init(&bars[tid], 1);
         mbar_fence_init();
     }
+    if (cta == 0 && tid == 0) P.sync[5] = smem_u32(bars);      // so that a copy timeout can be reported by barrier index
     build_grid_table(tab, P.grid_packed);
     __syncthreads();
 
@@ -809,7 +810,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
                 const float pn = __shfl_down_sync(0xffffffffu, pj, 1);
                 const int en = __shfl_down_sync(0xffffffffu, ej, 1);
                 const bool fine = lane >= K || (pj == pj && pj > -INFINITY && (lane == K - 1 || pj > pn || (pj == pn && ej < en)));
-                bad = bad || !__all_sync(0xffffffffu, fine);
+                const bool all_fine = __all_sync(0xffffffffu, fine);   // the vote on its own: every lane must take part
+                bad = bad || !all_fine;
                 const float w = router_weights_warp(pj, K, P.w_scale, lane);
                 if (lane < K) sel_w[lane] = w;
             }

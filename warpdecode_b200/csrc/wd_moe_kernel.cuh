@@ -64,6 +64,8 @@ struct MoeParams {
     // recency order); miss_info lives in page-locked host memory.
     int stop_on_miss;
     int *miss_info;
+    int threshold_select;        // 1: expert ids from a threshold on the logits, proven afterwards (wd_router.cuh); 0: the rungs
+    unsigned *fallbacks;         // nullable: counts the rows whose proof failed and that took the exact rungs (CTA 0)
     const uint8_t *pool;         // slot pool base
     unsigned long long slot_bytes;
     unsigned gate_off, up_off, down_off;        // offsets of the three matrices inside a slot
@@ -267,6 +269,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
         mbar_init(&bars[tid], 1);
         mbar_fence_init();
     }
+    if (cta == 0 && tid == 0) P.sync[5] = smem_u32(bars);      // so that a copy timeout can be reported by barrier index
     if (P.gu_type == kTypeIq3s || P.d_type == kTypeIq3s) build_grid_table(tab, P.grid_packed);   // first needed in phase 2
     if (P.gu_type == kTypeIq2s || P.d_type == kTypeIq2s) build_iq2_table(tab2, P.grid2_packed);
     __syncthreads();
@@ -274,6 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_layer_kernel(const __grid_con
     const int seq_end = P.n_tokens > 1 ? P.layer_begin + P.n_tokens : P.layer_end;   // end of the launch's sequence
     int seq_done = seq_end - P.layer_begin;             // positions that consumed a tag (less when a miss stops the launch)
     int *miss_flag = reinterpret_cast<int *>(misc + kMiscMiss);
+    uint32_t tflip = 0;         // flips when a layer issued its tile copies twice (the proof of the picked set failed)
 #pragma unroll 1
     for (int layer = P.layer_begin; layer < seq_end; ++layer) {     // position in the sequence: a layer, or a token
     const int tok = P.n_tokens > 1 ? layer - P.layer_begin : 0;

@@ -270,3 +270,137 @@ __device__ __forceinline__ void router_select_cta(float l0, float l1, int E, int
 }
 
 }  // namespace wd
+
+namespace wd {
+
+// ---------------------------------------------------------------------------------------------
+// Expert ids from a threshold on the LOGITS, proven afterwards against the probabilities.
+//
+// The rungs of the reference pick by probability (larger first, ties to the lower index). Probabilities are a
+// non-decreasing function of the logits, so the k largest logits are the k rungs unless probabilities tie or fall
+// out of order at the last bit, a sum degenerates, or non-finite values are involved. The ids therefore come from
+// the logits at once (the tile copies can start), and while the tiles are in flight the softmax and a proof run:
+// nothing outside the picked set may beat its weakest member by PROBABILITY, and inside it the probabilities must
+// fall in exactly the picked order, every one an ordinary number. A row that fails the proof (or has more than 32
+// candidates above the threshold, or fewer than k groups with a finite logit) takes the exact rungs.
+//
+// Stages, with one __syncthreads by the caller after each of the first three:
+//   a  16 group maxima of the order keys
+//   b  threshold = k-th best group maximum (at least k experts reach it); candidates above it into a list
+//   c  warp 0 ranks the candidates: sel_ids / sel_keys in rank order, a bit mask of the picked
+//   proof (router_threshold_proof): softmax with the known maximum, the test above, the weights
+// Thread t owns experts t and t + kThreads (E <= 1024), as in router_select_cta.
+// ---------------------------------------------------------------------------------------------
+struct ThresholdScratch {
+    uint32_t *gm;        // [16]
+    int *cnt;            // [1]
+    uint2 *cand;         // [64] (key, expert)
+    uint32_t *sel_keys;  // [kMaxK]
+    uint32_t *selmask;   // [kMaxExperts / 32]
+};
+constexpr int kThresholdMaxCand = 64;
+
+__device__ __forceinline__ void router_threshold_stage_a(uint32_t key0, uint32_t key1, int E, const ThresholdScratch &T) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t m = max(key0, key1);
+    if (E >= kThreads) {
+        m = __reduce_max_sync(0xffffffffu, m);
+        if (lane == 0) T.gm[warp] = m;
+    } else {
+        int group = 1;                          // lanes per group: the power of two that lets 16 groups cover E experts
+        while (16 * group < E) group <<= 1;
+#pragma unroll 1
+        for (int s = 1; s < group; s <<= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, s));
+        if (tid < 16 * group) {
+            if ((tid % group) == 0) T.gm[tid / group] = tid < E ? m : 0u;
+        }
+    }
+    if (tid == 0) *T.cnt = 0;
+    if (tid < kMaxExperts / 32) T.selmask[tid] = 0u;
+}
+
+// Returns true when the row must take the exact rungs already (fewer than K groups hold a selectable logit).
+__device__ __forceinline__ bool router_threshold_stage_b(uint32_t key0, uint32_t key1, bool h0, bool h1, int K,
+                                                         const ThresholdScratch &T) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    const uint32_t mine = T.gm[lane & 15];
+    int rank = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const uint32_t o = T.gm[j];
+        rank += (o > mine) || (o == mine && j < (lane & 15));
+    }
+    const uint32_t thr = T.gm[__ffs(__ballot_sync(0xffffffffu, lane < 16 && rank == K - 1)) - 1];
+    const bool c0 = h0 && key0 >= thr, c1 = h1 && key1 >= thr;
+    const unsigned b0 = __ballot_sync(0xffffffffu, c0), b1 = __ballot_sync(0xffffffffu, c1);
+    int base = 0;
+    if (lane == 0 && (b0 | b1)) base = atom_add_shared(T.cnt, __popc(b0) + __popc(b1));
+    base = __shfl_sync(0xffffffffu, base, 0);
+    const unsigned lt = (1u << lane) - 1u;
+    if (c0) {
+        const int pos = base + __popc(b0 & lt);
+        if (pos < kThresholdMaxCand) T.cand[pos] = make_uint2(key0, static_cast<uint32_t>(tid));
+    }
+    if (c1) {
+        const int pos = base + __popc(b0) + __popc(b1 & lt);
+        if (pos < kThresholdMaxCand) T.cand[pos] = make_uint2(key1, static_cast<uint32_t>(tid + kThreads));
+    }
+    return thr <= kKeyNegInf;
+}
+
+// Warp 0 only, when the candidate count is in [K, 32]: ranks by (larger key, then lower index), a total order.
+__device__ __forceinline__ void router_threshold_rank_warp(int nc, int K, const ThresholdScratch &T, int *sel_ids, int lane) {
+    const uint2 me = lane < nc ? T.cand[lane] : make_uint2(0u, 0xffffffffu);
+    int rank = 0;
+#pragma unroll 8
+    for (int j = 0; j < nc; ++j) {          // the loads do not depend on one another
+        const uint2 o = T.cand[j];
+        rank += (o.x > me.x) || (o.x == me.x && o.y < me.y);
+    }
+    if (lane < nc && rank < K) {
+        sel_ids[rank] = static_cast<int>(me.y);
+        T.sel_keys[rank] = me.x;
+        red_or_shared(&T.selmask[me.y >> 5], 1u << (me.y & 31u));
+    }
+    __syncwarp();
+}
+
+__device__ __noinline__ float exp_ggml_call(float x) { return exp_ggml(x); }
+
+// The proof (all threads; one __syncthreads inside the softmax and one vote). `slow`: the row already failed an
+// earlier stage. Returns true when sel_ids are the reference's rungs; sel_w then holds their weights. p0 / p1: this
+// thread's probabilities, for router_rungs_cta when the proof fails.
+__device__ __forceinline__ bool router_threshold_proof(float l0, float l1, bool h0, bool h1, int E, int K, float w_scale,
+                                                       bool slow, const ThresholdScratch &T, const RouterScratch &S,
+                                                       const int *sel_ids, float *sel_w, float &p0, float &p1) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t mk = __reduce_max_sync(0xffffffffu, lane < 16 ? T.gm[lane] : 0u);     // row maximum = best group maximum
+    const float mx = __uint_as_float((mk & 0x80000000u) ? (mk ^ 0x80000000u) : ~mk);
+    float inv = 0.0f;
+    router_softmax_given_max(l0, l1, mx, E, S, p0, p1, nullptr, &inv);
+    bool bad = slow;
+    if (!slow) {
+        // every thread forms the weakest member's probability itself, with the operations its owner used
+        const float pb = __fmul_rn(exp_ggml_call(__fsub_rn(key_to_float(T.sel_keys[K - 1]), mx)), inv);
+        const int eb = sel_ids[K - 1];
+        const bool s0 = h0 && ((T.selmask[tid >> 5] >> (tid & 31)) & 1u);
+        const bool s1 = h1 && ((T.selmask[(tid + kThreads) >> 5] >> (tid & 31)) & 1u);
+        bad = (h0 && !s0 && (p0 > pb || (p0 == pb && tid < eb))) || (h1 && !s1 && (p1 > pb || (p1 == pb && tid + kThreads < eb)));
+        bad = bad || !(inv > 0.0f && inv < INFINITY);
+        if (warp == 0) {
+            const float pj = lane < K ? __fmul_rn(exp_ggml_call(__fsub_rn(key_to_float(T.sel_keys[lane]), mx)), inv) : 0.0f;
+            const int ej = lane < K ? sel_ids[lane] : 0x7fffffff;
+            const float pn = __shfl_down_sync(0xffffffffu, pj, 1);
+            const int en = __shfl_down_sync(0xffffffffu, ej, 1);
+            const bool fine = lane >= K || (pj == pj && pj > -INFINITY && (lane == K - 1 || pj > pn || (pj == pn && ej < en)));
+            // the vote first, on its own: `bad || !vote` would let the lanes whose `bad` is already set skip it
+            const bool all_fine = __all_sync(0xffffffffu, fine);
+            bad = bad || !all_fine;
+            const float w = router_weights_warp(pj, K, w_scale, lane);
+            if (lane < K) sel_w[lane] = w;
+        }
+    }
+    return !__syncthreads_or(bad);
+}
+
+}  // namespace wd
