@@ -156,6 +156,9 @@ int wd_set_profiling(wd_engine *e, int on);
 int wd_sm_count(const wd_engine *e);
 /* Name of the kernel a stack step of this engine launches (for bench records). */
 const char *wd_kernel_name(const wd_engine *e);
+/* Name of the kernel a token batch (wd_moe_forward with n_tokens > 1) runs on: the batch kernel when the engine has
+ * every expert resident on one GPU and the geometry fits it, else the kernel above walking the tokens. */
+const char *wd_batch_kernel_name(const wd_engine *e);
 /* Device error word of the last forward (0 = none) and a reset of the barrier state. */
 int wd_device_status(wd_engine *e, int *status);
 

@@ -51,16 +51,20 @@ def test_max_tokens_out_of_range_is_refused(wd):
         wd.Engine(H, F, E, K, SF, 1, max_tokens=5)
 
 
-def test_batch_of_four_at_the_model_shape(wd, oracle):
+@pytest.mark.parametrize("batch_kernel", [True, False])
+def test_batch_of_four_at_the_model_shape(wd, oracle, batch_kernel, monkeypatch):
     """Four tokens x ten experts = forty (token, slot) pairs at the 48-layer model's block shape (hidden 2048, 512
     experts, top-10), weights generated on the device. Token 3 repeats token 0, so ten of the pairs share their
-    experts. One call (one launch of the layer kernel) must give, for every token, the oracle's ids, weights and
-    output bit for bit, and the same bits as four single-token calls. The pair map follows the reference's batch
-    verify (p = t * k + j; tests/moe_batch_verify_host_test.cpp:137-186): swapping two tokens' activations must
-    change the result (negative control)."""
+    experts. One call (one launch: of the batch kernel, or with WD_BATCH_KERNEL=0 of the layer kernel walking the
+    tokens) must give, for every token, the oracle's ids, weights and output bit for bit, and the same bits as four
+    single-token calls. The pair map follows the reference's batch verify (p = t * k + j;
+    tests/moe_batch_verify_host_test.cpp:137-186): swapping two tokens' activations must change the result (negative
+    control). Batches of two and three tokens must agree with the same single-token results."""
     Hh, Fh, Eh, Kh, SFh = 2048, 512, 512, 10, 512
+    monkeypatch.setenv("WD_BATCH_KERNEL", "1" if batch_kernel else "0")
     eng = wd.Engine(Hh, Fh, Eh, Kh, SFh, 1, max_tokens=4)
     assert eng.kernel_name() == "moe_layer_kernel"
+    assert eng.batch_kernel_name() == ("moe_batch_kernel" if batch_kernel else "moe_layer_kernel")
     eng.synth_model(31, 0.02, 1.0)
     dense = eng.synth_dense_host(31, 0.02, 1.0, 0)
     gb = Fh * (Hh // 256) * 110
@@ -86,4 +90,9 @@ def test_batch_of_four_at_the_model_shape(wd, oracle):
     assert np.array_equal(ids[0], ids[3]) and not np.array_equal(ids[0], ids[1])
     swapped = eng.forward_host(0, x[[1, 0, 2, 3]])
     assert np.array_equal(bits(swapped[0]), bits(out[1])) and not np.array_equal(bits(swapped[0]), bits(out[0]))
+    for n in (2, 3):
+        part = eng.forward_host(0, x[:n]).reshape(n, Hh)
+        assert np.array_equal(bits(part), bits(out[:n])), n
+        assert np.array_equal(eng.tap("ids", n - 1), ids[n - 1])
+    assert eng.device_status() == 0
     eng.close()

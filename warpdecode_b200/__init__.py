@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 LIB_PATH = os.path.join(HERE, "libwarpdecode_b200.so")
 SOURCES = [os.path.join(HERE, "csrc", f) for f in
-           ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_moe_kernel_phases.inc", "wd_moe_fast.cuh",
+           ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_moe_kernel_phases.inc", "wd_moe_fast.cuh", "wd_moe_batch.cuh",
             "wd_blocks.cuh", "wd_router.cuh",
             "wd_formats.cuh", "wd_device.cuh", "wd_dense.cuh", "wd_gguf.inc",
             "wd_grids.h")] + [os.path.join(ROOT, "include", "warpdecode_b200.h")]
@@ -98,6 +98,8 @@ def lib():
         L.wd_synth_tensor_device.argtypes = [i, i, i, C.c_float, C.c_uint64, C.c_uint64, vp, vp]
         L.wd_kernel_name.argtypes = [vp]
         L.wd_kernel_name.restype = C.c_char_p
+        L.wd_batch_kernel_name.argtypes = [vp]
+        L.wd_batch_kernel_name.restype = C.c_char_p
         L.wd_synth_expert_host.argtypes = [vp, C.c_uint64, C.c_float, i, i, vp, vp, vp]
         L.wd_synth_dense_host.argtypes = [vp, C.c_uint64, C.c_float, C.c_float, i, vp, vp, vp, vp, vp, vp]
         L.wd_ep_export.argtypes = [vp, vp]
@@ -314,6 +316,10 @@ class Engine:
     def kernel_name(self):
         """Name of the kernel that this engine's stack step launches."""
         return lib().wd_kernel_name(self.h).decode()
+
+    def batch_kernel_name(self):
+        """Name of the kernel a token batch (forward with several tokens) runs on."""
+        return lib().wd_batch_kernel_name(self.h).decode()
 
     def set_profiling(self, on):
         _check(lib().wd_set_profiling(self.h, int(on)))

@@ -22,10 +22,11 @@ constexpr int kMaxExperts = 1024;
 // ---------------------------------------------------------------------------------------------
 // Q8_0 of n floats (n multiple of 128) held in shared `xf`; output: quants in task layout
 // [g][l][16 B] (word i = values 4l..4l+3 of block 4g+i) and per-block scales as the f16-rounded float.
-__device__ __forceinline__ void quantize_q8_0_cta(const float *xf, int n, uint8_t *q_out, float *d_out) {
+// by `nthreads` threads (a multiple of 32, whole warps) of which this one is number `thread`
+__device__ __forceinline__ void quantize_q8_0_part(const float *xf, int n, uint8_t *q_out, float *d_out, int thread, int nthreads) {
     const int nchunks = n >> 2;    // groups of four values; 8 chunks form a block
 #pragma unroll 1
-    for (int ch = threadIdx.x; ch < ((nchunks + 31) & ~31); ch += blockDim.x) {
+    for (int ch = thread; ch < ((nchunks + 31) & ~31); ch += nthreads) {
         const bool live = ch < nchunks;
         float4 v = live ? *reinterpret_cast<const float4 *>(xf + 4 * ch) : make_float4(0, 0, 0, 0);
         float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
@@ -49,6 +50,9 @@ __device__ __forceinline__ void quantize_q8_0_cta(const float *xf, int n, uint8_
         *reinterpret_cast<uint32_t *>(q_out + (((b >> 2) * 8 + l) * 16 + (b & 3) * 4)) = packed;
         if (l == 0) d_out[b] = __half2float(dh);
     }
+}
+__device__ __forceinline__ void quantize_q8_0_cta(const float *xf, int n, uint8_t *q_out, float *d_out) {
+    quantize_q8_0_part(xf, n, q_out, d_out, threadIdx.x, blockDim.x);
 }
 
 // Q8_K of one 256-value superblock by one warp: lane quantises src[8*lane .. 8*lane+7].
@@ -192,11 +196,12 @@ __device__ __forceinline__ void iq_tile_rows(const int partial[8], float scale, 
 // sums into rows_out. `a` / `dx` are this lane's superblock of activations and its scale. The single
 // shared copy of the decoder: gate tiles, up tiles and down tiles all come through here.
 // partial_dump (optional, global): receives this lane's eight integer partials.
+template <int UNROLL = 1>
 __device__ __noinline__ void iq3_tile_to_rows(const uint8_t *tile, const uint8_t *a, float dx, int nsb, int lane,
                                               uint32_t lane4x2, const uint8_t *tab, float *scr, float *rows_out,
                                               int *partial_dump) {
     int p[8];
-    iq3_block_partials(tile, lane, a, lane4x2, tab, p);
+    iq3_block_partials<UNROLL>(tile, lane, a, lane4x2, tab, p);
     if (partial_dump) {
 #pragma unroll
         for (int c = 0; c < 8; ++c) partial_dump[c] = p[c];
@@ -219,11 +224,12 @@ __device__ __noinline__ void iq2_tile_to_rows(const uint8_t *tile, const uint8_t
 }
 
 // Either type (a warp-uniform branch). tab3: lane-private IQ3_S table, tab2: IQ2_S table.
+template <int UNROLL = 1>
 __device__ __forceinline__ void iq_tile_to_rows_any(int type, const uint8_t *tile, const uint8_t *a, float dx, int nsb,
                                                     int lane, uint32_t lane4x2, const uint8_t *tab3, const uint8_t *tab2,
                                                     float *scr, float *rows_out, int *partial_dump) {
     if (type == kTypeIq2s) iq2_tile_to_rows(tile, a, dx, nsb, lane, tab2, scr, rows_out, partial_dump);
-    else iq3_tile_to_rows(tile, a, dx, nsb, lane, lane4x2, tab3, scr, rows_out, partial_dump);
+    else iq3_tile_to_rows<UNROLL>(tile, a, dx, nsb, lane, lane4x2, tab3, scr, rows_out, partial_dump);
 }
 
 }  // namespace wd

@@ -106,6 +106,18 @@ __device__ __forceinline__ int atom_add_shared(int *p, int v) {
     return old;
 }
 
+// with acquire-release ordering at CTA scope: what the thread wrote before is visible to whoever reads the new count
+__device__ __forceinline__ int atom_add_shared_acq_rel(int *p, int v) {
+    int old;
+    asm volatile("atom.acq_rel.cta.shared.add.s32 %0, [%1], %2;" : "=r"(old) : "r"(smem_u32(p)), "r"(v) : "memory");
+    return old;
+}
+__device__ __forceinline__ int atom_cas_shared(int *p, int expect, int v) {
+    int old;
+    asm volatile("atom.shared.cas.b32 %0, [%1], %2, %3;" : "=r"(old) : "r"(smem_u32(p)), "r"(expect), "r"(v) : "memory");
+    return old;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Tagged words: a float and the tag of the layer that produced it, published with ONE 8-byte store.
 // A consumer polls the word itself until the tag matches, so no fence and no separate flag is needed

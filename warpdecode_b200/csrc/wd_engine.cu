@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "wd_aux_kernels.cuh"
+#include "wd_moe_batch.cuh"
 #include "wd_dense.cuh"
 #include "wd_grids.h"
 
@@ -195,6 +196,12 @@ struct wd_engine {
     const void *fast_fn = nullptr;
     wd::FastParams fbase{};
     size_t fast_smem = 0;
+    // the batch kernel (wd_moe_batch.cuh): token batches of a resident single-GPU engine in one pass
+    bool batch_ok = false;
+    bool last_batch = false;                // the last forward call ran on the batch kernel (it keeps fewer taps)
+    wd::BatchParams bbase{};
+    size_t batch_smem = 0;
+    wd::tagged_t *btagged = nullptr;        // its exchange words
     float *eo_plain = nullptr, *shdown_plain = nullptr;     // inspection copies the fast kernel writes
     wd::tagged_t *xbuf = nullptr;                           // the compiled kernel's per-CTA mailboxes
     size_t xbuf_words = 0;
@@ -341,6 +348,95 @@ int plan_shared_memory(wd_engine *e) {
     return WD_OK;
 }
 
+// Shared-memory plan of the batch kernel for up to cfg.max_tokens tokens. Leaves e->batch_ok false (and the batch on
+// the single-token kernel's token loop) when the geometry does not fit.
+void plan_batch(wd_engine *e) {
+    const wd_config &c = e->cfg;
+    const wd::MoeParams &m = e->base;
+    wd::BatchParams &p = e->bbase;
+    e->batch_ok = false;
+    const int ncta = e->n_sm, Tm = c.max_tokens, H = c.hidden, F = c.expert_ffn, SF = c.shared_ffn, E = c.n_experts, K = c.top_k;
+    if (Tm < 2 || !e->resident || c.ep_size > 1 || E > wd::kMaxExperts || SF > 2 * wd::kThreads || Tm * K > 64) return;
+    if (const char *v = std::getenv("WD_BATCH_KERNEL")) if (std::atoi(v) == 0) return;
+    const int nbh = H / 32, nbs = SF / 32;
+    p.H = H; p.F = F; p.SF = SF; p.E = E; p.K = K; p.T = Tm;
+    p.nsb_h = m.nsb_h; p.nsb_f = m.nsb_f; p.t2_log2 = m.t2_log2; p.t3_log2 = m.t3_log2;
+    p.w_scale = m.w_scale;
+    p.pool = m.pool; p.slot_bytes = m.slot_bytes; p.gate_off = m.gate_off; p.up_off = m.up_off; p.down_off = m.down_off;
+    p.grid_packed = m.grid_packed; p.grid2_packed = m.grid2_packed;
+    p.gu_type = m.gu_type; p.d_type = m.d_type; p.gu_tile = m.gu_tile; p.d_tile = m.d_tile;
+    p.sync = m.sync; p.host_status = m.host_status;
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off = align_up(off + bytes, 128);
+        return static_cast<unsigned>(o);
+    };
+    const bool any3 = c.gate_type == WD_TYPE_IQ3_S || c.down_type == WD_TYPE_IQ3_S;
+    const bool any2 = c.gate_type == WD_TYPE_IQ2_S || c.down_type == WD_TYPE_IQ2_S;
+    p.off_tab = take(any3 ? wd::kGridTableBytes : 128);
+    p.off_tab2 = take(any2 ? wd::kIq2TableBytes : 128);
+    {   // one token's region
+        size_t t = 0;
+        auto sub = [&](size_t bytes) { const size_t o = t; t = align_up(t + bytes, 16); return static_cast<unsigned>(o); };
+        sub(std::max(H, SF * 4));                            // Q8_0 quants of x (offset 0); later the shared activation as floats
+        p.tok_xd0 = sub(static_cast<size_t>(nbh) * 4);
+        p.tok_xk = sub(static_cast<size_t>(m.nsb_h) * wd::kActSbStride);
+        p.tok_xdk = sub(static_cast<size_t>(m.nsb_h) * 4);
+        p.tok_shq = sub(std::max(SF, 16));
+        p.tok_shd = sub(static_cast<size_t>(std::max(nbs, 4)) * 4);
+        p.tok_sel = sub(wd::kMaxK * 8);
+        p.tok_stride = static_cast<unsigned>(align_up(t, 128));
+    }
+    p.off_tok = take(static_cast<size_t>(p.tok_stride) * Tm);
+    p.off_misc = take(4 * static_cast<size_t>(wd::kMiscSharedAct + std::max(SF, 32)));
+    const int r_h = 32 / m.nsb_h, r_f = 32 / m.nsb_f;
+    const int scr_floats = std::max(r_h * (m.nsb_h * 8 + 8) + 32, r_f * (m.nsb_f * 8 + 8) + 32);
+    p.scr_rows = static_cast<unsigned>(scr_floats);
+    p.scr_bytes = static_cast<unsigned>(align_up((scr_floats + 64) * 4, 128));
+    p.off_scr = take(static_cast<size_t>(p.scr_bytes) * wd::kWarps);
+    p.off_bar = take(wd::kBatchMaxBars * 8);
+    p.off_slots = take(static_cast<size_t>(E) * 4);
+    p.off_pairs = take(64 * 4);
+    p.off_seq = take(wd::kBatchMaxRing * 4);
+    p.off_seg = take(96 * 4 + static_cast<size_t>(wd::kMaxTokens) * K * m.nsb_f * 4);     // segments, pair counters, activation states
+    {
+        const int t2 = F / r_h, t3d = H / r_f;
+        if (t2 > 4096 || t3d > 4096) return;
+        p.max_tasks = static_cast<unsigned>(Tm * (2 * ((K * t2 + ncta - 1) / ncta) + (K * t3d + ncta - 1) / ncta + 1));
+        p.off_tasks = take(static_cast<size_t>(p.max_tasks) * 16);
+    }
+    p.off_pairbuf = take(static_cast<size_t>(32) * 2 * r_h * 4);
+    const int t3 = H / r_f;                                  // down tiles per pair
+    const int max3 = (K * t3 + ncta - 1) / ncta;             // longest run of one token's down tiles in one CTA
+    const int n_exp_tok = std::min(K, (max3 - 1) / t3 + 2);  // pairs such a run can touch
+    p.n_act = static_cast<unsigned>(wd::kMaxTokens * n_exp_tok * m.nsb_f);
+    if (p.n_act > 62) return;
+    p.off_actk = take(static_cast<size_t>(p.n_act) * wd::kActSbStride);
+    p.off_actd = take(static_cast<size_t>(p.n_act) * 4);
+    const int n_rt = E / 4, n_st = SF / 4, n_sd = SF > 0 ? H / 4 : 0;
+    p.n1r = (n_rt + ncta - 1) / ncta;
+    p.n1s = (n_st + ncta - 1) / ncta;
+    p.nsd = (n_sd + ncta - 1) / ncta;
+    p.off_sd = take(static_cast<size_t>(p.nsd) * nbs * 136);
+    p.off_ring = take(0);
+    p.ring_slot = static_cast<unsigned>(align_up(std::max(p.gu_tile, p.d_tile), 16));
+    const size_t limit = 227 * 1024;
+    if (off >= limit) return;
+    const size_t front = static_cast<size_t>(p.n1r + p.n1s) * 2 * nbh * 136 + static_cast<size_t>(H) * 4 * (1 + Tm);
+    const int bars_fixed = static_cast<int>(p.n1r + p.n1s + 3 + p.nsd + wd::kMaxTokens + p.n_act);
+    int ring = static_cast<int>((limit - off) / p.ring_slot);
+    ring = std::min(ring, std::min(wd::kBatchMaxRing, wd::kBatchMaxBars - bars_fixed));
+    if (const char *v = std::getenv("WD_BATCH_RING")) ring = std::min(ring, std::max(1, std::atoi(v)));
+    // sixteen slots are being read at any time; the rest is how far ahead the copies run
+    if (ring < wd::kWarps + 4 || static_cast<size_t>(ring) * p.ring_slot < front) return;
+    const int rpc = (H + ncta - 1) / ncta;
+    if (rpc * Tm > wd::kThreads) return;
+    p.ring = static_cast<unsigned>(ring);
+    e->batch_smem = off + static_cast<size_t>(ring) * p.ring_slot;
+    e->batch_ok = true;
+}
+
 // ggml Q8_0 blocks -> the layout of the engine's layer kernel (4-row tasks, or single rows for the compiled kernel)
 void launch_repack_q8(const wd_engine *e, const uint8_t *src, uint8_t *dst, int rows, int nb, cudaStream_t s) {
     const long long n = static_cast<long long>(rows) * nb;
@@ -465,11 +561,41 @@ int launch_layers(wd_engine *e, int begin, int end, const float *x, float *resid
     e->epoch += static_cast<uint32_t>(n_tokens > 1 && !e->fast_fn ? n_tokens : end - begin);
     e->last_parity = static_cast<int>(e->epoch & 1u);   // the last layer's tag is the new epoch; halves follow the tag
     e->last_tokens = 1;
+    e->last_batch = false;
     return WD_OK;
 }
 
 int launch_layer(wd_engine *e, int layer, const float *x, float *residual, float *out, cudaStream_t s) {
     return launch_layers(e, layer, layer + 1, x, residual, out, s);
+}
+
+// A batch of n_tokens activations through one layer on the batch kernel (one cooperative launch).
+int launch_batch(wd_engine *e, int layer, const float *x, float *out, int n_tokens, cudaStream_t s) {
+    const Layer &L = e->layers[layer];
+    if (!L.have_router || !L.have_experts || (e->cfg.shared_ffn > 0 && !L.have_shared))
+        return fail(WD_E_STATE, "layer " + std::to_string(layer) + " has no weights yet");
+    int rc = sync_layer_table(e, s);
+    if (rc) return rc;
+    wd::BatchParams p = e->bbase;
+    p.layers = e->layer_table;
+    p.layer = layer;
+    p.T = n_tokens;
+    p.threshold_select = e->threshold_select ? 1 : 0;
+    p.fallbacks = e->fallbacks;
+    p.x = x;
+    p.out = out;
+    p.ids = e->tok_ids;
+    p.weights = e->tok_weights;
+    p.routed = e->routed;
+    p.stamps = e->profiling ? e->stamps : nullptr;
+    void *args[] = {&p};
+    WD_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<void *>(wd::moe_batch_kernel), dim3(e->n_sm), dim3(wd::kThreads), args,
+                                        e->batch_smem, s));
+    e->epoch += 1u;         // the whole batch carries one tag
+    e->last_parity = static_cast<int>(e->epoch & 1u);
+    e->last_tokens = n_tokens;
+    e->last_batch = true;
+    return WD_OK;
 }
 
 // Capped cache: one layer = a selection pass, the host's slot bookkeeping with the misses streamed in on
@@ -876,6 +1002,29 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
         }
         rc = WD_OK;
     }
+    if (!e->fast_fn) plan_batch(e);
+    if (e->batch_ok) {
+        wd::BatchParams &b = e->bbase;
+        const size_t Tm = static_cast<size_t>(c.max_tokens);
+        auto up16 = [](size_t w) { return (w + 15) / 16 * 16; };
+        const size_t w_logits = 0, w_shact = up16(w_logits + Tm * E), w_shgate = up16(w_shact + Tm * std::max(c.shared_ffn, 1)),
+                     w_act = w_shgate + 16, w_eo = up16(w_act + Tm * K * F), w_shdown = up16(w_eo + Tm * K * H),
+                     w_sel = up16(w_shdown + Tm * H), w_end = up16(w_sel + Tm * 2 * wd::kMaxK);
+        cudaError_t be = cudaMalloc(&e->btagged, w_end * sizeof(wd::tagged_t));
+        if (be == cudaSuccess) be = cudaMemset(e->btagged, 0, w_end * sizeof(wd::tagged_t));
+        if (be == cudaSuccess)
+            be = cudaFuncSetAttribute(wd::moe_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(e->batch_smem));
+        int bocc = 0;
+        if (be == cudaSuccess) be = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&bocc, wd::moe_batch_kernel, wd::kThreads, e->batch_smem);
+        if (be != cudaSuccess) {
+            fail(WD_E_CUDA, std::string("setting up the batch kernel: ") + cudaGetErrorString(be));
+            return bail(WD_E_CUDA);
+        }
+        if (bocc < 1) e->batch_ok = false;
+        b.t_logits = e->btagged + w_logits; b.t_shact = e->btagged + w_shact; b.t_shgate = e->btagged + w_shgate;
+        b.t_act = e->btagged + w_act; b.t_eo = e->btagged + w_eo; b.t_shdown = e->btagged + w_shdown;
+        b.t_sel = e->btagged + w_sel;
+    }
     *out = e;
     return WD_OK;
 }
@@ -891,7 +1040,7 @@ void wd_engine_destroy(wd_engine *e) {
         if (L.owned_host) cudaFreeHost(L.owned_host);
     }
     void *bufs[] = {e->pool, e->grid_packed, e->grid2_packed, e->synth_lut, e->sync, e->tagged, e->ids, e->weights, e->routed, e->tok_ids, e->tok_weights,
-                    e->x_buf, e->out_buf, e->residual_buf, e->staging, e->stamps, e->layer_table, e->eo_plain, e->shdown_plain, e->fallbacks, e->xbuf};
+                    e->x_buf, e->out_buf, e->residual_buf, e->staging, e->stamps, e->layer_table, e->eo_plain, e->shdown_plain, e->fallbacks, e->xbuf, e->btagged};
     for (void *b : bufs) cudaFree(b);
     delete e->copy_pool;
     cudaFree(e->miss_staging);
@@ -1187,6 +1336,8 @@ int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, 
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
     const int H = e->cfg.hidden, K = e->cfg.top_k;
+    if (e->batch_ok && n_tokens > 1 && e->n_peers == 0 && reinterpret_cast<uintptr_t>(x_dev) % 16 == 0)
+        return launch_batch(e, layer, x_dev, out_dev, n_tokens, s);
     if (e->resident && !e->fast_fn && n_tokens > 1) {
         rc = launch_layers(e, layer, layer + 1, x_dev, nullptr, out_dev, s, false, n_tokens);
         if (rc) return rc;
@@ -1288,8 +1439,12 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
     if (!e || !dst) return fail(WD_E_INVALID, "null argument");
     if (token == -1) token = e->last_tokens - 1;     // the last token of the last call
     if (token < 0 || token >= e->last_tokens) return fail(WD_E_INVALID, "token out of range");
-    if (token != e->last_tokens - 1 && tap != WD_TAP_IDS && tap != WD_TAP_WEIGHTS)
+    const bool per_launch = tap == WD_TAP_STAMPS || tap == WD_TAP_FALLBACKS;     // not tied to a token
+    if (token != e->last_tokens - 1 && tap != WD_TAP_IDS && tap != WD_TAP_WEIGHTS && !per_launch)
         return fail(WD_E_STATE, "only the ids and weights of earlier tokens of a batch are kept; other taps show its last token");
+    if (e->last_batch && tap != WD_TAP_IDS && tap != WD_TAP_WEIGHTS && tap != WD_TAP_ROUTED && !per_launch)
+        return fail(WD_E_STATE, "a token batch keeps the ids and weights of every token and the routed sum of the last one; "
+                                "the other taps need a single-token call");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     const wd_config &c = e->cfg;
     const wd::MoeParams &p = e->base;
@@ -1361,6 +1516,7 @@ int wd_set_profiling(wd_engine *e, int on) {
 
 int wd_sm_count(const wd_engine *e) { return e ? e->n_sm : 0; }
 const char *wd_kernel_name(const wd_engine *e) { return e && e->fast_fn ? "moe_fast_kernel" : "moe_layer_kernel"; }
+const char *wd_batch_kernel_name(const wd_engine *e) { return e && e->batch_ok ? "moe_batch_kernel" : wd_kernel_name(e); }
 
 // ---- expert parallelism ----------------------------------------------------------------------------
 int wd_ep_handle_bytes(void) { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }

@@ -130,6 +130,9 @@ __device__ __forceinline__ void iq3_subblock(const uint8_t *tile, const Iq3Head 
 }
 
 // Sub-blocks [i0, i1) of one block against the 256 int8 activations at `a` (shared memory, 16-byte aligned).
+// UNROLL: sub-blocks decoded per loop iteration. 1 keeps the code small (the single-token kernel runs every instruction
+// only a few times per layer and is sensitive to instruction fetch); 8 lets the loads of all sub-blocks run ahead.
+template <int UNROLL = 1>
 __device__ __forceinline__ void iq3_block_partials_range(const uint8_t *tile, int lane, const uint8_t *a,
                                                          uint32_t lane4x2, const uint8_t *tab, int partial[8], int i0,
                                                          int i1) {
@@ -138,7 +141,7 @@ __device__ __forceinline__ void iq3_block_partials_range(const uint8_t *tile, in
 #pragma unroll
     for (int c = 0; c < 8; ++c) partial[c] = 0;
     const uint4 *av = reinterpret_cast<const uint4 *>(a);
-#pragma unroll 1
+#pragma unroll(UNROLL)
     for (int i = i0; i < i1; ++i) iq3_subblock(tile, h, i, lane, av[2 * i], av[2 * i + 1], lane4x2, tab, partial);
 }
 
@@ -183,9 +186,10 @@ __device__ __forceinline__ void iq2_block_partials_range(const uint8_t *tile, in
 }
 
 // Full block.
+template <int UNROLL = 1>
 __device__ __forceinline__ void iq3_block_partials(const uint8_t *tile, int lane, const uint8_t *a, uint32_t lane4x2,
                                                    const uint8_t *tab, int partial[8]) {
-    iq3_block_partials_range(tile, lane, a, lane4x2, tab, partial, 0, 8);
+    iq3_block_partials_range<UNROLL>(tile, lane, a, lane4x2, tab, partial, 0, 8);
 }
 
 }  // namespace wd
