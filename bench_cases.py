@@ -5,6 +5,12 @@ were captured from (ncu wants a short program with few launches), and the kernel
         a few forward calls of the MoE layer kernel at the 48-layer model's block shape, direct launches, about
         0.7 GB per layer on the device; --stamps prints the kernel's per-phase timestamps (mean over CTAs)
         instead (generic kernel), which needs no profiler; --compiled runs the kernel compiled for the geometry
+    python bench_cases.py batch [--layers 2] [--tokens 4] [--iters 4] [--stamps]
+        token batches (speculative verify) through the per-layer forward on the batch kernel; --stamps prints the
+        kernel's own step times (median over CTAs)
+    python bench_cases.py decoder
+        the IQ3_S tile decoder alone, tiles resident in shared memory: cycles per round of tiles for 16, 8, 4 and 1
+        active warps per SM (the issue bound of the expert GEMVs)
     python bench_cases.py dense [--rows 128256] [--cols 2048] [--mats 2] [--iters 20]
         streams Q4_0 matrices of the plain decoder's output-head size through the dense matvec kernel
     python bench_cases.py head [--rows 151936] [--cols 2048] [--iters 20]
@@ -87,6 +93,60 @@ def profile_case(a):
 
 
 # ---- dense: Q4_0 matvec and the Q8_0 head ---------------------------------------------------------------------------
+
+
+# ---- batch: the batch kernel ---------------------------------------------------------------------------------------
+BATCH_STEPS = [(1, "copies_issued_tables"), (2, "activations_quantised"), (3, "row_tasks"), (4, "block_sync"),
+               (5, "picks_gathered"), (6, "first_tiles_issued"), (9, "tile_tasks"), (10, "shared_down"), (11, "combine"),
+               (12, "end")]
+
+
+def batch_case(a):
+    import torch
+    H = 2048
+    eng = wd.Engine(H, 512, 512, 10, 512, a.layers, max_tokens=4)
+    print("kernel:", eng.batch_kernel_name())
+    eng.synth_model(3, 0.02, 1.0)
+    x = torch.randn(4, H, generator=torch.Generator().manual_seed(2), dtype=torch.float32).cuda()
+    out = torch.zeros_like(x)
+    ts = torch.cuda.Stream()
+    sp = ts.cuda_stream
+    if a.stamps:
+        eng.set_profiling(True)
+    with torch.cuda.stream(ts):
+        for _ in range(2):
+            for l in range(a.layers):
+                eng.forward_device(l, x.data_ptr(), out.data_ptr(), sp, a.tokens)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(ts):
+        e0.record(ts)
+        for _ in range(a.iters):
+            for l in range(a.layers):
+                eng.forward_device(l, x.data_ptr(), out.data_ptr(), sp, a.tokens)
+        e1.record(ts)
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (a.iters * a.layers)
+    print("%d tokens per call: %.2f us per call, %.2f us per token and layer, status %d" % (a.tokens, us, us / a.tokens, eng.device_status()))
+    if a.stamps:
+        st = eng.stamps().astype(np.int64)
+        mhz = 1965.0          # the stamps are SM clock cycles; the bench box runs the SMs at their maximum under this load
+        prev = 0
+        for idx, name in BATCH_STEPS:
+            d = np.median(st[:, idx] - st[:, 0]) / mhz
+            print("  %-24s ends at %6.2f us (+%.2f)" % (name, d, d - prev))
+            prev = d
+    eng.close()
+
+
+def decoder_case(a):
+    mhz = 1965.0
+    for unroll in (1, 8):
+        for nsb in (8, 2):
+            for warps in (16, 8, 4, 1):
+                c = wd.measure_tile_decoder(nsb, warps, unroll)
+                print("unroll %d, %d superblocks per row, %2d warps: %6.0f cycles per round, %5.1f cycles per tile and SM, "
+                      "%.2f us per 16 tiles at %.0f MHz" % (unroll, nsb, warps, c, c / warps, c / warps * 16 / mhz, mhz))
 
 
 def head_case(a):
@@ -215,6 +275,14 @@ def main():
     p.add_argument("--stack", action="store_true", help="run every layer in one launch (wd_stack_step)")
     p.add_argument("--compiled", action="store_true", help="the kernel compiled for the geometry (WD_COMPILED_KERNEL=1)")
     p.set_defaults(fn=profile_case)
+    p = sub.add_parser("batch")
+    p.add_argument("--layers", type=int, default=2)
+    p.add_argument("--tokens", type=int, default=4)
+    p.add_argument("--iters", type=int, default=4)
+    p.add_argument("--stamps", action="store_true")
+    p.set_defaults(fn=batch_case)
+    p = sub.add_parser("decoder")
+    p.set_defaults(fn=decoder_case)
     p = sub.add_parser("dense")
     p.add_argument("--rows", type=int, default=128256)
     p.add_argument("--cols", type=int, default=2048)

@@ -156,6 +156,11 @@ int wd_set_profiling(wd_engine *e, int on);
 int wd_sm_count(const wd_engine *e);
 /* Name of the kernel a stack step of this engine launches (for bench records). */
 const char *wd_kernel_name(const wd_engine *e);
+/* Measurement, no counterpart in the reference: SM clock cycles one SM of `device` needs to decode a round of `warps`
+ * IQ3_S tiles (32 blocks = 8192 weights each, one per warp) that already sit in shared memory, against Q8_K activations
+ * of nsb superblocks, with the layer kernels' own decoder (unroll 1: as the single-token kernel runs it; 8: as the batch
+ * kernel does). Median over the SMs. This is the instruction-issue bound of the expert GEMVs. */
+int wd_measure_tile_decoder(int device, int nsb, int warps, int unroll, double *cycles_per_round);
 /* Name of the kernel a token batch (wd_moe_forward with n_tokens > 1) runs on: the batch kernel when the engine has
  * every expert resident on one GPU and the geometry fits it, else the kernel above walking the tokens. */
 const char *wd_batch_kernel_name(const wd_engine *e);

@@ -100,6 +100,7 @@ def lib():
         L.wd_kernel_name.restype = C.c_char_p
         L.wd_batch_kernel_name.argtypes = [vp]
         L.wd_batch_kernel_name.restype = C.c_char_p
+        L.wd_measure_tile_decoder.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]
         L.wd_synth_expert_host.argtypes = [vp, C.c_uint64, C.c_float, i, i, vp, vp, vp]
         L.wd_synth_dense_host.argtypes = [vp, C.c_uint64, C.c_float, C.c_float, i, vp, vp, vp, vp, vp, vp]
         L.wd_ep_export.argtypes = [vp, vp]
@@ -428,6 +429,13 @@ class HeadQ8_0:
             self.close()
         except Exception:
             pass
+
+
+def measure_tile_decoder(nsb=8, warps=16, unroll=1, device=0):
+    """SM clock cycles per round of `warps` IQ3_S tiles decoded from shared memory (the issue bound of the expert GEMVs)."""
+    c = C.c_double()
+    _check(lib().wd_measure_tile_decoder(device, nsb, warps, unroll, C.byref(c)))
+    return c.value
 
 
 def embed_q8_0(table_dev_ptr, rows, cols, token_ptr, out_ptr, stream=None):

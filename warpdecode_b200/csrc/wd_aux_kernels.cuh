@@ -302,6 +302,42 @@ __global__ void iq_matvec_tiles_kernel(const uint8_t *tiles, int rows, int nsb, 
     }
 }
 
+// Measurement: how fast one SM decodes IQ3_S tiles that already sit in shared memory. `warps` warps of every CTA
+// run `iters` rounds of one tile each (sixteen pseudo-random tiles, Q8_K activations of `nsb` superblocks);
+// cycles[cta] = SM clock cycles of the slowest warp. The decoder is the layer kernels' own (iq3_tile_to_rows).
+template <int UNROLL>
+__global__ void __launch_bounds__(kThreads, 1) iq3_decoder_rate_kernel(const uint16_t *grid_packed, int nsb, int iters, int warps,
+                                                                       unsigned long long *cycles, float *sink) {
+    extern __shared__ __align__(128) uint8_t tsm[];
+    uint8_t *tab = tsm;
+    uint8_t *tiles = tab + kGridTableBytes;                   // 16 tiles
+    uint8_t *act = tiles + 16 * kIq3TileBytes;                // 32 superblocks
+    float *actd = reinterpret_cast<float *>(act + 32 * kActSbStride);
+    float *scr_all = actd + 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    build_grid_table(tab, grid_packed);
+    for (int i = tid; i < 16 * kIq3TileBytes; i += kThreads) tiles[i] = static_cast<uint8_t>((i * 2654435761u) >> 13);
+    for (int i = tid; i < 32 * kActSbStride; i += kThreads) act[i] = static_cast<uint8_t>((i * 40503u) >> 7);
+    if (tid < 32) actd[tid] = 0.01f;
+    __syncthreads();
+    float *scr = scr_all + warp * 640, *rows = scr + 576;
+    const uint32_t lane4x2 = static_cast<uint32_t>(lane * 4) * 0x0101u;
+    const int sb = lane % nsb;
+    float acc = 0.0f;
+    const long long t0 = clock64();
+    if (warp < warps) {
+#pragma unroll 1
+        for (int it = 0; it < iters; ++it) {
+            iq3_tile_to_rows<UNROLL>(tiles + ((warp + it) & 15) * kIq3TileBytes, act + sb * kActSbStride, actd[sb], nsb, lane, lane4x2,
+                                     tab, scr, rows, nullptr);
+            acc += rows[lane % (32 / nsb)];
+        }
+    }
+    __syncthreads();
+    if (tid == 0) cycles[blockIdx.x] = static_cast<unsigned long long>(clock64() - t0);
+    sink[blockIdx.x * kThreads + tid] = acc;
+}
+
 // y = W x for a repacked Q8_0 matrix, one warp per 4-row task, x quantised to Q8_0 in shared memory.
 __global__ void test_matvec_q8_0_kernel(const uint8_t *tasks, int rows, int nb, const float *x, float *y) {
     extern __shared__ __align__(128) uint8_t tsm[];

@@ -1515,6 +1515,34 @@ int wd_set_profiling(wd_engine *e, int on) {
 }
 
 int wd_sm_count(const wd_engine *e) { return e ? e->n_sm : 0; }
+// Cycles one SM needs for a round of `warps` IQ3_S tiles resident in shared memory (see iq3_decoder_rate_kernel).
+int wd_measure_tile_decoder(int device, int nsb, int warps, int unroll, double *cycles_per_round) {
+    if (!cycles_per_round || warps < 1 || warps > wd::kWarps || (unroll != 1 && unroll != 8) || nsb < 1 || nsb > 32 || (32 % nsb) != 0)
+        return fail(WD_E_INVALID, "tile decoder measurement: warps 1..16, unroll 1 or 8, nsb a power of two up to 32");
+    WD_CUDA(cudaSetDevice(device));
+    int n_sm = 0;
+    WD_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, device));
+    ScopedDev hold;
+    uint16_t *grid = nullptr;
+    unsigned long long *cyc = nullptr;
+    float *sink = nullptr;
+    WD_CUDA(hold.alloc(&grid, sizeof(wd_iq3s_grid_packed)));
+    WD_CUDA(hold.alloc(&cyc, static_cast<size_t>(n_sm) * sizeof(unsigned long long)));
+    WD_CUDA(hold.alloc(&sink, static_cast<size_t>(n_sm) * wd::kThreads * sizeof(float)));
+    WD_CUDA(cudaMemcpy(grid, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
+    const size_t sm = wd::kGridTableBytes + 16 * wd::kIq3TileBytes + 32 * wd::kActSbStride + 128 + static_cast<size_t>(wd::kWarps) * 640 * 4;
+    const int iters = 200;
+    auto fn = unroll == 8 ? wd::iq3_decoder_rate_kernel<8> : wd::iq3_decoder_rate_kernel<1>;
+    WD_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(sm)));
+    for (int rep = 0; rep < 2; ++rep) fn<<<n_sm, wd::kThreads, sm>>>(grid, nsb, iters, warps, cyc, sink);
+    WD_CUDA(cudaDeviceSynchronize());
+    std::vector<unsigned long long> h(n_sm);
+    WD_CUDA(cudaMemcpy(h.data(), cyc, h.size() * sizeof(h[0]), cudaMemcpyDeviceToHost));
+    std::sort(h.begin(), h.end());
+    *cycles_per_round = static_cast<double>(h[h.size() / 2]) / iters;
+    return WD_OK;
+}
+
 const char *wd_kernel_name(const wd_engine *e) { return e && e->fast_fn ? "moe_fast_kernel" : "moe_layer_kernel"; }
 const char *wd_batch_kernel_name(const wd_engine *e) { return e && e->batch_ok ? "moe_batch_kernel" : wd_kernel_name(e); }
 
