@@ -308,7 +308,8 @@ float wdo_row_iq4_nl_q8_0(const uint8_t *w_row, const uint8_t *y, int cols) {
  * 0..15 and the high nibbles to values 16..31, sums four consecutive products per
  * lane, and does one fmaf(d_w * d_x, (float)p_lane, acc_lane) per block for the
  * eight lanes, blocks ascending, then the same 8-lane tree as the Q8_0 row.
- * Parity unpinned for this function: no golden vector of the reference covers it. */
+ * No golden vector of the reference covers this function; it is pinned against an independent decoder
+ * instead (gguf-py's dequantize plus an exact integer reconstruction, tests/test_oracle_pins.py). */
 float wdo_row_q4_0_q8_0(const uint8_t *w_row, const uint8_t *y, int cols) {
     const int nb = cols / 32;
     float lane[8] = {0, 0, 0, 0, 0, 0, 0, 0};
