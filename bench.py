@@ -1,7 +1,7 @@
 """Bench of the batch-1 MoE decode hot path (48-layer, 512-expert IQ3_S MoE stack).
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--repeats R] [--impl reference]
-                  [--cache-mib M] [--no-decode] [--no-verify]
+                  [--cache-mib M] [--no-decode] [--no-verify] [--no-dense]
 
 One step = one decode token through the 48 MoE blocks of the synthetic model (hidden 2048, 512
 routed experts of ffn 512 in IQ3_S, top-10, one Q8_0 shared expert per layer, every expert resident
@@ -382,6 +382,27 @@ def run_ours(args, rank, world, local_rank):
                           "calls with one token; fastest of 3 runs of 10 batches. The stack value above is the rate "
                           "to compare a verify step with: it is what decoding the same tokens one by one costs"}
 
+    # ---- config 1: the plain Q4_0 decoder (rank 0 of a 1-GPU run only; the MoE engine's memory stays allocated) ------------
+    dense = None
+    if not args.no_dense and world == 1 and not capped:
+        dec = wd.DenseDecoder(2048, 32, 8, 64, 8192, 128256, 16, 128, 1e-5, 500000.0, device=local_rank)
+        dec.synth(2, 0.02)
+        prompt = np.random.Generator(np.random.PCG64(2)).integers(0, 128256, 8)
+        best_ms, toks = None, None
+        for _ in range(3):
+            toks, ms_d = dec.decode(prompt, 64)
+            best_ms = ms_d if best_ms is None else min(best_ms, ms_d)
+        q4 = lambda r, c: r * (c // 32) * 18
+        tok_bytes = 16 * (q4(3072, 2048) + q4(2048, 2048) + q4(16384, 2048) + q4(2048, 8192)) + q4(128256, 2048)
+        us_tok = best_ms * 1e3 / 71
+        dense = {"value": 1e6 / us_tok, "unit": "tok/s", "us_per_token": us_tok, "bytes_per_token": tok_bytes,
+                 "hbm_gbs": tok_bytes / us_tok / 1e3, "token_hash": token_hash(toks.tolist()),
+                 "distinct_tokens": len(set(toks[8:].tolist())), "launches_per_token": 129,
+                 "what": "config 1: Llama-style dense decoder (16 layers, hidden 2048, 32 query / 8 KV heads of 64, SwiGLU 8192, "
+                         "vocab 128256, RoPE theta 5e5, every 2-D tensor Q4_0 from N(0, 0.02), norms 1), greedy decode of 64 tokens "
+                         "after an 8-token prompt, one CUDA-graph replay per token; fastest of 3 runs"}
+        dec.close()
+
     t = torch.tensor([float(np.median(rep_ms)), min(rep_ms), max(rep_ms), float(np.median(e2e_rep))],
                      dtype=torch.float64, device="cuda")
     if world > 1:
@@ -439,6 +460,9 @@ def run_ours(args, rank, world, local_rank):
         line["decode"] = decode
     if verify is not None:
         line["verify_m4"] = verify
+    if dense is not None:
+        dense["hbm_frac"] = dense["hbm_gbs"] / peak
+        line["dense_cfg1"] = dense
     if cache_stats is not None:
         hits, misses, evictions, h2d_bytes, host_ns, placed = cache_stats
         line["cache"] = {"cache_mib": args.cache_mib, "slots": eng.slot_count(), "hits": hits, "misses": misses,
@@ -463,6 +487,7 @@ def main():
     ap.add_argument("--cache-bias", type=float, default=0.0, help="router bias sigma of the capped-cache model (cfg4: 0)")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-verify", action="store_true")
+    ap.add_argument("--no-dense", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

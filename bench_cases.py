@@ -11,6 +11,10 @@ were captured from (ncu wants a short program with few launches), and the kernel
     python bench_cases.py decoder
         the IQ3_S tile decoder alone, tiles resident in shared memory: cycles per round of tiles for 16, 8, 4 and 1
         active warps per SM (the issue bound of the expert GEMVs)
+    python bench_cases.py dense-decode [--layers 16] [--vocab 128256] [--gen 64] [--runs 3]
+        the plain Q4_0 decoder on the dense benchmark model (Llama-style, hidden 2048, 32 query / 8 KV heads of 64,
+        SwiGLU 8192, RoPE theta 5e5, weights N(0, 0.02) generated on the device): greedy decode of 64 tokens after an
+        8-token prompt, one CUDA-graph replay per token; fastest of the runs, with the token hash
     python bench_cases.py dense [--rows 128256] [--cols 2048] [--mats 2] [--iters 20]
         streams Q4_0 matrices of the plain decoder's output-head size through the dense matvec kernel
     python bench_cases.py head [--rows 151936] [--cols 2048] [--iters 20]
@@ -149,6 +153,34 @@ def decoder_case(a):
                       "%.2f us per 16 tiles at %.0f MHz" % (unroll, nsb, warps, c, c / warps, c / warps * 16 / mhz, mhz))
 
 
+def dense_decode_case(a):
+    H, nh, nkv, hd, F = 2048, 32, 8, 64, 8192
+    dec = wd.DenseDecoder(H, nh, nkv, hd, F, a.vocab, a.layers, 128, 1e-5, 500000.0)
+    t0 = time.perf_counter()
+    dec.synth(2, 0.02)
+    gen_s = time.perf_counter() - t0
+    prompt = np.random.Generator(np.random.PCG64(2)).integers(0, a.vocab, 8)
+    q4 = lambda r, c: r * (c // 32) * 18
+    layer_bytes = q4((nh + 2 * nkv) * hd, H) + q4(H, nh * hd) + q4(2 * F, H) + q4(H, F)
+    token_bytes = a.layers * layer_bytes + q4(a.vocab, H)
+    best, toks = None, None
+    for _ in range(a.runs):
+        toks, ms = dec.decode(prompt, a.gen)
+        best = ms if best is None else min(best, ms)
+    steps = len(prompt) + a.gen - 1
+    h = 0xcbf29ce484222325
+    for t in toks.tolist():
+        for k in range(4):
+            h = ((h ^ ((t >> (8 * k)) & 0xff)) * 0x100000001b3) & 0xffffffffffffffff
+    us = best * 1e3 / steps
+    peak = measured_peak()
+    print("model generated in %.2f s; %d layers, vocab %d; %d bytes of weights per token" % (gen_s, a.layers, a.vocab, token_bytes))
+    print("%d steps in %.3f ms: %.1f us per token, %.1f tok/s, %.0f GB/s = %.3f of the measured HBM peak (%.0f GB/s)"
+          % (steps, best, us, 1e6 / us, token_bytes / us / 1e3, token_bytes / us / 1e3 / peak, peak))
+    print("token_hash %016x, %d distinct generated tokens" % (h, len(set(toks[len(prompt):].tolist()))))
+    dec.close()
+
+
 def head_case(a):
     """Q8_0 matrix [rows][cols] (default: the 48-layer decoder's head, 151936 x 2048 = 331 MB) + arg-max."""
     import torch
@@ -281,6 +313,12 @@ def main():
     p.add_argument("--iters", type=int, default=4)
     p.add_argument("--stamps", action="store_true")
     p.set_defaults(fn=batch_case)
+    p = sub.add_parser("dense-decode")
+    p.add_argument("--layers", type=int, default=16)
+    p.add_argument("--vocab", type=int, default=128256)
+    p.add_argument("--gen", type=int, default=64)
+    p.add_argument("--runs", type=int, default=3)
+    p.set_defaults(fn=dense_decode_case)
     p = sub.add_parser("decoder")
     p.set_defaults(fn=decoder_case)
     p = sub.add_parser("dense")

@@ -156,6 +156,41 @@ int wd_set_profiling(wd_engine *e, int on);
 int wd_sm_count(const wd_engine *e);
 /* Name of the kernel a stack step of this engine launches (for bench records). */
 const char *wd_kernel_name(const wd_engine *e);
+/* ---- The plain (dense) Q4_0 decoder: the Llama-style per-token step of the reference's dense path
+ * (Model / Runtime / emit_step, src/warodecode.cu:1211-2150): embedding row, per layer RMSNorm -> fused QKV product ->
+ * rotary embedding (GPT-NeoX pairing) + cache store -> decode attention -> output product -> RMSNorm -> gate/up
+ * product -> SiLU(g) * u -> down product, output norm, output head, greedy arg-max. Every 2-D tensor is Q4_0 in ggml
+ * block layout ([rows][cols / 32] blocks of 18 bytes); activations are quantised to Q8_0 for the products, as the
+ * reference does (:1504-1562). One CUDA-graph replay per token; token and position stay on the device. ---- */
+typedef struct wd_dense_config {
+    int hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, n_layers, max_ctx;
+    float rms_eps, rope_theta;
+    int device;
+} wd_dense_config;
+typedef struct wd_dense_decoder wd_dense_decoder;
+#define WD_DT_TOKEN_EMBD 0   /* Q4_0 [vocab][hidden] */
+#define WD_DT_OUTPUT_NORM 1  /* F32  [hidden] */
+#define WD_DT_OUTPUT 2       /* Q4_0 [vocab][hidden] */
+#define WD_DT_ATTN_NORM 3    /* F32  [hidden], per layer */
+#define WD_DT_WQKV 4         /* Q4_0 [(n_heads + 2 n_kv_heads) * head_dim][hidden]: q rows, k rows, v rows (Layer::qkv) */
+#define WD_DT_WO 5           /* Q4_0 [hidden][n_heads * head_dim] */
+#define WD_DT_FFN_NORM 6     /* F32  [hidden] */
+#define WD_DT_W_GATE_UP 7    /* Q4_0 [2 * ffn][hidden]: gate rows, then up rows (Layer::gate_up) */
+#define WD_DT_W_DOWN 8       /* Q4_0 [hidden][ffn] */
+int wd_dense_decoder_create(const wd_dense_config *cfg, wd_dense_decoder **out);
+void wd_dense_decoder_destroy(wd_dense_decoder *d);
+/* `layer` is ignored for the three model-level tensors. The bytes are copied; the pointer is not kept. */
+int wd_dense_decoder_set_tensor(wd_dense_decoder *d, int layer, int which, const void *host);
+int wd_dense_decoder_get_tensor(wd_dense_decoder *d, int layer, int which, void *host_out, size_t bytes);
+/* Every 2-D tensor drawn N(0, sigma) and quantised to Q4_0 on the device, norms 1 (synthetic models for measurements). */
+int wd_dense_decoder_synth(wd_dense_decoder *d, unsigned long long seed, float sigma);
+/* Greedy decode from position 0: the prompt is fed token by token, then n_gen tokens are generated (Runtime::run,
+ * src/warodecode.cu:2120-2150). out_tokens [n_prompt + n_gen] receives the prompt followed by the generated tokens;
+ * ms_total (optional) the device time of the n_prompt + n_gen - 1 steps. */
+int wd_dense_decoder_decode(wd_dense_decoder *d, const int *prompt, int n_prompt, int n_gen, int *out_tokens, float *ms_total);
+/* Logits of the last step [vocab] and the residual stream before the output norm [hidden]; either may be null. */
+int wd_dense_decoder_read(wd_dense_decoder *d, float *logits_host, float *hidden_host);
+
 /* Measurement, no counterpart in the reference: SM clock cycles one SM of `device` needs to decode a round of `warps`
  * IQ3_S tiles (32 blocks = 8192 weights each, one per warp) that already sit in shared memory, against Q8_K activations
  * of nsb superblocks, with the layer kernels' own decoder (unroll 1: as the single-token kernel runs it; 8: as the batch

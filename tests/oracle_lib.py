@@ -67,6 +67,67 @@ def build_oracle():
                        stdout=subprocess.DEVNULL)
 
 
+class DenseLayerC(C.Structure):
+    _fields_ = [("attn_norm", C.c_void_p), ("wqkv", C.c_void_p), ("wo", C.c_void_p), ("ffn_norm", C.c_void_p),
+                ("w_gate_up", C.c_void_p), ("w_down", C.c_void_p)]
+
+
+class DenseModelC(C.Structure):
+    _fields_ = [("hidden", C.c_int), ("n_heads", C.c_int), ("n_kv_heads", C.c_int), ("head_dim", C.c_int), ("ffn", C.c_int),
+                ("vocab", C.c_int), ("n_layers", C.c_int), ("max_ctx", C.c_int), ("rms_eps", C.c_float),
+                ("token_embd", C.c_void_p), ("output_norm", C.c_void_p), ("output", C.c_void_p),
+                ("layers", C.POINTER(DenseLayerC)), ("rope_table", C.c_void_p), ("hidden_out", C.c_void_p)]
+
+
+class DenseOracle:
+    """The dense decoder of oracle/wd_oracle_dense.c over numpy tensors (ggml Q4_0 bytes, F32 norms)."""
+
+    def __init__(self, oracle, cfg, tensors, layers, rope_theta):
+        """cfg: dict(hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, n_layers, max_ctx, rms_eps); tensors: dict with
+        token_embd, output_norm, output; layers: list of dicts attn_norm, wqkv, wo, ffn_norm, w_gate_up, w_down."""
+        self.L = oracle.lib
+        self.keep = []
+
+        def ptr(a, dt):
+            a = np.ascontiguousarray(a, dt)
+            self.keep.append(a)
+            return a.ctypes.data
+
+        self.layers = (DenseLayerC * cfg["n_layers"])()
+        for i, l in enumerate(layers):
+            self.layers[i] = DenseLayerC(ptr(l["attn_norm"], np.float32), ptr(l["wqkv"], np.uint8), ptr(l["wo"], np.uint8),
+                                         ptr(l["ffn_norm"], np.float32), ptr(l["w_gate_up"], np.uint8), ptr(l["w_down"], np.uint8))
+        self.rope = np.zeros(cfg["max_ctx"] * (cfg["head_dim"] // 2) * 2, np.float32)
+        self.L.wdo_rope_table.argtypes = [C.c_int, C.c_int, C.c_double, C.c_void_p]
+        self.L.wdo_rope_table(cfg["max_ctx"], cfg["head_dim"], float(rope_theta), self.rope.ctypes.data)
+        self.hidden = np.zeros(cfg["hidden"], np.float32)
+        self.m = DenseModelC(cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["ffn"], cfg["vocab"],
+                             cfg["n_layers"], cfg["max_ctx"], cfg["rms_eps"], ptr(tensors["token_embd"], np.uint8),
+                             ptr(tensors["output_norm"], np.float32), ptr(tensors["output"], np.uint8), self.layers,
+                             self.rope.ctypes.data, self.hidden.ctypes.data)
+        kv = cfg["n_layers"] * cfg["max_ctx"] * cfg["n_kv_heads"] * cfg["head_dim"]
+        self.kc, self.vc = np.zeros(kv, np.float32), np.zeros(kv, np.float32)
+        self.logits = np.zeros(cfg["vocab"], np.float32)
+        self.L.wdo_dense_step.argtypes = [C.POINTER(DenseModelC), C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        self.L.wdo_dense_step.restype = C.c_int
+
+    def step(self, token, pos):
+        return int(self.L.wdo_dense_step(C.byref(self.m), self.kc.ctypes.data, self.vc.ctypes.data, int(token), int(pos),
+                                         self.logits.ctypes.data))
+
+    def decode(self, prompt, n_gen):
+        toks = list(map(int, prompt))
+        tok = toks[0]
+        for pos in range(len(prompt) + n_gen - 1):
+            nxt = self.step(tok, pos)
+            if pos + 1 < len(prompt):
+                nxt = toks[pos + 1]
+            else:
+                toks.append(nxt)
+            tok = nxt
+        return np.array(toks, np.int32)
+
+
 class Oracle:
     """The plain-C restatement."""
 
@@ -81,7 +142,7 @@ class Oracle:
         L.wdo_f32_to_f16.argtypes = [C.c_float]
         L.wdo_iq3s_grid.restype = C.c_uint32
         L.wdo_iq2s_grid.restype = C.c_uint64
-        for name in ("wdo_row_q8_0_q8_0", "wdo_row_iq4_nl_q8_0", "wdo_row_q4_0_q8_0"):
+        for name in ("wdo_row_q8_0_q8_0", "wdo_row_iq4_nl_q8_0", "wdo_row_q4_0_q8_0", "wdo_row_q4_0_q8_0_lanes"):
             getattr(L, name).restype = C.c_float
             getattr(L, name).argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.wdo_matvec_q8_0_argmax.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]

@@ -209,3 +209,36 @@ def test_q4_0_row_dot_against_gguf_py_decoder_and_exact_integers(oracle):
         want = np.float32(np.float32(s[0] + s[2]) + np.float32(s[1] + s[3]))
         got = oracle.row(ol.TYPE_Q4_0, w[r * nb:(r + 1) * nb].reshape(-1), xq.reshape(-1), cols)
         assert ol.fbits(np.array([got]))[0] == ol.fbits(np.array([want]))[0], r
+
+
+def test_q4_0_row_dot_in_lane_order_against_gguf_py_decoder(oracle):
+    """The dense decoder's row dot (a warp splits a row's blocks over its 32 lanes, one fmaf per block, then a
+    butterfly) pinned the same way: gguf-py's decoder gives the block values, the integer dot of every block is
+    rebuilt in int64, the float side replays the stated order with every step rounded once."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    rng = np.random.Generator(np.random.PCG64(405))
+    for cols in (256, 2048, 8192):
+        rows, nb = 12, cols // 32
+        w = rng.integers(0, 256, (rows * nb, 18), dtype=np.uint8)
+        w[:, 0:2] = (rng.random(rows * nb) * 0.01 + 0.001).astype(np.float16).view(np.uint8).reshape(-1, 2)
+        x = rng.standard_normal(cols).astype(np.float32)
+        xq = oracle.quantize_q8_0(x).reshape(nb, 34)
+        wf = quants.dequantize(w.reshape(rows, nb * 18), gguf.GGMLQuantizationType.Q4_0).reshape(rows, nb, 32)
+        d_w = w[:, 0:2].copy().view(np.float16).astype(np.float32).reshape(rows, nb)
+        d_x = xq[:, 0:2].copy().view(np.float16).astype(np.float32).reshape(nb)
+        qw = np.rint(wf.astype(np.float64) / d_w[:, :, None]).astype(np.int64)
+        qx = xq[:, 2:].view(np.int8).astype(np.int64)
+        dots = (qw * qx[None]).sum(-1)                                                  # [row][block], int64
+        f = oracle.lib.wdo_row_q4_0_q8_0_lanes
+        for r in range(rows):
+            lane = np.zeros(32, np.float32)
+            for b in range(nb):
+                d = np.float32(d_w[r, b] * d_x[b])
+                lane[b & 31] = np.float32(np.float64(d) * np.float64(dots[r, b]) + np.float64(lane[b & 31]))    # fmaf
+            for sft in (16, 8, 4, 2, 1):
+                lane = np.array([np.float32(lane[l] + lane[l ^ sft]) for l in range(32)], np.float32)
+            wr = np.ascontiguousarray(w[r * nb:(r + 1) * nb].reshape(-1))
+            xr = np.ascontiguousarray(xq.reshape(-1))
+            got = np.float32(f(wr.ctypes.data, xr.ctypes.data, cols))
+            assert ol.fbits(np.array([got]))[0] == ol.fbits(np.array([lane[0]]))[0], (cols, r)

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 LIB_PATH = os.path.join(HERE, "libwarpdecode_b200.so")
 SOURCES = [os.path.join(HERE, "csrc", f) for f in
-           ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_moe_kernel_phases.inc", "wd_moe_fast.cuh", "wd_moe_batch.cuh",
+           ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_moe_kernel_phases.inc", "wd_moe_fast.cuh", "wd_moe_batch.cuh", "wd_dense_decoder.cuh", "wd_dense_decoder.inc",
             "wd_blocks.cuh", "wd_router.cuh",
             "wd_formats.cuh", "wd_device.cuh", "wd_dense.cuh", "wd_gguf.inc",
             "wd_grids.h")] + [os.path.join(ROOT, "include", "warpdecode_b200.h")]
@@ -50,6 +50,12 @@ class Config(C.Structure):
                 ("w_scale", C.c_float), ("ep_rank", C.c_int32), ("ep_size", C.c_int32),
                 ("max_tokens", C.c_int32), ("device", C.c_int32), ("cache_mib", C.c_int64),
                 ("rms_eps", C.c_float)]
+
+
+class DenseConfig(C.Structure):
+    _fields_ = [("hidden", C.c_int32), ("n_heads", C.c_int32), ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32),
+                ("ffn", C.c_int32), ("vocab", C.c_int32), ("n_layers", C.c_int32), ("max_ctx", C.c_int32),
+                ("rms_eps", C.c_float), ("rope_theta", C.c_float), ("device", C.c_int32)]
 
 
 _lib = None
@@ -101,6 +107,14 @@ def lib():
         L.wd_batch_kernel_name.argtypes = [vp]
         L.wd_batch_kernel_name.restype = C.c_char_p
         L.wd_measure_tile_decoder.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]
+        L.wd_dense_decoder_create.argtypes = [C.POINTER(DenseConfig), C.POINTER(C.c_void_p)]
+        L.wd_dense_decoder_destroy.argtypes = [C.c_void_p]
+        L.wd_dense_decoder_destroy.restype = None
+        L.wd_dense_decoder_set_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        L.wd_dense_decoder_get_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t]
+        L.wd_dense_decoder_synth.argtypes = [C.c_void_p, C.c_uint64, C.c_float]
+        L.wd_dense_decoder_decode.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_float)]
+        L.wd_dense_decoder_read.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
         L.wd_synth_expert_host.argtypes = [vp, C.c_uint64, C.c_float, i, i, vp, vp, vp]
         L.wd_synth_dense_host.argtypes = [vp, C.c_uint64, C.c_float, C.c_float, i, vp, vp, vp, vp, vp, vp]
         L.wd_ep_export.argtypes = [vp, vp]
@@ -423,6 +437,66 @@ class HeadQ8_0:
         if self.p:
             lib().wd_dense_free(self.p)
             self.p = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+DT_TOKEN_EMBD, DT_OUTPUT_NORM, DT_OUTPUT, DT_ATTN_NORM, DT_WQKV, DT_WO, DT_FFN_NORM, DT_W_GATE_UP, DT_W_DOWN = range(9)
+
+
+class DenseDecoder:
+    """The plain (dense) Q4_0 decoder (wd_dense_decoder_*): Llama-style layers, greedy decode on the device."""
+
+    def __init__(self, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, n_layers, max_ctx, rms_eps=1e-5, rope_theta=500000.0,
+                 device=0):
+        self.cfg = DenseConfig(hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, n_layers, max_ctx, rms_eps, rope_theta, device)
+        self.h = C.c_void_p()
+        _check(lib().wd_dense_decoder_create(C.byref(self.cfg), C.byref(self.h)))
+
+    def shape(self, which):
+        c = self.cfg
+        q = c.n_heads * c.head_dim
+        kv = c.n_kv_heads * c.head_dim
+        return {DT_TOKEN_EMBD: (c.vocab, c.hidden), DT_OUTPUT: (c.vocab, c.hidden), DT_WQKV: (q + 2 * kv, c.hidden),
+                DT_WO: (c.hidden, q), DT_W_GATE_UP: (2 * c.ffn, c.hidden), DT_W_DOWN: (c.hidden, c.ffn)}.get(which)
+
+    def set_tensor(self, layer, which, data):
+        shp = self.shape(which)
+        a = np.ascontiguousarray(data, np.float32 if shp is None else np.uint8)
+        assert a.size == (self.cfg.hidden if shp is None else shp[0] * (shp[1] // 32) * 18)
+        _check(lib().wd_dense_decoder_set_tensor(self.h, layer, which, _ptr(a)))
+
+    def get_tensor(self, layer, which):
+        shp = self.shape(which)
+        a = np.zeros(self.cfg.hidden, np.float32) if shp is None else np.zeros(shp[0] * (shp[1] // 32) * 18, np.uint8)
+        _check(lib().wd_dense_decoder_get_tensor(self.h, layer, which, _ptr(a), a.nbytes))
+        return a
+
+    def synth(self, seed, sigma=0.02):
+        _check(lib().wd_dense_decoder_synth(self.h, seed, sigma))
+
+    def decode(self, prompt, n_gen):
+        """Greedy decode; returns (tokens [len(prompt) + n_gen], device milliseconds of the whole run)."""
+        pr = np.ascontiguousarray(prompt, np.int32)
+        out = np.zeros(pr.size + n_gen, np.int32)
+        ms = C.c_float()
+        _check(lib().wd_dense_decoder_decode(self.h, _ptr(pr), pr.size, n_gen, _ptr(out), C.byref(ms)))
+        return out, ms.value
+
+    def read(self):
+        logits = np.zeros(self.cfg.vocab, np.float32)
+        hidden = np.zeros(self.cfg.hidden, np.float32)
+        _check(lib().wd_dense_decoder_read(self.h, _ptr(logits), _ptr(hidden)))
+        return logits, hidden
+
+    def close(self):
+        if self.h:
+            lib().wd_dense_decoder_destroy(self.h)
+            self.h = C.c_void_p()
 
     def __del__(self):
         try:

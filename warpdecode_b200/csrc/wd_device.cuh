@@ -30,6 +30,12 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while its
+// predecessor in the stream still runs. grid_dep_launch() lets the successor be scheduled from now on;
+// grid_dep_wait() returns once the predecessor has completed and its memory is visible (at once for an ordinary launch).
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -22,6 +22,7 @@
 #include "wd_aux_kernels.cuh"
 #include "wd_moe_batch.cuh"
 #include "wd_dense.cuh"
+#include "wd_dense_decoder.cuh"
 #include "wd_grids.h"
 
 namespace {
@@ -2206,3 +2207,4 @@ extern "C" int wd_matvec_iq3s_noalloc(const void *w_dev, int rows, int cols, con
 }
 
 #include "wd_gguf.inc"
+#include "wd_dense_decoder.inc"
