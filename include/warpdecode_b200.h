@@ -179,6 +179,9 @@ typedef struct wd_dense_decoder wd_dense_decoder;
 #define WD_DT_W_DOWN 8       /* Q4_0 [hidden][ffn] */
 int wd_dense_decoder_create(const wd_dense_config *cfg, wd_dense_decoder **out);
 void wd_dense_decoder_destroy(wd_dense_decoder *d);
+/* What a token runs on: a CUDA graph of per-operation kernels (the default, and the faster of the two as measured), or
+ * with WD_DENSE_TOKEN_KERNEL=1 and a geometry that fits it one persistent launch of the token kernel. Same results. */
+const char *wd_dense_decoder_kernel_name(const wd_dense_decoder *d);
 /* `layer` is ignored for the three model-level tensors. The bytes are copied; the pointer is not kept. */
 int wd_dense_decoder_set_tensor(wd_dense_decoder *d, int layer, int which, const void *host);
 int wd_dense_decoder_get_tensor(wd_dense_decoder *d, int layer, int which, void *host_out, size_t bytes);
@@ -188,6 +191,10 @@ int wd_dense_decoder_synth(wd_dense_decoder *d, unsigned long long seed, float s
  * src/warodecode.cu:2120-2150). out_tokens [n_prompt + n_gen] receives the prompt followed by the generated tokens;
  * ms_total (optional) the device time of the n_prompt + n_gen - 1 steps. */
 int wd_dense_decoder_decode(wd_dense_decoder *d, const int *prompt, int n_prompt, int n_gen, int *out_tokens, float *ms_total);
+/* Profiling of the token kernel: when WD_DENSE_STAMPS was set at creation, the SM clock counter of one CTA at the twelve
+ * steps of layer 1 of the last token (residual gathered, norm, QKV rows, attention, attention output gathered, O rows,
+ * residual gathered, norm, gate/up rows, activations gathered, down rows). */
+int wd_dense_decoder_stamps(wd_dense_decoder *d, unsigned long long *out12);
 /* Logits of the last step [vocab] and the residual stream before the output norm [hidden]; either may be null. */
 int wd_dense_decoder_read(wd_dense_decoder *d, float *logits_host, float *hidden_host);
 

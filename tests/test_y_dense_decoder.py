@@ -27,14 +27,18 @@ def _oracle_for(wd, oracle, dec, cfg, rope_theta):
     return ol.DenseOracle(oracle, cfg, tensors, layers, rope_theta)
 
 
-def test_greedy_64_tokens_of_a_small_model_from_host_tensors(wd, oracle):
-    """Tensors quantised on the host by gguf-py's Q4_0 encoder and handed over in ggml layout; norms random."""
+@pytest.mark.parametrize("hidden,token_kernel", [(256, False), (512, True), (512, False)])
+def test_greedy_64_tokens_of_a_small_model_from_host_tensors(wd, oracle, hidden, token_kernel, monkeypatch):
+    """Tensors quantised on the host by gguf-py's Q4_0 encoder and handed over in ggml layout; norms random. On the
+    graph of per-operation kernels and (hidden >= 512) on the one-launch-per-token kernel."""
     gguf = pytest.importorskip("gguf")
     from gguf import quants
-    cfg = dict(hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=1024, n_layers=2, max_ctx=96, rms_eps=1e-5)
+    cfg = dict(hidden=hidden, n_heads=4, n_kv_heads=2, head_dim=64, ffn=512, vocab=1024, n_layers=2, max_ctx=96, rms_eps=1e-5)
     theta = 500000.0
+    monkeypatch.setenv("WD_DENSE_TOKEN_KERNEL", "1" if token_kernel else "0")
     dec = wd.DenseDecoder(cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["ffn"], cfg["vocab"],
                           cfg["n_layers"], cfg["max_ctx"], cfg["rms_eps"], theta)
+    assert (dec.kernel_name() == "dense_token_kernel") == token_kernel
     rng = np.random.Generator(np.random.PCG64(2024))
 
     def q4(which, layer, sigma):
@@ -72,14 +76,17 @@ def test_greedy_64_tokens_of_a_small_model_from_host_tensors(wd, oracle):
     dec.close()
 
 
-def test_layers_of_the_benchmark_width_match_the_oracle(wd, oracle):
+@pytest.mark.parametrize("token_kernel", [True, False])
+def test_layers_of_the_benchmark_width_match_the_oracle(wd, oracle, token_kernel, monkeypatch):
     """Two layers of the dense benchmark model's shape (hidden 2048, 32 query / 8 KV heads of 64, SwiGLU 8192, RoPE
     theta 5e5), vocabulary cut to 4096 so that the oracle finishes in seconds; weights N(0, 0.02) generated on the
     device, norms 1, as the benchmark configuration says. 8 prompt tokens + 8 generated."""
     cfg = dict(hidden=2048, n_heads=32, n_kv_heads=8, head_dim=64, ffn=8192, vocab=4096, n_layers=2, max_ctx=128, rms_eps=1e-5)
     theta = 500000.0
+    monkeypatch.setenv("WD_DENSE_TOKEN_KERNEL", "1" if token_kernel else "0")
     dec = wd.DenseDecoder(cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["ffn"], cfg["vocab"],
                           cfg["n_layers"], cfg["max_ctx"], cfg["rms_eps"], theta)
+    assert (dec.kernel_name() == "dense_token_kernel") == token_kernel
     dec.synth(2, 0.02)
     prompt = np.random.Generator(np.random.PCG64(2)).integers(0, cfg["vocab"], 8)
     got, _ = dec.decode(prompt, 8)

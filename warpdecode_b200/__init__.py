@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 LIB_PATH = os.path.join(HERE, "libwarpdecode_b200.so")
 SOURCES = [os.path.join(HERE, "csrc", f) for f in
-           ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_moe_kernel_phases.inc", "wd_moe_fast.cuh", "wd_moe_batch.cuh", "wd_dense_decoder.cuh", "wd_dense_decoder.inc",
+           ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_moe_kernel_phases.inc", "wd_moe_fast.cuh", "wd_moe_batch.cuh", "wd_dense_decoder.cuh", "wd_dense_decoder.inc", "wd_dense_token.cuh",
             "wd_blocks.cuh", "wd_router.cuh",
             "wd_formats.cuh", "wd_device.cuh", "wd_dense.cuh", "wd_gguf.inc",
             "wd_grids.h")] + [os.path.join(ROOT, "include", "warpdecode_b200.h")]
@@ -110,6 +110,8 @@ def lib():
         L.wd_dense_decoder_create.argtypes = [C.POINTER(DenseConfig), C.POINTER(C.c_void_p)]
         L.wd_dense_decoder_destroy.argtypes = [C.c_void_p]
         L.wd_dense_decoder_destroy.restype = None
+        L.wd_dense_decoder_kernel_name.argtypes = [C.c_void_p]
+        L.wd_dense_decoder_kernel_name.restype = C.c_char_p
         L.wd_dense_decoder_set_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         L.wd_dense_decoder_get_tensor.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t]
         L.wd_dense_decoder_synth.argtypes = [C.c_void_p, C.c_uint64, C.c_float]
@@ -475,6 +477,9 @@ class DenseDecoder:
         a = np.zeros(self.cfg.hidden, np.float32) if shp is None else np.zeros(shp[0] * (shp[1] // 32) * 18, np.uint8)
         _check(lib().wd_dense_decoder_get_tensor(self.h, layer, which, _ptr(a), a.nbytes))
         return a
+
+    def kernel_name(self):
+        return lib().wd_dense_decoder_kernel_name(self.h).decode()
 
     def synth(self, seed, sigma=0.02):
         _check(lib().wd_dense_decoder_synth(self.h, seed, sigma))

@@ -31,6 +31,19 @@ __global__ void repack_q4_0_rows_kernel(const uint8_t *src, uint8_t *dst, long l
     for (int j = 0; j < 16; ++j) q[j] = s[2 + j];
 }
 
+// ggml Q4_0 blocks [rows][nb][18 B] -> per row [nb][16 B] quants followed by [nb] f16 scales (18 * nb bytes per row).
+__global__ void repack_q4_0_rowpack_kernel(const uint8_t *src, uint8_t *dst, long long nblocks, int nb) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= nblocks) return;
+    const long long row = i / nb;
+    const int b = static_cast<int>(i - row * nb);
+    const uint8_t *s = src + i * 18;
+    uint8_t *r = dst + row * nb * 18;
+    for (int j = 0; j < 16; ++j) r[b * 16 + j] = s[2 + j];
+    r[nb * 16 + b * 2] = s[0];
+    r[nb * 16 + b * 2 + 1] = s[1];
+}
+
 // N(0, sigma) values quantised to ggml Q4_0 blocks by ggml's published rule (quantize_row_q4_0_ref): d = (the value of
 // largest magnitude, sign kept) / -8; q = min(15, (int)(v / d + 8.5)); byte j = q[j] | q[j + 16] << 4.
 __global__ void synth_q4_0_kernel(uint8_t *dst, long long nblocks, float sigma, uint64_t seed, uint64_t stream_id) {
@@ -260,18 +273,92 @@ __global__ void __launch_bounds__(kDecThreads, 4) dense_gemv_q4_0_kernel(const u
     }
 }
 
+// The attention of one query head over cache positions 0..pos by one CTA of `nthreads` threads. qs: the rotated q head,
+// kn / vn: the new (rotated) k and the new v of position pos (shared memory); kc / vc: the head's KV group in the
+// caches, row stride kv_dim; sc: [max_ctx] scores; vbuf: [32][head_dim] staging for the values. Returns the head's
+// output element `tid` to threads tid < head_dim. Order (the oracle's): score_t = lane-strided fmaf dot + butterfly,
+// times inv_sqrt; m = max; p_t = exp(score_t - m); l and out ascending in t. The loads are arranged so that a warp's
+// keys are in flight together and the values come through shared memory in chunks of 32 positions.
+__device__ __forceinline__ float dense_attention_core(const float *qs, const float *kn, const float *vn, const float *kc, const float *vc,
+                                                      int pos, int kv_dim, int head_dim, float inv_sqrt, float *sc, float *vbuf,
+                                                      int nthreads) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = nthreads >> 5;
+    const float q0 = qs[lane], q1 = lane + 32 < head_dim ? qs[lane + 32] : 0.0f, q2 = lane + 64 < head_dim ? qs[lane + 64] : 0.0f,
+                q3 = lane + 96 < head_dim ? qs[lane + 96] : 0.0f;
+#pragma unroll 1
+    for (int t0 = warp; t0 <= pos; t0 += 8 * nw) {
+        float k0[8], k1[8], k2[8], k3[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {               // every position's loads leave before the first dot
+            const int t = t0 + i * nw;
+            k0[i] = k1[i] = k2[i] = k3[i] = 0.0f;
+            if (t <= pos) {
+                const float *k = t == pos ? kn : kc + static_cast<size_t>(t) * kv_dim;
+                k0[i] = k[lane];
+                if (lane + 32 < head_dim) k1[i] = k[lane + 32];
+                if (lane + 64 < head_dim) k2[i] = k[lane + 64];
+                if (lane + 96 < head_dim) k3[i] = k[lane + 96];
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int t = t0 + i * nw;
+            if (t <= pos) {
+                float acc = __fmaf_rn(q0, k0[i], 0.0f);
+                if (head_dim > 32) acc = __fmaf_rn(q1, k1[i], acc);
+                if (head_dim > 64) acc = __fmaf_rn(q2, k2[i], acc);
+                if (head_dim > 96) acc = __fmaf_rn(q3, k3[i], acc);
+#pragma unroll
+                for (int s = 16; s >= 1; s >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, s));
+                if (lane == 0) sc[t] = __fmul_rn(acc, inv_sqrt);
+            }
+        }
+    }
+    __syncthreads();
+    float m = -INFINITY;
+    for (int t = 0; t <= pos; ++t) m = sc[t] > m ? sc[t] : m;
+    __syncthreads();
+    for (int t = tid; t <= pos; t += nthreads) sc[t] = exp_ggml(__fadd_rn(sc[t], -m));
+    float l = 0.0f, acc = 0.0f;
+#pragma unroll 1
+    for (int c0 = 0; c0 < pos; c0 += 32) {
+        const int n = min(32, pos - c0);
+        __syncthreads();                            // the scores are final; the previous chunk has been consumed
+        for (int i = tid; i < n * head_dim; i += nthreads) {
+            const int r = i / head_dim, d = i - r * head_dim;
+            vbuf[i] = vc[static_cast<size_t>(c0 + r) * kv_dim + d];
+        }
+        __syncthreads();
+        if (tid < head_dim) {
+            for (int r = 0; r < n; ++r) {
+                const float p = sc[c0 + r];
+                l = __fadd_rn(l, p);
+                acc = __fmaf_rn(p, vbuf[r * head_dim + tid], acc);
+            }
+        }
+    }
+    __syncthreads();
+    if (tid < head_dim) {
+        l = __fadd_rn(l, sc[pos]);
+        acc = __fmaf_rn(sc[pos], vn[tid], acc);
+        return __fdiv_rn(acc, l);
+    }
+    return 0.0f;
+}
+
 // Rotary embedding + cache store + decode attention + Q8_0 of the head's output, one CTA (128 threads) per query head
 // (rope_store_kernel :1855 and attention_decode_kernel :1902 of src/warodecode.cu, the latter as two passes; orders in
 // the header and in the oracle). The rotary embedding pairs element p with p + head_dim / 2 (GPT-NeoX) and takes
 // cos/sin from the table row of *pos. Every CTA rotates its own q head and, for itself, the new k head of its KV
 // group; the first CTA of a group also stores the rotated k and the v into the caches [max_ctx][kv_dim]. Cache
 // position pos itself is taken from the CTA's own copy, so no CTA waits for another's store.
-// head_dim a multiple of 32, at most 128; dynamic shared memory: max_ctx floats.
+// head_dim a multiple of 32, at most 128; dynamic shared memory: max_ctx + 32 * head_dim floats.
 __global__ void __launch_bounds__(128) dense_attention_kernel(const float *qkv, const float *table, float *kcache, float *vcache,
-                                                              const int *pos_ptr, int heads, int kv_heads, int head_dim,
+                                                              const int *pos_ptr, int heads, int kv_heads, int head_dim, int max_ctx,
                                                               float inv_sqrt, int8_t *oq, float *od) {
-    extern __shared__ __align__(16) float sc[];
+    extern __shared__ __align__(16) float sc[];        // [max_ctx] scores, then [32][head_dim] value staging
     __shared__ float qs[128], kn[128], vn[128], outv[128];
+    float *vbuf = sc + max_ctx;
     grid_dep_launch();
     grid_dep_wait();
     const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -304,36 +391,8 @@ __global__ void __launch_bounds__(128) dense_attention_kernel(const float *qkv, 
         }
     }
     __syncthreads();
-    for (int t = warp; t <= pos; t += 4) {
-        float acc = 0.0f;
-        if (t == pos) {
-            for (int d = lane; d < head_dim; d += 32) acc = __fmaf_rn(qs[d], kn[d], acc);
-        } else {
-            const float *k = kc + static_cast<size_t>(t) * kv_dim;
-            for (int d = lane; d < head_dim; d += 32) acc = __fmaf_rn(qs[d], k[d], acc);
-        }
-#pragma unroll
-        for (int s = 16; s >= 1; s >>= 1) acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, s));
-        if (lane == 0) sc[t] = __fmul_rn(acc, inv_sqrt);
-    }
-    __syncthreads();
-    float m = -INFINITY;
-    for (int t = 0; t <= pos; ++t) m = sc[t] > m ? sc[t] : m;
-    __syncthreads();
-    for (int t = tid; t <= pos; t += 128) sc[t] = exp_ggml(__fadd_rn(sc[t], -m));
-    __syncthreads();
-    if (tid < head_dim) {
-        float l = 0.0f, acc = 0.0f;
-#pragma unroll 4
-        for (int t = 0; t < pos; ++t) {
-            const float p = sc[t];
-            l = __fadd_rn(l, p);
-            acc = __fmaf_rn(p, vc[static_cast<size_t>(t) * kv_dim + tid], acc);
-        }
-        l = __fadd_rn(l, sc[pos]);
-        acc = __fmaf_rn(sc[pos], vn[tid], acc);
-        outv[tid] = __fdiv_rn(acc, l);
-    }
+    const float o = dense_attention_core(qs, kn, vn, kc, vc, pos, kv_dim, head_dim, inv_sqrt, sc, vbuf, 128);
+    if (tid < head_dim) outv[tid] = o;
     __syncthreads();
     if (warp < head_dim / 32) {
         const int b = (h * head_dim) / 32 + warp;

@@ -23,6 +23,7 @@
 #include "wd_moe_batch.cuh"
 #include "wd_dense.cuh"
 #include "wd_dense_decoder.cuh"
+#include "wd_dense_token.cuh"
 #include "wd_grids.h"
 
 namespace {
