@@ -399,7 +399,6 @@ void plan_batch(wd_engine *e) {
     p.off_scr = take(static_cast<size_t>(p.scr_bytes) * wd::kWarps);
     p.off_bar = take(wd::kBatchMaxBars * 8);
     p.off_slots = take(static_cast<size_t>(E) * 4);
-    p.off_pairs = take(64 * 4);
     p.off_seq = take(wd::kBatchMaxRing * 4);
     p.off_seg = take(96 * 4 + static_cast<size_t>(wd::kMaxTokens) * K * m.nsb_f * 4);     // segments, pair counters, activation states
     {

@@ -60,7 +60,7 @@ struct BatchParams {
     unsigned long long *stamps;  // nullable: [cta][kStampStride] SM clock counter of thread 0 at the steps of the launch (profiling)
     // shared memory plan (byte offsets, 128-byte aligned)
     unsigned off_tab, off_tab2, off_tok, tok_stride, tok_xd0, tok_xk, tok_xdk, tok_shq, tok_shd, tok_sel;
-    unsigned off_misc, off_scr, scr_bytes, scr_rows, off_bar, off_slots, off_pairs, off_seq, off_seg, off_tasks, off_pairbuf, off_actk,
+    unsigned off_misc, off_scr, scr_bytes, scr_rows, off_bar, off_slots, off_seq, off_seg, off_tasks, off_pairbuf, off_actk,
         off_actd, off_ring, off_sd;
     unsigned ring, ring_slot;    // staging slots of the ring and bytes of one
     unsigned max_tasks;          // tile tasks of one CTA at most
@@ -89,7 +89,6 @@ __global__ void __launch_bounds__(kThreads, 1) moe_batch_kernel(const __grid_con
     float *misc = reinterpret_cast<float *>(sm + P.off_misc);
     uint64_t *bars = reinterpret_cast<uint64_t *>(sm + P.off_bar);
     int *slot_tab = reinterpret_cast<int *>(sm + P.off_slots);
-    int *pair_slot = reinterpret_cast<int *>(sm + P.off_pairs);      // [T * K] slot of every pair's expert
     int *ring_seq = reinterpret_cast<int *>(sm + P.off_seq);         // [ring] how often each slot has been asked for again
     float *pairbuf = reinterpret_cast<float *>(sm + P.off_pairbuf);  // [32][2][R] row sums of gate/up tile pairs in flight
     int *unit_cnt = reinterpret_cast<int *>(sm + P.off_seg) + 64;    // [32] halves of a pair that are done

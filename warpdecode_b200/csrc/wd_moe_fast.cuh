@@ -328,7 +328,6 @@ __global__ void __launch_bounds__(kThreads, 1) moe_fast_kernel(const __grid_cons
     int *sel_ids = reinterpret_cast<int *>(misc + kFmIds);
     float *sel_w = misc + kFmW;
     uint32_t *sel_keys = reinterpret_cast<uint32_t *>(misc + kFmSelP);   // order keys of the picked logits, rank order
-    int *flags = reinterpret_cast<int *>(misc + kFmFlag);          // [0] order proven, [1] boundary id; floats: [2] boundary p
     int *loc_j = reinterpret_cast<int *>(misc + kFmLocJ), *loc_slot = reinterpret_cast<int *>(misc + kFmLocSlot);
     int *loc_n = reinterpret_cast<int *>(misc + kFmLocN);
     uint32_t *selmask = reinterpret_cast<uint32_t *>(misc + kFmSelMask);
