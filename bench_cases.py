@@ -61,6 +61,7 @@ def phase_row(st, with_period):
 
 
 def profile_case(a):
+    os.environ["WD_BATCH_SINGLE"] = "0"          # this case is about the layer kernel, also for one-layer calls
     if a.compiled:
         os.environ["WD_COMPILED_KERNEL"] = "1"
     eng = wd.Engine(2048, 512, 512, 10, 512, a.layers)

@@ -206,6 +206,9 @@ int wd_measure_tile_decoder(int device, int nsb, int warps, int unroll, double *
 /* Name of the kernel a token batch (wd_moe_forward with n_tokens > 1) runs on: the batch kernel when the engine has
  * every expert resident on one GPU and the geometry fits it, else the kernel above walking the tokens. */
 const char *wd_batch_kernel_name(const wd_engine *e);
+/* Name of the kernel the LAST forward call ran on. One-token calls of wd_moe_forward take the batch kernel too where it
+ * is available (it is the faster one for a single layer); WD_BATCH_SINGLE=0 keeps them on the layer kernel. */
+const char *wd_last_kernel_name(const wd_engine *e);
 /* Device error word of the last forward (0 = none) and a reset of the barrier state. */
 int wd_device_status(wd_engine *e, int *status);
 

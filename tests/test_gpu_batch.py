@@ -37,7 +37,19 @@ def test_batch_of_tokens_equals_single_token_calls_and_oracle(wd, oracle, cache_
             assert np.array_equal(bits(eng.tap("weights", t)), bits(r["weights"])), (n, t)
             assert np.array_equal(bits(out[t]), bits(r["out"])), (n, t)
         assert np.array_equal(bits(eng.tap("routed")), bits(oracle.moe_block(m, x[n - 1])["routed"]))
-        if n > 1:
+        if n > 1 and cache_mib == 0:
+            # the batch kernel keeps every token's intermediate values (all but the routed sum, which is the last token's)
+            assert eng.last_kernel_name() == "moe_batch_kernel"
+            r0 = oracle.moe_block(m, x[0])
+            assert np.array_equal(bits(eng.tap("logits", 0)), bits(r0["logits"]))
+            assert np.array_equal(bits(eng.tap("act", 0)), bits(r0["act"]))
+            assert np.array_equal(bits(eng.tap("expert_out", 0)), bits(r0["expert_out"]))
+            assert np.array_equal(bits(eng.tap("shared", 0)), bits(r0["shared"]))
+            assert np.array_equal(bits(eng.tap("shared_gate", 0)), bits(r0["shared_gate"]))
+            with pytest.raises(wd.WdError, match="earlier tokens"):
+                eng.tap("routed", 0)
+        elif n > 1:
+            # the token walk of the layer kernel (capped cache) keeps the earlier tokens' ids and weights only
             with pytest.raises(wd.WdError, match="earlier tokens"):
                 eng.tap("logits", 0)
     assert eng.device_status() == 0

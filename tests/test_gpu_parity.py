@@ -127,13 +127,23 @@ def test_q8_0_matvec_rows(wd, oracle, cols):
     assert np.array_equal(bits(y), bits(ref))
 
 
+@pytest.fixture(params=["batch_kernel", "layer_kernel"])
+def single_path(request, monkeypatch):
+    """One-token calls of the per-layer forward run on the batch kernel where the geometry fits it (the default) and on
+    the layer kernel otherwise or with WD_BATCH_SINGLE=0: the block tests run on both."""
+    monkeypatch.setenv("WD_BATCH_SINGLE", "1" if request.param == "batch_kernel" else "0")
+    return request.param
+
+
 def _engine_for(wd, m, n_layers=1, **kw):
     return wd.Engine(m["hidden"], m["expert_ffn"], m["n_experts"], m["top_k"], m["shared_ffn"], n_layers,
                      w_scale=m.get("w_scale", 1.0), **kw)
 
 
-def _compare_block(eng, oracle, m, x, golden_out=None):
+def _compare_block(eng, oracle, m, x, golden_out=None, path=None):
     out = eng.forward_host(0, x)
+    if path is not None:
+        assert eng.last_kernel_name() == ("moe_batch_kernel" if path == "batch_kernel" else "moe_layer_kernel")
     r = oracle.moe_block(m, x)
     assert np.array_equal(bits(eng.tap("logits")), bits(r["logits"]))
     assert np.array_equal(eng.tap("ids"), r["ids"])                      # expert indices: bit-exact
@@ -154,17 +164,17 @@ def _compare_block(eng, oracle, m, x, golden_out=None):
 
 
 @pytest.mark.parametrize("bi", [0, 1])
-def test_moe_block_small_against_oracle_and_golden(wd, oracle, bi):
+def test_moe_block_small_against_oracle_and_golden(wd, oracle, bi, single_path):
     m, xs = mg.block_cases()[bi]
     eng = _engine_for(wd, m)
     eng.load_block(0, m)
     for xi, x in enumerate(xs):
-        _compare_block(eng, oracle, m, x, GOLD[f"block{bi}_out"][xi])
+        _compare_block(eng, oracle, m, x, GOLD[f"block{bi}_out"][xi], path=single_path)
     assert eng.device_status() == 0
     eng.close()
 
 
-def test_moe_block_edge_inputs(wd, oracle):
+def test_moe_block_edge_inputs(wd, oracle, single_path):
     m, xs = mg.block_cases()[0]
     eng = _engine_for(wd, m)
     eng.load_block(0, m)
@@ -174,11 +184,11 @@ def test_moe_block_edge_inputs(wd, oracle):
     tiny = (xs[0] * 1e-30).astype(np.float32)
     big = (xs[0] * 1e4).astype(np.float32)
     for x in (zero, spike, tiny, big):
-        _compare_block(eng, oracle, m, x)
+        _compare_block(eng, oracle, m, x, path=single_path)
     eng.close()
 
 
-def test_moe_block_baseline_row_shapes(wd, oracle):
+def test_moe_block_baseline_row_shapes(wd, oracle, single_path):
     # hidden 2048 / ffn 512 / top-10 as in the headline configuration, 32 experts to keep the CPU side short
     from warpdecode_b200 import synth
     m = synth.make_moe_block(7, 2048, 512, 32, 10, 512)
@@ -186,28 +196,28 @@ def test_moe_block_baseline_row_shapes(wd, oracle):
     eng.load_block(0, m)
     rng = np.random.Generator(np.random.PCG64(8))
     for _ in range(3):
-        _compare_block(eng, oracle, m, rng.standard_normal(2048).astype(np.float32))
+        _compare_block(eng, oracle, m, rng.standard_normal(2048).astype(np.float32), path=single_path)
     eng.close()
 
 
-def test_moe_block_router_bias_and_scale(wd, oracle):
+def test_moe_block_router_bias_and_scale(wd, oracle, single_path):
     from warpdecode_b200 import synth
     m = synth.make_moe_block(9, 512, 256, 64, 10, 128, bias_sigma=1.0, w_scale=2.5)
     eng = _engine_for(wd, m)
     eng.load_block(0, m)
     rng = np.random.Generator(np.random.PCG64(10))
     for _ in range(4):
-        _compare_block(eng, oracle, m, rng.standard_normal(512).astype(np.float32))
+        _compare_block(eng, oracle, m, rng.standard_normal(512).astype(np.float32), path=single_path)
     eng.close()
 
 
-def test_moe_block_without_shared_expert(wd, oracle):
+def test_moe_block_without_shared_expert(wd, oracle, single_path):
     from warpdecode_b200 import synth
     m = synth.make_moe_block(11, 256, 256, 16, 4, 0)
     eng = _engine_for(wd, m)
     eng.load_block(0, m)
     rng = np.random.Generator(np.random.PCG64(12))
-    _compare_block(eng, oracle, m, rng.standard_normal(256).astype(np.float32))
+    _compare_block(eng, oracle, m, rng.standard_normal(256).astype(np.float32), path=single_path)
     eng.close()
 
 

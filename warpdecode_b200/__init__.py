@@ -106,6 +106,8 @@ def lib():
         L.wd_kernel_name.restype = C.c_char_p
         L.wd_batch_kernel_name.argtypes = [vp]
         L.wd_batch_kernel_name.restype = C.c_char_p
+        L.wd_last_kernel_name.argtypes = [vp]
+        L.wd_last_kernel_name.restype = C.c_char_p
         L.wd_measure_tile_decoder.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]
         L.wd_dense_decoder_create.argtypes = [C.POINTER(DenseConfig), C.POINTER(C.c_void_p)]
         L.wd_dense_decoder_destroy.argtypes = [C.c_void_p]
@@ -333,6 +335,10 @@ class Engine:
     def kernel_name(self):
         """Name of the kernel that this engine's stack step launches."""
         return lib().wd_kernel_name(self.h).decode()
+
+    def last_kernel_name(self):
+        """Name of the kernel the last forward call ran on."""
+        return lib().wd_last_kernel_name(self.h).decode()
 
     def batch_kernel_name(self):
         """Name of the kernel a token batch (forward with several tokens) runs on."""

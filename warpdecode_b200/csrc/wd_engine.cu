@@ -200,6 +200,7 @@ struct wd_engine {
     size_t fast_smem = 0;
     // the batch kernel (wd_moe_batch.cuh): token batches of a resident single-GPU engine in one pass
     bool batch_ok = false;
+    bool batch_single = false;              // one-token calls of wd_moe_forward run on the batch kernel as well
     bool last_batch = false;                // the last forward call ran on the batch kernel (it keeps fewer taps)
     wd::BatchParams bbase{};
     size_t batch_smem = 0;
@@ -358,8 +359,11 @@ void plan_batch(wd_engine *e) {
     wd::BatchParams &p = e->bbase;
     e->batch_ok = false;
     const int ncta = e->n_sm, Tm = c.max_tokens, H = c.hidden, F = c.expert_ffn, SF = c.shared_ffn, E = c.n_experts, K = c.top_k;
-    if (Tm < 2 || !e->resident || c.ep_size > 1 || E > wd::kMaxExperts || SF > 2 * wd::kThreads || Tm * K > 64) return;
+    if (!e->resident || c.ep_size > 1 || E > wd::kMaxExperts || SF > 2 * wd::kThreads || Tm * K > 64) return;
     if (const char *v = std::getenv("WD_BATCH_KERNEL")) if (std::atoi(v) == 0) return;
+    // one-token calls take the batch kernel too (29 against 34 us per call at the 48-layer model's shape) unless told otherwise
+    e->batch_single = true;
+    if (const char *v = std::getenv("WD_BATCH_SINGLE")) e->batch_single = std::atoi(v) != 0;
     const int nbh = H / 32, nbs = SF / 32;
     p.H = H; p.F = F; p.SF = SF; p.E = E; p.K = K; p.T = Tm;
     p.nsb_h = m.nsb_h; p.nsb_f = m.nsb_f; p.t2_log2 = m.t2_log2; p.t3_log2 = m.t3_log2;
@@ -1337,7 +1341,9 @@ int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, 
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
     const int H = e->cfg.hidden, K = e->cfg.top_k;
-    if (e->batch_ok && n_tokens > 1 && e->n_peers == 0 && reinterpret_cast<uintptr_t>(x_dev) % 16 == 0)
+    // (with profiling on, a one-token call stays on the layer kernel, whose phase stamps the caller is asking for)
+    if (e->batch_ok && (n_tokens > 1 || (e->batch_single && !e->profiling)) && e->n_peers == 0 &&
+        reinterpret_cast<uintptr_t>(x_dev) % 16 == 0)
         return launch_batch(e, layer, x_dev, out_dev, n_tokens, s);
     if (e->resident && !e->fast_fn && n_tokens > 1) {
         rc = launch_layers(e, layer, layer + 1, x_dev, nullptr, out_dev, s, false, n_tokens);
@@ -1441,11 +1447,11 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
     if (token == -1) token = e->last_tokens - 1;     // the last token of the last call
     if (token < 0 || token >= e->last_tokens) return fail(WD_E_INVALID, "token out of range");
     const bool per_launch = tap == WD_TAP_STAMPS || tap == WD_TAP_FALLBACKS;     // not tied to a token
-    if (token != e->last_tokens - 1 && tap != WD_TAP_IDS && tap != WD_TAP_WEIGHTS && !per_launch)
+    // the token walk of the layer kernel keeps ids and weights of every token and everything else of the last one; the batch
+    // kernel keeps everything of every token except the routed sum (last token only)
+    if (token != e->last_tokens - 1 && !per_launch &&
+        (e->last_batch ? tap == WD_TAP_ROUTED : (tap != WD_TAP_IDS && tap != WD_TAP_WEIGHTS)))
         return fail(WD_E_STATE, "only the ids and weights of earlier tokens of a batch are kept; other taps show its last token");
-    if (e->last_batch && tap != WD_TAP_IDS && tap != WD_TAP_WEIGHTS && tap != WD_TAP_ROUTED && !per_launch)
-        return fail(WD_E_STATE, "a token batch keeps the ids and weights of every token and the routed sum of the last one; "
-                                "the other taps need a single-token call");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     const wd_config &c = e->cfg;
     const wd::MoeParams &p = e->base;
@@ -1453,6 +1459,21 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
     const void *src = nullptr;              // plain buffer
     const wd::tagged_t *tsrc = nullptr;     // or tagged words of the last layer's half
     size_t n = 0;
+    if (e->last_batch && !per_launch && tap != WD_TAP_ROUTED) {       // the batch kernel's exchange words, [token][...]
+        const wd::BatchParams &b = e->bbase;
+        const size_t t = static_cast<size_t>(token);
+        switch (tap) {
+            case WD_TAP_LOGITS: tsrc = b.t_logits + t * c.n_experts; n = c.n_experts * 4; break;
+            case WD_TAP_IDS: src = e->tok_ids + t * c.top_k; n = c.top_k * 4; break;
+            case WD_TAP_WEIGHTS: src = e->tok_weights + t * c.top_k; n = c.top_k * 4; break;
+            case WD_TAP_ACT: n = static_cast<size_t>(c.top_k) * c.expert_ffn * 4; tsrc = b.t_act + t * (n / 4); break;
+            case WD_TAP_EXPERT_OUT: n = static_cast<size_t>(c.top_k) * c.hidden * 4; tsrc = b.t_eo + t * (n / 4); break;
+            case WD_TAP_SHARED: tsrc = b.t_shdown + t * c.hidden; n = c.hidden * 4; break;
+            case WD_TAP_SHARED_GATE: tsrc = b.t_shgate + t; n = 4; break;
+            case WD_TAP_SHARED_ACT: tsrc = b.t_shact + t * c.shared_ffn; n = static_cast<size_t>(c.shared_ffn) * 4; break;
+            default: return fail(WD_E_INVALID, "unknown tap");
+        }
+    } else
     switch (tap) {
         case WD_TAP_LOGITS:      // the compiled kernel: CTA 0's mailbox ([2][E] logits | [2][SF] shared act | [2][16] gate | ..)
             tsrc = e->fast_fn ? e->xbuf + par * c.n_experts : p.t_logits + par * c.n_experts;
@@ -1545,6 +1566,7 @@ int wd_measure_tile_decoder(int device, int nsb, int warps, int unroll, double *
 }
 
 const char *wd_kernel_name(const wd_engine *e) { return e && e->fast_fn ? "moe_fast_kernel" : "moe_layer_kernel"; }
+const char *wd_last_kernel_name(const wd_engine *e) { return e && e->last_batch ? "moe_batch_kernel" : wd_kernel_name(e); }
 const char *wd_batch_kernel_name(const wd_engine *e) { return e && e->batch_ok ? "moe_batch_kernel" : wd_kernel_name(e); }
 
 // ---- expert parallelism ----------------------------------------------------------------------------
