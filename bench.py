@@ -345,7 +345,7 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- speculative verify: batches of 4 tokens through the per-layer forward (one launch per layer and batch) --------
     verify = None
-    if not args.no_verify and not capped:
+    if not args.no_verify:
         gx = torch.Generator(device="cpu").manual_seed(SEED + 1)
         xb = torch.randn(4, H, generator=gx, dtype=torch.float32).cuda()
         ob = torch.zeros(4, H, dtype=torch.float32, device="cuda")

@@ -19,8 +19,11 @@ def wd():
     return w
 
 
-@pytest.mark.parametrize("cache_mib", [0, 2])
+@pytest.mark.parametrize("cache_mib", [0, 2, 4])
 def test_batch_of_tokens_equals_single_token_calls_and_oracle(wd, oracle, cache_mib):
+    """cache 0: every expert resident (batch kernel); 2 MiB: 12 slots, fewer than one batch's 16 picks (the layer kernel
+    walks the tokens, the host placing each token's experts); 4 MiB: 24 of the 32 experts fit (the batch kernel stops when
+    a pick has no slot, the host places the batch's experts, the batch runs again)."""
     from warpdecode_b200 import synth
     m = synth.make_moe_block(640, H, F, E, K, SF)
     eng = wd.Engine(H, F, E, K, SF, 1, max_tokens=4, cache_mib=cache_mib)
@@ -37,7 +40,7 @@ def test_batch_of_tokens_equals_single_token_calls_and_oracle(wd, oracle, cache_
             assert np.array_equal(bits(eng.tap("weights", t)), bits(r["weights"])), (n, t)
             assert np.array_equal(bits(out[t]), bits(r["out"])), (n, t)
         assert np.array_equal(bits(eng.tap("routed")), bits(oracle.moe_block(m, x[n - 1])["routed"]))
-        if n > 1 and cache_mib == 0:
+        if n > 1 and cache_mib != 2:
             # the batch kernel keeps every token's intermediate values (all but the routed sum, which is the last token's)
             assert eng.last_kernel_name() == "moe_batch_kernel"
             r0 = oracle.moe_block(m, x[0])
@@ -53,6 +56,10 @@ def test_batch_of_tokens_equals_single_token_calls_and_oracle(wd, oracle, cache_
             with pytest.raises(wd.WdError, match="earlier tokens"):
                 eng.tap("logits", 0)
     assert eng.device_status() == 0
+    if cache_mib:
+        hits, misses, evictions = eng.cache_stats()[:3]
+        assert misses > 0 and hits > 0
+        assert (evictions > 0) == (cache_mib == 2) or cache_mib == 4
     with pytest.raises(wd.WdError, match="max_tokens"):
         eng.forward_host(0, np.zeros((5, H), np.float32))
     eng.close()

@@ -359,7 +359,8 @@ void plan_batch(wd_engine *e) {
     wd::BatchParams &p = e->bbase;
     e->batch_ok = false;
     const int ncta = e->n_sm, Tm = c.max_tokens, H = c.hidden, F = c.expert_ffn, SF = c.shared_ffn, E = c.n_experts, K = c.top_k;
-    if (!e->resident || c.ep_size > 1 || E > wd::kMaxExperts || SF > 2 * wd::kThreads || Tm * K > 64) return;
+    if (c.ep_size > 1 || E > wd::kMaxExperts || SF > 2 * wd::kThreads || Tm * K > 64) return;
+    if (!e->resident && e->n_slots < static_cast<int64_t>(Tm) * K) return;      // a capped pool must hold one batch's picks
     if (const char *v = std::getenv("WD_BATCH_KERNEL")) if (std::atoi(v) == 0) return;
     // one-token calls take the batch kernel too (29 against 34 us per call at the 48-layer model's shape) unless told otherwise
     e->batch_single = true;
@@ -575,7 +576,7 @@ int launch_layer(wd_engine *e, int layer, const float *x, float *residual, float
 }
 
 // A batch of n_tokens activations through one layer on the batch kernel (one cooperative launch).
-int launch_batch(wd_engine *e, int layer, const float *x, float *out, int n_tokens, cudaStream_t s) {
+int launch_batch(wd_engine *e, int layer, const float *x, float *out, int n_tokens, cudaStream_t s, bool stop_on_miss = false) {
     const Layer &L = e->layers[layer];
     if (!L.have_router || !L.have_experts || (e->cfg.shared_ffn > 0 && !L.have_shared))
         return fail(WD_E_STATE, "layer " + std::to_string(layer) + " has no weights yet");
@@ -587,6 +588,8 @@ int launch_batch(wd_engine *e, int layer, const float *x, float *out, int n_toke
     p.T = n_tokens;
     p.threshold_select = e->threshold_select ? 1 : 0;
     p.fallbacks = e->fallbacks;
+    p.stop_on_miss = stop_on_miss ? 1 : 0;
+    p.miss_info = stop_on_miss ? e->miss_info : nullptr;
     p.x = x;
     p.out = out;
     p.ids = e->tok_ids;
@@ -777,6 +780,40 @@ int forward_capped(wd_engine *e, int layer, const float *x, float *residual, flo
     return launch_layers(e, layer, layer + 1, x, residual, out, s, false);
 }
 
+// A token batch on a capped cache: the batch kernel stops before its tile phase when a picked expert has no slot; the host
+// then places every token's picks (hits are touched first, so one token's misses cannot evict another's picks as long as
+// the pool holds a whole batch) and launches again.
+int forward_capped_batch(wd_engine *e, int layer, const float *x, float *out, int n_tokens, cudaStream_t s) {
+    const int K = e->cfg.top_k;
+    for (int attempt = 0;; ++attempt) {
+        e->miss_info[0] = -1;
+        int rc = launch_batch(e, layer, x, out, n_tokens, s, true);
+        if (rc) return rc;
+        WD_CUDA(cudaStreamSynchronize(s));
+        const int missed = e->miss_info[0];
+        if (missed < 0) return fail(WD_E_DEVICE, "the batch kernel left no report of its picks");
+        if (missed == 0) {
+            if (attempt == 0) {         // every pick was a hit: count and touch them (a relaunch was counted when it was placed)
+                for (int i = 0; i < n_tokens * K; ++i) {
+                    const int x_id = e->miss_info[1 + i];
+                    if (x_id >= 0 && x_id < e->cfg.n_experts && e->layers[layer].h_slot[x_id] >= 0) {
+                        ++e->hits;
+                        touch_slot(e, e->layers[layer].h_slot[x_id]);
+                    }
+                }
+            }
+            return WD_OK;
+        }
+        if (attempt >= 2) return fail(WD_E_DEVICE, "a token batch missed again right after its experts were placed");
+        std::vector<int> picks(e->miss_info + 1, e->miss_info + 1 + n_tokens * K);   // acquire_selected reuses the pinned words
+        for (int t = 0; t < n_tokens; ++t) {
+            if ((rc = acquire_selected(e, layer, s, picks.data() + t * K))) return rc;
+            // the next token's misses go through the same pinned ring and device staging: this token's copies must have left them
+            WD_CUDA(cudaStreamSynchronize(e->copy_stream));
+        }
+    }
+}
+
 int check_device_status(wd_engine *e) {
     unsigned st = 0;
     WD_CUDA(cudaMemcpy(&st, e->sync + 2, sizeof(st), cudaMemcpyDeviceToHost));
@@ -933,7 +970,7 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
         WD_TRY(cudaMallocHost(&e->miss_pinned, one_expert * K));
         WD_TRY(cudaMalloc(&e->miss_staging, one_expert * K));
         WD_TRY(cudaMallocHost(&e->pinned_ids, sizeof(int) * K));
-        WD_TRY(cudaMallocHost(&e->miss_info, sizeof(int) * (1 + static_cast<size_t>(c.n_layers) * K)));
+        WD_TRY(cudaMallocHost(&e->miss_info, sizeof(int) * (1 + static_cast<size_t>(std::max(c.n_layers, c.max_tokens)) * K)));
         e->copy_pool = new CopyPool(std::max(1, std::min(8, static_cast<int>(std::thread::hardware_concurrency()))));
     }
 #undef WD_TRY
@@ -1342,9 +1379,10 @@ int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, 
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
     const int H = e->cfg.hidden, K = e->cfg.top_k;
     // (with profiling on, a one-token call stays on the layer kernel, whose phase stamps the caller is asking for)
-    if (e->batch_ok && (n_tokens > 1 || (e->batch_single && !e->profiling)) && e->n_peers == 0 &&
-        reinterpret_cast<uintptr_t>(x_dev) % 16 == 0)
-        return launch_batch(e, layer, x_dev, out_dev, n_tokens, s);
+    if (e->batch_ok && e->n_peers == 0 && reinterpret_cast<uintptr_t>(x_dev) % 16 == 0) {
+        if (!e->resident && n_tokens > 1) return forward_capped_batch(e, layer, x_dev, out_dev, n_tokens, s);
+        if (e->resident && (n_tokens > 1 || (e->batch_single && !e->profiling))) return launch_batch(e, layer, x_dev, out_dev, n_tokens, s);
+    }
     if (e->resident && !e->fast_fn && n_tokens > 1) {
         rc = launch_layers(e, layer, layer + 1, x_dev, nullptr, out_dev, s, false, n_tokens);
         if (rc) return rc;

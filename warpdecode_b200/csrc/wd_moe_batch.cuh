@@ -57,6 +57,11 @@ struct BatchParams {
     unsigned *sync;              // the engine's status / epoch words (see MoeParams::sync)
     unsigned *host_status;
     unsigned *fallbacks;
+    // Capped expert cache: when a picked expert has no slot the launch stops before any tile is touched (every CTA
+    // sees the same picks and the same slot table, so all of them stop), miss_info[0] = 1, and the host places the
+    // experts and launches again. miss_info (page-locked host memory, nullable): [0] missed, then the picks [T][K].
+    int stop_on_miss;
+    int *miss_info;
     unsigned long long *stamps;  // nullable: [cta][kStampStride] SM clock counter of thread 0 at the steps of the launch (profiling)
     // shared memory plan (byte offsets, 128-byte aligned)
     unsigned off_tab, off_tab2, off_tok, tok_stride, tok_xd0, tok_xk, tok_xdk, tok_shq, tok_shd, tok_sel;
@@ -321,9 +326,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_batch_kernel(const __grid_con
             __syncthreads();
         }
     }
-    const int n_tiles = seg_begin[2 * T];
+    int n_tiles = seg_begin[2 * T];
     const int n_sd = P.SF > 0 ? (P.H >> 2) : 0;
-    const int my_sd = n_sd > cta ? (n_sd - cta + ncta - 1) / ncta : 0;
+    int my_sd = n_sd > cta ? (n_sd - cta + ncta - 1) / ncta : 0;
+    bool stopped = false;
     const unsigned sd_bytes = static_cast<unsigned>(nbs) * 136u;
     const int ns = static_cast<int>(P.ring);
     const int act_per_tok = n_exp_tok * P.nsb_f;
@@ -389,6 +395,23 @@ __global__ void __launch_bounds__(kThreads, 1) moe_batch_kernel(const __grid_con
         }
         mbar_wait(&bars[bar_tab], 0, err);
         __syncthreads();
+        if (P.miss_info != nullptr) {
+            int miss = 0, e = 0;
+            if (tid < T * P.K) {
+                e = ids_of(tid / P.K)[tid % P.K];
+                miss = slot_tab[e] < 0;
+            }
+            miss = __syncthreads_or(miss);
+            if (cta == 0) {
+                if (tid < T * P.K) P.miss_info[1 + tid] = e;
+                if (tid == 0) P.miss_info[0] = miss ? 1 : 0;
+            }
+            if (miss && P.stop_on_miss) {       // nothing of the tile phase runs; the front's copies have all been waited for
+                stopped = true;
+                n_tiles = 0;
+                my_sd = 0;
+            }
+        }
         // the picked experts' slots complete the tile addresses
 #pragma unroll 1
         for (int i = tid; i < n_tiles; i += kThreads) {
@@ -549,7 +572,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_batch_kernel(const __grid_con
         const int rpc = (P.H + ncta - 1) / ncta;
         const int t = tid / rpc, r = tid - t * rpc;
         const int row = cta * rpc + r;
-        if (t < T && row < P.H) {
+        if (t < T && row < P.H && !stopped) {
             const float *sel_w = w_of(t);
             tagged_t w[kMaxK] = {}, wsd = 0, wsg = 0;
             const tagged_t *src = P.t_eo + static_cast<size_t>(t) * P.K * P.H + row;
