@@ -202,6 +202,7 @@ struct RefMoeWeights {
     const uint8_t * shared_gate;
     const uint8_t * shared_up;
     const uint8_t * shared_down;
+    const float * router_f32;   // F32 router [n_experts][hidden] (src/qwen38_moe.cuh:2252-2258); null: the Q8_0 one
 };
 
 // One MoE block on `threads` host threads. ids/weights/out are outputs; ids_in, when
@@ -209,7 +210,9 @@ struct RefMoeWeights {
 int ref_moe_block(const RefMoeWeights * w, const float * x, int threads, int * ids, float * weights,
                   float * logits_out, float * out) {
     const int H = w->hidden, F = w->expert_ffn, SF = w->shared_ffn, E = w->n_experts, K = w->top_k;
-    if (H % 256 || F % 256 || SF % 32 || K > 16 || K <= 0) return -1;
+    // q38_moe_expert_q8_act_geometry (src/qwen38_moe.cuh:2181-2183): hidden % 256, expert_ffn % 64; a Q8_K activation
+    // for the down projection needs whole superblocks
+    if (H % 256 || F % (uses_q8k(w->down_type) ? 256 : 64) || SF % 32 || K > 16 || K <= 0) return -1;
     const int gt = cm::block_type_from_ggml(w->gate_type);
     const int ut = cm::block_type_from_ggml(w->up_type);
     const int dt = cm::block_type_from_ggml(w->down_type);
@@ -223,7 +226,8 @@ int ref_moe_block(const RefMoeWeights * w, const float * x, int threads, int * i
     std::vector<float> logits(static_cast<size_t>(E)), probs(static_cast<size_t>(E));
     pool->parallel_for(threads, [&](int t) {
         for (int e = t; e < E; e += threads) {
-            float v = cm::row_q8_0_q8_0(w->router + static_cast<size_t>(e) * q8_h, x_q80.data(), H);
+            float v = w->router_f32 ? cm::dot_f32_avx2(w->router_f32 + static_cast<size_t>(e) * H, x, H)
+                                    : cm::row_q8_0_q8_0(w->router + static_cast<size_t>(e) * q8_h, x_q80.data(), H);
             if (w->router_bias) v = v + w->router_bias[e];
             logits[static_cast<size_t>(e)] = v;
         }

@@ -479,8 +479,9 @@ static float dot_any(int type, const uint8_t *row, const wdo_q8k *yk, const uint
 }
 
 /* Composition of one block, in the order the reference engine runs it:
- *   router   : Q8_0-quantised x, Q8_0 GEMV, (+bias), softmax/top-k
- *              (src/qwen38_moe.cuh:2323-2361)
+ *   router   : Q8_0-quantised x, Q8_0 GEMV (or, for an F32 router, one
+ *              ggml_vec_dot_f32 per expert on the F32 x), (+bias), softmax/top-k
+ *              (src/qwen38_moe.cuh:2242-2258, :2323-2361)
  *   experts  : Q8_K-quantised x; per selected expert gate and up rows, silu(g)*u
  *              as a separate rounded product, re-quantise with the quantiser the
  *              down type calls for, down rows (src/qwen38_cpu_moe.cuh:1169-1217)
@@ -492,7 +493,8 @@ static float dot_any(int type, const uint8_t *row, const wdo_q8k *yk, const uint
 int wdo_moe_block(const wdo_moe_weights *w, const float *x, wdo_moe_result *r, int first_expert,
                   int n_local) {
     const int H = w->hidden, F = w->expert_ffn, SF = w->shared_ffn, E = w->n_experts, K = w->top_k;
-    if (H <= 0 || H % 256 || F <= 0 || F % 256 || E <= 0 || K <= 0 || K > 64 || K > E) return -1;
+    if (H <= 0 || H % 256 || F <= 0 || E <= 0 || K <= 0 || K > 64 || K > E) return -1;
+    if (F % (uses_q8k(w->down_type) ? 256 : 64)) return -1;
     if (SF % 32 || !r || !r->out) return -1;
     if (!uses_q8k(w->gate_type) || !uses_q8k(w->up_type)) return -2;
     const size_t gate_rb = wdo_row_bytes(w->gate_type, H), up_rb = wdo_row_bytes(w->up_type, H);
@@ -515,7 +517,8 @@ int wdo_moe_block(const wdo_moe_weights *w, const float *x, wdo_moe_result *r, i
 
     wdo_quantize_q8_0(x, x_q80, H / 32);
     for (int e = 0; e < E; ++e) {
-        logits[e] = wdo_row_q8_0_q8_0(w->router + (size_t)e * q8_rb_h, x_q80, H);
+        logits[e] = w->router_f32 ? wdo_dot_f32(w->router_f32 + (size_t)e * H, x, H)
+                                  : wdo_row_q8_0_q8_0(w->router + (size_t)e * q8_rb_h, x_q80, H);
         if (w->router_bias) logits[e] = logits[e] + w->router_bias[e];
     }
     wdo_router_exact(logits, E, K, w->w_scale, probs, ids, wts);

@@ -91,15 +91,20 @@ def router_cases():
 
 
 def block_cases():
-    """(model dict, inputs [n, H]) for small MoE blocks."""
+    """(model dict, inputs [n, H]) for small MoE blocks. The last three have the geometry rules of the reference's own
+    model (src/qwen38_moe.cuh:2181-2211, :2252-2258): hidden a multiple of 256 that is not a power of two, expert_ffn
+    a multiple of 64, IQ4_NL down tensors with a Q8_0 activation, and (two of them) an F32 router."""
     out = []
-    for i, (H, F, E, K, SF, et, dt, bias) in enumerate([
-            (256, 256, 16, 4, 256, ol.TYPE_IQ3_S, ol.TYPE_IQ3_S, 0.0),
-            (512, 256, 32, 10, 128, ol.TYPE_IQ3_S, ol.TYPE_IQ3_S, 1.0),
-            (512, 512, 16, 6, 256, ol.TYPE_IQ2_S, ol.TYPE_IQ2_S, 0.0),
-            (256, 512, 24, 8, 64, ol.TYPE_IQ2_S, ol.TYPE_IQ3_S, 0.0)]):
+    for i, (H, F, E, K, SF, et, dt, bias, rf32) in enumerate([
+            (256, 256, 16, 4, 256, ol.TYPE_IQ3_S, ol.TYPE_IQ3_S, 0.0, False),
+            (512, 256, 32, 10, 128, ol.TYPE_IQ3_S, ol.TYPE_IQ3_S, 1.0, False),
+            (512, 512, 16, 6, 256, ol.TYPE_IQ2_S, ol.TYPE_IQ2_S, 0.0, False),
+            (256, 512, 24, 8, 64, ol.TYPE_IQ2_S, ol.TYPE_IQ3_S, 0.0, False),
+            (768, 192, 16, 4, 128, ol.TYPE_IQ3_S, ol.TYPE_IQ4_NL, 0.5, False),
+            (2560, 640, 8, 4, 640, ol.TYPE_IQ2_S, ol.TYPE_IQ4_NL, 0.0, True),
+            (1280, 256, 24, 10, 0, ol.TYPE_IQ3_S, ol.TYPE_IQ2_S, 1.0, True)]):
         m = synth.make_moe_block(100 + i, H, F, E, K, SF, et, dt, sigma=0.02, bias_sigma=bias,
-                                 w_scale=1.0 if i != 2 else 1.25)
+                                 w_scale=1.0 if i not in (2, 5) else 1.25, router_f32=rf32)
         rng = np.random.Generator(np.random.PCG64(200 + i))
         out.append((m, rng.standard_normal((4, H)).astype(np.float32)))
     return out

@@ -49,6 +49,7 @@ class MoeWeightsC(C.Structure):
         ("gate", _u8p), ("up", _u8p), ("down", _u8p),
         ("shared_gate_vec", _f32p),
         ("shared_gate", _u8p), ("shared_up", _u8p), ("shared_down", _u8p),
+        ("router_f32", _f32p),
     ]
 
 
@@ -256,9 +257,9 @@ class Oracle:
 
         w = MoeWeightsC(m["hidden"], m["expert_ffn"], m.get("shared_ffn", 0), m["n_experts"], m["top_k"],
                         m["gate_type"], m["up_type"], m["down_type"], m.get("w_scale", 1.0),
-                        u8(m["router"]), f32(m.get("router_bias")), u8(m["gate"]), u8(m["up"]), u8(m["down"]),
+                        u8(m.get("router")), f32(m.get("router_bias")), u8(m["gate"]), u8(m["up"]), u8(m["down"]),
                         f32(m.get("shared_gate_vec")), u8(m.get("shared_gate")), u8(m.get("shared_up")),
-                        u8(m.get("shared_down")))
+                        u8(m.get("shared_down")), f32(m.get("router_f32")))
         H, F, E, K = m["hidden"], m["expert_ffn"], m["n_experts"], m["top_k"]
         res = {
             "logits": np.zeros(E, np.float32), "probs": np.zeros(E, np.float32),
@@ -381,9 +382,9 @@ class Reference:
 
         w = MoeWeightsC(m["hidden"], m["expert_ffn"], m.get("shared_ffn", 0), m["n_experts"], m["top_k"],
                         m["gate_type"], m["up_type"], m["down_type"], m.get("w_scale", 1.0),
-                        u8(m["router"]), f32(m.get("router_bias")), u8(m["gate"]), u8(m["up"]), u8(m["down"]),
+                        u8(m.get("router")), f32(m.get("router_bias")), u8(m["gate"]), u8(m["up"]), u8(m["down"]),
                         f32(m.get("shared_gate_vec")), u8(m.get("shared_gate")), u8(m.get("shared_up")),
-                        u8(m.get("shared_down")))
+                        u8(m.get("shared_down")), f32(m.get("router_f32")))
         H, E, K = m["hidden"], m["n_experts"], m["top_k"]
         ids = np.zeros(K, np.int32)
         wts = np.zeros(K, np.float32)

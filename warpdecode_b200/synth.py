@@ -178,8 +178,27 @@ def quantize_iq2_s(w):
     return out.reshape(rows, -1)
 
 
+IQ4_NL_VALUES = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.int8)
+
+
+def quantize_iq4_nl(w):
+    """IQ4_NL: per block of 32 an f16 scale d = max|w| / 127 and the nearest of the sixteen codebook values;
+    byte j holds value j in its low nibble and value j + 16 in its high nibble (src/qwen38_cpu_moe.cuh:377-422)."""
+    w = np.ascontiguousarray(w, np.float32)
+    rows, cols = w.shape
+    b = w.reshape(rows, cols // 32, 32)
+    d = (np.abs(b).max(-1) / np.float32(127)).astype(np.float16)
+    df = d.astype(np.float32)
+    inv = np.where(df > 0, 1 / np.where(df > 0, df, 1), 0).astype(np.float32)
+    idx = np.abs((b * inv[..., None])[..., None] - IQ4_NL_VALUES.astype(np.float32)).argmin(-1).astype(np.uint8)
+    out = np.empty((rows, cols // 32, 18), np.uint8)
+    out[..., 0:2] = d.view(np.uint8).reshape(rows, cols // 32, 2)
+    out[..., 2:] = idx[..., :16] | (idx[..., 16:] << 4)
+    return out.reshape(rows, -1)
+
+
 QUANTIZERS = {TYPE_Q8_0: quantize_q8_0, TYPE_Q4_0: quantize_q4_0, TYPE_IQ3_S: quantize_iq3_s,
-              TYPE_IQ2_S: quantize_iq2_s}
+              TYPE_IQ2_S: quantize_iq2_s, TYPE_IQ4_NL: quantize_iq4_nl}
 
 
 def dequantize(t, blob, rows, cols):
@@ -191,6 +210,10 @@ def dequantize(t, blob, rows, cols):
     if t == TYPE_Q4_0:
         q = blob[..., 2:]
         v = np.concatenate([(q & 15), (q >> 4)], -1).astype(np.float32) - 8
+        return (v * d[..., None]).reshape(rows, cols)
+    if t == TYPE_IQ4_NL:
+        q = blob[..., 2:]
+        v = IQ4_NL_VALUES[np.concatenate([(q & 15), (q >> 4)], -1)].astype(np.float32)
         return (v * d[..., None]).reshape(rows, cols)
     g3, g2 = grids()
     if t == TYPE_IQ3_S:
@@ -222,9 +245,10 @@ def dequantize(t, blob, rows, cols):
 # synthetic MoE block
 # ---------------------------------------------------------------------------
 def make_moe_block(seed, hidden, expert_ffn, n_experts, top_k, shared_ffn=None, expert_type=TYPE_IQ3_S,
-                   down_type=None, sigma=0.02, bias_sigma=0.0, w_scale=1.0):
+                   down_type=None, sigma=0.02, bias_sigma=0.0, w_scale=1.0, router_f32=False):
     """One block's weights in ggml layout, N(0, sigma) from `seed`, in a fixed tensor order:
-    router, gate, up, down, shared gate vector, shared gate/up/down, router bias."""
+    router, gate, up, down, shared gate vector, shared gate/up/down, router bias. `router_f32`: the router stays
+    F32 [E][H] under the key "router_f32" (the reference model's ffn_gate_inp) instead of Q8_0 under "router"."""
     rng = np.random.Generator(np.random.PCG64(seed))
     shared_ffn = expert_ffn if shared_ffn is None else shared_ffn
     down_type = expert_type if down_type is None else down_type
@@ -235,7 +259,10 @@ def make_moe_block(seed, hidden, expert_ffn, n_experts, top_k, shared_ffn=None, 
 
     m = dict(hidden=H, expert_ffn=F, shared_ffn=shared_ffn, n_experts=E, top_k=top_k,
              gate_type=expert_type, up_type=expert_type, down_type=down_type, w_scale=w_scale)
-    m["router"] = quantize_q8_0(normal((E, H))).reshape(-1)
+    if router_f32:
+        m["router_f32"] = normal((E, H)).reshape(-1)
+    else:
+        m["router"] = quantize_q8_0(normal((E, H))).reshape(-1)
     qe, qd = QUANTIZERS[expert_type], QUANTIZERS[down_type]
     m["gate"] = np.concatenate([qe(normal((F, H))).reshape(-1) for _ in range(E)])
     m["up"] = np.concatenate([qe(normal((F, H))).reshape(-1) for _ in range(E)])
@@ -299,7 +326,9 @@ def moe_block_tensors(m, layer):
     (src/qwen38_moe.cuh:569-573, :601-612)."""
     p = f"blk.{layer}."
     H, F, E, SF = m["hidden"], m["expert_ffn"], m["n_experts"], m["shared_ffn"]
-    t = [(p + "ffn_gate_inp.weight", [H, E], TYPE_Q8_0, m["router"]),
+    router = (p + "ffn_gate_inp.weight", [H, E], TYPE_F32, m["router_f32"]) if "router_f32" in m else \
+        (p + "ffn_gate_inp.weight", [H, E], TYPE_Q8_0, m["router"])
+    t = [router,
          (p + "ffn_gate_exps.weight", [H, F, E], m["gate_type"], m["gate"]),
          (p + "ffn_up_exps.weight", [H, F, E], m["up_type"], m["up"]),
          (p + "ffn_down_exps.weight", [F, H, E], m["down_type"], m["down"])]
