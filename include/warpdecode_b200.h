@@ -34,6 +34,7 @@ extern "C" {
 #define WD_TYPE_F32 0
 #define WD_TYPE_Q4_0 2
 #define WD_TYPE_Q8_0 8
+#define WD_TYPE_IQ4_NL 20
 #define WD_TYPE_IQ3_S 21
 #define WD_TYPE_IQ2_S 22
 
@@ -42,14 +43,21 @@ typedef struct wd_engine wd_engine;
 /* Geometry of the MoE stack. Replaces the fields load_qwen38_runtime() derives from the
  * GGUF (src/qwen38_runtime.cuh:117-147, src/qwen38_layout.hpp:102-211) and the limits of
  * Qwen38MoeScratch::initialize (src/qwen38_moe.cuh:1709-1714: experts <= 4096, k <= 16). */
+/* Two families of kernels serve an engine. The TILED kernels (one launch per layer, per token batch or per stack of
+ * layers; slot cache; expert parallelism) take hidden = 256 * 2^n (n <= 5), expert_ffn = 256 * 2^n (n <= 3), IQ3_S or
+ * IQ2_S experts with gate and up of one type, and a Q8_0 router. Any other configuration that the reference's
+ * ggml-exact path accepts (q38_moe_separate_experts_q8_act_compatible, src/qwen38_moe.cuh:2181-2211: hidden % 256 == 0,
+ * expert_ffn % 64 == 0, IQ4_NL down tensors; an F32 router, :2252-2258) - the reference's own 2560 / 640 model among
+ * them - runs on the PLAIN-LAYOUT path: tensors stay in ggml layout, one warp per row, every expert resident, one GPU,
+ * per-layer calls only (wd_moe_forward, wd_moe_forward_host, wd_read_tap); the other entry points return WD_E_INVALID. */
 typedef struct {
-    int32_t hidden;          /* multiple of 256, power-of-two number of superblocks <= 32 */
-    int32_t expert_ffn;      /* same constraint */
+    int32_t hidden;          /* multiple of 256 */
+    int32_t expert_ffn;      /* multiple of 256 (IQ3_S / IQ2_S down) or of 64 (IQ4_NL down) */
     int32_t shared_ffn;      /* 0 = no shared expert; else multiple of 128 */
     int32_t n_experts;       /* multiple of 8, <= 1024 */
     int32_t top_k;           /* 1..16 */
     int32_t n_layers;
-    int32_t gate_type, up_type, down_type;   /* WD_TYPE_IQ3_S or WD_TYPE_IQ2_S */
+    int32_t gate_type, up_type, down_type;   /* WD_TYPE_IQ3_S or WD_TYPE_IQ2_S; down also WD_TYPE_IQ4_NL */
     float w_scale;           /* expert_weights_scale; 0 or 1 = none */
     int32_t ep_rank, ep_size;/* this engine owns experts [rank*E/size, (rank+1)*E/size) */
     int32_t max_tokens;      /* tokens per forward call, 1..4 (batch verify) */
@@ -58,6 +66,9 @@ typedef struct {
                                 Same meaning as WARODECODE_EXPERT_CACHE_MIB
                                 (src/qwen38_tuning.hpp:113-116). */
     float rms_eps;           /* epsilon of the optional fused RMSNorm prologue */
+    int32_t router_f32;      /* nonzero: the router is F32 [n_experts][hidden], set with wd_set_router_f32 and applied
+                                to the F32 input in ggml_vec_dot_f32 order (src/qwen38_moe.cuh:2252-2258,
+                                src/matrix.cuh:218-250); 0: Q8_0, set with wd_set_router */
 } wd_config;
 
 /* ---- lifetime ------------------------------------------------------------------------ */
@@ -80,6 +91,9 @@ int64_t wd_default_cache_mib(int64_t memory_mib);
 /* Router of one layer: Q8_0 [n_experts][hidden] in ggml layout, host memory; optional F32
  * per-expert logit bias. Replaces upload_matrix(router) (src/qwen38_runtime.cuh:198). */
 int wd_set_router(wd_engine *e, int layer, const void *router_q8_0, const float *bias);
+/* Same for an engine created with router_f32: F32 [n_experts][hidden], host memory (launch_matrix_gemv_f32_weights,
+ * src/matrix.cuh:257). */
+int wd_set_router_f32(wd_engine *e, int layer, const float *router, const float *bias);
 /* Shared expert of one layer: F32 gate vector [hidden] and Q8_0 gate/up [shared_ffn][hidden],
  * down [hidden][shared_ffn]. Replaces load_qwen38_shared_expert (src/qwen38_moe.cuh:564-599). */
 int wd_set_shared(wd_engine *e, int layer, const float *gate_vec, const void *gate_q8_0,
@@ -91,6 +105,11 @@ int wd_set_norm(wd_engine *e, int layer, const float *weight);
  * lifetime, exactly as the reference requires of its GgufFile (src/qwen38_runtime.cuh:201).
  * Experts this rank owns are uploaded now when the pool holds them all, otherwise on demand. */
 int wd_set_experts(wd_engine *e, int layer, const void *gate, const void *up, const void *down);
+/* Same with the ggml type of each tensor given per layer (the reference model's routed experts are IQ2_S in every
+ * layer but one, which is IQ3_S: src/qwen38_moe.cuh:2185-2190). An engine on the plain-layout path takes any accepted
+ * combination per layer; a tiled engine only the types it was created with. */
+int wd_set_experts_typed(wd_engine *e, int layer, const void *gate, int gate_type, const void *up, int up_type,
+                         const void *down, int down_type);
 /* Same, from ggml-layout tensors already in DEVICE memory (used by the synthetic model
  * generator); needs a pool that holds every owned expert. Nothing is retained. */
 int wd_set_experts_device(wd_engine *e, int layer, const void *gate, const void *up, const void *down);

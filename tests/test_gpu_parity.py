@@ -270,7 +270,9 @@ def test_device_generated_model_round_trips_through_oracle(wd, oracle):
 
 def test_unsupported_geometry_is_refused_with_a_message(wd):
     with pytest.raises(wd.WdError, match="hidden"):
-        wd.Engine(2560, 512, 64, 10, 512)
+        wd.Engine(2500, 512, 64, 10, 512)
+    with pytest.raises(wd.WdError, match="expert_ffn"):       # 640 columns are not whole superblocks for an IQ3_S down tensor
+        wd.Engine(2560, 640, 64, 10, 640)
     with pytest.raises(wd.WdError, match="top_k"):
         wd.Engine(2048, 512, 64, 32, 512)
     eng = wd.Engine(256, 256, 16, 4, 0)

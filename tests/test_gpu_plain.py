@@ -1,0 +1,123 @@
+"""GPU parity of the plain-layout path: the geometries and tensor types of the reference's own model
+(src/qwen38_moe.cuh:2181-2211, :2252-2258: hidden 2560, expert_ffn 640, IQ4_NL down tensors fed by a Q8_0 activation,
+an F32 router), which the tiled kernels do not take. Same bar as everywhere else: every intermediate and the output
+equal to the CPU oracle bit for bit, and to the golden outputs the reference composition produced."""
+import os
+
+import numpy as np
+import pytest
+
+import make_golden as mg
+import oracle_lib as ol
+from warpdecode_b200 import synth
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "oracle_pins.npz"))
+bits = ol.fbits
+
+
+@pytest.fixture(scope="module")
+def wd():
+    import warpdecode_b200 as w
+    w.lib()
+    return w
+
+
+def _engine_for(wd, m, **kw):
+    return wd.Engine(m["hidden"], m["expert_ffn"], m["n_experts"], m["top_k"], m["shared_ffn"], 1,
+                     expert_type=m["gate_type"], down_type=m["down_type"], w_scale=m.get("w_scale", 1.0),
+                     router_f32="router_f32" in m, **kw)
+
+
+def _compare(eng, r, out, token=None):
+    assert np.array_equal(bits(eng.tap("logits", token)), bits(r["logits"]))
+    assert np.array_equal(eng.tap("ids", token), r["ids"])
+    assert np.array_equal(bits(eng.tap("weights", token)), bits(r["weights"]))
+    assert np.array_equal(bits(eng.tap("act", token)), bits(r["act"]))
+    assert np.array_equal(bits(eng.tap("expert_out", token)), bits(r["expert_out"]))
+    assert np.array_equal(bits(eng.tap("routed", token)), bits(r["routed"]))
+    if eng.cfg.shared_ffn:
+        assert np.array_equal(bits(eng.tap("shared_gate", token)), bits(r["shared_gate"]))
+        assert np.array_equal(bits(eng.tap("shared", token)), bits(r["shared"]))
+    assert np.array_equal(bits(out), bits(r["out"]))
+
+
+@pytest.mark.parametrize("bi", [4, 5, 6])
+def test_blocks_outside_the_tiled_geometries_match_oracle_and_golden(wd, oracle, bi):
+    m, xs = mg.block_cases()[bi]
+    eng = _engine_for(wd, m)
+    assert eng.kernel_name() == "plain_gate_up_kernel"
+    eng.load_block(0, m)
+    for xi, x in enumerate(xs):
+        out = eng.forward_host(0, x)
+        _compare(eng, oracle.moe_block(m, x), out)
+        assert np.array_equal(bits(out), GOLD[f"block{bi}_out"][xi])
+        assert np.array_equal(eng.tap("ids"), GOLD[f"block{bi}_ids"][xi])
+    H = m["hidden"]
+    spike = np.zeros(H, np.float32); spike[7] = 1000.0
+    for x in (np.zeros(H, np.float32), spike, (xs[0] * 1e-30).astype(np.float32), (xs[0] * 1e4).astype(np.float32)):
+        _compare(eng, oracle.moe_block(m, x), eng.forward_host(0, x))
+    assert eng.device_status() == 0
+    eng.close()
+
+
+@pytest.mark.parametrize("bi", [4, 5])
+def test_token_batch_equals_single_calls(wd, oracle, bi):
+    m, xs = mg.block_cases()[bi]
+    eng = _engine_for(wd, m, max_tokens=4)
+    eng.load_block(0, m)
+    outs = eng.forward_host(0, xs)
+    for t in range(4):
+        r = oracle.moe_block(m, xs[t])
+        assert np.array_equal(bits(outs[t]), bits(r["out"]))
+        assert np.array_equal(eng.tap("ids", t), r["ids"])
+        assert np.array_equal(bits(eng.tap("expert_out", t)), bits(r["expert_out"]))
+    eng.close()
+
+
+def test_reference_model_block_shape_512_experts(wd, oracle):
+    """hidden 2560, expert_ffn 640, 512 experts, top 10, IQ2_S gate/up, IQ4_NL down, F32 router with a bias, shared
+    expert of 640: the block of the reference's model. Expert tensors are random block bytes with sane scales, the way
+    the reference's host tests fill rows (tests/qwen38_cpu_moe_host_test.cpp:72-119); the oracle reads the same bytes."""
+    H, F, E, K, SF = 2560, 640, 512, 10, 640
+    rng = np.random.Generator(np.random.PCG64(77))
+    m = synth.make_moe_block(5, H, F, 8, 8, SF, ol.TYPE_IQ2_S, ol.TYPE_IQ4_NL, sigma=0.02, router_f32=True)   # the shared expert
+    m.update(n_experts=E, top_k=K, w_scale=1.25)
+    m["router_f32"] = (rng.standard_normal(E * H) * 0.02).astype(np.float32)
+    m["router_bias"] = (rng.standard_normal(E) * 0.5).astype(np.float32)
+    m["gate"] = ol.random_blocks(rng, ol.TYPE_IQ2_S, E * F * H // 256)
+    m["up"] = ol.random_blocks(rng, ol.TYPE_IQ2_S, E * F * H // 256)
+    m["down"] = ol.random_blocks(rng, ol.TYPE_IQ4_NL, E * H * F // 32)
+    eng = _engine_for(wd, m, max_tokens=4)
+    eng.load_block(0, m)
+    xs = rng.standard_normal((4, H)).astype(np.float32)
+    outs = eng.forward_host(0, xs)
+    for t in range(4):
+        r = oracle.moe_block(m, xs[t])
+        assert np.array_equal(eng.tap("ids", t), r["ids"])
+        assert np.array_equal(bits(eng.tap("act", t)), bits(r["act"]))
+        assert np.array_equal(bits(outs[t]), bits(r["out"]))
+    _compare(eng, oracle.moe_block(m, xs[0]), eng.forward_host(0, xs[0]))
+    eng.close()
+
+
+def test_layers_of_different_expert_types_and_a_gguf_file(wd, oracle, tmp_path):
+    """The reference model mixes IQ2_S and IQ3_S layers (src/qwen38_moe.cuh:2185-2190); the loader gives each layer
+    the types the file holds."""
+    m0 = synth.make_moe_block(31, 768, 192, 16, 4, 128, ol.TYPE_IQ2_S, ol.TYPE_IQ4_NL, sigma=0.02, router_f32=True)
+    m1 = synth.make_moe_block(32, 768, 192, 16, 4, 128, ol.TYPE_IQ3_S, ol.TYPE_IQ4_NL, sigma=0.02, router_f32=True)
+    path = str(tmp_path / "plain.gguf")
+    meta = {"general.architecture": "qwen4exp", "qwen4exp.embedding_length": 768, "qwen4exp.expert_count": 16,
+            "qwen4exp.expert_used_count": 4, "qwen4exp.expert_feed_forward_length": 192,
+            "qwen4exp.expert_shared_feed_forward_length": 128, "qwen4exp.expert_weights_scale": 1.0}
+    synth.write_gguf(path, meta, synth.moe_block_tensors(m0, 0) + synth.moe_block_tensors(m1, 1))
+    g = wd.Gguf(path)
+    eng = wd.Engine.from_gguf(g)
+    x = np.random.Generator(np.random.PCG64(9)).standard_normal(768).astype(np.float32)
+    for layer, m in ((0, m0), (1, m1)):
+        out = eng.forward_host(layer, x)
+        assert np.array_equal(bits(out), bits(oracle.moe_block(m, x)["out"]))
+    with pytest.raises(wd.WdError, match="plain-layout"):
+        eng.stack_step_host(x)
+    eng.close()
+    g.close()

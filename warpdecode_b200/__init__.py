@@ -16,11 +16,11 @@ ROOT = os.path.dirname(HERE)
 LIB_PATH = os.path.join(HERE, "libwarpdecode_b200.so")
 SOURCES = [os.path.join(HERE, "csrc", f) for f in
            ("wd_engine.cu", "wd_aux_kernels.cuh", "wd_moe_kernel.cuh", "wd_moe_kernel_phases.inc", "wd_moe_fast.cuh", "wd_moe_batch.cuh", "wd_dense_decoder.cuh", "wd_dense_decoder.inc", "wd_dense_token.cuh",
-            "wd_blocks.cuh", "wd_router.cuh",
+            "wd_plain_moe.cuh", "wd_plain_moe.inc", "wd_blocks.cuh", "wd_router.cuh",
             "wd_formats.cuh", "wd_device.cuh", "wd_dense.cuh", "wd_gguf.inc",
             "wd_grids.h")] + [os.path.join(ROOT, "include", "warpdecode_b200.h")]
 
-TYPE_F32, TYPE_Q4_0, TYPE_Q8_0, TYPE_IQ3_S, TYPE_IQ2_S = 0, 2, 8, 21, 22
+TYPE_F32, TYPE_Q4_0, TYPE_Q8_0, TYPE_IQ4_NL, TYPE_IQ3_S, TYPE_IQ2_S = 0, 2, 8, 20, 21, 22
 TAPS = dict(logits=0, ids=1, weights=2, act=3, expert_out=4, routed=5, shared=6, shared_gate=7, shared_act=8)
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -49,7 +49,7 @@ class Config(C.Structure):
                 ("gate_type", C.c_int32), ("up_type", C.c_int32), ("down_type", C.c_int32),
                 ("w_scale", C.c_float), ("ep_rank", C.c_int32), ("ep_size", C.c_int32),
                 ("max_tokens", C.c_int32), ("device", C.c_int32), ("cache_mib", C.c_int64),
-                ("rms_eps", C.c_float)]
+                ("rms_eps", C.c_float), ("router_f32", C.c_int32)]
 
 
 class DenseConfig(C.Structure):
@@ -81,9 +81,11 @@ def lib():
         L.wd_engine_destroy.restype = None
         vp, i = C.c_void_p, C.c_int
         L.wd_set_router.argtypes = [vp, i, vp, vp]
+        L.wd_set_router_f32.argtypes = [vp, i, vp, vp]
         L.wd_set_shared.argtypes = [vp, i, vp, vp, vp, vp]
         L.wd_set_norm.argtypes = [vp, i, vp]
         L.wd_set_experts.argtypes = [vp, i, vp, vp, vp]
+        L.wd_set_experts_typed.argtypes = [vp, i, vp, i, vp, i, vp, i]
         L.wd_set_experts_device.argtypes = [vp, i, vp, vp, vp]
         L.wd_cache_acquire.argtypes = [vp, i, i, C.POINTER(C.c_int)]
         L.wd_cache_stats.argtypes = [vp, C.POINTER(C.c_int64)]
@@ -196,16 +198,17 @@ class Engine:
         """Engine with the file's geometry, every layer loaded (the Gguf must outlive the engine)."""
         c = gguf.config()
         eng = cls(c.hidden, c.expert_ffn, c.n_experts, c.top_k, c.shared_ffn, c.n_layers, expert_type=c.gate_type,
-                  down_type=c.down_type, w_scale=c.w_scale, rms_eps=c.rms_eps, **kw)
+                  down_type=c.down_type, w_scale=c.w_scale, rms_eps=c.rms_eps, router_f32=bool(c.router_f32), **kw)
         _check(lib().wd_engine_load_gguf(eng.h, gguf.h))
         eng._keep.append(gguf)
         return eng
 
     def __init__(self, hidden, expert_ffn, n_experts, top_k, shared_ffn=0, n_layers=1, expert_type=TYPE_IQ3_S,
-                 w_scale=1.0, ep_rank=0, ep_size=1, device=0, cache_mib=0, rms_eps=1e-6, max_tokens=1, down_type=None):
+                 w_scale=1.0, ep_rank=0, ep_size=1, device=0, cache_mib=0, rms_eps=1e-6, max_tokens=1, down_type=None,
+                 router_f32=False):
         self.cfg = Config(hidden, expert_ffn, shared_ffn, n_experts, top_k, n_layers, expert_type, expert_type,
                           expert_type if down_type is None else down_type, w_scale, ep_rank, ep_size, max_tokens,
-                          device, cache_mib, rms_eps)
+                          device, cache_mib, rms_eps, int(router_f32))
         self.h = C.c_void_p()
         _check(lib().wd_engine_create(C.byref(self.cfg), C.byref(self.h)))
         self._keep = []
@@ -226,15 +229,21 @@ class Engine:
         """m: dict in the layout of synth.make_moe_block (ggml block bytes, host numpy arrays)."""
         u8 = lambda a: np.ascontiguousarray(a, np.uint8)
         f32 = lambda a: np.ascontiguousarray(a, np.float32)
-        router = u8(m["router"])
         bias = f32(m["router_bias"]) if m.get("router_bias") is not None else None
-        _check(lib().wd_set_router(self.h, layer, _ptr(router), _ptr(bias)))
+        if self.cfg.router_f32:
+            _check(lib().wd_set_router_f32(self.h, layer, _ptr(f32(m["router_f32"])), _ptr(bias)))
+        else:
+            _check(lib().wd_set_router(self.h, layer, _ptr(u8(m["router"])), _ptr(bias)))
         if self.cfg.shared_ffn:
             gv, sg, su, sd = f32(m["shared_gate_vec"]), u8(m["shared_gate"]), u8(m["shared_up"]), u8(m["shared_down"])
             _check(lib().wd_set_shared(self.h, layer, _ptr(gv), _ptr(sg), _ptr(su), _ptr(sd)))
         g, u, d = u8(m["gate"]), u8(m["up"]), u8(m["down"])
         self._keep += [g, u, d]           # the library retains these host pointers
-        _check(lib().wd_set_experts(self.h, layer, _ptr(g), _ptr(u), _ptr(d)))
+        if (m["gate_type"], m["up_type"], m["down_type"]) != (self.cfg.gate_type, self.cfg.up_type, self.cfg.down_type):
+            _check(lib().wd_set_experts_typed(self.h, layer, _ptr(g), m["gate_type"], _ptr(u), m["up_type"], _ptr(d),
+                                              m["down_type"]))
+        else:
+            _check(lib().wd_set_experts(self.h, layer, _ptr(g), _ptr(u), _ptr(d)))
 
     def set_norm(self, layer, w):
         w = None if w is None else np.ascontiguousarray(w, np.float32)

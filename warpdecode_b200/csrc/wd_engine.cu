@@ -24,6 +24,7 @@
 #include "wd_dense.cuh"
 #include "wd_dense_decoder.cuh"
 #include "wd_dense_token.cuh"
+#include "wd_plain_moe.cuh"
 #include "wd_grids.h"
 
 namespace {
@@ -135,8 +136,11 @@ private:
 
 }  // namespace
 
+struct wd_plain_moe;
+
 struct wd_engine {
     wd_config cfg{};
+    wd_plain_moe *plain = nullptr;          // set: the engine runs the plain-layout path (wd_plain_moe.inc) and nothing else
     int n_sm = 0;
     cudaStream_t stream = nullptr;
     int nsb_h = 0, nsb_f = 0, e_first = 0, e_count = 0;
@@ -835,6 +839,11 @@ int check_device_status(wd_engine *e) {
 
 }  // namespace
 
+#include "wd_plain_moe.inc"
+
+#define WD_TILED_ONLY(e)                                                                                              \
+    if ((e) && (e)->plain) return fail(WD_E_INVALID, "not available on an engine that runs the plain-layout path (wd_engine_create)")
+
 extern "C" {
 
 const char *wd_last_error(void) { return g_error.c_str(); }
@@ -853,9 +862,10 @@ int64_t wd_default_cache_mib(int64_t memory_mib) {
 int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     if (!cfg || !out) return fail(WD_E_INVALID, "null argument");
     const wd_config &c = *cfg;
-    if (c.hidden % 256 || !pow2(c.hidden / 256) || c.hidden / 256 > 32)
+    const bool plain = plain_wanted(c);
+    if (!plain && (c.hidden % 256 || !pow2(c.hidden / 256) || c.hidden / 256 > 32))
         return fail(WD_E_INVALID, "hidden must be 256 * 2^n, n <= 5");
-    if (c.expert_ffn % 256 || !pow2(c.expert_ffn / 256) || c.expert_ffn / 256 > 8)
+    if (!plain && (c.expert_ffn % 256 || !pow2(c.expert_ffn / 256) || c.expert_ffn / 256 > 8))
         return fail(WD_E_INVALID, "expert_ffn must be 256 * 2^n, n <= 3");
     if (c.shared_ffn < 0 || c.shared_ffn % 128) return fail(WD_E_INVALID, "shared_ffn must be a multiple of 128");
     if (c.n_experts <= 0 || c.n_experts % 8 || c.n_experts > wd::kMaxExperts)
@@ -863,7 +873,7 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     if (c.top_k < 1 || c.top_k > wd::kMaxK || c.top_k > c.n_experts) return fail(WD_E_INVALID, "top_k must be 1..16");
     if (c.n_layers < 1) return fail(WD_E_INVALID, "n_layers must be positive");
     auto iq = [](int t) { return t == WD_TYPE_IQ3_S || t == WD_TYPE_IQ2_S; };
-    if (!iq(c.gate_type) || !iq(c.down_type) || c.up_type != c.gate_type)
+    if (!plain && (!iq(c.gate_type) || !iq(c.down_type) || c.up_type != c.gate_type))
         return fail(WD_E_INVALID, "expert tensors must be IQ3_S or IQ2_S, gate and up of the same type");
     if (c.ep_size < 1 || c.ep_rank < 0 || c.ep_rank >= c.ep_size || c.n_experts % c.ep_size)
         return fail(WD_E_INVALID, "ep_rank/ep_size must partition n_experts evenly");
@@ -875,6 +885,9 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
     cudaDeviceProp prop{};
     WD_CUDA(cudaGetDeviceProperties(&prop, c.device));
     if (prop.major < 10) return fail(WD_E_INVALID, "this library is built for sm_100a only");
+    // geometries and tensor types outside the tiled kernels (the reference's own 2560 / 640 model, IQ4_NL down tensors,
+    // an F32 router) run on ggml-layout tensors, one warp per row
+    if (plain) return plain_create(c, prop, out);
 
     wd_engine *e = new wd_engine();
     e->cfg = c;
@@ -1075,6 +1088,7 @@ void wd_engine_destroy(wd_engine *e) {
     if (!e) return;
     cudaSetDevice(e->cfg.device);
     if (e->stream) cudaStreamSynchronize(e->stream);
+    plain_destroy(e);
     wd_ep_disconnect(e);
     for (Layer &L : e->layers) {
         cudaFree(L.router); cudaFree(L.bias); cudaFree(L.gate_vec); cudaFree(L.sh_gate); cudaFree(L.sh_up);
@@ -1105,6 +1119,7 @@ int wd_set_router(wd_engine *e, int layer, const void *router_q8_0, const float 
     int rc = check_layer(e, layer);
     if (rc) return rc;
     if (!router_q8_0) return fail(WD_E_INVALID, "null router");
+    if (e->cfg.router_f32) return fail(WD_E_STATE, "this engine was created for an F32 router: use wd_set_router_f32");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     Layer &L = e->layers[layer];
     if ((rc = upload_repacked_q8(e, router_q8_0, e->cfg.n_experts, e->cfg.hidden, &L.router))) return rc;
@@ -1113,6 +1128,18 @@ int wd_set_router(wd_engine *e, int layer, const void *router_q8_0, const float 
     }
     L.have_router = true;
     e->layer_table_dirty = true;
+    return WD_OK;
+}
+
+int wd_set_router_f32(wd_engine *e, int layer, const float *router, const float *bias) {
+    int rc = check_layer(e, layer);
+    if (rc) return rc;
+    if (!router) return fail(WD_E_INVALID, "null router");
+    if (!e->plain || !e->cfg.router_f32) return fail(WD_E_STATE, "this engine was not created with router_f32 set");
+    WD_CUDA(cudaSetDevice(e->cfg.device));
+    if ((rc = upload_f32(e, router, static_cast<size_t>(e->cfg.n_experts) * e->cfg.hidden, &e->plain->layers[layer].router_f32))) return rc;
+    if (bias && (rc = upload_f32(e, bias, e->cfg.n_experts, &e->layers[layer].bias))) return rc;
+    e->layers[layer].have_router = true;
     return WD_OK;
 }
 
@@ -1256,7 +1283,18 @@ static int load_layer_resident(wd_engine *e, int layer) {
 static int set_experts_from(wd_engine *e, int layer, const void *gate, const void *up, const void *down, int fd,
                             uint64_t file_gate, uint64_t file_up, uint64_t file_down);
 
+int wd_set_experts_typed(wd_engine *e, int layer, const void *gate, int gate_type, const void *up, int up_type,
+                         const void *down, int down_type) {
+    if (!e) return fail(WD_E_INVALID, "null engine");
+    if (e->plain) return plain_set_experts(e, layer, gate, gate_type, up, up_type, down, down_type, cudaMemcpyHostToDevice);
+    if (gate_type != e->cfg.gate_type || up_type != e->cfg.up_type || down_type != e->cfg.down_type)
+        return fail(WD_E_INVALID, "this engine takes the tensor types it was created with in every layer");
+    return wd_set_experts(e, layer, gate, up, down);
+}
+
 int wd_set_experts(wd_engine *e, int layer, const void *gate, const void *up, const void *down) {
+    if (e && e->plain)
+        return plain_set_experts(e, layer, gate, e->cfg.gate_type, up, e->cfg.up_type, down, e->cfg.down_type, cudaMemcpyHostToDevice);
     return set_experts_from(e, layer, gate, up, down, -1, 0, 0, 0);
 }
 
@@ -1291,6 +1329,8 @@ static int set_experts_from(wd_engine *e, int layer, const void *gate, const voi
 }
 
 int wd_set_experts_device(wd_engine *e, int layer, const void *gate, const void *up, const void *down) {
+    if (e && e->plain)
+        return plain_set_experts(e, layer, gate, e->cfg.gate_type, up, e->cfg.up_type, down, e->cfg.down_type, cudaMemcpyDeviceToDevice);
     int rc = check_layer(e, layer);
     if (rc) return rc;
     if (!e->resident) return fail(WD_E_STATE, "device-side expert upload needs a pool that holds every owned expert");
@@ -1330,6 +1370,7 @@ int64_t wd_cache_slot_count(const wd_engine *e) { return e ? e->n_slots : 0; }
 int64_t wd_cache_slot_bytes(const wd_engine *e) { return e ? static_cast<int64_t>(e->slot_bytes) : 0; }
 
 int wd_cache_acquire(wd_engine *e, int layer, int expert, int *slot_out) {
+    WD_TILED_ONLY(e);
     int rc = check_layer(e, layer);
     if (rc) return rc;
     if (expert < e->e_first || expert >= e->e_first + e->e_count)
@@ -1377,6 +1418,7 @@ int wd_moe_forward(wd_engine *e, int layer, const float *x_dev, float *out_dev, 
     if (!x_dev || !out_dev) return fail(WD_E_INVALID, "null buffer");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
+    if (e->plain) return plain_forward(e, layer, x_dev, out_dev, n_tokens, s);
     const int H = e->cfg.hidden, K = e->cfg.top_k;
     // (with profiling on, a one-token call stays on the layer kernel, whose phase stamps the caller is asking for)
     if (e->batch_ok && e->n_peers == 0 && reinterpret_cast<uintptr_t>(x_dev) % 16 == 0) {
@@ -1419,6 +1461,7 @@ int wd_moe_forward_host(wd_engine *e, int layer, const float *x_host, float *out
 }
 
 int wd_stack_step(wd_engine *e, float *residual_dev, void *stream) {
+    WD_TILED_ONLY(e);
     if (!e || !residual_dev) return fail(WD_E_INVALID, "null argument");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
@@ -1435,6 +1478,7 @@ int wd_stack_step(wd_engine *e, float *residual_dev, void *stream) {
 }
 
 int wd_stack_step_host(wd_engine *e, const float *in_host, float *out_host) {
+    WD_TILED_ONLY(e);
     if (!e || !in_host || !out_host) return fail(WD_E_INVALID, "null argument");
     const size_t bytes = static_cast<size_t>(e->cfg.hidden) * 4;
     WD_CUDA(cudaSetDevice(e->cfg.device));
@@ -1484,6 +1528,10 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
     if (!e || !dst) return fail(WD_E_INVALID, "null argument");
     if (token == -1) token = e->last_tokens - 1;     // the last token of the last call
     if (token < 0 || token >= e->last_tokens) return fail(WD_E_INVALID, "token out of range");
+    if (e->plain) {
+        WD_CUDA(cudaSetDevice(e->cfg.device));
+        return plain_read_tap(e, tap, token, dst, bytes);
+    }
     const bool per_launch = tap == WD_TAP_STAMPS || tap == WD_TAP_FALLBACKS;     // not tied to a token
     // the token walk of the layer kernel keeps ids and weights of every token and everything else of the last one; the batch
     // kernel keeps everything of every token except the routed sum (last token only)
@@ -1568,6 +1616,7 @@ int wd_read_tap(wd_engine *e, int tap, int token, void *dst, size_t bytes) {
 }
 
 int wd_set_profiling(wd_engine *e, int on) {
+    WD_TILED_ONLY(e);
     if (!e) return fail(WD_E_INVALID, "null engine");
     e->profiling = on != 0;
     e->stamp_layer = on > 1 ? on - 1 : 0;   // on = 1 + offset of the profiled layer within a launch
@@ -1603,7 +1652,10 @@ int wd_measure_tile_decoder(int device, int nsb, int warps, int unroll, double *
     return WD_OK;
 }
 
-const char *wd_kernel_name(const wd_engine *e) { return e && e->fast_fn ? "moe_fast_kernel" : "moe_layer_kernel"; }
+const char *wd_kernel_name(const wd_engine *e) {
+    if (e && e->plain) return "plain_gate_up_kernel";     // the longest of the seven kernels of a plain-layout call
+    return e && e->fast_fn ? "moe_fast_kernel" : "moe_layer_kernel";
+}
 const char *wd_last_kernel_name(const wd_engine *e) { return e && e->last_batch ? "moe_batch_kernel" : wd_kernel_name(e); }
 const char *wd_batch_kernel_name(const wd_engine *e) { return e && e->batch_ok ? "moe_batch_kernel" : wd_kernel_name(e); }
 
@@ -1611,6 +1663,7 @@ const char *wd_batch_kernel_name(const wd_engine *e) { return e && e->batch_ok ?
 int wd_ep_handle_bytes(void) { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
 
 int wd_ep_export(wd_engine *e, void *handle_out) {
+    WD_TILED_ONLY(e);
     if (!e || !handle_out) return fail(WD_E_INVALID, "null argument");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaIpcMemHandle_t h;
@@ -1640,6 +1693,7 @@ int ep_check_connect(wd_engine *e, int n_peers) {
 }  // namespace
 
 int wd_ep_connect(wd_engine *e, int n_peers, const void *handles) {
+    WD_TILED_ONLY(e);
     int rc = ep_check_connect(e, n_peers);
     if (rc) return rc;
     if (n_peers > 0 && !handles) return fail(WD_E_INVALID, "null handles");
@@ -1666,6 +1720,7 @@ int wd_ep_connect(wd_engine *e, int n_peers, const void *handles) {
 }
 
 int wd_ep_connect_local(wd_engine *e, int n_peers, wd_engine *const *peers) {
+    WD_TILED_ONLY(e);
     int rc = ep_check_connect(e, n_peers);
     if (rc) return rc;
     if (n_peers > 0 && !peers) return fail(WD_E_INVALID, "null peers");
@@ -1709,6 +1764,7 @@ int wd_ep_disconnect(wd_engine *e) {
 }
 
 int wd_reset_exchange(wd_engine *e) {
+    WD_TILED_ONLY(e);
     if (!e) return fail(WD_E_INVALID, "null engine");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     WD_CUDA(cudaDeviceSynchronize());
@@ -2065,6 +2121,7 @@ int wd_synth_tensor_device(int type, int rows, int cols, float sigma, uint64_t s
 static uint64_t sid(int layer, int which) { return static_cast<uint64_t>(layer) * 16 + which; }
 
 int wd_synth_model(wd_engine *e, uint64_t seed, float sigma, float bias_sigma) {
+    WD_TILED_ONLY(e);
     if (!e) return fail(WD_E_INVALID, "null engine");
     e->layer_table_dirty = true;
     if (e->cfg.gate_type != WD_TYPE_IQ3_S || e->cfg.down_type != WD_TYPE_IQ3_S)
@@ -2132,6 +2189,7 @@ int wd_synth_model(wd_engine *e, uint64_t seed, float sigma, float bias_sigma) {
 
 int wd_synth_expert_host(wd_engine *e, uint64_t seed, float sigma, int layer, int expert, void *gate, void *up,
                          void *down) {
+    WD_TILED_ONLY(e);
     int rc = check_layer(e, layer);
     if (rc) return rc;
     if (expert < 0 || expert >= e->cfg.n_experts || !gate || !up || !down) return fail(WD_E_INVALID, "bad argument");
@@ -2155,6 +2213,7 @@ int wd_synth_expert_host(wd_engine *e, uint64_t seed, float sigma, int layer, in
 
 int wd_synth_dense_host(wd_engine *e, uint64_t seed, float sigma, float bias_sigma, int layer, void *router,
                         float *bias, float *gate_vec, void *sh_gate, void *sh_up, void *sh_down) {
+    WD_TILED_ONLY(e);
     int rc = check_layer(e, layer);
     if (rc) return rc;
     WD_CUDA(cudaSetDevice(e->cfg.device));
