@@ -8,6 +8,10 @@ were captured from (ncu wants a short program with few launches), and the kernel
     python bench_cases.py batch [--layers 2] [--tokens 4] [--iters 4] [--stamps]
         token batches (speculative verify) through the per-layer forward on the batch kernel; --stamps prints the
         kernel's own step times (median over CTAs)
+    python bench_cases.py plain [--layers 2] [--tokens 1] [--iters 20]
+        the plain-layout path at the block shape of the reference's own model (hidden 2560, expert_ffn 640, 512
+        experts, top 10, IQ2_S gate/up, IQ4_NL down, F32 router, shared expert 640; random block bytes): per-layer
+        forward calls, time per call from CUDA events on the launching stream
     python bench_cases.py decoder
         the IQ3_S tile decoder alone, tiles resident in shared memory: cycles per round of tiles for 16, 8, 4 and 1
         active warps per SM (the issue bound of the expert GEMVs)
@@ -141,6 +145,51 @@ def batch_case(a):
             d = np.median(st[:, idx] - st[:, 0]) / mhz
             print("  %-24s ends at %6.2f us (+%.2f)" % (name, d, d - prev))
             prev = d
+    eng.close()
+
+
+def plain_case(a):
+    import torch
+    from warpdecode_b200 import synth
+    H, F, E, K, SF = 2560, 640, 512, 10, 640
+    eng = wd.Engine(H, F, E, K, SF, a.layers, expert_type=synth.TYPE_IQ2_S, down_type=synth.TYPE_IQ4_NL, w_scale=1.25,
+                    router_f32=True, max_tokens=4)
+    print("kernel:", eng.kernel_name())
+    rng = np.random.Generator(np.random.PCG64(4))
+    small = synth.make_moe_block(5, H, F, 8, 8, SF, synth.TYPE_IQ2_S, synth.TYPE_IQ4_NL, sigma=0.02, router_f32=True)
+    for l in range(a.layers):
+        m = dict(small)
+        m["router_f32"] = (rng.standard_normal(E * H) * 0.02).astype(np.float32)
+        m["router_bias"] = (rng.standard_normal(E) * 0.5).astype(np.float32)
+        m["gate"] = synth.random_blocks(rng, synth.TYPE_IQ2_S, E * F * H // 256)
+        m["up"] = synth.random_blocks(rng, synth.TYPE_IQ2_S, E * F * H // 256)
+        m["down"] = synth.random_blocks(rng, synth.TYPE_IQ4_NL, E * H * F // 32)
+        eng.load_block(l, m)
+    x = torch.randn(4, H, generator=torch.Generator().manual_seed(2), dtype=torch.float32).cuda()
+    out = torch.zeros_like(x)
+    ts = torch.cuda.Stream()
+    sp = ts.cuda_stream
+    with torch.cuda.stream(ts):
+        for _ in range(3):
+            for l in range(a.layers):
+                eng.forward_device(l, x.data_ptr(), out.data_ptr(), sp, a.tokens)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(ts):
+        e0.record(ts)
+        for _ in range(a.iters):
+            for l in range(a.layers):
+                eng.forward_device(l, x.data_ptr(), out.data_ptr(), sp, a.tokens)
+        e1.record(ts)
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (a.iters * a.layers)
+    # bytes one token reads in a layer: ten experts' gate, up and down rows, the F32 router, the shared expert
+    layer_bytes = K * (2 * F * (H // 256) * 82 + H * (F // 32) * 18) + E * H * 4 + 3 * SF * (H // 32) * 34
+    peak = measured_peak()
+    print("%d tokens per call: %.2f us per call, %.2f us per token and layer; %.1f MB per token and layer -> %.0f GB/s = %.3f of "
+          "the measured HBM peak (%.0f GB/s); status %d" % (a.tokens, us, us / a.tokens, layer_bytes / 1e6,
+                                                          layer_bytes * a.tokens / us / 1e3, layer_bytes * a.tokens / us / 1e3 / peak, peak,
+                                                          eng.device_status()))
     eng.close()
 
 
@@ -314,6 +363,11 @@ def main():
     p.add_argument("--iters", type=int, default=4)
     p.add_argument("--stamps", action="store_true")
     p.set_defaults(fn=batch_case)
+    p = sub.add_parser("plain")
+    p.add_argument("--layers", type=int, default=2)
+    p.add_argument("--tokens", type=int, default=1)
+    p.add_argument("--iters", type=int, default=20)
+    p.set_defaults(fn=plain_case)
     p = sub.add_parser("dense-decode")
     p.add_argument("--layers", type=int, default=16)
     p.add_argument("--vocab", type=int, default=128256)

@@ -45,6 +45,24 @@ int fail(int code, const std::string &msg) {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Launch with the programmatic-serialization attribute: the kernel may be scheduled while its predecessor in the
+// stream still runs; it orders itself behind it with grid_dep_wait() (wd_device.cuh).
+template <class... KArgs, class... Args>
+cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+
 bool pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 
 // Device buffers of a stand-alone entry point: released when the function returns, on every path.

@@ -8,8 +8,16 @@
 // else in this library: integer sums per (superblock or block, chunk-lane), one fmaf per block and chunk-lane in
 // block order, ggml's 8-lane closing tree (src/qwen38_cpu_moe.cuh:290-440).
 //
-// One call is seven small kernels on the caller's stream (quantise, router + shared gate/up rows, selection, expert
-// gate/up rows, activation quantiser, down rows, ordered combine); blockIdx.y is the token of a verify batch.
+// One call is four kernels on the caller's stream, launched with programmatic stream serialization so that each one's
+// start-up (and every weight copy that does not depend on its predecessor) overlaps the kernel before it:
+//   rows     x -> Q8_0; router logits, the shared expert's gate/up rows with SiLU * up, its sigmoid gate
+//   select   softmax / top-k; x -> Q8_K; the shared activation -> Q8_0
+//   gate_up  gate and up rows of the selected experts, SiLU * up
+//   down     activation quantiser, down rows of the selected experts and of the shared expert, ordered combine
+// Every CTA brings the weight bytes it will read into shared memory with bulk copies issued at once (a chunk of
+// sixteen consecutive rows is contiguous and a multiple of 16 bytes in every format), so no row product waits on
+// HBM in its dependent chain. Each kernel first waits for its predecessor, then releases its successor: whatever a
+// kernel reads before that wait was written at least two kernels earlier.
 #pragma once
 
 #include "wd_blocks.cuh"
@@ -20,7 +28,7 @@ namespace wd {
 constexpr int kTypeIq4nl = 20;
 
 struct PlainParams {
-    int H, F, SF, E, K;
+    int H, F, SF, E, K, T;                  // T: tokens of this call
     int gate_type, up_type, down_type;      // ggml ids: IQ3_S / IQ2_S; down also IQ4_NL
     float w_scale;
     // weights of the layer
@@ -49,6 +57,7 @@ struct PlainParams {
     float *eo;          // [K][H]
     float *shdown;      // [H]
     float *routed;      // [H]
+    unsigned *status;   // error word of the engine (a copy that never arrives raises kErrCopyTimeout there)
 };
 
 // 0xff in byte j where bit j of the nibble is set
@@ -148,7 +157,7 @@ __device__ __forceinline__ float plain_row_iq4nl_half(const uint8_t *row, int nb
                                                       const uint8_t *lut, int lane) {
     const int par = (lane >> 3) & 1, l = lane & 7, hi = l >> 2, k = 4 * (l & 3);
     float acc = 0.0f;
-#pragma unroll 2
+#pragma unroll 5
     for (int b = par; b < nb; b += 2) {
         const uint8_t *wb = row + b * 18;
         const uint32_t w = *reinterpret_cast<const uint16_t *>(wb + 2 + k) |
@@ -162,6 +171,118 @@ __device__ __forceinline__ float plain_row_iq4nl_half(const uint8_t *row, int nb
     }
     acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
     return hsum8_lanes(acc);
+}
+
+// ---- gate and up row of one expert row index in one pass -------------------------------------------------------------
+// The rows above spend most of their instructions on meeting the integer sums of the eight sub-blocks by shuffles. Here
+// a lane keeps a whole superblock to itself: unit u in [0, 2 nsb) is superblock u of the gate row or superblock u - nsb
+// of the up row; lane (grp = lane / 4, p = lane % 4) takes chunk-lanes 2p and 2p + 1 of units grp, grp + 8, ..., all
+// eight sub-blocks, so its two integer sums per unit are complete. The float chains (one fmaf per superblock in
+// superblock order for each row and chunk-lane) then run on every lane from values handed round by shuffles.
+// Codebooks are read expanded from shared memory: IQ3_S 512 x 4 magnitudes, IQ2_S 1024 x 8.
+constexpr int kPlainActStride = 272;        // bytes between superblocks of the activation: groups hit different banks
+
+__device__ __forceinline__ void plain_build_tables(uint32_t *t3, uint64_t *t2, const uint16_t *grid3, const uint16_t *grid2,
+                                                   bool need3, bool need2) {
+    if (need3)
+        for (int i = threadIdx.x; i < 512; i += blockDim.x) {
+            const uint32_t pk = grid3[i];
+            uint32_t g = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) g |= (2u * ((pk >> (3 * j)) & 7u) + 1u) << (8 * j);
+            t3[i] = g;
+        }
+    if (need2)
+        for (int i = threadIdx.x; i < 1024; i += blockDim.x) t2[i] = wd_iq2s_unpack(grid2[i]);
+}
+
+__device__ __forceinline__ void plain_unit_iq3s(const uint8_t *blk, const int8_t *a, int p, const uint32_t *t3, int &s0, int &s1) {
+    uint32_t qh[4], sc[2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) qh[i] = *reinterpret_cast<const uint16_t *>(blk + 66 + 2 * i);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) sc[i] = *reinterpret_cast<const uint16_t *>(blk + 106 + 2 * i);
+    s0 = s1 = 0;
+#pragma unroll
+    for (int ib = 0; ib < 8; ++ib) {
+        const uint32_t q2 = *reinterpret_cast<const uint16_t *>(blk + 2 + ib * 8 + 2 * p);
+        const uint32_t sg = blk[74 + ib * 4 + p];
+        const uint32_t h = (qh[ib >> 1] >> (8 * (ib & 1) + 2 * p));
+        const int ls = 1 + 2 * static_cast<int>((sc[ib >> 2] >> (4 * (ib & 3))) & 15u);
+        const int2 av = *reinterpret_cast<const int2 *>(a + ib * 32 + p * 8);
+        const uint32_t g0 = t3[(q2 & 0xffu) | ((h & 1u) << 8)], g1 = t3[(q2 >> 8) | ((h & 2u) << 7)];
+        s0 += dp4a_s8(av.x, apply_signs(g0, sg & 15u), 0) * ls;
+        s1 += dp4a_s8(av.y, apply_signs(g1, sg >> 4), 0) * ls;
+    }
+}
+
+__device__ __forceinline__ void plain_unit_iq2s(const uint8_t *blk, const int8_t *a, int p, const uint64_t *t2, int &s0, int &s1) {
+    uint32_t qh[4], sc[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        qh[i] = *reinterpret_cast<const uint16_t *>(blk + 66 + 2 * i);
+        sc[i] = *reinterpret_cast<const uint16_t *>(blk + 74 + 2 * i);
+    }
+    s0 = s1 = 0;
+#pragma unroll
+    for (int ib = 0; ib < 8; ++ib) {
+        const uint32_t hb = (qh[ib >> 1] >> (8 * (ib & 1))) & 0xffu, scb = (sc[ib >> 1] >> (8 * (ib & 1))) & 0xffu;
+        const uint32_t idx = blk[2 + ib * 4 + p] | (((hb >> (2 * p)) & 3u) << 8);
+        const uint32_t sg = blk[34 + ib * 4 + p];
+        const int ls = 1 + 2 * static_cast<int>(p < 2 ? (scb & 15u) : (scb >> 4));
+        const int2 av = *reinterpret_cast<const int2 *>(a + ib * 32 + p * 8);
+        const uint2 g = *reinterpret_cast<const uint2 *>(t2 + idx);
+        s0 += dp4a_s8(av.x, apply_signs(g.x, sg & 15u), 0) * ls;
+        s1 += dp4a_s8(av.y, apply_signs(g.y, sg >> 4), 0) * ls;
+    }
+}
+
+// a: the Q8_K activation in shared memory with kPlainActStride bytes per superblock; da: its scales. nsb <= 16.
+__device__ __forceinline__ void plain_gate_up_pair(int gtype, int utype, const uint8_t *grow, const uint8_t *urow, int nsb,
+                                                   const int8_t *a, const float *da, const uint32_t *t3, const uint64_t *t2,
+                                                   int lane, float &g_out, float &u_out) {
+    const int grp = lane >> 2, p = lane & 3, total = 2 * nsb;
+    int s0[4], s1[4];
+    float dd[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        s0[k] = s1[k] = 0;
+        dd[k] = 0.0f;
+        const int unit = k * 8 + grp;
+        if (k * 8 < total && unit < total) {
+            const bool is_up = unit >= nsb;
+            const int sb = is_up ? unit - nsb : unit, type = is_up ? utype : gtype;
+            const uint8_t *blk = (is_up ? urow : grow) + sb * iq_block_bytes(type);
+            if (type == kTypeIq2s) plain_unit_iq2s(blk, a + sb * kPlainActStride, p, t2, s0[k], s1[k]);
+            else plain_unit_iq3s(blk, a + sb * kPlainActStride, p, t3, s0[k], s1[k]);
+            dd[k] = __fmul_rn(half_bits_to_float(*reinterpret_cast<const uint16_t *>(blk)), da[sb]);
+        }
+    }
+    float ge = 0.0f, go = 0.0f, ue = 0.0f, uo = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (k * 8 >= total) break;
+#pragma unroll
+        for (int gq = 0; gq < 8; ++gq) {
+            const int unit = k * 8 + gq;
+            if (unit >= total) break;
+            const int src = gq * 4 + p;
+            const float v0 = static_cast<float>(__shfl_sync(0xffffffffu, s0[k], src));
+            const float v1 = static_cast<float>(__shfl_sync(0xffffffffu, s1[k], src));
+            const float d = __shfl_sync(0xffffffffu, dd[k], src);
+            if (unit < nsb) {
+                ge = __fmaf_rn(d, v0, ge);
+                go = __fmaf_rn(d, v1, go);
+            } else {
+                ue = __fmaf_rn(d, v0, ue);
+                uo = __fmaf_rn(d, v1, uo);
+            }
+        }
+    }
+    g_out = hsum8_pairs(ge, go);
+    u_out = hsum8_pairs(ue, uo);
+    if (gtype == kTypeIq2s) g_out = __fmul_rn(0.125f, g_out);
+    if (utype == kTypeIq2s) u_out = __fmul_rn(0.125f, u_out);
 }
 
 // Q8_0 of 32 floats held one per lane, plain layout (same rule as quantize_q8_0_part).
@@ -178,54 +299,94 @@ __device__ __forceinline__ void plain_q8_0_block(float v, int lane, int8_t *q_ou
     if (lane == 0) *d_out = __half2float(__float2half_rn(__fdiv_rn(amax, 127.0f)));
 }
 
-// ---- 1: x -> Q8_0 (task layout) and Q8_K --------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads) plain_quant_kernel(const PlainParams P) {
-    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float *x = P.x + static_cast<size_t>(t) * P.H;
-    quantize_q8_0_cta(x, P.H, P.xq0 + static_cast<size_t>(t) * P.H, P.xd0 + static_cast<size_t>(t) * (P.H / 32));
-    for (int sb = warp; sb < P.H / 256; sb += kWarps)
-        quantize_q8_K_warp(x + sb * 256, lane, reinterpret_cast<uint8_t *>(P.xk) + static_cast<size_t>(t) * P.H + sb * 256,
-                           P.xdk + static_cast<size_t>(t) * (P.H / 256) + sb);
+// Shared-memory plans (bytes); the host sizes the launches with the same functions.
+__host__ __device__ inline size_t plain_rows_stage_bytes(int H) { return static_cast<size_t>(H / 32) * 272; }   // two 4-row Q8_0 tasks
+__host__ __device__ inline size_t plain_rows_fixed_bytes(int H, int T) {
+    return 128 + static_cast<size_t>(T) * H * 4 + static_cast<size_t>(T) * H + static_cast<size_t>(T) * (H / 32) * 4;
+}
+__host__ __device__ inline size_t plain_iq_row_bytes(int type, int cols) {
+    return type == kTypeIq4nl ? static_cast<size_t>(cols / 32) * 18 : static_cast<size_t>(cols / 256) * iq_block_bytes(type);
+}
+__host__ __device__ inline size_t plain_gate_up_chunks_off(int H) {       // header, padded activation, both codebooks
+    return (256 + static_cast<size_t>(H / 256) * 272 + 2048 + 8192 + 127) / 128 * 128;
+}
+__host__ __device__ inline size_t plain_gate_up_smem(int H, int gate_type, int up_type) {
+    return plain_gate_up_chunks_off(H) + 16 * (plain_iq_row_bytes(gate_type, H) + plain_iq_row_bytes(up_type, H));
+}
+// offset of the staged weight chunks of the down kernel: after the header, the quantised activations and their scales
+__host__ __device__ inline size_t plain_down_chunks_off(int F, int K) {
+    return (256 + static_cast<size_t>(K) * F + static_cast<size_t>(K) * (F / 32) * 4 + 127) / 128 * 128;
+}
+__host__ __device__ inline size_t plain_down_smem(int F, int SF, int K, int down_type) {
+    return plain_down_chunks_off(F, K) + static_cast<size_t>(K) * 16 * plain_iq_row_bytes(down_type, F) + static_cast<size_t>(4) * (SF / 32) * 136 +
+           static_cast<size_t>(K) * F * 4;
 }
 
-// ---- 2: router logits, shared expert gate/up rows with SiLU * up, the shared expert's sigmoid gate ------------------
-// one warp per task: [router tasks | shared gate/up 4-row tasks | the gate dot]
-__global__ void __launch_bounds__(kThreads) plain_rows_kernel(const PlainParams P) {
-    extern __shared__ __align__(16) uint8_t psm[];
-    const int t = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nbh = P.H / 32;
-    uint8_t *xq = psm;
-    float *xd = reinterpret_cast<float *>(psm + P.H);
-    for (int i = threadIdx.x; i < P.H / 16; i += kThreads)
-        reinterpret_cast<uint4 *>(xq)[i] = reinterpret_cast<const uint4 *>(P.xq0 + static_cast<size_t>(t) * P.H)[i];
-    for (int i = threadIdx.x; i < nbh; i += kThreads) xd[i] = P.xd0[static_cast<size_t>(t) * nbh + i];
-    __syncthreads();
-    const float *x = P.x + static_cast<size_t>(t) * P.H;
+// ---- 1: x -> Q8_0; router logits, shared expert gate/up rows with SiLU * up, the shared expert's sigmoid gate -------
+// One warp per task, [router tasks | shared gate/up pairs of 4-row tasks | the gate dot]; the task's weights are staged
+// by one bulk copy and applied to every token of the call.
+__global__ void __launch_bounds__(256) plain_rows_kernel(const PlainParams P) {
+    extern __shared__ __align__(128) uint8_t psm[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, W = blockDim.x >> 5;
+    const int H = P.H, nbh = H / 32, T = P.T;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(psm);
+    float *xf = reinterpret_cast<float *>(psm + 128);
+    uint8_t *xq = reinterpret_cast<uint8_t *>(xf + static_cast<size_t>(T) * H);
+    float *xd = reinterpret_cast<float *>(xq + static_cast<size_t>(T) * H);
+    uint8_t *stage = reinterpret_cast<uint8_t *>(xd + static_cast<size_t>(T) * nbh) + warp * plain_rows_stage_bytes(H);
     const int n_router = P.router_f32 ? P.E : P.E / 4, n_sh = P.SF / 4;
-    const int task = blockIdx.x * kWarps + warp;
-    if (task < n_router) {
-        if (P.router_f32) {
-            float v = dot_f32_warp(P.router_f32 + static_cast<size_t>(task) * P.H, x, P.H, lane);
+    const int task = blockIdx.x * W + warp;
+    const bool is_router = task < n_router, is_pair = !is_router && task < n_router + n_sh;
+    const bool is_gate = task == n_router + n_sh && P.SF > 0;
+    if (lane == 0 && (is_router || is_pair || is_gate)) {
+        mbar_init(&bars[warp], 1);
+        mbar_fence_init();
+        const uint32_t tb = static_cast<uint32_t>(nbh) * 136u;
+        if (is_gate || (is_router && P.router_f32)) {
+            mbar_expect_tx(&bars[warp], static_cast<uint32_t>(H) * 4u);
+            bulk_load(stage, is_gate ? P.gate_vec : P.router_f32 + static_cast<size_t>(task) * H, static_cast<uint32_t>(H) * 4u, &bars[warp]);
+        } else if (is_router) {
+            mbar_expect_tx(&bars[warp], tb);
+            bulk_load(stage, P.router_tasks + static_cast<size_t>(task) * tb, tb, &bars[warp]);
+        } else {
+            const size_t i = static_cast<size_t>(task - n_router);
+            mbar_expect_tx(&bars[warp], 2u * tb);
+            bulk_load(stage, P.sh_gate + i * tb, tb, &bars[warp]);
+            bulk_load(stage + tb, P.sh_up + i * tb, tb, &bars[warp]);
+        }
+    }
+    __syncwarp();
+    grid_dep_wait();
+    grid_dep_launch();
+    for (int i = threadIdx.x; i < T * H / 4; i += blockDim.x) reinterpret_cast<float4 *>(xf)[i] = reinterpret_cast<const float4 *>(P.x)[i];
+    __syncthreads();
+    for (int t = 0; t < T; ++t) quantize_q8_0_part(xf + t * H, H, xq + t * H, xd + t * nbh, threadIdx.x, blockDim.x);
+    __syncthreads();
+    if (is_router || is_pair || is_gate) mbar_wait(&bars[warp], 0, P.status);
+    for (int t = 0; t < T; ++t) {
+        const float *x = xf + t * H;
+        if (is_router && P.router_f32) {
+            float v = dot_f32_warp(reinterpret_cast<const float *>(stage), x, H, lane);
             if (P.bias) v = __fadd_rn(v, P.bias[task]);
             if (lane == 0) P.logits[static_cast<size_t>(t) * P.E + task] = v;
-        } else {
-            float v = q8_task_row(P.router_tasks + static_cast<size_t>(task) * nbh * 136, nbh, xq, xd, lane);
+        } else if (is_router) {
+            float v = q8_task_row(stage, nbh, xq + t * H, xd + t * nbh, lane);
             const int e = task * 4 + (lane >> 3);
             if (P.bias) v = __fadd_rn(v, P.bias[e]);
             if ((lane & 7) == 0) P.logits[static_cast<size_t>(t) * P.E + e] = v;
+        } else if (is_pair) {
+            float g, u;
+            q8_task_row2(stage, stage + nbh * 136, nbh, xq + t * H, xd + t * nbh, lane, g, u);
+            if ((lane & 7) == 0)
+                P.shact[static_cast<size_t>(t) * P.SF + (task - n_router) * 4 + (lane >> 3)] = __fmul_rn(silu_ggml(g), u);
+        } else if (is_gate) {
+            const float v = dot_f32_warp(reinterpret_cast<const float *>(stage), x, H, lane);
+            if (lane == 0) P.sgate[t] = sigmoid_ggml(v);
         }
-    } else if (task < n_router + n_sh) {
-        const int i = task - n_router;
-        float g, u;
-        q8_task_row2(P.sh_gate + static_cast<size_t>(i) * nbh * 136, P.sh_up + static_cast<size_t>(i) * nbh * 136, nbh, xq, xd, lane, g, u);
-        if ((lane & 7) == 0) P.shact[static_cast<size_t>(t) * P.SF + i * 4 + (lane >> 3)] = __fmul_rn(silu_ggml(g), u);
-    } else if (task == n_router + n_sh && P.SF > 0) {
-        const float v = dot_f32_warp(P.gate_vec, x, P.H, lane);
-        if (lane == 0) P.sgate[t] = sigmoid_ggml(v);
     }
 }
 
-// ---- 3: softmax / top-k of one token's logits; the shared expert's activation -> Q8_0 -------------------------------
+// ---- 2: x -> Q8_K; softmax / top-k of one token's logits; the shared expert's activation -> Q8_0 --------------------
 __global__ void __launch_bounds__(kThreads) plain_select_kernel(const PlainParams P) {
     __shared__ float pr[kMaxExperts];
     __shared__ float gsum[kMaxExperts / 8];
@@ -234,7 +395,14 @@ __global__ void __launch_bounds__(kThreads) plain_select_kernel(const PlainParam
     __shared__ uint32_t cand[2 * kWarps * kMaxK];
     __shared__ int sid[kMaxK];
     __shared__ float sw[kMaxK];
-    const int t = blockIdx.x, tid = threadIdx.x;
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // x is older than the kernel before this one: its Q8_K form does not wait
+    const float *x = P.x + static_cast<size_t>(t) * P.H;
+    for (int sb = warp; sb < P.H / 256; sb += kWarps)
+        quantize_q8_K_warp(x + sb * 256, lane, reinterpret_cast<uint8_t *>(P.xk) + static_cast<size_t>(t) * P.H + sb * 256,
+                           P.xdk + static_cast<size_t>(t) * (P.H / 256) + sb);
+    grid_dep_wait();
+    grid_dep_launch();
     const float *logits = P.logits + static_cast<size_t>(t) * P.E;
     RouterScratch rs;
     rs.probs = pr; rs.gsum = gsum; rs.red = red; rs.first = first; rs.cand = cand;
@@ -251,87 +419,122 @@ __global__ void __launch_bounds__(kThreads) plain_select_kernel(const PlainParam
                           P.shd0 + static_cast<size_t>(t) * (P.SF / 32));
 }
 
-// ---- 4: gate and up rows of the selected experts, act = SiLU(gate) * up ---------------------------------------------
-// one warp per (slot j, row r)
+// ---- 3: gate and up rows of the selected experts, act = SiLU(gate) * up ---------------------------------------------
+// CTA = (slot j, sixteen consecutive rows) of token blockIdx.y; one warp per row
 __global__ void __launch_bounds__(kThreads) plain_gate_up_kernel(const PlainParams P) {
+    extern __shared__ __align__(128) uint8_t psm[];
     const int t = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int task = blockIdx.x * kWarps + warp;
-    if (task >= P.K * P.F) return;
-    const int j = task / P.F, r = task - j * P.F, nsb = P.H / 256;
-    const int e = P.ids[t * P.K + j];
-    const int8_t *a = P.xk + static_cast<size_t>(t) * P.H;
-    const float *da = P.xdk + static_cast<size_t>(t) * nsb;
-    const size_t grb = static_cast<size_t>(nsb) * iq_block_bytes(P.gate_type), urb = static_cast<size_t>(nsb) * iq_block_bytes(P.up_type);
-    const float g = plain_row_iq(P.gate_type, P.gate + (static_cast<size_t>(e) * P.F + r) * grb, nsb, a, da, P.grid3, P.grid2, lane);
-    const float u = plain_row_iq(P.up_type, P.up + (static_cast<size_t>(e) * P.F + r) * urb, nsb, a, da, P.grid3, P.grid2, lane);
-    if (lane == 0) P.act[(static_cast<size_t>(t) * P.K + j) * P.F + r] = __fmul_rn(silu_ggml(g), u);
-}
-
-// ---- 5: the activation of every (token, slot) in the format the down tensor's type takes ----------------------------
-__global__ void __launch_bounds__(256) plain_act_quant_kernel(const PlainParams P) {
-    const int j = blockIdx.x, t = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const size_t row = static_cast<size_t>(t) * P.K + j;
-    const float *act = P.act + row * P.F;
-    int8_t *q = P.actq + row * P.F;
-    float *d = P.actd + row * (P.F / 32);
-    if (P.down_type == kTypeIq4nl) {
-        for (int b = warp; b < P.F / 32; b += 8) plain_q8_0_block(act[b * 32 + lane], lane, q + b * 32, d + b);
-    } else {
-        for (int sb = warp; sb < P.F / 256; sb += 8)
-            quantize_q8_K_warp(act + sb * 256, lane, reinterpret_cast<uint8_t *>(q) + sb * 256, d + sb);
+    const int chunks = P.F / 16, j = blockIdx.x / chunks, r0 = (blockIdx.x - j * chunks) * 16, nsb = P.H / 256;
+    uint64_t *bar = reinterpret_cast<uint64_t *>(psm);
+    float *da = reinterpret_cast<float *>(psm + 128);
+    int8_t *a = reinterpret_cast<int8_t *>(psm + 256);
+    uint32_t *t3 = reinterpret_cast<uint32_t *>(psm + 256 + nsb * kPlainActStride);
+    uint64_t *t2 = reinterpret_cast<uint64_t *>(reinterpret_cast<uint8_t *>(t3) + 2048);
+    const size_t grb = plain_iq_row_bytes(P.gate_type, P.H), urb = plain_iq_row_bytes(P.up_type, P.H);
+    uint8_t *gs = psm + plain_gate_up_chunks_off(P.H), *us = gs + 16 * grb;
+    // the codebooks do not depend on anything this call computes
+    plain_build_tables(t3, t2, P.grid3, P.grid2, P.gate_type != kTypeIq2s || P.up_type != kTypeIq2s,
+                       P.gate_type == kTypeIq2s || P.up_type == kTypeIq2s);
+    grid_dep_wait();
+    grid_dep_launch();
+    if (threadIdx.x == 0) {
+        const size_t e = static_cast<size_t>(P.ids[t * P.K + j]);
+        mbar_init(bar, 1);
+        mbar_fence_init();
+        mbar_expect_tx(bar, static_cast<uint32_t>(16 * (grb + urb)));
+        bulk_load(gs, P.gate + (e * P.F + r0) * grb, static_cast<uint32_t>(16 * grb), bar);
+        bulk_load(us, P.up + (e * P.F + r0) * urb, static_cast<uint32_t>(16 * urb), bar);
     }
+    for (int i = threadIdx.x; i < P.H / 16; i += kThreads)       // sixteen bytes at a time, superblock i / 16
+        *reinterpret_cast<uint4 *>(a + (i >> 4) * kPlainActStride + (i & 15) * 16) =
+            reinterpret_cast<const uint4 *>(P.xk + static_cast<size_t>(t) * P.H)[i];
+    if (threadIdx.x < nsb) da[threadIdx.x] = P.xdk[static_cast<size_t>(t) * nsb + threadIdx.x];
+    __syncthreads();
+    mbar_wait(bar, 0, P.status);
+    float g, u;
+    plain_gate_up_pair(P.gate_type, P.up_type, gs + warp * grb, us + warp * urb, nsb, a, da, t3, t2, lane, g, u);
+    if (lane == 0) P.act[(static_cast<size_t>(t) * P.K + j) * P.F + r0 + warp] = __fmul_rn(silu_ggml(g), u);
 }
 
-// ---- 6: down rows of the selected experts and of the shared expert ---------------------------------------------------
-// warp tasks: [K * H rows (IQ4_NL: two rows per warp) | H / 4 shared-expert tasks]
+// ---- 4: activation quantiser, down rows of the selected experts and of the shared expert, ordered combine -----------
+// CTA = sixteen consecutive output rows of token blockIdx.y, all K slots. IQ4_NL: 8 warps, two rows each; IQ3_S / IQ2_S:
+// 16 warps, one row each. out = sum over slots in rank order of mul_rn(row, weight), + shared * gate
+// (src/qwen38_cpu_moe.cuh:1281-1290, src/qwen38_precision.hpp:32-34).
 __global__ void __launch_bounds__(kThreads) plain_down_kernel(const PlainParams P) {
-    __shared__ uint8_t lut[16];
+    extern __shared__ __align__(128) uint8_t psm[];
+    const int t = blockIdx.y, h0 = blockIdx.x * 16, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const bool nl = P.down_type == kTypeIq4nl;
+    const int K = P.K, F = P.F, nbs = P.SF / 32;
+    uint64_t *bar = reinterpret_cast<uint64_t *>(psm);
+    uint8_t *lut = psm + 64;
+    float *routed_s = reinterpret_cast<float *>(psm + 128), *shd_s = routed_s + 16;
+    int8_t *actq = reinterpret_cast<int8_t *>(psm + 256);
+    float *actd = reinterpret_cast<float *>(psm + 256 + static_cast<size_t>(K) * F);
+    const size_t drb = plain_iq_row_bytes(P.down_type, F);
+    uint8_t *chunks = psm + plain_down_chunks_off(F, K);
+    uint8_t *shs = chunks + static_cast<size_t>(K) * 16 * drb;
+    // The ids come from the selection, two kernels back: the weight copies leave before the wait for the gate/up rows.
+    if (warp == 0) {        // lane j fetches slot j's expert id and issues its copy; the loads of the ids overlap
+        const uint32_t shb = P.SF > 0 ? 4u * static_cast<uint32_t>(nbs) * 136u : 0u;
+        const size_t e = lane < K ? static_cast<size_t>(P.ids[t * K + lane]) : 0;
+        if (lane == 0) {
+            mbar_init(bar, 1);
+            mbar_fence_init();
+            mbar_expect_tx(bar, static_cast<uint32_t>(K * 16 * drb) + shb);
+        }
+        __syncwarp();
+        if (lane < K) bulk_load(chunks + static_cast<size_t>(lane) * 16 * drb, P.down + (e * P.H + h0) * drb, static_cast<uint32_t>(16 * drb), bar);
+        if (lane == K && shb) bulk_load(shs, P.sh_down + static_cast<size_t>(h0 / 4) * nbs * 136, shb, bar);
+    }
     if (threadIdx.x < 16) {
         const int v[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
         lut[threadIdx.x] = static_cast<uint8_t>(v[threadIdx.x]);
     }
+    grid_dep_wait();
+    grid_dep_launch();
+    // the activations of all slots arrive in one round of loads, into a region of their own (the weight copies are in flight)
+    float *actf = reinterpret_cast<float *>(shs + 4 * static_cast<size_t>(nbs) * 136);
+    const float *act = P.act + static_cast<size_t>(t) * K * F;
+    for (int i = threadIdx.x; i < K * F / 4; i += blockDim.x) reinterpret_cast<float4 *>(actf)[i] = reinterpret_cast<const float4 *>(act)[i];
     __syncthreads();
-    const int t = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int task = blockIdx.x * kWarps + warp;
-    const bool nl = P.down_type == kTypeIq4nl;
-    const int n_rows = nl ? P.K * P.H / 2 : P.K * P.H;
-    if (task < n_rows) {
-        if (nl) {
-            const int idx = task * 2 + (lane >> 4);                 // (slot, row) of this half of the warp
-            const int j = idx / P.H, h = idx - j * P.H, nb = P.F / 32;
-            const int e = P.ids[t * P.K + j];
-            const size_t arow = static_cast<size_t>(t) * P.K + j;
-            const float v = plain_row_iq4nl_half(P.down + (static_cast<size_t>(e) * P.H + h) * nb * 18, nb, P.actq + arow * P.F,
-                                                 P.actd + arow * nb, lut, lane);
-            if ((lane & 15) == 0) P.eo[arow * P.H + h] = v;
-        } else {
-            const int j = task / P.H, h = task - j * P.H, nsb = P.F / 256;
-            const int e = P.ids[t * P.K + j];
-            const size_t arow = static_cast<size_t>(t) * P.K + j;
-            const size_t rb = static_cast<size_t>(nsb) * iq_block_bytes(P.down_type);
-            const float v = plain_row_iq(P.down_type, P.down + (static_cast<size_t>(e) * P.H + h) * rb, nsb, P.actq + arow * P.F,
-                                         P.actd + arow * (P.F / 32), P.grid3, P.grid2, lane);
-            if (lane == 0) P.eo[arow * P.H + h] = v;
+    if (nl) {
+        for (int b = warp; b < K * F / 32; b += nwarps) plain_q8_0_block(actf[b * 32 + lane], lane, actq + b * 32, actd + b);
+    } else {
+        for (int s = warp; s < K * F / 256; s += nwarps) {
+            const int j = s / (F / 256), q = s - j * (F / 256);
+            quantize_q8_K_warp(actf + s * 256, lane, reinterpret_cast<uint8_t *>(actq) + s * 256, actd + j * (F / 32) + q);
         }
-    } else if (P.SF > 0 && task - n_rows < P.H / 4) {
-        const int i = task - n_rows, nbs = P.SF / 32;
-        const float v = q8_task_row(P.sh_down + static_cast<size_t>(i) * nbs * 136, nbs, P.shq0 + static_cast<size_t>(t) * P.SF,
-                                    P.shd0 + static_cast<size_t>(t) * nbs, lane);
-        if ((lane & 7) == 0) P.shdown[static_cast<size_t>(t) * P.H + i * 4 + (lane >> 3)] = v;
     }
-}
-
-// ---- 7: out = sum over slots in rank order of mul_rn(expert row, weight), + shared * gate ----------------------------
-// (src/qwen38_cpu_moe.cuh:1281-1290, src/qwen38_precision.hpp:32-34)
-__global__ void __launch_bounds__(256) plain_combine_kernel(const PlainParams P) {
-    const int t = blockIdx.y, h = blockIdx.x * 256 + threadIdx.x;
-    if (h >= P.H) return;
-    float r = 0.0f;
-    for (int j = 0; j < P.K; ++j)
-        r = __fadd_rn(r, __fmul_rn(P.eo[(static_cast<size_t>(t) * P.K + j) * P.H + h], P.weights[t * P.K + j]));
-    P.routed[static_cast<size_t>(t) * P.H + h] = r;
-    P.out[static_cast<size_t>(t) * P.H + h] =
-        P.SF > 0 ? __fadd_rn(r, __fmul_rn(P.shdown[static_cast<size_t>(t) * P.H + h], P.sgate[t])) : r;
+    __syncthreads();
+    mbar_wait(bar, 0, P.status);
+    const int row = nl ? 2 * warp + (lane >> 4) : warp;         // of the sixteen
+    const bool writer = nl ? (lane & 15) == 0 : lane == 0;
+    float routed = 0.0f;
+    for (int j = 0; j < K; ++j) {
+        const uint8_t *w = chunks + (static_cast<size_t>(j) * 16 + row) * drb;
+        const float v = nl ? plain_row_iq4nl_half(w, F / 32, actq + j * F, actd + j * (F / 32), lut, lane)
+                           : plain_row_iq(P.down_type, w, F / 256, actq + j * F, actd + j * (F / 32), P.grid3, P.grid2, lane);
+        if (writer) P.eo[(static_cast<size_t>(t) * K + j) * P.H + h0 + row] = v;
+        routed = __fadd_rn(routed, __fmul_rn(v, P.weights[t * K + j]));
+    }
+    if (writer) routed_s[row] = routed;
+    if (P.SF > 0 && warp < 4) {
+        const float v = q8_task_row(shs + static_cast<size_t>(warp) * nbs * 136, nbs, P.shq0 + static_cast<size_t>(t) * P.SF,
+                                    P.shd0 + static_cast<size_t>(t) * nbs, lane);
+        if ((lane & 7) == 0) shd_s[warp * 4 + (lane >> 3)] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < 16) {
+        const size_t o = static_cast<size_t>(t) * P.H + h0 + threadIdx.x;
+        const float r = routed_s[threadIdx.x];
+        P.routed[o] = r;
+        if (P.SF > 0) {
+            P.shdown[o] = shd_s[threadIdx.x];
+            P.out[o] = __fadd_rn(r, __fmul_rn(shd_s[threadIdx.x], P.sgate[t]));
+        } else {
+            P.out[o] = r;
+        }
+    }
 }
 
 }  // namespace wd

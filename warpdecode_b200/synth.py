@@ -201,6 +201,14 @@ QUANTIZERS = {TYPE_Q8_0: quantize_q8_0, TYPE_Q4_0: quantize_q4_0, TYPE_IQ3_S: qu
               TYPE_IQ2_S: quantize_iq2_s, TYPE_IQ4_NL: quantize_iq4_nl}
 
 
+def random_blocks(rng, t, nblocks):
+    """Random block bytes with an f16 scale in [0.0005, 0.05]: valid input for every row product, and the cheapest way
+    to fill a full-size tensor of a type that has no encoder on the device."""
+    raw = rng.integers(0, 256, size=(nblocks, BLOCK_BYTES[t]), dtype=np.uint8)
+    raw[:, 0:2] = rng.uniform(0.0005, 0.05, size=nblocks).astype(np.float16).view(np.uint8).reshape(nblocks, 2)
+    return raw.reshape(-1)
+
+
 def dequantize(t, blob, rows, cols):
     """Reference decoder for the encoders' own tests."""
     blob = np.ascontiguousarray(blob, np.uint8).reshape(rows, cols // BLOCK_ELEMS[t], BLOCK_BYTES[t])
