@@ -186,6 +186,18 @@ def plain_case(a):
     # bytes one token reads in a layer: ten experts' gate, up and down rows, the F32 router, the shared expert
     layer_bytes = K * (2 * F * (H // 256) * 82 + H * (F // 32) * 18) + E * H * 4 + 3 * SF * (H // 32) * 34
     peak = measured_peak()
+    if os.environ.get("WD_PLAIN_STAMPS") == "1":
+        import ctypes as C
+        st = np.zeros(2 * 512 * 8, np.uint64)
+        wd._check(wd.lib().wd_read_tap(eng.h, 9, -1, st.ctypes.data, st.nbytes))
+        st = st.reshape(2, 512, 8).astype(np.int64)
+        for k, (name, n, steps) in enumerate((("gate_up", K * F // 16, ["tables", "wait for select", "issue + activation", "wait for chunks", "rows"]),
+                                              ("down", H // 16, ["issue", "wait for gate_up", "load act", "quantise", "wait for chunks", "rows", "shared + combine"]))):
+            v = st[k, :min(n, 512)]
+            t0 = v[:, 0].min()
+            print(name, "first CTA starts 0, last CTA starts %.2f us, last CTA ends %.2f us" % ((v[:, 0].max() - t0) / 1e3, (v[:, len(steps)].max() - t0) / 1e3))
+            for i, sname in enumerate(steps):
+                print("   %-22s median %.2f us" % (sname, np.median(v[:, i + 1] - v[:, i]) / 1e3))
     print("%d tokens per call: %.2f us per call, %.2f us per token and layer; %.1f MB per token and layer -> %.0f GB/s = %.3f of "
           "the measured HBM peak (%.0f GB/s); status %d" % (a.tokens, us, us / a.tokens, layer_bytes / 1e6,
                                                           layer_bytes * a.tokens / us / 1e3, layer_bytes * a.tokens / us / 1e3 / peak, peak,

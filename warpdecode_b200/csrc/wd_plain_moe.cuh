@@ -11,9 +11,9 @@
 // One call is four kernels on the caller's stream, launched with programmatic stream serialization so that each one's
 // start-up (and every weight copy that does not depend on its predecessor) overlaps the kernel before it:
 //   rows     x -> Q8_0; router logits, the shared expert's gate/up rows with SiLU * up, its sigmoid gate
-//   select   softmax / top-k; x -> Q8_K; the shared activation -> Q8_0
+//   select   softmax / top-k; x -> Q8_K
 //   gate_up  gate and up rows of the selected experts, SiLU * up
-//   down     activation quantiser, down rows of the selected experts and of the shared expert, ordered combine
+//   down     activation quantisers, down rows of the selected experts and of the shared expert, ordered combine
 // Every CTA brings the weight bytes it will read into shared memory with bulk copies issued at once (a chunk of
 // sixteen consecutive rows is contiguous and a multiple of 16 bytes in every format), so no row product waits on
 // HBM in its dependent chain. Each kernel first waits for its predecessor, then releases its successor: whatever a
@@ -58,7 +58,12 @@ struct PlainParams {
     float *shdown;      // [H]
     float *routed;      // [H]
     unsigned *status;   // error word of the engine (a copy that never arrives raises kErrCopyTimeout there)
+    unsigned long long *stamps;     // optional [2][CTA][8] step times (ns) of the gate/up and down kernels of token 0
 };
+
+#define WD_PSTAMP(kernel, i)                                                                                   \
+    if (P.stamps != nullptr && threadIdx.x == 0 && blockIdx.y == 0)                                            \
+        P.stamps[((kernel) * 512 + (blockIdx.x & 511)) * 8 + (i)] = global_timer_ns();
 
 // 0xff in byte j where bit j of the nibble is set
 __device__ __forceinline__ uint32_t nibble_to_byte_mask(uint32_t nib) {
@@ -150,27 +155,65 @@ __device__ __forceinline__ float plain_row_iq(int type, const uint8_t *row, int 
     return type == kTypeIq2s ? plain_row_iq2s(row, nsb, a, da, grid2, lane) : plain_row_iq3s(row, nsb, a, da, grid3, lane);
 }
 
-// One IQ4_NL row (blocks of 32: d(2), sixteen bytes, value j in the low nibble and j + 16 in the high one) against a
-// Q8_0 activation, by HALF a warp: lane % 16 = (parity of the block, chunk-lane l). Even and odd blocks keep separate
-// fmaf chains per chunk-lane, which are added before the closing tree (src/qwen38_cpu_moe.cuh:377-422; nb is even).
-__device__ __forceinline__ float plain_row_iq4nl_half(const uint8_t *row, int nb, const int8_t *aq, const float *ad,
-                                                      const uint8_t *lut, int lane) {
-    const int par = (lane >> 3) & 1, l = lane & 7, hi = l >> 2, k = 4 * (l & 3);
-    float acc = 0.0f;
+// Four consecutive IQ4_NL rows (blocks of 32: d(2), sixteen bytes, value j in the low nibble and j + 16 in the high one)
+// against a Q8_0 activation, by one warp: lane = (row = lane / 8, parity of the block = (lane / 4) % 2, l = lane % 4).
+// A weight word holds chunk-lane l in its low nibbles and chunk-lane l + 4 in its high ones, so one lane carries both
+// fmaf chains of its blocks. Even and odd blocks keep separate chains per chunk-lane, which are added before the
+// closing tree (src/qwen38_cpu_moe.cuh:377-422; nb is even). Every lane of a row's eight ends with the row's sum.
+__device__ __forceinline__ float plain_rows4_iq4nl(const uint8_t *rows, size_t row_bytes, int nb, const int8_t *aq, const float *ad,
+                                                   const uint8_t *lut, int lane) {
+    const uint8_t *row = rows + (lane >> 3) * row_bytes;
+    const int par = (lane >> 2) & 1, k = 4 * (lane & 3);
+    float lo = 0.0f, hi = 0.0f;
 #pragma unroll 5
     for (int b = par; b < nb; b += 2) {
         const uint8_t *wb = row + b * 18;
         const uint32_t w = *reinterpret_cast<const uint16_t *>(wb + 2 + k) |
                            (static_cast<uint32_t>(*reinterpret_cast<const uint16_t *>(wb + 4 + k)) << 16);
-        const uint32_t nib = (hi ? (w >> 4) : w) & 0x0f0f0f0fu;
-        const uint32_t v = lut[nib & 15u] | (lut[(nib >> 8) & 15u] << 8) | (lut[(nib >> 16) & 15u] << 16) |
-                           (static_cast<uint32_t>(lut[nib >> 24]) << 24);
-        const int aw = *reinterpret_cast<const int *>(aq + b * 32 + 16 * hi + k);
+        const uint32_t n0 = w & 0x0f0f0f0fu, n1 = (w >> 4) & 0x0f0f0f0fu;
+        const uint32_t v0 = lut[n0 & 15u] | (lut[(n0 >> 8) & 15u] << 8) | (lut[(n0 >> 16) & 15u] << 16) |
+                            (static_cast<uint32_t>(lut[n0 >> 24]) << 24);
+        const uint32_t v1 = lut[n1 & 15u] | (lut[(n1 >> 8) & 15u] << 8) | (lut[(n1 >> 16) & 15u] << 16) |
+                            (static_cast<uint32_t>(lut[n1 >> 24]) << 24);
+        const int a0 = *reinterpret_cast<const int *>(aq + b * 32 + k), a1 = *reinterpret_cast<const int *>(aq + b * 32 + 16 + k);
         const float d = __fmul_rn(half_bits_to_float(*reinterpret_cast<const uint16_t *>(wb)), ad[b]);
-        acc = __fmaf_rn(d, static_cast<float>(dp4a_s8(aw, static_cast<int>(v), 0)), acc);
+        lo = __fmaf_rn(d, static_cast<float>(dp4a_s8(a0, static_cast<int>(v0), 0)), lo);
+        hi = __fmaf_rn(d, static_cast<float>(dp4a_s8(a1, static_cast<int>(v1), 0)), hi);
     }
-    acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
-    return hsum8_lanes(acc);
+    lo = __fadd_rn(lo, __shfl_xor_sync(0xffffffffu, lo, 4));        // even + odd blocks, chunk-lane l
+    hi = __fadd_rn(hi, __shfl_xor_sync(0xffffffffu, hi, 4));        // chunk-lane l + 4
+    float r = __fadd_rn(lo, hi);                                    // v[l] + v[l + 4]
+    r = __fadd_rn(r, __shfl_xor_sync(0xffffffffu, r, 2));           // r0 + r2, r1 + r3
+    return __fadd_rn(r, __shfl_xor_sync(0xffffffffu, r, 1));
+}
+
+// Q8_0 of n floats in shared memory, plain layout (quants [n], one f16-rounded scale per 32), by the whole CTA: a thread
+// takes four values, eight neighbouring lanes a block (the rule of quantize_q8_0_part).
+__device__ __forceinline__ void plain_quantize_q8_0_cta(const float *xf, int n, int8_t *q_out, float *d_out) {
+    const int nchunks = n >> 2;
+#pragma unroll 1
+    for (int ch = threadIdx.x; ch < ((nchunks + 31) & ~31); ch += blockDim.x) {
+        const bool live = ch < nchunks;
+        const float4 v = live ? *reinterpret_cast<const float4 *>(xf + 4 * ch) : make_float4(0, 0, 0, 0);
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        if (!live) continue;
+        uint32_t packed = 0;
+        if (amax != 0.0f) {
+            const float inv = __fdiv_rn(127.0f, amax);
+            const float f[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int q = __float2int_rn(__fmul_rn(f[j], inv));
+                q = max(-128, min(127, q));
+                packed |= static_cast<uint32_t>(q & 0xff) << (8 * j);
+            }
+        }
+        *reinterpret_cast<uint32_t *>(q_out + 4 * ch) = packed;
+        if ((ch & 7) == 0) d_out[ch >> 3] = __half2float(__float2half_rn(__fdiv_rn(amax, 127.0f)));
+    }
 }
 
 // ---- gate and up row of one expert row index in one pass -------------------------------------------------------------
@@ -315,11 +358,12 @@ __host__ __device__ inline size_t plain_gate_up_smem(int H, int gate_type, int u
 }
 // offset of the staged weight chunks of the down kernel: after the header, the quantised activations and their scales
 __host__ __device__ inline size_t plain_down_chunks_off(int F, int K) {
-    return (256 + static_cast<size_t>(K) * F + static_cast<size_t>(K) * (F / 32) * 4 + 127) / 128 * 128;
+    return (256 + 16 * 64 + static_cast<size_t>(K) * F + static_cast<size_t>(K) * (F / 32) * 4 + 127) / 128 * 128;
 }
 __host__ __device__ inline size_t plain_down_smem(int F, int SF, int K, int down_type) {
+    const size_t act_floats = static_cast<size_t>(K) * F > static_cast<size_t>(SF) ? static_cast<size_t>(K) * F : static_cast<size_t>(SF);
     return plain_down_chunks_off(F, K) + static_cast<size_t>(K) * 16 * plain_iq_row_bytes(down_type, F) + static_cast<size_t>(4) * (SF / 32) * 136 +
-           static_cast<size_t>(K) * F * 4;
+           SF + (SF / 32 + 3) / 4 * 16 + act_floats * 4;
 }
 
 // ---- 1: x -> Q8_0; router logits, shared expert gate/up rows with SiLU * up, the shared expert's sigmoid gate -------
@@ -386,7 +430,7 @@ __global__ void __launch_bounds__(256) plain_rows_kernel(const PlainParams P) {
     }
 }
 
-// ---- 2: x -> Q8_K; softmax / top-k of one token's logits; the shared expert's activation -> Q8_0 --------------------
+// ---- 2: x -> Q8_K; softmax / top-k of one token's logits ------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads) plain_select_kernel(const PlainParams P) {
     __shared__ float pr[kMaxExperts];
     __shared__ float gsum[kMaxExperts / 8];
@@ -414,9 +458,6 @@ __global__ void __launch_bounds__(kThreads) plain_select_kernel(const PlainParam
         P.weights[t * P.K + j] = sw[j];
     }
     for (int i = tid; i < P.E; i += kThreads) P.probs[static_cast<size_t>(t) * P.E + i] = pr[i];
-    if (P.SF > 0)
-        quantize_q8_0_cta(P.shact + static_cast<size_t>(t) * P.SF, P.SF, P.shq0 + static_cast<size_t>(t) * P.SF,
-                          P.shd0 + static_cast<size_t>(t) * (P.SF / 32));
 }
 
 // ---- 3: gate and up rows of the selected experts, act = SiLU(gate) * up ---------------------------------------------
@@ -433,10 +474,13 @@ __global__ void __launch_bounds__(kThreads) plain_gate_up_kernel(const PlainPara
     const size_t grb = plain_iq_row_bytes(P.gate_type, P.H), urb = plain_iq_row_bytes(P.up_type, P.H);
     uint8_t *gs = psm + plain_gate_up_chunks_off(P.H), *us = gs + 16 * grb;
     // the codebooks do not depend on anything this call computes
+    WD_PSTAMP(0, 0)
     plain_build_tables(t3, t2, P.grid3, P.grid2, P.gate_type != kTypeIq2s || P.up_type != kTypeIq2s,
                        P.gate_type == kTypeIq2s || P.up_type == kTypeIq2s);
+    WD_PSTAMP(0, 1)
     grid_dep_wait();
     grid_dep_launch();
+    WD_PSTAMP(0, 2)
     if (threadIdx.x == 0) {
         const size_t e = static_cast<size_t>(P.ids[t * P.K + j]);
         mbar_init(bar, 1);
@@ -450,32 +494,41 @@ __global__ void __launch_bounds__(kThreads) plain_gate_up_kernel(const PlainPara
             reinterpret_cast<const uint4 *>(P.xk + static_cast<size_t>(t) * P.H)[i];
     if (threadIdx.x < nsb) da[threadIdx.x] = P.xdk[static_cast<size_t>(t) * nsb + threadIdx.x];
     __syncthreads();
+    WD_PSTAMP(0, 3)
     mbar_wait(bar, 0, P.status);
+    WD_PSTAMP(0, 4)
     float g, u;
     plain_gate_up_pair(P.gate_type, P.up_type, gs + warp * grb, us + warp * urb, nsb, a, da, t3, t2, lane, g, u);
     if (lane == 0) P.act[(static_cast<size_t>(t) * P.K + j) * P.F + r0 + warp] = __fmul_rn(silu_ggml(g), u);
+    WD_PSTAMP(0, 5)
 }
 
-// ---- 4: activation quantiser, down rows of the selected experts and of the shared expert, ordered combine -----------
-// CTA = sixteen consecutive output rows of token blockIdx.y, all K slots. IQ4_NL: 8 warps, two rows each; IQ3_S / IQ2_S:
-// 16 warps, one row each. out = sum over slots in rank order of mul_rn(row, weight), + shared * gate
+// ---- 4: activation quantisers, down rows of the selected experts and of the shared expert, ordered combine ----------
+// CTA = sixteen consecutive output rows of token blockIdx.y, all K slots, 16 warps. Warp tasks: (slot, group of four rows)
+// for IQ4_NL, (slot, row) for IQ3_S / IQ2_S, then the four 4-row tasks of the shared expert. The rows land in shared
+// memory; sixteen threads then form out = sum over slots in rank order of mul_rn(row, weight), + shared * gate
 // (src/qwen38_cpu_moe.cuh:1281-1290, src/qwen38_precision.hpp:32-34).
 __global__ void __launch_bounds__(kThreads) plain_down_kernel(const PlainParams P) {
     extern __shared__ __align__(128) uint8_t psm[];
-    const int t = blockIdx.y, h0 = blockIdx.x * 16, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int t = blockIdx.y, h0 = blockIdx.x * 16, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const bool nl = P.down_type == kTypeIq4nl;
-    const int K = P.K, F = P.F, nbs = P.SF / 32;
+    const int K = P.K, F = P.F, SF = P.SF, nbs = SF / 32;
     uint64_t *bar = reinterpret_cast<uint64_t *>(psm);
     uint8_t *lut = psm + 64;
-    float *routed_s = reinterpret_cast<float *>(psm + 128), *shd_s = routed_s + 16;
-    int8_t *actq = reinterpret_cast<int8_t *>(psm + 256);
-    float *actd = reinterpret_cast<float *>(psm + 256 + static_cast<size_t>(K) * F);
+    float *shd_s = reinterpret_cast<float *>(psm + 128);                    // [16] shared expert rows
+    float *eo_s = reinterpret_cast<float *>(psm + 256);                     // [K][16] expert rows
+    int8_t *actq = reinterpret_cast<int8_t *>(psm + 256 + kMaxK * 64);
+    float *actd = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(actq) + static_cast<size_t>(K) * F);
     const size_t drb = plain_iq_row_bytes(P.down_type, F);
     uint8_t *chunks = psm + plain_down_chunks_off(F, K);
-    uint8_t *shs = chunks + static_cast<size_t>(K) * 16 * drb;
+    uint8_t *shs = chunks + static_cast<size_t>(K) * 16 * drb;             // the shared expert's four tasks
+    uint8_t *shq = shs + 4 * static_cast<size_t>(nbs) * 136;               // its activation, Q8_0 in task layout
+    float *shd = reinterpret_cast<float *>(shq + SF);
+    float *actf = reinterpret_cast<float *>(shq + SF + (nbs + 3) / 4 * 16); // F32 staging of the activations
+    WD_PSTAMP(1, 0)
     // The ids come from the selection, two kernels back: the weight copies leave before the wait for the gate/up rows.
     if (warp == 0) {        // lane j fetches slot j's expert id and issues its copy; the loads of the ids overlap
-        const uint32_t shb = P.SF > 0 ? 4u * static_cast<uint32_t>(nbs) * 136u : 0u;
+        const uint32_t shb = SF > 0 ? 4u * static_cast<uint32_t>(nbs) * 136u : 0u;
         const size_t e = lane < K ? static_cast<size_t>(P.ids[t * K + lane]) : 0;
         if (lane == 0) {
             mbar_init(bar, 1);
@@ -490,51 +543,69 @@ __global__ void __launch_bounds__(kThreads) plain_down_kernel(const PlainParams 
         const int v[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
         lut[threadIdx.x] = static_cast<uint8_t>(v[threadIdx.x]);
     }
+    // the shared expert's activation is older than the kernel before this one
+    for (int i = threadIdx.x; i < SF / 4; i += kThreads)
+        reinterpret_cast<float4 *>(actf)[i] = reinterpret_cast<const float4 *>(P.shact + static_cast<size_t>(t) * SF)[i];
+    __syncthreads();
+    if (SF > 0) quantize_q8_0_cta(actf, SF, shq, shd);
+    __syncthreads();
+    WD_PSTAMP(1, 1)
     grid_dep_wait();
     grid_dep_launch();
-    // the activations of all slots arrive in one round of loads, into a region of their own (the weight copies are in flight)
-    float *actf = reinterpret_cast<float *>(shs + 4 * static_cast<size_t>(nbs) * 136);
+    WD_PSTAMP(1, 2)
+    // the activations of all slots arrive in one round of loads
     const float *act = P.act + static_cast<size_t>(t) * K * F;
-    for (int i = threadIdx.x; i < K * F / 4; i += blockDim.x) reinterpret_cast<float4 *>(actf)[i] = reinterpret_cast<const float4 *>(act)[i];
+#pragma unroll 4
+    for (int i = threadIdx.x; i < K * F / 4; i += kThreads) reinterpret_cast<float4 *>(actf)[i] = reinterpret_cast<const float4 *>(act)[i];
     __syncthreads();
+    WD_PSTAMP(1, 3)
     if (nl) {
-        for (int b = warp; b < K * F / 32; b += nwarps) plain_q8_0_block(actf[b * 32 + lane], lane, actq + b * 32, actd + b);
+        plain_quantize_q8_0_cta(actf, K * F, actq, actd);
     } else {
-        for (int s = warp; s < K * F / 256; s += nwarps) {
+        for (int s = warp; s < K * F / 256; s += kWarps) {
             const int j = s / (F / 256), q = s - j * (F / 256);
             quantize_q8_K_warp(actf + s * 256, lane, reinterpret_cast<uint8_t *>(actq) + s * 256, actd + j * (F / 32) + q);
         }
     }
     __syncthreads();
+    WD_PSTAMP(1, 4)
     mbar_wait(bar, 0, P.status);
-    const int row = nl ? 2 * warp + (lane >> 4) : warp;         // of the sixteen
-    const bool writer = nl ? (lane & 15) == 0 : lane == 0;
-    float routed = 0.0f;
-    for (int j = 0; j < K; ++j) {
-        const uint8_t *w = chunks + (static_cast<size_t>(j) * 16 + row) * drb;
-        const float v = nl ? plain_row_iq4nl_half(w, F / 32, actq + j * F, actd + j * (F / 32), lut, lane)
-                           : plain_row_iq(P.down_type, w, F / 256, actq + j * F, actd + j * (F / 32), P.grid3, P.grid2, lane);
-        if (writer) P.eo[(static_cast<size_t>(t) * K + j) * P.H + h0 + row] = v;
-        routed = __fadd_rn(routed, __fmul_rn(v, P.weights[t * K + j]));
-    }
-    if (writer) routed_s[row] = routed;
-    if (P.SF > 0 && warp < 4) {
-        const float v = q8_task_row(shs + static_cast<size_t>(warp) * nbs * 136, nbs, P.shq0 + static_cast<size_t>(t) * P.SF,
-                                    P.shd0 + static_cast<size_t>(t) * nbs, lane);
-        if ((lane & 7) == 0) shd_s[warp * 4 + (lane >> 3)] = v;
+    WD_PSTAMP(1, 5)
+    const int n_exp = nl ? K * 4 : K * 16, n_tasks = n_exp + (SF > 0 ? 4 : 0);
+    for (int task = warp; task < n_tasks; task += kWarps) {
+        if (task >= n_exp) {
+            const int i = task - n_exp;
+            const float v = q8_task_row(shs + static_cast<size_t>(i) * nbs * 136, nbs, shq, shd, lane);
+            if ((lane & 7) == 0) shd_s[i * 4 + (lane >> 3)] = v;
+        } else if (nl) {
+            const int j = task >> 2, rg = task & 3;
+            const float v = plain_rows4_iq4nl(chunks + (static_cast<size_t>(j) * 16 + rg * 4) * drb, drb, F / 32, actq + j * F,
+                                              actd + j * (F / 32), lut, lane);
+            if ((lane & 7) == 0) eo_s[j * 16 + rg * 4 + (lane >> 3)] = v;
+        } else {
+            const int j = task >> 4, row = task & 15;
+            const float v = plain_row_iq(P.down_type, chunks + (static_cast<size_t>(j) * 16 + row) * drb, F / 256, actq + j * F,
+                                         actd + j * (F / 32), P.grid3, P.grid2, lane);
+            if (lane == 0) eo_s[j * 16 + row] = v;
+        }
     }
     __syncthreads();
+    WD_PSTAMP(1, 6)
+    for (int i = threadIdx.x; i < K * 16; i += kThreads)
+        P.eo[(static_cast<size_t>(t) * K + (i >> 4)) * P.H + h0 + (i & 15)] = eo_s[i];
     if (threadIdx.x < 16) {
         const size_t o = static_cast<size_t>(t) * P.H + h0 + threadIdx.x;
-        const float r = routed_s[threadIdx.x];
+        float r = 0.0f;
+        for (int j = 0; j < K; ++j) r = __fadd_rn(r, __fmul_rn(eo_s[j * 16 + threadIdx.x], P.weights[t * K + j]));
         P.routed[o] = r;
-        if (P.SF > 0) {
+        if (SF > 0) {
             P.shdown[o] = shd_s[threadIdx.x];
             P.out[o] = __fadd_rn(r, __fmul_rn(shd_s[threadIdx.x], P.sgate[t]));
         } else {
             P.out[o] = r;
         }
     }
+    WD_PSTAMP(1, 7)
 }
 
 }  // namespace wd
