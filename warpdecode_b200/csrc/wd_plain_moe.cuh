@@ -41,19 +41,13 @@ struct PlainParams {
     // activations and scratch, all [token][...]
     const float *x;
     float *out;
-    uint8_t *xq0;       // Q8_0 of x in task layout [H]
-    float *xd0;         // [H / 32]
     int8_t *xk;         // Q8_K of x [H]
     float *xdk;         // [H / 256]
     float *logits, *probs, *weights;
     int *ids;
     float *shact;       // [SF]
-    uint8_t *shq0;      // its Q8_0, task layout
-    float *shd0;
     float *sgate;       // [1]
     float *act;         // [K][F]
-    int8_t *actq;       // [K][F] quants of act (Q8_0 blocks of 32 or Q8_K superblocks of 256)
-    float *actd;        // [K][F / 32]
     float *eo;          // [K][H]
     float *shdown;      // [H]
     float *routed;      // [H]
@@ -326,20 +320,6 @@ __device__ __forceinline__ void plain_gate_up_pair(int gtype, int utype, const u
     u_out = hsum8_pairs(ue, uo);
     if (gtype == kTypeIq2s) g_out = __fmul_rn(0.125f, g_out);
     if (utype == kTypeIq2s) u_out = __fmul_rn(0.125f, u_out);
-}
-
-// Q8_0 of 32 floats held one per lane, plain layout (same rule as quantize_q8_0_part).
-__device__ __forceinline__ void plain_q8_0_block(float v, int lane, int8_t *q_out, float *d_out) {
-    float amax = fabsf(v);
-#pragma unroll
-    for (int s = 16; s >= 1; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
-    int q = 0;
-    if (amax != 0.0f) {
-        q = __float2int_rn(__fmul_rn(v, __fdiv_rn(127.0f, amax)));
-        q = max(-128, min(127, q));
-    }
-    q_out[lane] = static_cast<int8_t>(q);
-    if (lane == 0) *d_out = __half2float(__float2half_rn(__fdiv_rn(amax, 127.0f)));
 }
 
 // Shared-memory plans (bytes); the host sizes the launches with the same functions.
