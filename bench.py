@@ -1,7 +1,7 @@
 """Bench of the batch-1 MoE decode hot path (48-layer, 512-expert IQ3_S MoE stack).
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--repeats R] [--impl reference]
-                  [--cache-mib M] [--no-decode] [--no-verify] [--no-dense]
+                  [--cache-mib M] [--no-decode] [--no-verify] [--no-dense] [--no-plain]
 
 One step = one decode token through the 48 MoE blocks of the synthetic model (hidden 2048, 512
 routed experts of ffn 512 in IQ3_S, top-10, one Q8_0 shared expert per layer, every expert resident
@@ -403,6 +403,51 @@ def run_ours(args, rank, world, local_rank):
                          "after an 8-token prompt, one CUDA-graph replay per token; fastest of 3 runs"}
         dec.close()
 
+    # ---- the block shape of the reference's own model on the plain-layout path (1-GPU run only) -----------------------------
+    plain = None
+    if not args.no_plain and world == 1 and not capped:
+        from warpdecode_b200 import synth
+        PH, PF, PE, PK, PSF, PL = 2560, 640, 512, 10, 640, 2
+        peng = wd.Engine(PH, PF, PE, PK, PSF, PL, expert_type=synth.TYPE_IQ2_S, down_type=synth.TYPE_IQ4_NL, w_scale=1.25,
+                         router_f32=True, max_tokens=4, device=local_rank)
+        prng = np.random.Generator(np.random.PCG64(4))
+        small = synth.make_moe_block(5, PH, PF, 8, 8, PSF, synth.TYPE_IQ2_S, synth.TYPE_IQ4_NL, sigma=0.02, router_f32=True)
+        for l in range(PL):
+            m = dict(small)
+            m["router_f32"] = (prng.standard_normal(PE * PH) * 0.02).astype(np.float32)
+            m["router_bias"] = (prng.standard_normal(PE) * 0.5).astype(np.float32)
+            m["gate"] = synth.random_blocks(prng, synth.TYPE_IQ2_S, PE * PF * PH // 256)
+            m["up"] = synth.random_blocks(prng, synth.TYPE_IQ2_S, PE * PF * PH // 256)
+            m["down"] = synth.random_blocks(prng, synth.TYPE_IQ4_NL, PE * PH * PF // 32)
+            peng.load_block(l, m)
+        px = torch.randn(4, PH, generator=torch.Generator().manual_seed(2), dtype=torch.float32).cuda()
+        po = torch.zeros_like(px)
+        us_call = {}
+        for n_tok in (1, 4):
+            best = None
+            for rep in range(4):
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                with torch.cuda.stream(stream):
+                    ev0.record(stream)
+                    for _ in range(20):
+                        for l in range(PL):
+                            peng.forward_device(l, px.data_ptr(), po.data_ptr(), sp, n_tok)
+                    ev1.record(stream)
+                torch.cuda.synchronize()
+                if rep:         # the first round warms up
+                    v = ev0.elapsed_time(ev1) * 1e3 / (20 * PL)
+                    best = v if best is None else min(best, v)
+            us_call[n_tok] = best
+        if peng.device_status() != 0 or not bool(torch.isfinite(po).all()):
+            raise RuntimeError("the plain-layout calls left a status or non-finite outputs")
+        p_bytes = PK * (2 * PF * (PH // 256) * 82 + PH * (PF // 32) * 18) + PE * PH * 4 + 3 * PSF * (PH // 32) * 34
+        plain = {"us_per_call": us_call[1], "us_per_call_4_tokens": us_call[4], "bytes_per_token_layer": p_bytes,
+                 "hbm_gbs": p_bytes / us_call[1] / 1e3, "kernel": peng.kernel_name(), "launches_per_call": 4,
+                 "what": "one MoE block call (wd_moe_forward) at the block shape of the reference's own model: hidden 2560, "
+                         "expert_ffn 640, 512 experts, top 10, shared expert 640, IQ2_S gate/up, IQ4_NL down, F32 router with "
+                         "bias; two layers of random block bytes, device-resident input, fastest of 3 rounds of 40 calls"}
+        peng.close()
+
     t = torch.tensor([float(np.median(rep_ms)), min(rep_ms), max(rep_ms), float(np.median(e2e_rep))],
                      dtype=torch.float64, device="cuda")
     if world > 1:
@@ -463,6 +508,9 @@ def run_ours(args, rank, world, local_rank):
     if dense is not None:
         dense["hbm_frac"] = dense["hbm_gbs"] / peak
         line["dense_cfg1"] = dense
+    if plain is not None:
+        plain["hbm_frac"] = plain["hbm_gbs"] / peak
+        line["plain_ref_shape"] = plain
     if cache_stats is not None:
         hits, misses, evictions, h2d_bytes, host_ns, placed = cache_stats
         line["cache"] = {"cache_mib": args.cache_mib, "slots": eng.slot_count(), "hits": hits, "misses": misses,
@@ -488,6 +536,7 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-verify", action="store_true")
     ap.add_argument("--no-dense", action="store_true")
+    ap.add_argument("--no-plain", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -48,8 +48,9 @@ typedef struct wd_engine wd_engine;
  * IQ2_S experts with gate and up of one type, and a Q8_0 router. Any other configuration that the reference's
  * ggml-exact path accepts (q38_moe_separate_experts_q8_act_compatible, src/qwen38_moe.cuh:2181-2211: hidden % 256 == 0,
  * expert_ffn % 64 == 0, IQ4_NL down tensors; an F32 router, :2252-2258) - the reference's own 2560 / 640 model among
- * them - runs on the PLAIN-LAYOUT path: tensors stay in ggml layout, one warp per row, every expert resident, one GPU,
- * per-layer calls only (wd_moe_forward, wd_moe_forward_host, wd_read_tap); the other entry points return WD_E_INVALID. */
+ * them - runs on the PLAIN-LAYOUT path: tensors stay in ggml layout, one warp per row, every expert resident, one GPU;
+ * wd_moe_forward, wd_moe_forward_host, wd_read_tap and wd_stack_step (as a chain of per-layer calls) serve such an
+ * engine, the slot cache, expert parallelism, profiling stamps and the device-side generator return WD_E_INVALID. */
 typedef struct {
     int32_t hidden;          /* multiple of 256 */
     int32_t expert_ffn;      /* multiple of 256 (IQ3_S / IQ2_S down) or of 64 (IQ4_NL down) */

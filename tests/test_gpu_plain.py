@@ -117,7 +117,60 @@ def test_layers_of_different_expert_types_and_a_gguf_file(wd, oracle, tmp_path):
     for layer, m in ((0, m0), (1, m1)):
         out = eng.forward_host(layer, x)
         assert np.array_equal(bits(out), bits(oracle.moe_block(m, x)["out"]))
-    with pytest.raises(wd.WdError, match="plain-layout"):
-        eng.stack_step_host(x)
     eng.close()
     g.close()
+
+
+def test_what_the_plain_layout_path_refuses(wd):
+    """Call order and configuration errors come back as messages, not as wrong results."""
+    m, xs = mg.block_cases()[5]
+    with pytest.raises(wd.WdError, match="expert parallelism"):
+        _engine_for(wd, m, ep_size=2, ep_rank=0)
+    with pytest.raises(wd.WdError, match="resident"):
+        _engine_for(wd, m, cache_mib=64)
+    with pytest.raises(wd.WdError, match="4096"):
+        wd.Engine(8192, 640, 64, 4, 0, 1, expert_type=ol.TYPE_IQ2_S, down_type=ol.TYPE_IQ4_NL)
+    eng = _engine_for(wd, m)
+    with pytest.raises(wd.WdError, match="not all set"):
+        eng.forward_host(0, xs[0])
+    with pytest.raises(wd.WdError, match="wd_set_router_f32"):          # the Q8_0 setter on an engine made for an F32 router
+        wd._check(wd.lib().wd_set_router(eng.h, 0, np.zeros(8 * 2560 // 32 * 34, np.uint8).ctypes.data, None))
+    eng.load_block(0, m)
+    out = eng.forward_host(0, xs[0])
+    assert np.array_equal(bits(out), GOLD["block5_out"][0])
+    for call in (lambda: eng.synth_model(1), lambda: eng.set_profiling(True)):
+        with pytest.raises(wd.WdError, match="plain-layout"):
+            call()
+    assert eng.device_status() == 0
+    eng.close()
+    # an engine of a tiled geometry does not take an F32 router through the Q8_0 path either
+    tiled = wd.Engine(256, 256, 16, 4, 0)
+    with pytest.raises(wd.WdError, match="router_f32"):
+        wd._check(wd.lib().wd_set_router_f32(tiled.h, 0, np.zeros(16 * 256, np.float32).ctypes.data, None))
+    tiled.close()
+
+
+@pytest.mark.parametrize("shape", [(768, 192, 16, 4, 128, ol.TYPE_IQ3_S, False), (2560, 640, 8, 4, 640, ol.TYPE_IQ2_S, True)])
+def test_stack_step_matches_oracle_chain(wd, oracle, shape):
+    """wd_stack_step on the plain-layout path: per layer x = RMSNorm(residual) * w, residual += block(x), three layers,
+    three tokens; hidden 768 and 2560 make the RMSNorm tree pad to 1024 and 4096 leaves."""
+    H, F, E, K, SF, et, rf32 = shape
+    L = 3
+    ms = [synth.make_moe_block(60 + l, H, F, E, K, SF, et, ol.TYPE_IQ4_NL, sigma=0.02, router_f32=rf32) for l in range(L)]
+    eng = wd.Engine(H, F, E, K, SF, L, expert_type=et, down_type=ol.TYPE_IQ4_NL, router_f32=rf32, rms_eps=1e-6)
+    rng = np.random.Generator(np.random.PCG64(61))
+    norms = [(1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32) for _ in range(L)]
+    for l in range(L):
+        eng.load_block(l, ms[l])
+        eng.set_norm(l, norms[l] if l != 1 else None)        # a layer without a norm weight scales only
+    res = rng.standard_normal(H).astype(np.float32)
+    for step in range(3):
+        got = eng.stack_step_host(res)
+        ref = res.copy()
+        for l in range(L):
+            x = oracle.rmsnorm(ref, norms[l] if l != 1 else None, 1e-6)
+            ref = (ref + oracle.moe_block(ms[l], x)["out"]).astype(np.float32)
+        assert np.array_equal(bits(got), bits(ref)), step
+        res = got
+    assert eng.device_status() == 0
+    eng.close()

@@ -1479,10 +1479,10 @@ int wd_moe_forward_host(wd_engine *e, int layer, const float *x_host, float *out
 }
 
 int wd_stack_step(wd_engine *e, float *residual_dev, void *stream) {
-    WD_TILED_ONLY(e);
     if (!e || !residual_dev) return fail(WD_E_INVALID, "null argument");
     WD_CUDA(cudaSetDevice(e->cfg.device));
     cudaStream_t s = stream ? static_cast<cudaStream_t>(stream) : e->stream;
+    if (e->plain) return plain_stack_step(e, residual_dev, s);
     if (!e->resident && !e->fast_fn && e->n_peers == 0)
         return run_capped_optimistic(e, 0, e->cfg.n_layers, nullptr, residual_dev, e->out_buf, s);
     if (!e->resident) {     // layer by layer: the host places the selected experts between the two passes
@@ -1496,7 +1496,6 @@ int wd_stack_step(wd_engine *e, float *residual_dev, void *stream) {
 }
 
 int wd_stack_step_host(wd_engine *e, const float *in_host, float *out_host) {
-    WD_TILED_ONLY(e);
     if (!e || !in_host || !out_host) return fail(WD_E_INVALID, "null argument");
     const size_t bytes = static_cast<size_t>(e->cfg.hidden) * 4;
     WD_CUDA(cudaSetDevice(e->cfg.device));
@@ -1511,7 +1510,7 @@ int wd_stack_step_host(wd_engine *e, const float *in_host, float *out_host) {
     // the last CTA of every launch leaves the status word in pinned host memory: no copy to read it.
     // (Letting the kernel read and write the residual in pinned memory directly was measured slower: every CTA
     // fetches the whole vector over PCIe.)
-    if (*e->host_status == 0u) return WD_OK;
+    if (!e->plain && *e->host_status == 0u) return WD_OK;
     return check_device_status(e);
 }
 

@@ -346,6 +346,66 @@ __host__ __device__ inline size_t plain_down_smem(int F, int SF, int K, int down
            SF + (SF / 32 + 3) / 4 * 16 + act_floats * 4;
 }
 
+// ---- 0 (stack step only): x = RMSNorm(residual) * w -----------------------------------------------------------------
+// The sum of squares is the perfect binary tree in double over consecutive elements, zero-padded to `width` (the power
+// of two at or above n), that defines the RMSNorm between the blocks of the stack on the CPU side as well; one CTA of
+// min(512, width) threads, a thread owns width / blockDim consecutive leaves. `prev_out`: the block output of the layer
+// before, still to be added to the residual stream (residual += out, one rounded addition), or null.
+__global__ void __launch_bounds__(kThreads) plain_norm_kernel(float *residual, const float *prev_out, const float *w, int n, int width,
+                                                              float eps, float *x_out) {
+    __shared__ double red[kWarps];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5, per = width / blockDim.x;
+    grid_dep_wait();
+    grid_dep_launch();
+    double acc[16];       // width <= 8192 with 512 threads
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        acc[i] = 0.0;
+        const int e = tid * per + i;
+        if (i < per && e < n) {
+            float v = residual[e];
+            if (prev_out != nullptr) {
+                v = __fadd_rn(v, prev_out[e]);
+                residual[e] = v;
+            }
+            acc[i] = __dmul_rn(static_cast<double>(v), static_cast<double>(v));
+        }
+    }
+#pragma unroll
+    for (int s = 1; s < 16; s <<= 1)
+#pragma unroll
+        for (int i = 0; i + s < 16; i += 2 * s) acc[i] = __dadd_rn(acc[i], acc[i + s]);     // zeros beyond `per` add nothing
+    double ss = acc[0];
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) ss = __dadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, s));
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    double tot[kWarps];
+#pragma unroll
+    for (int i = 0; i < kWarps; ++i) tot[i] = i < nwarps ? red[i] : 0.0;
+#pragma unroll
+    for (int s = 1; s < kWarps; s <<= 1)
+#pragma unroll
+        for (int i = 0; i + s < kWarps; i += 2 * s) tot[i] = __dadd_rn(tot[i], tot[i + s]);
+    const float scale = __double2float_rn(
+        __ddiv_rn(1.0, __dsqrt_rn(__dadd_rn(__ddiv_rn(tot[0], static_cast<double>(n)), static_cast<double>(eps)))));
+    for (int i = 0; i < per; ++i) {
+        const int e = tid * per + i;
+        if (e < n) {
+            const float v = __fmul_rn(residual[e], scale);
+            x_out[e] = w != nullptr ? __fmul_rn(v, w[e]) : v;
+        }
+    }
+}
+
+// residual += out after the last layer of a stack step
+__global__ void plain_add_kernel(float *residual, const float *out, int n) {
+    grid_dep_wait();
+    grid_dep_launch();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) residual[i] = __fadd_rn(residual[i], out[i]);
+}
+
 // ---- 1: x -> Q8_0; router logits, shared expert gate/up rows with SiLU * up, the shared expert's sigmoid gate -------
 // One warp per task, [router tasks | shared gate/up pairs of 4-row tasks | the gate dot]; the task's weights are staged
 // by one bulk copy and applied to every token of the call.
