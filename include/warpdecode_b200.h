@@ -65,7 +65,8 @@ typedef struct {
     int32_t device;          /* CUDA device ordinal */
     int64_t cache_mib;       /* expert slot pool size; <= 0: size it to hold every owned expert.
                                 Same meaning as WARODECODE_EXPERT_CACHE_MIB
-                                (src/qwen38_tuning.hpp:113-116). */
+                                (src/qwen38_tuning.hpp:113-116). On the plain-layout path: the room
+                                the experts may take; they must all fit. */
     float rms_eps;           /* epsilon of the optional fused RMSNorm prologue */
     int32_t router_f32;      /* nonzero: the router is F32 [n_experts][hidden], set with wd_set_router_f32 and applied
                                 to the F32 input in ggml_vec_dot_f32 order (src/qwen38_moe.cuh:2252-2258,

@@ -126,8 +126,9 @@ def test_what_the_plain_layout_path_refuses(wd):
     m, xs = mg.block_cases()[5]
     with pytest.raises(wd.WdError, match="expert parallelism"):
         _engine_for(wd, m, ep_size=2, ep_rank=0)
-    with pytest.raises(wd.WdError, match="resident"):
-        _engine_for(wd, m, cache_mib=64)
+    with pytest.raises(wd.WdError, match="resident"):           # 8 experts of this shape are 16 MiB
+        _engine_for(wd, m, cache_mib=8)
+    _engine_for(wd, m, cache_mib=64).close()                     # room for all of them: accepted, nothing is cached
     with pytest.raises(wd.WdError, match="4096"):
         wd.Engine(8192, 640, 64, 4, 0, 1, expert_type=ol.TYPE_IQ2_S, down_type=ol.TYPE_IQ4_NL)
     eng = _engine_for(wd, m)
