@@ -112,6 +112,10 @@ int wd_set_experts(wd_engine *e, int layer, const void *gate, const void *up, co
  * combination per layer; a tiled engine only the types it was created with. */
 int wd_set_experts_typed(wd_engine *e, int layer, const void *gate, int gate_type, const void *up, int up_type,
                          const void *down, int down_type);
+/* Same from the fused form some files carry: ONE tensor [n_experts][2 * expert_ffn][hidden] per layer, each expert's
+ * gate rows followed by its up rows (ffn_gate_up_exps, qwen38_moe_tensors, src/qwen38_moe.cuh:601-612, :2688).
+ * Engines on the plain-layout path only. */
+int wd_set_experts_fused(wd_engine *e, int layer, const void *gate_up, int gate_up_type, const void *down, int down_type);
 /* Same, from ggml-layout tensors already in DEVICE memory (used by the synthetic model
  * generator); needs a pool that holds every owned expert. Nothing is retained. */
 int wd_set_experts_device(wd_engine *e, int layer, const void *gate, const void *up, const void *down);

@@ -110,7 +110,9 @@ def test_layers_of_different_expert_types_and_a_gguf_file(wd, oracle, tmp_path):
     meta = {"general.architecture": "qwen4exp", "qwen4exp.embedding_length": 768, "qwen4exp.expert_count": 16,
             "qwen4exp.expert_used_count": 4, "qwen4exp.expert_feed_forward_length": 192,
             "qwen4exp.expert_shared_feed_forward_length": 128, "qwen4exp.expert_weights_scale": 1.0}
-    synth.write_gguf(path, meta, synth.moe_block_tensors(m0, 0) + synth.moe_block_tensors(m1, 1))
+    # layer 0 stores its gate and up rows as one fused tensor (the other form the reference's loader reads); the file's
+    # geometry is then read from that tensor
+    synth.write_gguf(path, meta, synth.moe_block_tensors(m0, 0, fused=True) + synth.moe_block_tensors(m1, 1))
     g = wd.Gguf(path)
     eng = wd.Engine.from_gguf(g)
     x = np.random.Generator(np.random.PCG64(9)).standard_normal(768).astype(np.float32)

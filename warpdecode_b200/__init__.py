@@ -86,6 +86,7 @@ def lib():
         L.wd_set_norm.argtypes = [vp, i, vp]
         L.wd_set_experts.argtypes = [vp, i, vp, vp, vp]
         L.wd_set_experts_typed.argtypes = [vp, i, vp, i, vp, i, vp, i]
+        L.wd_set_experts_fused.argtypes = [vp, i, vp, i, vp, i]
         L.wd_set_experts_device.argtypes = [vp, i, vp, vp, vp]
         L.wd_cache_acquire.argtypes = [vp, i, i, C.POINTER(C.c_int)]
         L.wd_cache_stats.argtypes = [vp, C.POINTER(C.c_int64)]

@@ -1310,6 +1310,14 @@ int wd_set_experts_typed(wd_engine *e, int layer, const void *gate, int gate_typ
     return wd_set_experts(e, layer, gate, up, down);
 }
 
+int wd_set_experts_fused(wd_engine *e, int layer, const void *gate_up, int gate_up_type, const void *down, int down_type) {
+    if (!e) return fail(WD_E_INVALID, "null engine");
+    if (!e->plain)
+        return fail(WD_E_INVALID, "a fused gate_up tensor is taken by engines on the plain-layout path only; give the tiled kernels "
+                                  "separate gate and up tensors");
+    return plain_set_experts_fused(e, layer, gate_up, gate_up_type, down, down_type);
+}
+
 int wd_set_experts(wd_engine *e, int layer, const void *gate, const void *up, const void *down) {
     if (e && e->plain)
         return plain_set_experts(e, layer, gate, e->cfg.gate_type, up, e->cfg.up_type, down, e->cfg.down_type, cudaMemcpyHostToDevice);

@@ -329,9 +329,10 @@ def write_gguf(path, metadata, tensors, alignment=32):
             f.write(b"\0" * ((-data.nbytes) % alignment))
 
 
-def moe_block_tensors(m, layer):
+def moe_block_tensors(m, layer, fused=False):
     """GGUF tensor list for one block, named as the reference loader expects
-    (src/qwen38_moe.cuh:569-573, :601-612)."""
+    (src/qwen38_moe.cuh:569-573, :601-612). `fused`: gate and up as ONE tensor ffn_gate_up_exps [H, 2F, E], each
+    expert's gate rows followed by its up rows."""
     p = f"blk.{layer}."
     H, F, E, SF = m["hidden"], m["expert_ffn"], m["n_experts"], m["shared_ffn"]
     router = (p + "ffn_gate_inp.weight", [H, E], TYPE_F32, m["router_f32"]) if "router_f32" in m else \
@@ -340,6 +341,11 @@ def moe_block_tensors(m, layer):
          (p + "ffn_gate_exps.weight", [H, F, E], m["gate_type"], m["gate"]),
          (p + "ffn_up_exps.weight", [H, F, E], m["up_type"], m["up"]),
          (p + "ffn_down_exps.weight", [F, H, E], m["down_type"], m["down"])]
+    if fused:
+        assert m["gate_type"] == m["up_type"]
+        g = np.ascontiguousarray(m["gate"], np.uint8).reshape(E, -1)
+        u = np.ascontiguousarray(m["up"], np.uint8).reshape(E, -1)
+        t[1:3] = [(p + "ffn_gate_up_exps.weight", [H, 2 * F, E], m["gate_type"], np.concatenate([g, u], 1).reshape(-1))]
     if SF:
         t += [(p + "ffn_gate_inp_shexp.weight", [H], TYPE_F32, m["shared_gate_vec"]),
               (p + "ffn_gate_shexp.weight", [H, SF], TYPE_Q8_0, m["shared_gate"]),
