@@ -414,6 +414,7 @@ def run_ours(args, rank, world, local_rank):
         small = synth.make_moe_block(5, PH, PF, 8, 8, PSF, synth.TYPE_IQ2_S, synth.TYPE_IQ4_NL, sigma=0.02, router_f32=True)
         for l in range(PL):
             m = dict(small)
+            m.update(n_experts=PE, top_k=PK, w_scale=1.25)
             m["router_f32"] = (prng.standard_normal(PE * PH) * 0.02).astype(np.float32)
             m["router_bias"] = (prng.standard_normal(PE) * 0.5).astype(np.float32)
             m["gate"] = synth.random_blocks(prng, synth.TYPE_IQ2_S, PE * PF * PH // 256)
@@ -440,9 +441,31 @@ def run_ours(args, rank, world, local_rank):
             us_call[n_tok] = best
         if peng.device_status() != 0 or not bool(torch.isfinite(po).all()):
             raise RuntimeError("the plain-layout calls left a status or non-finite outputs")
+        # the reference's own host code on the same block (the last layer's bytes), all its threads: beside, not instead
+        cpu_us, cpu_threads = None, None
+        try:
+            import oracle_lib as ol
+            ol.build_oracle()
+            if ol.Reference.available():
+                pref = ol.Reference()
+                cpu_threads = pref.threads()
+                xs_host = px.cpu().numpy()
+                got = peng.forward_host(PL - 1, xs_host[0])
+                want = pref.moe_block(m, xs_host[0], cpu_threads)["out"]
+                if not np.array_equal(got.view(np.uint32), want.view(np.uint32)):
+                    raise RuntimeError("the plain-layout block differs from the reference's host code on the bench input")
+                times = []
+                for rep in range(6):
+                    t0 = time.perf_counter()
+                    pref.moe_block(m, xs_host[rep % 4], cpu_threads)
+                    times.append(time.perf_counter() - t0)
+                cpu_us = float(np.median(times[1:])) * 1e6
+        except (ImportError, OSError):
+            pass
         p_bytes = PK * (2 * PF * (PH // 256) * 82 + PH * (PF // 32) * 18) + PE * PH * 4 + 3 * PSF * (PH // 32) * 34
         plain = {"us_per_call": us_call[1], "us_per_call_4_tokens": us_call[4], "bytes_per_token_layer": p_bytes,
                  "hbm_gbs": p_bytes / us_call[1] / 1e3, "kernel": peng.kernel_name(), "launches_per_call": 4,
+                 "cpu_reference_us_per_call": cpu_us, "cpu_threads": cpu_threads, "equals_cpu_reference": cpu_us is not None,
                  "what": "one MoE block call (wd_moe_forward) at the block shape of the reference's own model: hidden 2560, "
                          "expert_ffn 640, 512 experts, top 10, shared expert 640, IQ2_S gate/up, IQ4_NL down, F32 router with "
                          "bias; two layers of random block bytes, device-resident input, fastest of 3 rounds of 40 calls"}

@@ -159,6 +159,7 @@ def plain_case(a):
     small = synth.make_moe_block(5, H, F, 8, 8, SF, synth.TYPE_IQ2_S, synth.TYPE_IQ4_NL, sigma=0.02, router_f32=True)
     for l in range(a.layers):
         m = dict(small)
+        m.update(n_experts=E, top_k=K, w_scale=1.25)
         m["router_f32"] = (rng.standard_normal(E * H) * 0.02).astype(np.float32)
         m["router_bias"] = (rng.standard_normal(E) * 0.5).astype(np.float32)
         m["gate"] = synth.random_blocks(rng, synth.TYPE_IQ2_S, E * F * H // 256)
