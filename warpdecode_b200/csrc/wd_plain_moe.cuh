@@ -3,8 +3,9 @@
 // The tiled kernels (wd_moe_kernel.cuh, wd_moe_batch.cuh) want a power-of-two number of superblocks per row and
 // IQ3_S / IQ2_S tensors throughout. The reference's own model has hidden 2560 (ten superblocks), expert_ffn 640,
 // IQ4_NL down tensors fed by a Q8_0 activation, and an F32 router (src/qwen38_moe.cuh:2181-2211, :2252-2258). Here
-// every row product is one warp (IQ4_NL: half a warp) reading the ggml blocks where they lie, so any hidden that is a
-// multiple of 256 and any expert_ffn that is a multiple of 64 runs. The arithmetic contract is the same as everywhere
+// a warp computes whole rows (a gate and an up row together, four IQ4_NL rows, or one IQ3_S / IQ2_S down row) from the
+// ggml blocks as they lie, so any hidden that is a multiple of 256 and any expert_ffn that is a multiple of 64 runs.
+// The arithmetic contract is the same as everywhere
 // else in this library: integer sums per (superblock or block, chunk-lane), one fmaf per block and chunk-lane in
 // block order, ggml's 8-lane closing tree (src/qwen38_cpu_moe.cuh:290-440).
 //
