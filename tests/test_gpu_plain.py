@@ -177,3 +177,36 @@ def test_stack_step_matches_oracle_chain(wd, oracle, shape):
         res = got
     assert eng.device_status() == 0
     eng.close()
+
+
+@pytest.mark.parametrize("shape", [(4096, 64, 1024, 16, 128, ol.TYPE_IQ3_S, True, 4), (256, 64, 8, 1, 0, ol.TYPE_IQ2_S, False, 2),
+                                   (1024, 512, 64, 8, 256, ol.TYPE_IQ2_S, True, 3)])
+def test_limits_of_the_plain_layout_geometry(wd, oracle, shape):
+    """The ends of what the path accepts: the widest hidden (16 superblocks, four tokens: the largest shared-memory plan of
+    the rows kernel), 1,024 experts with an F32 router, top 16, the smallest expert_ffn (two IQ4_NL blocks per down row), a
+    single expert per token without a shared expert; and a tiled-looking geometry (1024 / 512) that is here only because
+    its down tensors are IQ4_NL. Random block bytes for the experts; every token of the batch against the oracle."""
+    H, F, E, K, SF, et, rf32, T = shape
+    rng = np.random.Generator(np.random.PCG64(H + E))
+    m = synth.make_moe_block(71, H, F, 8, 1, SF, et, ol.TYPE_IQ4_NL, sigma=0.02, router_f32=rf32)     # shared expert, types
+    m.update(n_experts=E, top_k=K, w_scale=1.0)
+    if rf32:
+        m["router_f32"] = (rng.standard_normal(E * H) * 0.05).astype(np.float32)
+    else:
+        m["router"] = synth.quantize_q8_0((rng.standard_normal((E, H)) * 0.05).astype(np.float32)).reshape(-1)
+    m["router_bias"] = (rng.standard_normal(E) * 0.3).astype(np.float32)
+    m["gate"] = ol.random_blocks(rng, et, E * F * H // 256)
+    m["up"] = ol.random_blocks(rng, et, E * F * H // 256)
+    m["down"] = ol.random_blocks(rng, ol.TYPE_IQ4_NL, E * H * F // 32)
+    eng = _engine_for(wd, m, max_tokens=T)
+    eng.load_block(0, m)
+    xs = rng.standard_normal((T, H)).astype(np.float32)
+    outs = eng.forward_host(0, xs)
+    for t in range(T):
+        r = oracle.moe_block(m, xs[t])
+        assert np.array_equal(eng.tap("ids", t), r["ids"])
+        assert np.array_equal(bits(eng.tap("weights", t)), bits(r["weights"]))
+        assert np.array_equal(bits(eng.tap("act", t)), bits(r["act"]))
+        assert np.array_equal(bits(outs[t]), bits(r["out"]))
+    assert eng.device_status() == 0
+    eng.close()
