@@ -38,7 +38,7 @@ def test_default_cache_rule_and_env_override(monkeypatch):
     assert L.wd_default_cache_mib(183359) == 65536
 
 
-@pytest.mark.parametrize("t", [ol.TYPE_Q8_0, ol.TYPE_Q4_0, ol.TYPE_IQ3_S, ol.TYPE_IQ2_S])
+@pytest.mark.parametrize("t", [ol.TYPE_Q8_0, ol.TYPE_Q4_0, ol.TYPE_IQ3_S, ol.TYPE_IQ2_S, ol.TYPE_IQ4_NL])
 def test_synth_encoders_decode_close_to_the_weights(t):
     from warpdecode_b200 import synth
     rng = np.random.Generator(np.random.PCG64(3))
@@ -47,14 +47,15 @@ def test_synth_encoders_decode_close_to_the_weights(t):
     assert blob.shape == (8, synth.row_bytes(t, 512))
     back = synth.dequantize(t, blob, 8, 512)
     rel = np.linalg.norm(back - w) / np.linalg.norm(w)
-    assert rel < {ol.TYPE_Q8_0: 0.01, ol.TYPE_Q4_0: 0.12, ol.TYPE_IQ3_S: 0.35, ol.TYPE_IQ2_S: 0.6}[t]
+    assert rel < {ol.TYPE_Q8_0: 0.01, ol.TYPE_Q4_0: 0.12, ol.TYPE_IQ3_S: 0.35, ol.TYPE_IQ2_S: 0.6, ol.TYPE_IQ4_NL: 0.12}[t]
     try:
         import gguf
         from gguf import quants
     except Exception:
         return
     qt = {ol.TYPE_Q8_0: gguf.GGMLQuantizationType.Q8_0, ol.TYPE_Q4_0: gguf.GGMLQuantizationType.Q4_0,
-          ol.TYPE_IQ3_S: gguf.GGMLQuantizationType.IQ3_S, ol.TYPE_IQ2_S: gguf.GGMLQuantizationType.IQ2_S}[t]
+          ol.TYPE_IQ3_S: gguf.GGMLQuantizationType.IQ3_S, ol.TYPE_IQ2_S: gguf.GGMLQuantizationType.IQ2_S,
+          ol.TYPE_IQ4_NL: gguf.GGMLQuantizationType.IQ4_NL}[t]
     theirs = quants.dequantize(blob, qt)
     assert np.array_equal(theirs.astype(np.float32), back.astype(np.float32))
 
@@ -141,6 +142,46 @@ def test_gguf_reader_geometry_and_tensors_without_a_gpu(tmp_path):
     g2 = wd.Gguf(path2)
     assert g2.config().gate_type == ol.TYPE_IQ2_S and g2.config().n_layers == 1
     g2.close()
+
+
+def test_gguf_reader_takes_the_reference_models_tensor_forms(tmp_path):
+    """A file shaped like the reference's own model (src/qwen38_moe.cuh:601-612, :2181-2258): F32 router, IQ4_NL down
+    tensors, hidden that is not a power of two, expert_ffn a multiple of 64, gate and up rows fused into one tensor in
+    the first layer. The geometry comes out of the fused tensor; no CUDA call is involved."""
+    import warpdecode_b200 as wd
+    from warpdecode_b200 import synth
+    ms = [synth.make_moe_block(40 + l, 768, 192, 8, 2, 128, ol.TYPE_IQ2_S, ol.TYPE_IQ4_NL, sigma=0.02, router_f32=True)
+          for l in range(2)]
+    path = str(tmp_path / "ref_forms.gguf")
+    meta = {"general.architecture": "qwen4exp", "qwen4exp.embedding_length": 768, "qwen4exp.expert_count": 8,
+            "qwen4exp.expert_used_count": 2, "qwen4exp.expert_feed_forward_length": 192,
+            "qwen4exp.expert_shared_feed_forward_length": 128}
+    synth.write_gguf(path, meta, synth.moe_block_tensors(ms[0], 0, fused=True) + synth.moe_block_tensors(ms[1], 1))
+    g = wd.Gguf(path)
+    c = g.config()
+    assert (c.hidden, c.expert_ffn, c.shared_ffn, c.n_experts, c.top_k, c.n_layers) == (768, 192, 128, 8, 2, 2)
+    assert (c.gate_type, c.up_type, c.down_type, c.router_f32) == (ol.TYPE_IQ2_S, ol.TYPE_IQ2_S, ol.TYPE_IQ4_NL, 1)
+    data, t, dims = g.tensor("blk.0.ffn_gate_up_exps.weight")
+    assert (t, dims) == (ol.TYPE_IQ2_S, [768, 384, 8])
+    rb = 192 * 3 * 82                    # one expert's gate (or up) rows
+    fused = data.reshape(8, 2 * rb)
+    assert np.array_equal(fused[:, :rb].reshape(-1), ms[0]["gate"]) and np.array_equal(fused[:, rb:].reshape(-1), ms[0]["up"])
+    data, t, dims = g.tensor("blk.1.ffn_gate_inp.weight")
+    assert (t, dims) == (ol.TYPE_F32, [768, 8]) and np.array_equal(data.view(np.float32), ms[1]["router_f32"])
+    data, t, dims = g.tensor("blk.1.ffn_down_exps.weight")
+    assert (t, dims) == (ol.TYPE_IQ4_NL, [192, 768, 8]) and np.array_equal(data, ms[1]["down"])
+    g.close()
+
+
+def test_oracle_f32_router_block_against_the_reference_any_thread_count(oracle, reference):
+    """The reference composition run live (when its sources are present): F32 router, IQ4_NL down, hidden 2560."""
+    from warpdecode_b200 import synth
+    m = synth.make_moe_block(9, 2560, 640, 8, 4, 640, ol.TYPE_IQ2_S, ol.TYPE_IQ4_NL, sigma=0.02, router_f32=True, w_scale=1.25)
+    x = np.random.Generator(np.random.PCG64(10)).standard_normal(2560).astype(np.float32)
+    o = oracle.moe_block(m, x)
+    for th in (1, 3, 8):
+        r = reference.moe_block(m, x, threads=th)
+        assert np.array_equal(r["ids"], o["ids"]) and np.array_equal(ol.fbits(r["out"]), ol.fbits(o["out"]))
 
 
 def test_gguf_reader_refuses_broken_files(tmp_path):
