@@ -203,6 +203,14 @@ typedef struct wd_dense_decoder wd_dense_decoder;
 #define WD_DT_W_GATE_UP 7    /* Q4_0 [2 * ffn][hidden]: gate rows, then up rows (Layer::gate_up) */
 #define WD_DT_W_DOWN 8       /* Q4_0 [hidden][ffn] */
 int wd_dense_decoder_create(const wd_dense_config *cfg, wd_dense_decoder **out);
+/* Decoder with the geometry and every tensor of a Llama-style Q4_0 model file (architectures llama, qwen2, qwen3), read
+ * the way load_model does (src/warodecode.cu:1255-1345): q/k/v and gate/up joined row-wise, an absent output.weight tied
+ * to the embedding table. Files with q/k/v biases, q/k norms, partial or scaled rotary embeddings or 2-D tensors of
+ * another type than Q4_0 are refused by name. The file may be closed afterwards (wd_gguf is declared further down). */
+struct wd_gguf;
+int wd_dense_decoder_load_gguf(const struct wd_gguf *g, int max_ctx, int device, wd_dense_decoder **out);
+/* The configuration a decoder was created with. */
+int wd_dense_decoder_config(const wd_dense_decoder *d, wd_dense_config *cfg);
 void wd_dense_decoder_destroy(wd_dense_decoder *d);
 /* What a token runs on: a CUDA graph of per-operation kernels (the default, and the faster of the two as measured), or
  * with WD_DENSE_TOKEN_KERNEL=1 and a geometry that fits it one persistent launch of the token kernel. Same results. */

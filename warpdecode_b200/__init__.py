@@ -113,6 +113,8 @@ def lib():
         L.wd_last_kernel_name.restype = C.c_char_p
         L.wd_measure_tile_decoder.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]
         L.wd_dense_decoder_create.argtypes = [C.POINTER(DenseConfig), C.POINTER(C.c_void_p)]
+        L.wd_dense_decoder_load_gguf.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
+        L.wd_dense_decoder_config.argtypes = [C.c_void_p, C.POINTER(DenseConfig)]
         L.wd_dense_decoder_destroy.argtypes = [C.c_void_p]
         L.wd_dense_decoder_destroy.restype = None
         L.wd_dense_decoder_kernel_name.argtypes = [C.c_void_p]
@@ -474,6 +476,16 @@ class DenseDecoder:
         self.cfg = DenseConfig(hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, n_layers, max_ctx, rms_eps, rope_theta, device)
         self.h = C.c_void_p()
         _check(lib().wd_dense_decoder_create(C.byref(self.cfg), C.byref(self.h)))
+
+    @classmethod
+    def from_gguf(cls, gguf, max_ctx, device=0):
+        """Decoder with the geometry and tensors of a Llama-style Q4_0 file (wd_dense_decoder_load_gguf)."""
+        self = cls.__new__(cls)
+        self.h = C.c_void_p()
+        _check(lib().wd_dense_decoder_load_gguf(gguf.h, max_ctx, device, C.byref(self.h)))
+        self.cfg = DenseConfig()
+        _check(lib().wd_dense_decoder_config(self.h, C.byref(self.cfg)))
+        return self
 
     def shape(self, which):
         c = self.cfg

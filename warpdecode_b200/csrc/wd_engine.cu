@@ -45,6 +45,17 @@ int fail(int code, const std::string &msg) {
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// A copy whose result a kernel on one of this library's NON-BLOCKING streams reads next. cudaMemcpy from pageable host
+// memory may return as soon as the bytes sit in the driver's staging buffer, with the last chunk still on its way to the
+// device, and a device-to-device cudaMemcpy does not wait on the host side at all; a non-blocking stream is not ordered
+// behind either. Waiting for the legacy stream, on which both run, closes that window.
+cudaError_t copy_sync(void *dst, const void *src, size_t bytes, cudaMemcpyKind kind) {
+    cudaError_t ce = cudaMemcpy(dst, src, bytes, kind);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(cudaStreamLegacy);
+    return ce;
+}
+cudaError_t upload_sync(void *dst, const void *src, size_t bytes) { return copy_sync(dst, src, bytes, cudaMemcpyHostToDevice); }
+
 // Launch with the programmatic-serialization attribute: the kernel may be scheduled while its predecessor in the
 // stream still runs; it orders itself behind it with grid_dep_wait() (wd_device.cuh).
 template <class... KArgs, class... Args>
@@ -486,7 +497,7 @@ int upload_repacked_q8(wd_engine *e, const void *host_ggml, int rows, int cols, 
 
 int upload_f32(wd_engine *e, const float *host, size_t n, float **dev_out) {
     if (!*dev_out) WD_CUDA(cudaMalloc(dev_out, n * 4));
-    WD_CUDA(cudaMemcpy(*dev_out, host, n * 4, cudaMemcpyHostToDevice));
+    WD_CUDA(upload_sync(*dev_out, host, n * 4));
     (void)e;
     return WD_OK;
 }
@@ -955,9 +966,9 @@ int wd_engine_create(const wd_config *cfg, wd_engine **out) {
         e->lru_pos[s] = std::prev(e->lru.end());
     }
     WD_TRY(cudaMalloc(&e->grid_packed, sizeof(wd_iq3s_grid_packed)));
-    WD_TRY(cudaMemcpy(e->grid_packed, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
+    WD_TRY(upload_sync(e->grid_packed, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed)));
     WD_TRY(cudaMalloc(&e->grid2_packed, sizeof(wd_iq2s_grid_packed)));
-    WD_TRY(cudaMemcpy(e->grid2_packed, wd_iq2s_grid_packed, sizeof(wd_iq2s_grid_packed), cudaMemcpyHostToDevice));
+    WD_TRY(upload_sync(e->grid2_packed, wd_iq2s_grid_packed, sizeof(wd_iq2s_grid_packed)));
     WD_TRY(cudaMalloc(&e->sync, 8192));
     WD_TRY(cudaMemset(e->sync, 0, 8192));
     const int H = c.hidden, F = c.expert_ffn, K = c.top_k, E = c.n_experts, SF = std::max(c.shared_ffn, 1);
@@ -1663,7 +1674,7 @@ int wd_measure_tile_decoder(int device, int nsb, int warps, int unroll, double *
     WD_CUDA(hold.alloc(&grid, sizeof(wd_iq3s_grid_packed)));
     WD_CUDA(hold.alloc(&cyc, static_cast<size_t>(n_sm) * sizeof(unsigned long long)));
     WD_CUDA(hold.alloc(&sink, static_cast<size_t>(n_sm) * wd::kThreads * sizeof(float)));
-    WD_CUDA(cudaMemcpy(grid, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
+    WD_CUDA(upload_sync(grid, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed)));
     const size_t sm = wd::kGridTableBytes + 16 * wd::kIq3TileBytes + 32 * wd::kActSbStride + 128 + static_cast<size_t>(wd::kWarps) * 640 * 4;
     const int iters = 200;
     auto fn = unroll == 8 ? wd::iq3_decoder_rate_kernel<8> : wd::iq3_decoder_rate_kernel<1>;
@@ -1829,7 +1840,7 @@ int wd_router_topk_host(const float *logits, int n_experts, int k, float w_scale
     WD_CUDA(bufs.alloc(&d_p, n_experts * 4));
     WD_CUDA(bufs.alloc(&d_w, wd::kMaxK * 4));
     WD_CUDA(bufs.alloc(&d_i, wd::kMaxK * 4));
-    WD_CUDA(cudaMemcpy(d_l, logits, n_experts * 4, cudaMemcpyHostToDevice));
+    WD_CUDA(upload_sync(d_l, logits, n_experts * 4));
     wd::test_router_kernel<<<1, wd::kThreads>>>(d_l, n_experts, k, w_scale, d_i, d_w, d_p);
     WD_CUDA(cudaGetLastError());
     WD_CUDA(cudaDeviceSynchronize());
@@ -1845,7 +1856,7 @@ static int quantize_host(const float *x, int n, void *q80, void *q8k) {
     float *d_x = nullptr;
     uint8_t *d_0 = nullptr, *d_k = nullptr;
     WD_CUDA(bufs.alloc(&d_x, n * 4));
-    WD_CUDA(cudaMemcpy(d_x, x, n * 4, cudaMemcpyHostToDevice));
+    WD_CUDA(upload_sync(d_x, x, n * 4));
     if (q80) WD_CUDA(bufs.alloc(&d_0, n / 32 * 34));
     if (q8k) WD_CUDA(bufs.alloc(&d_k, n / 256 * 292));
     const size_t smem = n * 4 + n + n / 32 * 4 + (n / 256 + 1) * wd::kActSbStride + (n / 256 + 4) * 4 + 64;
@@ -1878,11 +1889,11 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
         WD_CUDA(bufs.alloc(&d_x, cols * 4));
         WD_CUDA(bufs.alloc(&d_y, rows * 4));
         WD_CUDA(bufs.alloc(&d_grid, sizeof(wd_iq2s_grid_packed)));      // the larger of the two codebooks
-        if (iq2) WD_CUDA(cudaMemcpy(d_grid, wd_iq2s_grid_packed, sizeof(wd_iq2s_grid_packed), cudaMemcpyHostToDevice));
-        else WD_CUDA(cudaMemcpy(d_grid, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
+        if (iq2) WD_CUDA(upload_sync(d_grid, wd_iq2s_grid_packed, sizeof(wd_iq2s_grid_packed)));
+        else WD_CUDA(upload_sync(d_grid, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed)));
         if (partials) WD_CUDA(bufs.alloc(&d_p, static_cast<size_t>(rows) * nsb * 8 * 4));
-        WD_CUDA(cudaMemcpy(d_src, w, bytes, cudaMemcpyHostToDevice));
-        WD_CUDA(cudaMemcpy(d_x, x, cols * 4, cudaMemcpyHostToDevice));
+        WD_CUDA(upload_sync(d_src, w, bytes));
+        WD_CUDA(upload_sync(d_x, x, cols * 4));
         const long long nblocks = static_cast<long long>(rows) * nsb;
         if (iq2) wd::repack_iq2s_kernel<<<static_cast<unsigned>((nblocks + 127) / 128), 128>>>(d_src, d_dst, nblocks, 0, 0);
         else wd::repack_iq3s_kernel<<<static_cast<unsigned>((nblocks + 127) / 128), 128>>>(d_src, d_dst, nblocks, 0, 0);
@@ -1902,8 +1913,8 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
         WD_CUDA(bufs.alloc(&d_dst, bytes));
         WD_CUDA(bufs.alloc(&d_x, cols * 4));
         WD_CUDA(bufs.alloc(&d_y, rows * 4));
-        WD_CUDA(cudaMemcpy(d_src, w, bytes, cudaMemcpyHostToDevice));
-        WD_CUDA(cudaMemcpy(d_x, x, cols * 4, cudaMemcpyHostToDevice));
+        WD_CUDA(upload_sync(d_src, w, bytes));
+        WD_CUDA(upload_sync(d_x, x, cols * 4));
         const long long n = static_cast<long long>(rows) * nb;
         wd::repack_q8_0_kernel<<<static_cast<unsigned>((n + 255) / 256), 256>>>(d_src, d_dst, rows, nb);
         const int nw = 8;
@@ -1919,7 +1930,7 @@ int wd_matvec_host(int type, const void *w, int rows, int cols, const float *x, 
         if (rc) return rc;
         WD_CUDA(bufs.alloc(&d_x, cols * 4));
         WD_CUDA(bufs.alloc(&d_y, rows * 4));
-        WD_CUDA(cudaMemcpy(d_x, x, cols * 4, cudaMemcpyHostToDevice));
+        WD_CUDA(upload_sync(d_x, x, cols * 4));
         rc = wd_dense_matvec_q4_0(packed, rows, cols, d_x, d_y, nullptr);
         if (rc == WD_OK) {
             WD_CUDA(cudaDeviceSynchronize());
@@ -1966,7 +1977,7 @@ int wd_dense_pack_q4_0(const void *w_ggml_host, int rows, int cols, void **packe
     const size_t bytes = static_cast<size_t>(rows) * (cols / 32) * 18;
     uint8_t *src = nullptr;
     WD_CUDA(cudaMalloc(&src, bytes));
-    cudaError_t ce = cudaMemcpy(src, w_ggml_host, bytes, cudaMemcpyHostToDevice);
+    cudaError_t ce = upload_sync(src, w_ggml_host, bytes);
     if (ce == cudaSuccess) {
         rc = wd_dense_pack_q4_0_device(src, rows, cols, packed_dev, nullptr);
         cudaDeviceSynchronize();
@@ -2048,7 +2059,7 @@ int wd_dense_pack_q8_0(const void *w_ggml_host, int rows, int cols, void **packe
     const size_t bytes = static_cast<size_t>(rows) * (cols / 32) * 34;
     uint8_t *src = nullptr;
     WD_CUDA(cudaMalloc(&src, bytes));
-    cudaError_t ce = cudaMemcpy(src, w_ggml_host, bytes, cudaMemcpyHostToDevice);
+    cudaError_t ce = upload_sync(src, w_ggml_host, bytes);
     if (ce == cudaSuccess) {
         rc = wd_dense_pack_q8_0_device(src, rows, cols, packed_dev, nullptr);
         cudaDeviceSynchronize();
@@ -2313,7 +2324,7 @@ int noalloc_scratch_for_current_device(void **out) {
         if (ce != cudaSuccess || p == nullptr)
             return fail(WD_E_CUDA, std::string("cudaGetSymbolAddress(wd_noalloc_scratch): ") + cudaGetErrorString(ce));
         static_assert(sizeof(wd_iq3s_grid_packed) == kNoAllocGridBytes, "packed codebook size");
-        WD_CUDA(cudaMemcpy(p, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed), cudaMemcpyHostToDevice));
+        WD_CUDA(upload_sync(p, wd_iq3s_grid_packed, sizeof(wd_iq3s_grid_packed)));
         g_noalloc_ptr[dev].store(p, std::memory_order_release);
     }
     *out = p;
