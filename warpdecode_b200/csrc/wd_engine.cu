@@ -858,6 +858,7 @@ int check_device_status(wd_engine *e) {
         cudaMemset(e->sync, 0, 8192);
         cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t));
         if (e->xbuf) cudaMemset(e->xbuf, 0, e->xbuf_words * sizeof(wd::tagged_t));
+        cudaDeviceSynchronize();                // the next launch runs on a stream that is not ordered behind these
         e->epoch = 0;
         return fail(WD_E_DEVICE, "kernel raised status " + std::to_string(st) +
                                      " (1 wait timeout, 2 copy timeout, 4 expert without slot, 8 geometry, "
@@ -1822,6 +1823,7 @@ int wd_device_status(wd_engine *e, int *status) {
         WD_CUDA(cudaMemset(e->sync, 0, 8192));
         WD_CUDA(cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t)));
         if (e->xbuf) WD_CUDA(cudaMemset(e->xbuf, 0, e->xbuf_words * sizeof(wd::tagged_t)));
+        WD_CUDA(cudaDeviceSynchronize());       // the next launch runs on a stream that is not ordered behind these
         e->epoch = 0;
     }
     return WD_OK;
