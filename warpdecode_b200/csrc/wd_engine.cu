@@ -1808,6 +1808,7 @@ int wd_reset_exchange(wd_engine *e) {
     WD_CUDA(cudaMemset(e->sync, 0, 8192));
     WD_CUDA(cudaMemset(e->tagged, 0, e->tagged_words * sizeof(wd::tagged_t)));
     if (e->xbuf) WD_CUDA(cudaMemset(e->xbuf, 0, e->xbuf_words * sizeof(wd::tagged_t)));
+    WD_CUDA(cudaDeviceSynchronize());           // the next launch runs on a stream that is not ordered behind these
     e->epoch = 0;
     return WD_OK;
 }
