@@ -46,6 +46,12 @@ static inline double __longlong_as_double(uint64_t x) { double r; std::memcpy(&r
 
 namespace cm = wd::cpu_moe;
 
+// src/ggml_dequant.hpp is host code that asks its includer for __half / __float2half when there is no CUDA compiler
+// (as tests/gemv_kquant_dequant_host_test.cpp of the reference does); the conversion is the reference's own.
+struct __half { unsigned short bits; };
+static inline __half __float2half(float v) { return __half{cm::f32_to_f16_bits(v)}; }
+#include "ggml_dequant.hpp"
+
 #include <atomic>
 #include <condition_variable>
 #include <functional>
@@ -174,6 +180,17 @@ float ref_row_iq4_nl_q8_0(const uint8_t * w, const uint8_t * y, int cols, int va
     const cm::q8_0 * yb = reinterpret_cast<const cm::q8_0 *>(y);
     return variant ? cm::scalar_iq4_nl_q8_0(w, yb, cols) : cm::row_iq4_nl_q8_0(w, yb, cols);
 }
+
+// The dense loader's host requantiser (ggml_requantize_row_to_q8_0, src/ggml_dequant.hpp:362-392) and its Q6_K value.
+int ref_requantize_row_to_q8_0(int type, const uint8_t * src, uint8_t * dst, int cols) {
+    try {
+        wd::ggml_requantize_row_to_q8_0(static_cast<wd::GgmlType>(type), src, dst, cols);
+    } catch (const std::exception &) {
+        return -1;
+    }
+    return 0;
+}
+float ref_q6_k_value(const uint8_t * blk, int i) { return wd::ggml_q6_k_value(blk, i); }
 
 float ref_exp_ggml(float x) { return cm::ggml_avx2_exp_f32(x); }
 float ref_silu_ggml(float x) { return cm::silu_ggml(x); }

@@ -63,29 +63,60 @@ float wdo_row_q4_0_q8_0_lanes(const uint8_t *w_row, const uint8_t *y, int cols) 
     return lane[0];
 }
 
-/* y = W x for W [rows][cols] in ggml Q4_0 blocks, x already Q8_0. Rows are independent: the thread count does not
- * change a bit. */
+/* The same for a Q8_0 matrix (the form every 2-D tensor that is not Q4_0 takes in the reference's dense loader,
+ * planarize_q4, src/warodecode.cu:1027-1075): int_dot = sum of q_w * a over the block's 32 values. */
+float wdo_row_q8_0_q8_0_lanes(const uint8_t *w_row, const uint8_t *y, int cols) {
+    const int nb = cols / 32;
+    float lane[32];
+    for (int l = 0; l < 32; ++l) lane[l] = 0.0f;
+    for (int b = 0; b < nb; ++b) {
+        const uint8_t *wb = w_row + (size_t)b * Q8_BYTES;
+        const uint8_t *yb = y + (size_t)b * Q8_BYTES;
+        const int8_t *wq = (const int8_t *)(wb + 2), *yq = (const int8_t *)(yb + 2);
+        uint16_t dw, dy;
+        memcpy(&dw, wb, 2);
+        memcpy(&dy, yb, 2);
+        int sum = 0;
+        for (int j = 0; j < 32; ++j) sum += (int)wq[j] * (int)yq[j];
+        const float d = mulf(wdo_f16_to_f32(dw), wdo_f16_to_f32(dy));
+        lane[b & 31] = fmaf(d, (float)sum, lane[b & 31]);
+    }
+    for (int s = 16; s >= 1; s >>= 1) {
+        float next[32];
+        for (int l = 0; l < 32; ++l) next[l] = addf(lane[l], lane[l ^ s]);
+        memcpy(lane, next, sizeof(lane));
+    }
+    return lane[0];
+}
+
+/* y = W x for W [rows][cols] in ggml Q4_0 or Q8_0 blocks, x already Q8_0. Rows are independent: the thread count does
+ * not change a bit. */
 typedef struct {
     const uint8_t *w, *xq;
     float *y;
-    int cols, r0, r1;
+    int cols, r0, r1, type;
 } mv_job;
 
 static void *mv_worker(void *arg) {
     const mv_job *j = (const mv_job *)arg;
-    const size_t row_bytes = (size_t)(j->cols / 32) * Q4_BYTES;
-    for (int r = j->r0; r < j->r1; ++r) j->y[r] = wdo_row_q4_0_q8_0_lanes(j->w + (size_t)r * row_bytes, j->xq, j->cols);
+    const int q8 = j->type == WDO_TYPE_Q8_0;
+    const size_t row_bytes = (size_t)(j->cols / 32) * (q8 ? Q8_BYTES : Q4_BYTES);
+    for (int r = j->r0; r < j->r1; ++r)
+        j->y[r] = q8 ? wdo_row_q8_0_q8_0_lanes(j->w + (size_t)r * row_bytes, j->xq, j->cols)
+                     : wdo_row_q4_0_q8_0_lanes(j->w + (size_t)r * row_bytes, j->xq, j->cols);
     return NULL;
 }
 
-void wdo_matvec_q4_0(const uint8_t *w, int rows, int cols, const uint8_t *xq, float *y) {
+void wdo_matvec_q4_0(const uint8_t *w, int rows, int cols, const uint8_t *xq, float *y) { wdo_matvec_typed(WDO_TYPE_Q4_0, w, rows, cols, xq, y); }
+
+void wdo_matvec_typed(int type, const uint8_t *w, int rows, int cols, const uint8_t *xq, float *y) {
     long ncpu = sysconf(_SC_NPROCESSORS_ONLN);
     int nt = ncpu > 16 ? 16 : (ncpu < 1 ? 1 : (int)ncpu);
     if (rows < 256) nt = 1;
     mv_job jobs[16];
     pthread_t th[16];
     for (int t = 0; t < nt; ++t) {
-        jobs[t].w = w; jobs[t].xq = xq; jobs[t].y = y; jobs[t].cols = cols;
+        jobs[t].w = w; jobs[t].xq = xq; jobs[t].y = y; jobs[t].cols = cols; jobs[t].type = type;
         jobs[t].r0 = (int)((long long)rows * t / nt);
         jobs[t].r1 = (int)((long long)rows * (t + 1) / nt);
     }
@@ -115,6 +146,71 @@ void wdo_embed_q4_0(const uint8_t *table, int cols, int token, float *out) {
             out[b * 32 + 16 + j] = mulf(d, (float)((int)(wb[2 + j] >> 4) - 8));
         }
     }
+}
+
+/* Embedding row of a Q8_0 table: value i = d(block) * q, one float multiply. */
+void wdo_embed_q8_0(const uint8_t *table, int cols, int token, float *out) {
+    const uint8_t *row = table + (size_t)token * (size_t)(cols / 32) * Q8_BYTES;
+    for (int b = 0; b < cols / 32; ++b) {
+        const uint8_t *wb = row + (size_t)b * Q8_BYTES;
+        uint16_t dw;
+        memcpy(&dw, wb, 2);
+        const float d = wdo_f16_to_f32(dw);
+        for (int j = 0; j < 32; ++j) out[b * 32 + j] = mulf(d, (float)(int8_t)wb[2 + j]);
+    }
+}
+
+/* One value of a Q6_K block (210 bytes per 256 values: ql(128) qh(64) scales(16, int8) d(2)); the expression of
+ * ggml_q6_k_value, src/ggml_dequant.hpp:102-133: (d * scale) * (v - 32), two float multiplies. */
+float wdo_q6_k_value(const uint8_t *blk, int i) {
+    const uint8_t *ql = blk, *qh = blk + 128;
+    const int8_t *sc = (const int8_t *)(blk + 192);
+    uint16_t db;
+    memcpy(&db, blk + 208, 2);
+    const float d = wdo_f16_to_f32(db);
+    const int half = i >> 7, r = i & 127, l = r & 31, q = r >> 5;
+    const uint8_t *ql64 = ql + half * 64, *qh32 = qh + half * 32;
+    const int8_t *sc8 = sc + half * 8;
+    int v;
+    if (q == 0) v = (ql64[l] & 0x0f) | (((qh32[l] >> 0) & 3) << 4);
+    else if (q == 1) v = (ql64[l + 32] & 0x0f) | (((qh32[l] >> 2) & 3) << 4);
+    else if (q == 2) v = (ql64[l] >> 4) | (((qh32[l] >> 4) & 3) << 4);
+    else v = (ql64[l + 32] >> 4) | (((qh32[l] >> 6) & 3) << 4);
+    return mulf(mulf(d, (float)sc8[(l >> 4) + 2 * q]), (float)(v - 32));
+}
+
+/* A row of a tensor that is not Q4_0, turned into Q8_0 blocks the way the reference's dense loader does it on the host
+ * (ggml_requantize_row_to_q8_0, src/ggml_dequant.hpp:362-392): per 32 values d = amax / 127 in F32, stored rounded to
+ * f16, quant = lround(v / d) with the UNROUNDED d, clamped to [-128, 127]. Source types: Q8_0 (8) and Q6_K (14).
+ * Returns 0, or -1 for another type or a column count that does not fit. */
+int wdo_requantize_row_to_q8_0(int type, const uint8_t *src, uint8_t *dst, int cols) {
+    if (cols % 32 || (type != WDO_TYPE_Q8_0 && type != 14) || (type == 14 && cols % 256)) return -1;
+    for (int b = 0; b < cols / 32; ++b) {
+        float v[32], amax = 0.0f;
+        for (int i = 0; i < 32; ++i) {
+            const int idx = b * 32 + i;
+            if (type == WDO_TYPE_Q8_0) {
+                const uint8_t *bp = src + (size_t)(idx / 32) * Q8_BYTES;
+                uint16_t dw;
+                memcpy(&dw, bp, 2);
+                v[i] = mulf(wdo_f16_to_f32(dw), (float)(int8_t)bp[2 + (idx & 31)]);
+            } else {
+                v[i] = wdo_q6_k_value(src + (size_t)(idx / 256) * 210, idx & 255);
+            }
+            if (fabsf(v[i]) > amax) amax = fabsf(v[i]);
+        }
+        const float d = amax / 127.0f;
+        uint8_t *out = dst + (size_t)b * Q8_BYTES;
+        const uint16_t dh = wdo_f32_to_f16(d);
+        memcpy(out, &dh, 2);
+        for (int i = 0; i < 32; ++i) {
+            long q = d == 0.0f ? 0 : lroundf(v[i] / d);
+            if (q > 127) q = 127;
+            if (q < -128) q = -128;
+            out[2 + i] = (uint8_t)(int8_t)q;
+        }
+    }
+    return 0;
 }
 
 /* cos/sin table of the rotary embedding: angle = pos * theta^(-2p / head_dim) in double, rounded to float once.
@@ -193,7 +289,8 @@ int wdo_dense_step(const wdo_dense_model *m, float *kcache, float *vcache, int t
     float *logits = logits_out ? logits_out : (float *)malloc(sizeof(float) * V);
     const float inv_sqrt = (float)(1.0 / sqrt((double)hd));
     const float *cs = m->rope_table + (size_t)pos * (hd / 2) * 2;
-    wdo_embed_q4_0(m->token_embd, H, token, hidden);
+    if (m->token_embd_type == WDO_TYPE_Q8_0) wdo_embed_q8_0(m->token_embd, H, token, hidden);
+    else wdo_embed_q4_0(m->token_embd, H, token, hidden);
     for (int li = 0; li < m->n_layers; ++li) {
         const wdo_dense_layer *L = &m->layers[li];
         float *kc = kcache + (size_t)li * m->max_ctx * kvdim, *vc = vcache + (size_t)li * m->max_ctx * kvdim;
@@ -201,7 +298,7 @@ int wdo_dense_step(const wdo_dense_model *m, float *kcache, float *vcache, int t
             for (int i = 0; i < H; ++i) hidden[i] = addf(hidden[i], proj[i]);
         wdo_rmsnorm(hidden, L->attn_norm, m->rms_eps, H, norm);
         wdo_quantize_q8_0(norm, xq, H / 32);
-        wdo_matvec_q4_0(L->wqkv, qkv_rows, H, xq, qkv);
+        wdo_matvec_typed(L->wqkv_type, L->wqkv, qkv_rows, H, xq, qkv);
         for (int h = 0; h < nh; ++h) rope_head(qkv + (size_t)h * hd, hd, cs);
         for (int h = 0; h < nkv; ++h) rope_head(qkv + qdim + (size_t)h * hd, hd, cs);
         memcpy(kc + (size_t)pos * kvdim, qkv + qdim, sizeof(float) * kvdim);
@@ -212,19 +309,19 @@ int wdo_dense_step(const wdo_dense_model *m, float *kcache, float *vcache, int t
                            attn + (size_t)h * hd, scores);
         }
         wdo_quantize_q8_0(attn, xq, qdim / 32);
-        wdo_matvec_q4_0(L->wo, H, qdim, xq, proj);
+        wdo_matvec_typed(L->wo_type, L->wo, H, qdim, xq, proj);
         for (int i = 0; i < H; ++i) hidden[i] = addf(hidden[i], proj[i]);
         wdo_rmsnorm(hidden, L->ffn_norm, m->rms_eps, H, norm);
         wdo_quantize_q8_0(norm, xq, H / 32);
-        wdo_matvec_q4_0(L->w_gate_up, 2 * F, H, xq, gu);
+        wdo_matvec_typed(L->w_gate_up_type, L->w_gate_up, 2 * F, H, xq, gu);
         for (int i = 0; i < F; ++i) norm[i] = mulf(wdo_silu_ggml(gu[i]), gu[F + i]);
         wdo_quantize_q8_0(norm, xq, F / 32);
-        wdo_matvec_q4_0(L->w_down, H, F, xq, proj);
+        wdo_matvec_typed(L->w_down_type, L->w_down, H, F, xq, proj);
     }
     for (int i = 0; i < H; ++i) hidden[i] = addf(hidden[i], proj[i]);
     wdo_rmsnorm(hidden, m->output_norm, m->rms_eps, H, norm);
     wdo_quantize_q8_0(norm, xq, H / 32);
-    wdo_matvec_q4_0(m->output, V, H, xq, logits);
+    wdo_matvec_typed(m->output_type, m->output, V, H, xq, logits);
     int best = 0;
     float bv = -INFINITY;
     for (int i = 0; i < V; ++i)

@@ -90,6 +90,20 @@ def router_cases():
     return out
 
 
+def requant_inputs():
+    """Rows of Q6_K (210 B / 256 values) and Q8_0 blocks with random bytes and f16 scales in [1e-4, 2e-2], for the host
+    requantiser of the reference's dense loader (ggml_requantize_row_to_q8_0, src/ggml_dequant.hpp:362-392): 8 rows of
+    512 columns each; one Q6_K block and one Q8_0 block are all zeros (d = 0)."""
+    rng = np.random.Generator(np.random.PCG64(606))
+    qk = rng.integers(0, 256, size=(16, 210), dtype=np.uint8)
+    qk[:, 208:210] = rng.uniform(1e-4, 2e-2, 16).astype(np.float16).view(np.uint8).reshape(16, 2)
+    qk[3] = 0
+    q8 = rng.integers(0, 256, size=(128, 34), dtype=np.uint8)
+    q8[:, 0:2] = rng.uniform(1e-4, 2e-2, 128).astype(np.float16).view(np.uint8).reshape(128, 2)
+    q8[17] = 0
+    return qk.reshape(-1), q8.reshape(-1)
+
+
 def block_cases():
     """(model dict, inputs [n, H]) for small MoE blocks. The last three have the geometry rules of the reference's own
     model (src/qwen38_moe.cuh:2181-2211, :2252-2258): hidden a multiple of 256 that is not a power of two, expert_ffn
@@ -147,6 +161,9 @@ def main():
         wts.append(np.pad(ol.fbits(w_), (0, 16 - k)))
         psha.append(digest(ol.fbits(p)))
     g["router_ids"], g["router_w"], g["router_probs_sha"] = np.array(ids, np.int32), np.array(wts, np.uint32), np.array(psha)
+    qk, q8 = requant_inputs()
+    g["requant_q6_k"] = ref.requantize_rows_to_q8_0(ol.TYPE_Q6_K, qk, 8, 512)
+    g["requant_q8_0"] = ref.requantize_rows_to_q8_0(ol.TYPE_Q8_0, q8, 8, 512)
     for bi, (m, xs) in enumerate(block_cases()):
         outs, sel, sw = [], [], []
         for x in xs:

@@ -13,6 +13,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 ORACLE_DIR = os.path.join(ROOT, "oracle")
 
 TYPE_F32, TYPE_Q4_0, TYPE_Q8_0, TYPE_IQ4_NL, TYPE_IQ3_S, TYPE_IQ2_S = 0, 2, 8, 20, 21, 22
+TYPE_Q6_K = 14
 BLOCK_BYTES = {TYPE_Q8_0: 34, TYPE_Q4_0: 18, TYPE_IQ4_NL: 18, TYPE_IQ3_S: 110, TYPE_IQ2_S: 82}
 BLOCK_ELEMS = {TYPE_Q8_0: 32, TYPE_Q4_0: 32, TYPE_IQ4_NL: 32, TYPE_IQ3_S: 256, TYPE_IQ2_S: 256}
 Q8K_BYTES = 292
@@ -70,14 +71,16 @@ def build_oracle():
 
 class DenseLayerC(C.Structure):
     _fields_ = [("attn_norm", C.c_void_p), ("wqkv", C.c_void_p), ("wo", C.c_void_p), ("ffn_norm", C.c_void_p),
-                ("w_gate_up", C.c_void_p), ("w_down", C.c_void_p)]
+                ("w_gate_up", C.c_void_p), ("w_down", C.c_void_p),
+                ("wqkv_type", C.c_int), ("wo_type", C.c_int), ("w_gate_up_type", C.c_int), ("w_down_type", C.c_int)]
 
 
 class DenseModelC(C.Structure):
     _fields_ = [("hidden", C.c_int), ("n_heads", C.c_int), ("n_kv_heads", C.c_int), ("head_dim", C.c_int), ("ffn", C.c_int),
                 ("vocab", C.c_int), ("n_layers", C.c_int), ("max_ctx", C.c_int), ("rms_eps", C.c_float),
                 ("token_embd", C.c_void_p), ("output_norm", C.c_void_p), ("output", C.c_void_p),
-                ("layers", C.POINTER(DenseLayerC)), ("rope_table", C.c_void_p), ("hidden_out", C.c_void_p)]
+                ("layers", C.POINTER(DenseLayerC)), ("rope_table", C.c_void_p), ("hidden_out", C.c_void_p),
+                ("token_embd_type", C.c_int), ("output_type", C.c_int)]
 
 
 class DenseOracle:
@@ -85,7 +88,8 @@ class DenseOracle:
 
     def __init__(self, oracle, cfg, tensors, layers, rope_theta):
         """cfg: dict(hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, n_layers, max_ctx, rms_eps); tensors: dict with
-        token_embd, output_norm, output; layers: list of dicts attn_norm, wqkv, wo, ffn_norm, w_gate_up, w_down."""
+        token_embd, output_norm, output; layers: list of dicts attn_norm, wqkv, wo, ffn_norm, w_gate_up, w_down. A
+        matrix is Q4_0 unless the dict holds "<name>_type" = TYPE_Q8_0."""
         self.L = oracle.lib
         self.keep = []
 
@@ -97,7 +101,8 @@ class DenseOracle:
         self.layers = (DenseLayerC * cfg["n_layers"])()
         for i, l in enumerate(layers):
             self.layers[i] = DenseLayerC(ptr(l["attn_norm"], np.float32), ptr(l["wqkv"], np.uint8), ptr(l["wo"], np.uint8),
-                                         ptr(l["ffn_norm"], np.float32), ptr(l["w_gate_up"], np.uint8), ptr(l["w_down"], np.uint8))
+                                         ptr(l["ffn_norm"], np.float32), ptr(l["w_gate_up"], np.uint8), ptr(l["w_down"], np.uint8),
+                                         l.get("wqkv_type", 0), l.get("wo_type", 0), l.get("w_gate_up_type", 0), l.get("w_down_type", 0))
         self.rope = np.zeros(cfg["max_ctx"] * (cfg["head_dim"] // 2) * 2, np.float32)
         self.L.wdo_rope_table.argtypes = [C.c_int, C.c_int, C.c_double, C.c_void_p]
         self.L.wdo_rope_table(cfg["max_ctx"], cfg["head_dim"], float(rope_theta), self.rope.ctypes.data)
@@ -105,7 +110,8 @@ class DenseOracle:
         self.m = DenseModelC(cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"], cfg["ffn"], cfg["vocab"],
                              cfg["n_layers"], cfg["max_ctx"], cfg["rms_eps"], ptr(tensors["token_embd"], np.uint8),
                              ptr(tensors["output_norm"], np.float32), ptr(tensors["output"], np.uint8), self.layers,
-                             self.rope.ctypes.data, self.hidden.ctypes.data)
+                             self.rope.ctypes.data, self.hidden.ctypes.data, tensors.get("token_embd_type", 0),
+                             tensors.get("output_type", 0))
         kv = cfg["n_layers"] * cfg["max_ctx"] * cfg["n_kv_heads"] * cfg["head_dim"]
         self.kc, self.vc = np.zeros(kv, np.float32), np.zeros(kv, np.float32)
         self.logits = np.zeros(cfg["vocab"], np.float32)
@@ -143,7 +149,11 @@ class Oracle:
         L.wdo_f32_to_f16.argtypes = [C.c_float]
         L.wdo_iq3s_grid.restype = C.c_uint32
         L.wdo_iq2s_grid.restype = C.c_uint64
-        for name in ("wdo_row_q8_0_q8_0", "wdo_row_iq4_nl_q8_0", "wdo_row_q4_0_q8_0", "wdo_row_q4_0_q8_0_lanes"):
+        L.wdo_requantize_row_to_q8_0.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int]
+        L.wdo_q6_k_value.restype = C.c_float
+        L.wdo_q6_k_value.argtypes = [C.c_void_p, C.c_int]
+        for name in ("wdo_row_q8_0_q8_0", "wdo_row_iq4_nl_q8_0", "wdo_row_q4_0_q8_0", "wdo_row_q4_0_q8_0_lanes",
+                     "wdo_row_q8_0_q8_0_lanes"):
             getattr(L, name).restype = C.c_float
             getattr(L, name).argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.wdo_matvec_q8_0_argmax.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
@@ -204,6 +214,17 @@ class Oracle:
         f = {TYPE_Q8_0: self.lib.wdo_row_q8_0_q8_0, TYPE_IQ4_NL: self.lib.wdo_row_iq4_nl_q8_0,
              TYPE_Q4_0: self.lib.wdo_row_q4_0_q8_0}[t]
         return np.float32(f(w_row.ctypes.data, y.ctypes.data, cols))
+
+    def requantize_rows_to_q8_0(self, t, blob, rows, cols):
+        """[rows][cols] of ggml type t (Q8_0 or Q6_K = 14) -> Q8_0 blocks, the dense loader's host rule."""
+        blob = np.ascontiguousarray(blob, np.uint8)
+        rb = cols // 32 * 34 if t == TYPE_Q8_0 else cols // 256 * 210
+        out = np.zeros(rows * (cols // 32) * 34, np.uint8)
+        for r in range(rows):
+            rc = self.lib.wdo_requantize_row_to_q8_0(t, blob.ctypes.data + r * rb, out.ctypes.data + r * (cols // 32) * 34, cols)
+            if rc != 0:
+                raise RuntimeError("wdo_requantize_row_to_q8_0 refused the row")
+        return out
 
     def head_argmax_q8_0(self, w, rows, cols, y, logits=False):
         """Greedy token of a Q8_0 head [rows][cols] (ggml blocks) for the Q8_0-quantised activation y:
@@ -301,6 +322,9 @@ class Reference:
         for name in ("ref_exp_ggml", "ref_silu_ggml", "ref_sigmoid_ggml", "ref_router_exp"):
             getattr(L, name).restype = C.c_float
             getattr(L, name).argtypes = [C.c_float]
+        L.ref_requantize_row_to_q8_0.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int]
+        L.ref_q6_k_value.restype = C.c_float
+        L.ref_q6_k_value.argtypes = [C.c_void_p, C.c_int]
         L.ref_dot_f32.restype = C.c_float
         L.ref_dot_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_int]
         L.ref_router_exact.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_void_p,
@@ -349,6 +373,16 @@ class Reference:
         a = np.ascontiguousarray(a, np.float32)
         b = np.ascontiguousarray(b, np.float32)
         return np.float32(self.lib.ref_dot_f32(a.ctypes.data, b.ctypes.data, a.size))
+
+    def requantize_rows_to_q8_0(self, t, blob, rows, cols):
+        blob = np.ascontiguousarray(blob, np.uint8)
+        rb = cols // 32 * 34 if t == TYPE_Q8_0 else cols // 256 * 210
+        out = np.zeros(rows * (cols // 32) * 34, np.uint8)
+        for r in range(rows):
+            rc = self.lib.ref_requantize_row_to_q8_0(t, blob.ctypes.data + r * rb, out.ctypes.data + r * (cols // 32) * 34, cols)
+            if rc != 0:
+                raise RuntimeError("ggml_requantize_row_to_q8_0 threw")
+        return out
 
     def router(self, logits, k, w_scale=1.0):
         logits = np.ascontiguousarray(logits, np.float32)

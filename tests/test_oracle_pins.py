@@ -242,3 +242,17 @@ def test_q4_0_row_dot_in_lane_order_against_gguf_py_decoder(oracle):
             xr = np.ascontiguousarray(xq.reshape(-1))
             got = np.float32(f(wr.ctypes.data, xr.ctypes.data, cols))
             assert ol.fbits(np.array([got]))[0] == ol.fbits(np.array([lane[0]]))[0], (cols, r)
+
+
+def test_dense_loader_requantiser_and_q6_k_values(oracle):
+    """Non-Q4_0 tensors of a dense model file become Q8_0 on the host, by the reference's rule (src/ggml_dequant.hpp:
+    362-392): golden bytes from the reference's function; Q6_K values also against gguf-py's decoder."""
+    qk, q8 = mg.requant_inputs()
+    assert np.array_equal(oracle.requantize_rows_to_q8_0(ol.TYPE_Q6_K, qk, 8, 512), GOLD["requant_q6_k"])
+    assert np.array_equal(oracle.requantize_rows_to_q8_0(ol.TYPE_Q8_0, q8, 8, 512), GOLD["requant_q8_0"])
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    theirs = quants.dequantize(qk.reshape(8, -1), gguf.GGMLQuantizationType.Q6_K).astype(np.float32)
+    mine = np.array([[oracle.lib.wdo_q6_k_value(qk.ctypes.data + (r * 2 + i // 256) * 210, i % 256) for i in range(512)]
+                     for r in range(8)], np.float32)
+    assert np.array_equal(bits(theirs), bits(mine))
