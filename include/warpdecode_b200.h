@@ -205,8 +205,9 @@ typedef struct wd_dense_decoder wd_dense_decoder;
 int wd_dense_decoder_create(const wd_dense_config *cfg, wd_dense_decoder **out);
 /* Decoder with the geometry and every tensor of a Llama-style Q4_0 model file (architectures llama, qwen2, qwen3), read
  * the way load_model does (src/warodecode.cu:1255-1345): q/k/v and gate/up joined row-wise, an absent output.weight tied
- * to the embedding table. Files with q/k/v biases, q/k norms, partial or scaled rotary embeddings or 2-D tensors of
- * another type than Q4_0 are refused by name. The file may be closed afterwards (wd_gguf is declared further down). */
+ * to the embedding table; Q8_0 and Q6_K matrices (the output head and some ffn_down tensors of the Q4_0 files llama.cpp
+ * writes) requantised to Q8_0 on the host by ggml_requantize_row_to_q8_0 (src/ggml_dequant.hpp:362-392). Files with q/k/v
+ * biases, q/k norms, partial or scaled rotary embeddings or 2-D tensors of other types are refused by name. The file may be closed afterwards (wd_gguf is declared further down). */
 struct wd_gguf;
 int wd_dense_decoder_load_gguf(const struct wd_gguf *g, int max_ctx, int device, wd_dense_decoder **out);
 /* The configuration a decoder was created with. */
@@ -217,6 +218,12 @@ void wd_dense_decoder_destroy(wd_dense_decoder *d);
 const char *wd_dense_decoder_kernel_name(const wd_dense_decoder *d);
 /* `layer` is ignored for the three model-level tensors. The bytes are copied; the pointer is not kept. */
 int wd_dense_decoder_set_tensor(wd_dense_decoder *d, int layer, int which, const void *host);
+/* Same for a 2-D tensor given as WD_TYPE_Q4_0 or WD_TYPE_Q8_0 blocks (34 bytes per 32 values): the reference's dense
+ * loader turns every 2-D tensor that is not Q4_0 into Q8_0 and multiplies with it as such (planarize_q4,
+ * src/warodecode.cu:1027-1075). A tensor keeps its type once the first token has been decoded. */
+int wd_dense_decoder_set_tensor_typed(wd_dense_decoder *d, int layer, int which, int type, const void *host);
+/* ggml type of a tensor as the decoder holds it (WD_TYPE_F32 for the norms), or a negative error code. */
+int wd_dense_decoder_tensor_type(wd_dense_decoder *d, int layer, int which);
 int wd_dense_decoder_get_tensor(wd_dense_decoder *d, int layer, int which, void *host_out, size_t bytes);
 /* Every 2-D tensor drawn N(0, sigma) and quantised to Q4_0 on the device, norms 1 (synthetic models for measurements). */
 int wd_dense_decoder_synth(wd_dense_decoder *d, unsigned long long seed, float sigma);

@@ -17,13 +17,17 @@ def wd():
 
 
 def _oracle_for(wd, oracle, dec, cfg, rope_theta):
+    """The CPU restatement fed with the decoder's own tensors (bytes and block types as it holds them)."""
     tensors = {"token_embd": dec.get_tensor(0, wd.DT_TOKEN_EMBD), "output_norm": dec.get_tensor(0, wd.DT_OUTPUT_NORM),
-               "output": dec.get_tensor(0, wd.DT_OUTPUT)}
+               "output": dec.get_tensor(0, wd.DT_OUTPUT), "token_embd_type": dec.tensor_type(0, wd.DT_TOKEN_EMBD),
+               "output_type": dec.tensor_type(0, wd.DT_OUTPUT)}
     layers = []
     for l in range(cfg["n_layers"]):
         layers.append({"attn_norm": dec.get_tensor(l, wd.DT_ATTN_NORM), "wqkv": dec.get_tensor(l, wd.DT_WQKV),
                        "wo": dec.get_tensor(l, wd.DT_WO), "ffn_norm": dec.get_tensor(l, wd.DT_FFN_NORM),
-                       "w_gate_up": dec.get_tensor(l, wd.DT_W_GATE_UP), "w_down": dec.get_tensor(l, wd.DT_W_DOWN)})
+                       "w_gate_up": dec.get_tensor(l, wd.DT_W_GATE_UP), "w_down": dec.get_tensor(l, wd.DT_W_DOWN),
+                       "wqkv_type": dec.tensor_type(l, wd.DT_WQKV), "wo_type": dec.tensor_type(l, wd.DT_WO),
+                       "w_gate_up_type": dec.tensor_type(l, wd.DT_W_GATE_UP), "w_down_type": dec.tensor_type(l, wd.DT_W_DOWN)})
     return ol.DenseOracle(oracle, cfg, tensors, layers, rope_theta)
 
 
@@ -158,5 +162,75 @@ def test_model_file_in_the_reference_loaders_tensor_names(wd, oracle, tmp_path):
     synth.write_gguf(path, dict(meta, **{"general.architecture": "qwen4exp"}), tensors)
     g = wd.Gguf(path)
     with pytest.raises(wd.WdError, match="architecture"):
+        wd.DenseDecoder.from_gguf(g, 64)
+    g.close()
+
+
+def _random_q6_k(rng, rows, cols):
+    """Q6_K blocks (210 bytes per 256 values) with random quants, small int8 sub-scales and f16 scales: valid input for
+    the decoder of that type; gguf-py has no encoder for it."""
+    n = rows * cols // 256
+    blk = rng.integers(0, 256, size=(n, 210), dtype=np.uint8)
+    blk[:, 192:208] = rng.integers(-24, 25, size=(n, 16)).astype(np.int8).view(np.uint8)
+    blk[:, 208:210] = rng.uniform(2e-4, 1e-3, n).astype(np.float16).view(np.uint8).reshape(n, 2)
+    return blk.reshape(-1)
+
+
+def test_model_file_with_q6_k_and_q8_0_tensors(wd, oracle, tmp_path):
+    """The Q4_0 files that llama.cpp writes keep the output head in Q6_K and some ffn_down tensors in Q8_0; the
+    reference's dense loader requantises every 2-D tensor that is not Q4_0 to Q8_0 on the host and multiplies with that
+    (planarize_q4, src/warodecode.cu:1027-1075; ggml_requantize_row_to_q8_0, src/ggml_dequant.hpp:362-392). Here: a tied
+    Q6_K embedding table (so the embedding row comes from Q8_0 blocks too), Q8_0 ffn_down in layer 1, Q8_0 q/k/v in
+    layer 0. The tensors the decoder holds equal the oracle's requantiser on the file's bytes; 32 tokens equal the oracle."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    from warpdecode_b200 import synth
+    H, nh, nkv, hd, F, V, L = 256, 4, 2, 64, 512, 640, 2
+    rng = np.random.Generator(np.random.PCG64(99))
+    enc = lambda rows, cols, sigma, t: quants.quantize((rng.standard_normal((rows, cols)) * sigma).astype(np.float32), t).reshape(-1)
+    q4 = lambda rows, cols, sigma=0.08: enc(rows, cols, sigma, gguf.GGMLQuantizationType.Q4_0)
+    q8 = lambda rows, cols, sigma=0.08: enc(rows, cols, sigma, gguf.GGMLQuantizationType.Q8_0)
+    vec = lambda: (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    emb = _random_q6_k(rng, V, H)
+    tensors = [("token_embd.weight", [H, V], ol.TYPE_Q6_K, emb), ("output_norm.weight", [H], ol.TYPE_F32, vec())]
+    for l in range(L):
+        p = f"blk.{l}."
+        qt, qf = (ol.TYPE_Q8_0, q8) if l == 0 else (ol.TYPE_Q4_0, q4)
+        dt, df = (ol.TYPE_Q8_0, q8) if l == 1 else (ol.TYPE_Q4_0, q4)
+        tensors += [(p + "attn_norm.weight", [H], ol.TYPE_F32, vec()), (p + "ffn_norm.weight", [H], ol.TYPE_F32, vec()),
+                    (p + "attn_q.weight", [H, nh * hd], qt, qf(nh * hd, H)), (p + "attn_k.weight", [H, nkv * hd], qt, qf(nkv * hd, H)),
+                    (p + "attn_v.weight", [H, nkv * hd], qt, qf(nkv * hd, H)),
+                    (p + "attn_output.weight", [H, H], ol.TYPE_Q4_0, q4(H, nh * hd)),
+                    (p + "ffn_gate.weight", [H, F], ol.TYPE_Q4_0, q4(F, H)), (p + "ffn_up.weight", [H, F], ol.TYPE_Q4_0, q4(F, H)),
+                    (p + "ffn_down.weight", [F, H], dt, df(H, F))]
+    meta = {"general.architecture": "llama", "llama.embedding_length": H, "llama.block_count": L,
+            "llama.attention.head_count": nh, "llama.attention.head_count_kv": nkv, "llama.feed_forward_length": F,
+            "llama.attention.layer_norm_rms_epsilon": 1e-5, "llama.rope.freq_base": 10000.0}
+    path = str(tmp_path / "mixed.gguf")
+    synth.write_gguf(path, meta, tensors)
+    g = wd.Gguf(path)
+    dec = wd.DenseDecoder.from_gguf(g, 64)
+    g.close()
+    by_name = {n: d for n, _, _, d in tensors}
+    assert dec.tensor_type(0, wd.DT_TOKEN_EMBD) == ol.TYPE_Q8_0 and dec.tensor_type(0, wd.DT_OUTPUT) == ol.TYPE_Q8_0
+    assert dec.tensor_type(0, wd.DT_WQKV) == ol.TYPE_Q8_0 and dec.tensor_type(1, wd.DT_WQKV) == ol.TYPE_Q4_0
+    assert dec.tensor_type(1, wd.DT_W_DOWN) == ol.TYPE_Q8_0 and dec.tensor_type(0, wd.DT_W_DOWN) == ol.TYPE_Q4_0
+    assert np.array_equal(dec.get_tensor(0, wd.DT_TOKEN_EMBD), oracle.requantize_rows_to_q8_0(ol.TYPE_Q6_K, emb, V, H))
+    assert np.array_equal(dec.get_tensor(1, wd.DT_W_DOWN), oracle.requantize_rows_to_q8_0(ol.TYPE_Q8_0, by_name["blk.1.ffn_down.weight"], H, F))
+    cfg = dict(hidden=H, n_heads=nh, n_kv_heads=nkv, head_dim=hd, ffn=F, vocab=V, n_layers=L, max_ctx=64, rms_eps=dec.cfg.rms_eps)
+    prompt = rng.integers(0, V, 8)
+    got, _ = dec.decode(prompt, 32)
+    logits, hidden = dec.read()
+    ref = _oracle_for(wd, oracle, dec, cfg, 10000.0)
+    want = ref.decode(prompt, 32)
+    assert np.array_equal(got, want)
+    assert np.array_equal(ol.fbits(logits), ol.fbits(ref.logits)) and np.array_equal(ol.fbits(hidden), ol.fbits(ref.hidden))
+    dec.close()
+    # q/k/v parts of different types are refused by name
+    bad = [(n, d, (ol.TYPE_Q4_0 if n == "blk.0.attn_k.weight" else t), (q4(nkv * hd, H) if n == "blk.0.attn_k.weight" else a))
+           for n, d, t, a in tensors]
+    synth.write_gguf(path, meta, bad)
+    g = wd.Gguf(path)
+    with pytest.raises(wd.WdError, match="differ in type"):
         wd.DenseDecoder.from_gguf(g, 64)
     g.close()

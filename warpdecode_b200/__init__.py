@@ -113,6 +113,8 @@ def lib():
         L.wd_last_kernel_name.restype = C.c_char_p
         L.wd_measure_tile_decoder.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_double)]
         L.wd_dense_decoder_create.argtypes = [C.POINTER(DenseConfig), C.POINTER(C.c_void_p)]
+        L.wd_dense_decoder_set_tensor_typed.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        L.wd_dense_decoder_tensor_type.argtypes = [C.c_void_p, C.c_int, C.c_int]
         L.wd_dense_decoder_load_gguf.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
         L.wd_dense_decoder_config.argtypes = [C.c_void_p, C.POINTER(DenseConfig)]
         L.wd_dense_decoder_destroy.argtypes = [C.c_void_p]
@@ -182,7 +184,7 @@ class Gguf:
         _check(lib().wd_gguf_tensor(self.h, name.encode(), C.byref(data), C.byref(t), dims, C.byref(nd)))
         dims = list(dims)[:nd.value]
         n = int(np.prod(dims))
-        per = {0: (4, 1), 1: (2, 1), 2: (18, 32), 8: (34, 32), 20: (18, 32), 21: (110, 256), 22: (82, 256)}[t.value]
+        per = {0: (4, 1), 1: (2, 1), 2: (18, 32), 8: (34, 32), 14: (210, 256), 20: (18, 32), 21: (110, 256), 22: (82, 256)}[t.value]
         nbytes = n // per[1] * per[0]
         buf = (C.c_uint8 * nbytes).from_address(data.value)
         return np.frombuffer(buf, np.uint8), t.value, dims
@@ -494,15 +496,23 @@ class DenseDecoder:
         return {DT_TOKEN_EMBD: (c.vocab, c.hidden), DT_OUTPUT: (c.vocab, c.hidden), DT_WQKV: (q + 2 * kv, c.hidden),
                 DT_WO: (c.hidden, q), DT_W_GATE_UP: (2 * c.ffn, c.hidden), DT_W_DOWN: (c.hidden, c.ffn)}.get(which)
 
-    def set_tensor(self, layer, which, data):
+    def set_tensor(self, layer, which, data, type=TYPE_Q4_0):
+        """A norm (F32) or a matrix in ggml blocks of `type` (Q4_0, or Q8_0 for what a model file holds in other types)."""
         shp = self.shape(which)
         a = np.ascontiguousarray(data, np.float32 if shp is None else np.uint8)
-        assert a.size == (self.cfg.hidden if shp is None else shp[0] * (shp[1] // 32) * 18)
-        _check(lib().wd_dense_decoder_set_tensor(self.h, layer, which, _ptr(a)))
+        assert a.size == (self.cfg.hidden if shp is None else shp[0] * (shp[1] // 32) * (34 if type == TYPE_Q8_0 else 18))
+        _check(lib().wd_dense_decoder_set_tensor_typed(self.h, layer, which, type, _ptr(a)))
+
+    def tensor_type(self, layer, which):
+        t = lib().wd_dense_decoder_tensor_type(self.h, layer, which)
+        if t < 0:
+            _check(t)
+        return t
 
     def get_tensor(self, layer, which):
         shp = self.shape(which)
-        a = np.zeros(self.cfg.hidden, np.float32) if shp is None else np.zeros(shp[0] * (shp[1] // 32) * 18, np.uint8)
+        per = 34 if shp is not None and self.tensor_type(layer, which) == TYPE_Q8_0 else 18
+        a = np.zeros(self.cfg.hidden, np.float32) if shp is None else np.zeros(shp[0] * (shp[1] // 32) * per, np.uint8)
         _check(lib().wd_dense_decoder_get_tensor(self.h, layer, which, _ptr(a), a.nbytes))
         return a
 

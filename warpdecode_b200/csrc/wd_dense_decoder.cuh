@@ -91,7 +91,7 @@ __device__ __forceinline__ void q8_0_block_warp(float v, int lane, int8_t *q_out
 // hidden is first filled with the token's embedding row (embedding_q4_kernel).
 template <int EPL>
 __device__ __forceinline__ void dense_norm_quant_body(float *hidden, const float *proj, const float *w, int n, float eps, int8_t *xq,
-                                                      float *xd, const uint8_t *embd_row) {
+                                                      float *xd, const uint8_t *embd_row, bool embd_q8 = false) {
     __shared__ double red[kDecThreads / 32];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float v[EPL];
@@ -99,10 +99,11 @@ __device__ __forceinline__ void dense_norm_quant_body(float *hidden, const float
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
             const int e = tid * EPL + i, b = e >> 5, j = e & 31;
-            const uint8_t *wb = embd_row + b * 18;
+            const uint8_t *wb = embd_row + b * (embd_q8 ? 34 : 18);
             const float d = half_bits_to_float(static_cast<uint16_t>(wb[0] | (wb[1] << 8)));
-            const int q = j < 16 ? (wb[2 + j] & 0x0f) : (wb[2 + j - 16] >> 4);
-            v[i] = __fmul_rn(d, static_cast<float>(q - 8));
+            const int q = embd_q8 ? static_cast<int>(static_cast<int8_t>(wb[2 + j]))
+                                  : (j < 16 ? (wb[2 + j] & 0x0f) : (wb[2 + j - 16] >> 4)) - 8;
+            v[i] = __fmul_rn(d, static_cast<float>(q));
             hidden[e] = v[i];
         }
     } else {
@@ -161,17 +162,18 @@ __device__ __forceinline__ void dense_norm_quant_body(float *hidden, const float
 
 __global__ void __launch_bounds__(kDecThreads) dense_norm_quant_kernel(float *hidden, const float *proj, const float *w, int n,
                                                                      float eps, int8_t *xq, float *xd, const uint8_t *embd,
-                                                                     const int *token, int vocab) {
+                                                                     const int *token, int vocab, int embd_q8) {
     grid_dep_launch();
     grid_dep_wait();
-    const uint8_t *row = nullptr;
-    if (embd != nullptr) row = embd + static_cast<size_t>(max(0, min(vocab - 1, *token))) * (n >> 5) * 18;
+    const uint8_t *row = nullptr;     // the embedding table in ggml layout: Q4_0 blocks of 18 bytes, or Q8_0 blocks of 34
+    if (embd != nullptr) row = embd + static_cast<size_t>(max(0, min(vocab - 1, *token))) * (n >> 5) * (embd_q8 ? 34 : 18);
+    const bool q8 = embd_q8 != 0;
     switch (n / kDecThreads) {
-        case 1: dense_norm_quant_body<1>(hidden, proj, w, n, eps, xq, xd, row); break;
-        case 2: dense_norm_quant_body<2>(hidden, proj, w, n, eps, xq, xd, row); break;
-        case 4: dense_norm_quant_body<4>(hidden, proj, w, n, eps, xq, xd, row); break;
-        case 8: dense_norm_quant_body<8>(hidden, proj, w, n, eps, xq, xd, row); break;
-        default: dense_norm_quant_body<16>(hidden, proj, w, n, eps, xq, xd, row); break;
+        case 1: dense_norm_quant_body<1>(hidden, proj, w, n, eps, xq, xd, row, q8); break;
+        case 2: dense_norm_quant_body<2>(hidden, proj, w, n, eps, xq, xd, row, q8); break;
+        case 4: dense_norm_quant_body<4>(hidden, proj, w, n, eps, xq, xd, row, q8); break;
+        case 8: dense_norm_quant_body<8>(hidden, proj, w, n, eps, xq, xd, row, q8); break;
+        default: dense_norm_quant_body<16>(hidden, proj, w, n, eps, xq, xd, row, q8); break;
     }
 }
 
@@ -241,6 +243,112 @@ __global__ void __launch_bounds__(kDecThreads, 4) dense_gemv_q4_0_kernel(const u
                                 s16 = dp4a_s8(static_cast<int>((ww[k] & 0xf0f0f0f0u) ^ 0x80808080u), static_cast<int>(ah[k]), s16);
                             }
                             acc[r] = __fmaf_rn(__fmul_rn(half_bits_to_float(dw[r][u]), dx), static_cast<float>(s16 >> 4), acc[r]);
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+#pragma unroll
+            for (int s = 16; s >= 1; s >>= 1) acc[r] = __fadd_rn(acc[r], __shfl_xor_sync(0xffffffffu, acc[r], s));
+        }
+        if (lane < R && row0 + lane < rows) {
+            float v = acc[0];
+#pragma unroll
+            for (int r = 1; r < R; ++r) v = lane == r ? acc[r] : v;
+            y[row0 + lane] = v;
+            if (key != nullptr && v == v && fabsf(v) != INFINITY) {
+                const unsigned long long k =
+                    (static_cast<unsigned long long>(order_key(v)) << 32) | (0xffffffffu - static_cast<unsigned>(row0 + lane));
+                best = k > best ? k : best;
+            }
+        }
+    }
+    if (key != nullptr) {
+#pragma unroll
+        for (int s = 1; s < R; s <<= 1) {
+            const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, s);
+            best = o > best ? o : best;
+        }
+        if (lane == 0 && best != 0ull) atomicMax(key, best);
+    }
+}
+
+// ggml Q8_0 [rows][nb] blocks of 34 bytes -> the row layout of dense_gemv_q8_0_kernel: [rows][nb][32 B] quants, then
+// [rows][nb] f16 scales. One thread per block.
+__global__ void repack_q8_0_dense_kernel(const uint8_t *src, uint8_t *dst, long long nblocks) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= nblocks) return;
+    const uint8_t *s = src + i * 34;
+    uint8_t *q = dst + i * 32;
+    uint16_t *d = reinterpret_cast<uint16_t *>(dst + nblocks * 32) + i;
+    *d = static_cast<uint16_t>(s[0] | (s[1] << 8));
+    for (int j = 0; j < 32; ++j) q[j] = s[2 + j];
+}
+
+// y = W x for a Q8_0 matrix (what every 2-D tensor of a model file that is not Q4_0 becomes: planarize_q4,
+// src/warodecode.cu:1027-1075), same structure and float order as dense_gemv_q4_0_kernel: lane l takes blocks l, l + 32,
+// ..., one fmaf(d_w * d_x, (float)int_dot, acc) per block with the exact integer dot of its 32 values, then the
+// butterfly. A block is two 16-byte loads.
+template <int R, int U>
+__global__ void __launch_bounds__(kDecThreads, 4) dense_gemv_q8_0_kernel(const uint8_t *wp, int rows, int nb, const int8_t *xq,
+                                                                       const float *xd, float *y, unsigned long long *key) {
+    extern __shared__ __align__(16) uint8_t dsm[];
+    grid_dep_launch();
+    uint4 *sq = reinterpret_cast<uint4 *>(dsm);
+    float *sd = reinterpret_cast<float *>(dsm + static_cast<size_t>(nb) * 32);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const uint4 *q_all = reinterpret_cast<const uint4 *>(wp);
+    const uint16_t *d_all = reinterpret_cast<const uint16_t *>(wp + static_cast<size_t>(rows) * nb * 32);
+    uint4 wl[R][U], wh[R][U];
+    uint16_t dw[R][U];
+    auto load = [&](int row0, int b0) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int b = b0 + 32 * u;
+                if (b < nb && row0 + r < rows) {
+                    const size_t blk = static_cast<size_t>(row0 + r) * nb + b;
+                    wl[r][u] = __ldg(q_all + 2 * blk);
+                    wh[r][u] = __ldg(q_all + 2 * blk + 1);
+                    dw[r][u] = __ldg(d_all + blk);
+                }
+            }
+    };
+    const int row_first = (blockIdx.x * nwarps + warp) * R;
+    if (row_first < rows) load(row_first, lane);     // weights do not depend on the kernel before this one
+    grid_dep_wait();
+    for (int i = threadIdx.x; i < nb * 2; i += blockDim.x) sq[i] = reinterpret_cast<const uint4 *>(xq)[i];
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) sd[i] = xd[i];
+    __syncthreads();
+    unsigned long long best = 0ull;
+    for (int row0 = row_first; row0 < rows; row0 += gridDim.x * nwarps * R) {
+        float acc[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = 0.0f;
+#pragma unroll 1
+        for (int b0 = lane; b0 < nb; b0 += 32 * U) {
+            if (row0 != row_first || b0 != lane) load(row0, b0);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int b = b0 + 32 * u;
+                if (b < nb) {
+                    const uint4 lo = sq[2 * b], hi = sq[2 * b + 1];
+                    const float dx = sd[b];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        if (row0 + r < rows) {
+                            int s = dp4a_s8(static_cast<int>(wl[r][u].x), static_cast<int>(lo.x), 0);
+                            s = dp4a_s8(static_cast<int>(wl[r][u].y), static_cast<int>(lo.y), s);
+                            s = dp4a_s8(static_cast<int>(wl[r][u].z), static_cast<int>(lo.z), s);
+                            s = dp4a_s8(static_cast<int>(wl[r][u].w), static_cast<int>(lo.w), s);
+                            s = dp4a_s8(static_cast<int>(wh[r][u].x), static_cast<int>(hi.x), s);
+                            s = dp4a_s8(static_cast<int>(wh[r][u].y), static_cast<int>(hi.y), s);
+                            s = dp4a_s8(static_cast<int>(wh[r][u].z), static_cast<int>(hi.z), s);
+                            s = dp4a_s8(static_cast<int>(wh[r][u].w), static_cast<int>(hi.w), s);
+                            acc[r] = __fmaf_rn(__fmul_rn(half_bits_to_float(dw[r][u]), dx), static_cast<float>(s), acc[r]);
                         }
                     }
                 }
