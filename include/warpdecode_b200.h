@@ -202,12 +202,16 @@ typedef struct wd_dense_decoder wd_dense_decoder;
 #define WD_DT_FFN_NORM 6     /* F32  [hidden] */
 #define WD_DT_W_GATE_UP 7    /* Q4_0 [2 * ffn][hidden]: gate rows, then up rows (Layer::gate_up) */
 #define WD_DT_W_DOWN 8       /* Q4_0 [hidden][ffn] */
+#define WD_DT_BQKV 9         /* F32  [(n_heads + 2 n_kv_heads) * head_dim], optional: q, k, v biases (Qwen2 files) */
+#define WD_DT_Q_NORM 10      /* F32  [head_dim], optional: RMSNorm weight of every q head before the rotary embedding (Qwen3) */
+#define WD_DT_K_NORM 11      /* F32  [head_dim], optional: the same for the k heads */
 int wd_dense_decoder_create(const wd_dense_config *cfg, wd_dense_decoder **out);
 /* Decoder with the geometry and every tensor of a Llama-style Q4_0 model file (architectures llama, qwen2, qwen3), read
  * the way load_model does (src/warodecode.cu:1255-1345): q/k/v and gate/up joined row-wise, an absent output.weight tied
  * to the embedding table; Q8_0 and Q6_K matrices (the output head and some ffn_down tensors of the Q4_0 files llama.cpp
- * writes) requantised to Q8_0 on the host by ggml_requantize_row_to_q8_0 (src/ggml_dequant.hpp:362-392). Files with q/k/v
- * biases, q/k norms, partial or scaled rotary embeddings or 2-D tensors of other types are refused by name. The file may be closed afterwards (wd_gguf is declared further down). */
+ * writes) requantised to Q8_0 on the host by ggml_requantize_row_to_q8_0 (src/ggml_dequant.hpp:362-392); q/k/v biases
+ * (Qwen2) and q/k head norms (Qwen3) read. Files with partial or scaled rotary embeddings or 2-D tensors of other types
+ * are refused by name. The file may be closed afterwards (wd_gguf is declared further down). */
 struct wd_gguf;
 int wd_dense_decoder_load_gguf(const struct wd_gguf *g, int max_ctx, int device, wd_dense_decoder **out);
 /* The configuration a decoder was created with. */

@@ -299,6 +299,20 @@ int wdo_dense_step(const wdo_dense_model *m, float *kcache, float *vcache, int t
         wdo_rmsnorm(hidden, L->attn_norm, m->rms_eps, H, norm);
         wdo_quantize_q8_0(norm, xq, H / 32);
         wdo_matvec_typed(L->wqkv_type, L->wqkv, qkv_rows, H, xq, qkv);
+        /* bias, then the per-head norms, then the rotary embedding: the order of emit_step (src/warodecode.cu:2069-2075:
+         * the product adds the bias, qk_norm_kernel :1836 runs before rope_store_kernel) */
+        if (L->bqkv)
+            for (int i = 0; i < qkv_rows; ++i) qkv[i] = addf(qkv[i], L->bqkv[i]);
+        if (L->q_norm)
+            for (int h = 0; h < nh; ++h) {
+                wdo_rmsnorm(qkv + (size_t)h * hd, L->q_norm, m->rms_eps, hd, norm);
+                memcpy(qkv + (size_t)h * hd, norm, sizeof(float) * hd);
+            }
+        if (L->k_norm)
+            for (int h = 0; h < nkv; ++h) {
+                wdo_rmsnorm(qkv + qdim + (size_t)h * hd, L->k_norm, m->rms_eps, hd, norm);
+                memcpy(qkv + qdim + (size_t)h * hd, norm, sizeof(float) * hd);
+            }
         for (int h = 0; h < nh; ++h) rope_head(qkv + (size_t)h * hd, hd, cs);
         for (int h = 0; h < nkv; ++h) rope_head(qkv + qdim + (size_t)h * hd, hd, cs);
         memcpy(kc + (size_t)pos * kvdim, qkv + qdim, sizeof(float) * kvdim);

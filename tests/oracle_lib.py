@@ -72,7 +72,8 @@ def build_oracle():
 class DenseLayerC(C.Structure):
     _fields_ = [("attn_norm", C.c_void_p), ("wqkv", C.c_void_p), ("wo", C.c_void_p), ("ffn_norm", C.c_void_p),
                 ("w_gate_up", C.c_void_p), ("w_down", C.c_void_p),
-                ("wqkv_type", C.c_int), ("wo_type", C.c_int), ("w_gate_up_type", C.c_int), ("w_down_type", C.c_int)]
+                ("wqkv_type", C.c_int), ("wo_type", C.c_int), ("w_gate_up_type", C.c_int), ("w_down_type", C.c_int),
+                ("bqkv", C.c_void_p), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p)]
 
 
 class DenseModelC(C.Structure):
@@ -102,7 +103,10 @@ class DenseOracle:
         for i, l in enumerate(layers):
             self.layers[i] = DenseLayerC(ptr(l["attn_norm"], np.float32), ptr(l["wqkv"], np.uint8), ptr(l["wo"], np.uint8),
                                          ptr(l["ffn_norm"], np.float32), ptr(l["w_gate_up"], np.uint8), ptr(l["w_down"], np.uint8),
-                                         l.get("wqkv_type", 0), l.get("wo_type", 0), l.get("w_gate_up_type", 0), l.get("w_down_type", 0))
+                                         l.get("wqkv_type", 0), l.get("wo_type", 0), l.get("w_gate_up_type", 0), l.get("w_down_type", 0),
+                                         ptr(l["bqkv"], np.float32) if l.get("bqkv") is not None else None,
+                                         ptr(l["q_norm"], np.float32) if l.get("q_norm") is not None else None,
+                                         ptr(l["k_norm"], np.float32) if l.get("k_norm") is not None else None)
         self.rope = np.zeros(cfg["max_ctx"] * (cfg["head_dim"] // 2) * 2, np.float32)
         self.L.wdo_rope_table.argtypes = [C.c_int, C.c_int, C.c_double, C.c_void_p]
         self.L.wdo_rope_table(cfg["max_ctx"], cfg["head_dim"], float(rope_theta), self.rope.ctypes.data)

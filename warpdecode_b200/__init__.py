@@ -468,6 +468,7 @@ class HeadQ8_0:
 
 
 DT_TOKEN_EMBD, DT_OUTPUT_NORM, DT_OUTPUT, DT_ATTN_NORM, DT_WQKV, DT_WO, DT_FFN_NORM, DT_W_GATE_UP, DT_W_DOWN = range(9)
+DT_BQKV, DT_Q_NORM, DT_K_NORM = 9, 10, 11          # optional F32 vectors: q/k/v biases, q and k head norms
 
 
 class DenseDecoder:
@@ -496,11 +497,15 @@ class DenseDecoder:
         return {DT_TOKEN_EMBD: (c.vocab, c.hidden), DT_OUTPUT: (c.vocab, c.hidden), DT_WQKV: (q + 2 * kv, c.hidden),
                 DT_WO: (c.hidden, q), DT_W_GATE_UP: (2 * c.ffn, c.hidden), DT_W_DOWN: (c.hidden, c.ffn)}.get(which)
 
+    def vector_len(self, which):
+        c = self.cfg
+        return {DT_BQKV: (c.n_heads + 2 * c.n_kv_heads) * c.head_dim, DT_Q_NORM: c.head_dim, DT_K_NORM: c.head_dim}.get(which, c.hidden)
+
     def set_tensor(self, layer, which, data, type=TYPE_Q4_0):
-        """A norm (F32) or a matrix in ggml blocks of `type` (Q4_0, or Q8_0 for what a model file holds in other types)."""
+        """A vector (F32) or a matrix in ggml blocks of `type` (Q4_0, or Q8_0 for what a model file holds in other types)."""
         shp = self.shape(which)
         a = np.ascontiguousarray(data, np.float32 if shp is None else np.uint8)
-        assert a.size == (self.cfg.hidden if shp is None else shp[0] * (shp[1] // 32) * (34 if type == TYPE_Q8_0 else 18))
+        assert a.size == (self.vector_len(which) if shp is None else shp[0] * (shp[1] // 32) * (34 if type == TYPE_Q8_0 else 18))
         _check(lib().wd_dense_decoder_set_tensor_typed(self.h, layer, which, type, _ptr(a)))
 
     def tensor_type(self, layer, which):
@@ -512,7 +517,7 @@ class DenseDecoder:
     def get_tensor(self, layer, which):
         shp = self.shape(which)
         per = 34 if shp is not None and self.tensor_type(layer, which) == TYPE_Q8_0 else 18
-        a = np.zeros(self.cfg.hidden, np.float32) if shp is None else np.zeros(shp[0] * (shp[1] // 32) * per, np.uint8)
+        a = np.zeros(self.vector_len(which), np.float32) if shp is None else np.zeros(shp[0] * (shp[1] // 32) * per, np.uint8)
         _check(lib().wd_dense_decoder_get_tensor(self.h, layer, which, _ptr(a), a.nbytes))
         return a
 

@@ -461,9 +461,14 @@ __device__ __forceinline__ float dense_attention_core(const float *qs, const flo
 // group; the first CTA of a group also stores the rotated k and the v into the caches [max_ctx][kv_dim]. Cache
 // position pos itself is taken from the CTA's own copy, so no CTA waits for another's store.
 // head_dim a multiple of 32, at most 128; dynamic shared memory: max_ctx + 32 * head_dim floats.
+// EXTRAS: the layer has q/k/v biases (Qwen2-style files: added to the QKV product's rows) and / or RMSNorm weights for
+// the q and k heads (Qwen3-style: qk_norm_kernel, src/warodecode.cu:1836), applied in that order before the rotary
+// embedding (emit_step :2069-2075). Layers without them run the instantiation that has none of that code.
+template <bool EXTRAS>
 __global__ void __launch_bounds__(128) dense_attention_kernel(const float *qkv, const float *table, float *kcache, float *vcache,
                                                               const int *pos_ptr, int heads, int kv_heads, int head_dim, int max_ctx,
-                                                              float inv_sqrt, int8_t *oq, float *od) {
+                                                              float inv_sqrt, int8_t *oq, float *od, const float *bqkv,
+                                                              const float *q_norm, const float *k_norm, float eps) {
     extern __shared__ __align__(16) float sc[];        // [max_ctx] scores, then [32][head_dim] value staging
     __shared__ float qs[128], kn[128], vn[128], outv[128];
     float *vbuf = sc + max_ctx;
@@ -474,6 +479,55 @@ __global__ void __launch_bounds__(128) dense_attention_kernel(const float *qkv, 
     const float *q_raw = qkv + static_cast<size_t>(h) * head_dim;
     const float *k_raw = qkv + static_cast<size_t>(heads + kvh) * head_dim;
     const float *v_raw = qkv + static_cast<size_t>(heads + kv_heads + kvh) * head_dim;
+    if constexpr (EXTRAS) {
+        __shared__ float qn[128], kn_in[128], vn_in[128];
+        __shared__ double nred[2][4];
+        float xq_ = 0.0f, xk_ = 0.0f, xv_ = 0.0f;
+        if (tid < head_dim) {
+            xq_ = q_raw[tid];
+            xk_ = k_raw[tid];
+            xv_ = v_raw[tid];
+            if (bqkv != nullptr) {
+                xq_ = __fadd_rn(xq_, bqkv[static_cast<size_t>(h) * head_dim + tid]);
+                xk_ = __fadd_rn(xk_, bqkv[static_cast<size_t>(heads + kvh) * head_dim + tid]);
+                xv_ = __fadd_rn(xv_, bqkv[static_cast<size_t>(heads + kv_heads + kvh) * head_dim + tid]);
+            }
+        }
+        if (q_norm != nullptr || k_norm != nullptr) {
+            // the sum of squares is the binary tree in double over the head's elements, zero-padded to 128 leaves (adding
+            // +0.0 changes nothing), thread t owns leaf t
+            double sq_ = __dmul_rn(static_cast<double>(xq_), static_cast<double>(xq_));
+            double sk_ = __dmul_rn(static_cast<double>(xk_), static_cast<double>(xk_));
+#pragma unroll
+            for (int s = 1; s < 32; s <<= 1) {
+                sq_ = __dadd_rn(sq_, __shfl_xor_sync(0xffffffffu, sq_, s));
+                sk_ = __dadd_rn(sk_, __shfl_xor_sync(0xffffffffu, sk_, s));
+            }
+            if (lane == 0) {
+                nred[0][warp] = sq_;
+                nred[1][warp] = sk_;
+            }
+            __syncthreads();
+            const double tq = __dadd_rn(__dadd_rn(nred[0][0], nred[0][1]), __dadd_rn(nred[0][2], nred[0][3]));
+            const double tk = __dadd_rn(__dadd_rn(nred[1][0], nred[1][1]), __dadd_rn(nred[1][2], nred[1][3]));
+            const double hd = static_cast<double>(head_dim), ep = static_cast<double>(eps);
+            const float scq = __double2float_rn(__ddiv_rn(1.0, __dsqrt_rn(__dadd_rn(__ddiv_rn(tq, hd), ep))));
+            const float sck = __double2float_rn(__ddiv_rn(1.0, __dsqrt_rn(__dadd_rn(__ddiv_rn(tk, hd), ep))));
+            if (tid < head_dim) {
+                if (q_norm != nullptr) xq_ = __fmul_rn(__fmul_rn(xq_, scq), q_norm[tid]);
+                if (k_norm != nullptr) xk_ = __fmul_rn(__fmul_rn(xk_, sck), k_norm[tid]);
+            }
+        }
+        if (tid < head_dim) {
+            qn[tid] = xq_;
+            kn_in[tid] = xk_;
+            vn_in[tid] = xv_;
+        }
+        __syncthreads();
+        q_raw = qn;
+        k_raw = kn_in;
+        v_raw = vn_in;
+    }
     float *kc = kcache + static_cast<size_t>(kvh) * head_dim, *vc = vcache + static_cast<size_t>(kvh) * head_dim;
     const bool writer = h % (heads / kv_heads) == 0;        // the first head of its KV group
     if (tid < half) {
