@@ -3,7 +3,8 @@
 //
 // The reference (one translation unit, namespace wd) calls its MoE path through inline C++ functions and
 // classes; it has no C ABI. A maintainer who swaps that path for this library includes this header in
-// place of the corresponding parts of src/qwen38_moe.cuh, src/expert_cache.cuh and src/qwen38_runtime.cuh:
+// place of the corresponding parts of src/qwen38_moe.cuh, src/expert_cache.cuh, src/qwen38_runtime.cuh and (the dense
+// path at the end of this file) src/warodecode.cu:
 // the functions below have the reference's names, parameter order and error behaviour (std::runtime_error
 // carrying the library's message), and forward to the C ABI. Each one names the reference declaration it
 // stands in for (paths inside the reference project).
@@ -223,6 +224,80 @@ inline void q38_finish_moe_f32(Qwen38MoeScratch &scratch, float *out, StreamT st
     if (out != scratch.pending_out) device_copy(out, scratch.pending_out, static_cast<size_t>(scratch.hidden()) * sizeof(float), stream);
     scratch.pending_out = nullptr;
 }
+
+// ---- the dense (Llama-style Q4_0) path: Model / load_model / Runtime of src/warodecode.cu:1211-2150 -------------------
+
+// Stands in for Model (src/warodecode.cu:1211-1248) as far as callers read it: the geometry. The tensors live in the
+// decoder that Runtime builds, because this library sizes the KV cache when the decoder is created.
+struct Model {
+    std::string path;
+    std::string arch;
+    int hidden = 0, layers = 0, heads = 0, kv_heads = 0, head_dim = 0, ffn = 0, vocab = 0;
+};
+
+// load_model(const GgufFile &) (src/warodecode.cu:1255): here the file is named, the library maps it itself. The
+// geometry is read at once (a file the dense path cannot run throws here, as in the reference); the weights are
+// uploaded by Runtime.
+template <class GgufFileT>
+inline Model load_model(const GgufFileT &, const std::string &model_path, int device = 0) {
+    Model m;
+    m.path = model_path;
+    wd_gguf *file = nullptr;
+    check(wd_gguf_open(model_path.c_str(), &file));
+    wd_dense_decoder *probe = nullptr;
+    const int rc = wd_dense_decoder_load_gguf(file, /*max_ctx=*/32, device, &probe);
+    wd_gguf_close(file);
+    check(rc);
+    wd_dense_config c{};
+    check(wd_dense_decoder_config(probe, &c));
+    wd_dense_decoder_destroy(probe);
+    m.hidden = c.hidden; m.layers = c.n_layers; m.heads = c.n_heads; m.kv_heads = c.n_kv_heads; m.head_dim = c.head_dim;
+    m.ffn = c.ffn; m.vocab = c.vocab;
+    return m;
+}
+
+// Stands in for Runtime (src/warodecode.cu:2011-2150): Runtime(model, ctx), run(steps, use_graph, start_token) returning
+// seconds, output_hash(steps) over the generated tokens (FNV-1a over their little-endian bytes, :2138-2147). One
+// CUDA-graph replay per token either way; `use_graph` is accepted for the signature.
+class Runtime {
+public:
+    Runtime(Model &model, int ctx, int device = 0) : max_ctx(ctx) {
+        wd_gguf *file = nullptr;
+        check(wd_gguf_open(model.path.c_str(), &file));
+        const int rc = wd_dense_decoder_load_gguf(file, ctx, device, &d_);
+        wd_gguf_close(file);
+        check(rc);
+    }
+    Runtime(const Runtime &) = delete;
+    Runtime &operator=(const Runtime &) = delete;
+    ~Runtime() {
+        if (d_) wd_dense_decoder_destroy(d_);
+    }
+    double run(int steps, bool /*use_graph*/, int start_token) {
+        if (steps < 1 || steps + 1 > max_ctx) throw std::runtime_error("warpdecode_b200: steps must fit the context");
+        tokens_.assign(static_cast<size_t>(steps) + 1, 0);
+        float ms = 0.0f;
+        check(wd_dense_decoder_decode(d_, &start_token, 1, steps, tokens_.data(), &ms));
+        return static_cast<double>(ms) / 1000.0;
+    }
+    uint64_t output_hash(int steps) const {
+        uint64_t h = 1469598103934665603ull;
+        for (int i = 1; i <= steps && i < static_cast<int>(tokens_.size()); ++i) {
+            const uint32_t x = static_cast<uint32_t>(tokens_[static_cast<size_t>(i)]);
+            for (int b = 0; b < 4; ++b) {
+                h ^= static_cast<uint8_t>(x >> (8 * b));
+                h *= 1099511628211ull;
+            }
+        }
+        return h;
+    }
+    const std::vector<int> &tokens() const { return tokens_; }      // the start token, then the generated ones
+    int max_ctx = 0;
+
+private:
+    wd_dense_decoder *d_ = nullptr;
+    std::vector<int> tokens_;
+};
 
 }  // namespace wd_b200
 

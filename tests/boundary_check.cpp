@@ -49,7 +49,20 @@ int main(int argc, char **argv) {
         moe_layer(rt, scratch, 0, nullptr, nullptr, nullptr);
     } catch (const std::runtime_error &e) {
         std::printf("runtime_error: %s\n", e.what());
-        return std::strstr(e.what(), "warpdecode_b200") ? 0 : 2;
+        if (!std::strstr(e.what(), "warpdecode_b200")) return 2;
+    }
+    // the dense path's load_model / Runtime / run / output_hash, written like the reference's bench loop
+    // (src/warodecode.cu:2706-2758); an unreadable file is the same kind of failure
+    try {
+        ref::GgufFile g;
+        wd_b200::Model model = wd_b200::load_model(g, argc > 2 ? argv[2] : "/nonexistent-dense.gguf");
+        wd_b200::Runtime rt(model, 128);
+        const double seconds = rt.run(64, true, 1);
+        std::printf("dense: %d layers, %.3f ms, hash %llx\n", model.layers, seconds * 1e3,
+                    static_cast<unsigned long long>(rt.output_hash(64)));
+    } catch (const std::runtime_error &e) {
+        std::printf("runtime_error: %s\n", e.what());
+        return std::strstr(e.what(), "warpdecode_b200") ? 0 : 3;
     }
     return 0;
 }

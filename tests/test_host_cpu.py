@@ -230,3 +230,4 @@ def test_cpp_wrappers_with_the_reference_signatures_compile_link_and_report_erro
     r = subprocess.run([exe], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "runtime_error: warpdecode_b200: cannot open" in r.stdout
+    assert r.stdout.count("runtime_error: warpdecode_b200: cannot open") == 2       # the MoE runtime and the dense load_model
