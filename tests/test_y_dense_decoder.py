@@ -250,3 +250,57 @@ def test_model_file_with_q6_k_and_q8_0_tensors(wd, oracle, tmp_path):
     with pytest.raises(wd.WdError, match="differ in type"):
         wd.DenseDecoder.from_gguf(g, 64)
     g.close()
+
+
+def test_cpp_runtime_wrapper_decodes_a_model_file(wd, oracle, tmp_path):
+    """include/warpdecode_b200.hpp's Model / load_model / Runtime (the reference's dense entry points,
+    src/warodecode.cu:1255, :2011-2150) run a small model file end to end from C++; the hash of the 64 generated tokens
+    equals the one of the tokens the Python binding decodes from the same file."""
+    import os
+    import shutil
+    import subprocess
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    from warpdecode_b200 import synth
+    if shutil.which("g++") is None:
+        pytest.skip("no g++")
+    H, nh, nkv, hd, F, V, L = 256, 4, 2, 64, 512, 512, 2
+    rng = np.random.Generator(np.random.PCG64(5))
+    q4 = lambda rows, cols, sigma: quants.quantize((rng.standard_normal((rows, cols)) * sigma).astype(np.float32),
+                                                   gguf.GGMLQuantizationType.Q4_0).reshape(-1)
+    vec = lambda: (1.0 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    tensors = [("token_embd.weight", [H, V], ol.TYPE_Q4_0, q4(V, H, 0.3)), ("output_norm.weight", [H], ol.TYPE_F32, vec()),
+               ("output.weight", [H, V], ol.TYPE_Q4_0, q4(V, H, 0.05))]
+    for l in range(L):
+        p = f"blk.{l}."
+        tensors += [(p + "attn_norm.weight", [H], ol.TYPE_F32, vec()), (p + "ffn_norm.weight", [H], ol.TYPE_F32, vec()),
+                    (p + "attn_q.weight", [H, H], ol.TYPE_Q4_0, q4(H, H, 0.08)), (p + "attn_k.weight", [H, nkv * hd], ol.TYPE_Q4_0, q4(nkv * hd, H, 0.08)),
+                    (p + "attn_v.weight", [H, nkv * hd], ol.TYPE_Q4_0, q4(nkv * hd, H, 0.08)),
+                    (p + "attn_output.weight", [H, H], ol.TYPE_Q4_0, q4(H, H, 0.08)), (p + "ffn_gate.weight", [H, F], ol.TYPE_Q4_0, q4(F, H, 0.08)),
+                    (p + "ffn_up.weight", [H, F], ol.TYPE_Q4_0, q4(F, H, 0.08)), (p + "ffn_down.weight", [F, H], ol.TYPE_Q4_0, q4(H, F, 0.08))]
+    meta = {"general.architecture": "llama", "llama.embedding_length": H, "llama.block_count": L, "llama.attention.head_count": nh,
+            "llama.attention.head_count_kv": nkv, "llama.feed_forward_length": F, "llama.attention.layer_norm_rms_epsilon": 1e-5,
+            "llama.rope.freq_base": 10000.0}
+    path = str(tmp_path / "rt.gguf")
+    synth.write_gguf(path, meta, tensors)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe, libdir = str(tmp_path / "boundary_check"), os.path.dirname(wd.LIB_PATH)
+    r = subprocess.run(["g++", "-std=c++17", "-I", os.path.join(root, "include"), "-o", exe, os.path.join(root, "tests", "boundary_check.cpp"),
+                        "-L", libdir, "-lwarpdecode_b200", f"-Wl,-rpath,{libdir}"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([exe, "/nonexistent.gguf", path], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    line = [ln for ln in r.stdout.splitlines() if ln.startswith("dense:")][0]
+    g = wd.Gguf(path)
+    dec = wd.DenseDecoder.from_gguf(g, 128)
+    g.close()
+    toks, _ = dec.decode(np.array([1]), 64)
+    h = 1469598103934665603
+    for t in toks[1:]:
+        for b in range(4):
+            h = ((h ^ ((int(t) >> (8 * b)) & 0xff)) * 1099511628211) & 0xffffffffffffffff
+    assert line.startswith("dense: 2 layers") and line.endswith("hash %x" % h), (line, hex(h))
+    want = _oracle_for(wd, oracle, dec, dict(hidden=H, n_heads=nh, n_kv_heads=nkv, head_dim=hd, ffn=F, vocab=V, n_layers=L, max_ctx=128,
+                                             rms_eps=dec.cfg.rms_eps), 10000.0).decode(np.array([1]), 64)
+    assert np.array_equal(toks, want)
+    dec.close()
