@@ -231,3 +231,27 @@ def test_cpp_wrappers_with_the_reference_signatures_compile_link_and_report_erro
     assert r.returncode == 0, r.stdout + r.stderr
     assert "runtime_error: warpdecode_b200: cannot open" in r.stdout
     assert r.stdout.count("runtime_error: warpdecode_b200: cannot open") == 2       # the MoE runtime and the dense load_model
+
+
+def test_dense_model_file_refusals_need_no_gpu(tmp_path):
+    """What wd_dense_decoder_load_gguf refuses is decided from the file's keys before any CUDA call (load_model,
+    src/warodecode.cu:1255-1284): another architecture, missing geometry, partial or scaled rotary embeddings."""
+    import ctypes as C
+    import warpdecode_b200 as wd
+    from warpdecode_b200 import synth
+    emb = np.zeros(64 * (256 // 32) * 18, np.uint8)
+    base = {"general.architecture": "llama", "llama.embedding_length": 256, "llama.block_count": 1, "llama.attention.head_count": 4,
+            "llama.attention.head_count_kv": 2, "llama.feed_forward_length": 512}
+    cases = [(dict(base, **{"general.architecture": "qwen4exp"}), "architecture"),
+             ({k: v for k, v in base.items() if k != "llama.feed_forward_length"}, "missing or inconsistent"),
+             (dict(base, **{"llama.attention.head_count": 3}), "missing or inconsistent"),
+             (dict(base, **{"llama.rope.dimension_count": 32}), "partial rotary"),
+             (dict(base, **{"llama.rope.scaling.type": "linear"}), "linear")]
+    for i, (meta, msg) in enumerate(cases):
+        path = str(tmp_path / f"d{i}.gguf")
+        synth.write_gguf(path, meta, [("token_embd.weight", [256, 64], ol.TYPE_Q4_0, emb)])
+        g = wd.Gguf(path)
+        h = C.c_void_p()
+        rc = wd.lib().wd_dense_decoder_load_gguf(g.h, 64, 0, C.byref(h))
+        assert rc != 0 and msg in wd.lib().wd_last_error().decode(), (msg, wd.lib().wd_last_error())
+        g.close()
